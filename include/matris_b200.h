@@ -1,0 +1,278 @@
+/*
+ * matris_b200 — C ABI of the B200 (sm_100a) evaluation path for MatRIS.
+ *
+ * Plain C: raw device pointers and sizes, int status returns, no C++/torch types.
+ * Every entry point launches on the CUDA stream passed as its last argument
+ * (a cudaStream_t passed as void*; NULL = default stream) on the CURRENT device.
+ * The library owns no device memory: every buffer is allocated by the caller.
+ * Unless stated otherwise calls are asynchronous and return MB_OK as soon as the
+ * launches are queued.
+ *
+ * Each declaration cites the reference code it replaces (paths are relative to
+ * the reference project root).
+ */
+#ifndef MATRIS_B200_H
+#define MATRIS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MB_VERSION 1
+
+/* status codes */
+#define MB_OK 0
+#define MB_ERR_INVALID 1   /* bad argument (null pointer, negative size, unsupported shape) */
+#define MB_ERR_CUDA 2      /* a CUDA runtime call failed; see mb_last_cuda_error() */
+#define MB_ERR_OVERFLOW 3  /* a count exceeds int32 or an image index exceeds +-127 */
+#define MB_ERR_UNPAIRED 4  /* a directed edge has no reverse edge (bond exactly on the cutoff) */
+#define MB_ERR_ISOLATED 5  /* an atom has no neighbour inside the cutoff */
+
+int mb_version(void);
+const char* mb_status_string(int status);
+const char* mb_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ graph build
+ * Replaces, for a whole batch of structures at once,
+ *   Structure.get_neighbor_list call        matris/graph/converter.py:85-87
+ *   create_graph (C) / Graph.add_edge       matris/graph/fast_converter_libraries/create_graph.c:100-219,
+ *                                           matris/graph/radiusgraph.py:298-386
+ *   adjacency_list / undirected2directed    matris/graph/radiusgraph.py:388-410, 489-496
+ *   line_graph_adjacency_list               matris/graph/radiusgraph.py:412-487
+ *   index offsetting of process_graphs      matris/model/processgraph.py:93-166
+ *
+ * All indices are global over the batch (atom, directed-edge, bond and triplet
+ * numbering runs through all structures in order).  Directed edges come out
+ * sorted by (centre, neighbour, image); bonds are numbered by their first
+ * directed edge; triplets are grouped by target bond.  This is exactly what the
+ * reference's Graph produces when fed a neighbour list in that order.
+ *
+ * Three phases, because the caller allocates the outputs:
+ *   mb_graph_count_edges     -> n_edges (host)
+ *   mb_graph_build_edges     -> n_bonds, n_triplets (host)
+ *   mb_graph_build_triplets
+ * Each phase synchronises the stream once to return its counts.
+ */
+typedef struct mb_graph {
+  /* sizes and parameters (host) */
+  int32_t n_atoms, n_struct, n_cells;
+  int32_t n_edges, n_bonds, n_triplets;        /* written by the phases */
+  double cutoff, line_cutoff, tol;             /* tol < d <= cutoff ; line graph: target d <= lc, source d < lc */
+  /* inputs (device) */
+  const double* cart;         /* [n_atoms,3] Cartesian, not wrapped */
+  const double* lattice;      /* [n_struct,3,3] rows = cell vectors */
+  const double* inv_lattice;  /* [n_struct,3,3] inverse of the above (frac = cart @ inv) */
+  const int32_t* atom_struct; /* [n_atoms] structure index of each atom (non-decreasing) */
+  const int32_t* grid;        /* [n_struct,8]: cells per axis g0,g1,g2; search half-width in cells s0,s1,s2;
+                                 first global cell index; unused */
+  /* scratch (device) */
+  int32_t* cell_ptr;          /* [n_cells+1] */
+  int32_t* cell_fill;         /* [n_cells] */
+  int32_t* cell_atoms;        /* [n_atoms] */
+  int32_t* atom_cell;         /* [n_atoms,4] */
+  int32_t* atom_wrap;         /* [n_atoms,4] */
+  int32_t* scan_tmp;          /* [mb_graph_scan_tmp_len(max(n_atoms, n_edges))] */
+  int32_t* status;            /* [8] device status words */
+  uint64_t* key_unsorted;     /* [n_edges]   (phase 2) */
+  double* dist_unsorted;      /* [n_edges]   (phase 2) */
+  uint64_t* key;              /* [n_edges]   (phase 2, 3) */
+  int32_t* atom_counts;       /* [n_atoms,2] src/tgt-eligible out-edge counts (phase 2, 3) */
+  int32_t* edge_rank;         /* [n_edges,2] (phase 2, 3) */
+  int32_t* bond_counts;       /* [n_bonds+1,2]... see graph.cu (phase 2, 3): length 2*(n_edges/2+1) suffices */
+  uint8_t* edge_flag;         /* [n_edges] bit0: may be a triplet target, bit1: may be a triplet source */
+  /* outputs phase 1 (device) */
+  int32_t* edge_ptr;          /* [n_atoms+1] CSR of directed edges by centre atom */
+  /* outputs phase 2 (device), caller-allocated with n_edges known */
+  int32_t* center;            /* [n_edges] */
+  int32_t* neighbor;          /* [n_edges] */
+  int32_t* image;             /* [n_edges,3] */
+  double* dist;               /* [n_edges] float64 bond lengths used for the membership tests */
+  int32_t* rev;               /* [n_edges] index of the reverse directed edge */
+  int32_t* d2u;               /* [n_edges] directed -> bond */
+  int32_t* u2d;               /* [n_edges/2] bond -> its first directed edge */
+  int32_t* trip_ptr;          /* [n_edges/2+1] CSR of triplets by target bond */
+  int32_t* trip_src_ptr;      /* [n_edges/2+1] CSR of triplets by source bond */
+  /* outputs phase 3 (device), caller-allocated with n_triplets known */
+  int32_t* line_graph;        /* [n_triplets,5] rows (centre atom, target bond, target DE, source bond, source DE) */
+  int32_t* trip_src_perm;     /* [n_triplets] triplet ids grouped by source bond (see trip_src_ptr) */
+} mb_graph;
+
+size_t mb_graph_scan_tmp_len(int64_t n);
+int mb_graph_count_edges(mb_graph* g, void* stream);
+int mb_graph_build_edges(mb_graph* g, void* stream);
+int mb_graph_build_triplets(mb_graph* g, void* stream);
+
+/* ------------------------------------------------------------------ dense row GEMM
+ * out[r, 128*j + n] = epilogue( sum_k A_j[r, k] * W_j[n, k] )        j = 0..n_blocks-1
+ *
+ * The one contraction kernel behind every 128-wide linear layer of the model
+ * (nn.Linear calls in matris/model/functions.py:112-126,157 via MLP / GatedMLP,
+ * matris/model/interaction_block.py:96-137, 232-273, matris/model/feature_embed.py,
+ * matris/model/readout.py) and behind their data-gradient products in the backward
+ * pass (the reference gets those from torch.autograd).  A_j is the concatenation
+ * of up to four 128-wide row segments, each optionally gathered through an index
+ * (this is the torch.cat([... index_select ...]) of interaction_block.py:96-108,
+ * 232-250 without materialising it) and optionally passed through SiLU on load.
+ * Epilogue, in order: + bias, * silu'(gate), SiLU, + res_w * res, * out_scale,
+ * then store / accumulate / atomic scatter-add through out_idx.
+ */
+typedef struct mb_src {
+  const float* ptr;      /* rows of >= 128 floats starting at column `col` */
+  const int32_t* idx;    /* optional gather index per output row (NULL: row r) */
+  int64_t ld;            /* row stride in floats */
+  int32_t col;           /* first column (multiple of 4) */
+  int32_t act;           /* 0: as is, 1: SiLU applied on load */
+} mb_src;
+
+#define MB_OUT_STORE 0
+#define MB_OUT_ADD 1      /* non-atomic read-modify-write (each destination row written once) */
+#define MB_OUT_ATOMIC 2   /* atomic add (destination rows may repeat) */
+
+typedef struct mb_colblock {
+  int32_t n_src;               /* 1..4 ; K = 128 * n_src */
+  int32_t out_act;             /* 0 none, 1 SiLU */
+  mb_src src[4];
+  const float* W;              /* [128, K] row-major: weight rows of this column block */
+  int64_t ldw;                 /* row stride of W in floats (>= K) */
+  const float* bias;           /* [128] or NULL */
+  const float* gate;           /* optional pre-activation z: multiply by d/dz SiLU(z) */
+  int64_t ld_gate; int32_t col_gate; int32_t pad0;
+  const float* res;            /* optional residual rows */
+  const float* res_w;          /* [128] per-channel residual weight (NULL: 1) */
+  int64_t ld_res; int32_t col_res; int32_t mode;
+  float* out; const int32_t* out_idx;
+  int64_t ld_out; int32_t col_out; float out_scale;
+} mb_colblock;
+
+typedef struct mb_gemm_desc {
+  int64_t n_rows;
+  int32_t n_blocks;            /* 1..4 column blocks of 128 outputs */
+  int32_t pad;
+  mb_colblock blk[4];
+} mb_gemm_desc;
+
+int mb_gemm(const mb_gemm_desc* desc, void* stream);
+
+/* ------------------------------------------------------------------ row-wise model kernels
+ * All feature tensors are float32 row-major with 128 channels unless noted.
+ */
+
+/* GatedMLP tail (matris/model/functions.py:300-311): z [R,256] = (core | gate) pre-norm;
+ * h = SiLU(RMSNorm(z_core)*w_core) * sigmoid(RMSNorm(z_gate)*w_gate); optional out2 = h + res_w*res. */
+int mb_gate_fwd(int64_t n_rows, const float* z, const float* w_core, const float* w_gate, float* h,
+                const float* res, const float* res_w, float* out2, void* stream);
+/* data gradient of the above: dz [R,256] from dh [R,128] (recomputes the norms from z) */
+int mb_gate_bwd(int64_t n_rows, const float* z, const float* w_core, const float* w_gate, const float* dh,
+                float* dz, void* stream);
+
+/* Per-channel segment softmax + weighted segment sums of the attention layer
+ * (Dimwise_softmax + aggregate, matris/model/functions.py:97-160, as used in
+ * matris/model/interaction_block.py:116-137).  Rows are grouped by target node
+ * (tgt_ptr CSR, contiguous) and by source node (src_ptr CSR over src_perm).
+ * logits [*,256]: columns 0..127 source logits, 128..255 target logits, row
+ * emap[r] (NULL: r).  stats [n_nodes,4,128] = (max_t, 1/sum_t, max_s, 1/sum_s). */
+int mb_seg_attn_fwd(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* src_ptr, const int32_t* src_perm,
+                    const int32_t* emap, const float* logits, const float* h, float* agg_t, float* agg_s,
+                    float* stats, void* stream);
+/* per row: dh = a_t*dagg_t[tgt] + a_s*dagg_s[src] + dh_scale*dh_in[dh_map ? dh_map[r] : r];
+ * dlogits[r] = (a_s*dagg_s*(h-agg_s) | a_t*dagg_t*(h-agg_t)) */
+int mb_seg_attn_bwd(int64_t n_rows, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
+                    const int32_t* emap, const float* logits, const float* h, const float* agg_t,
+                    const float* agg_s, const float* stats, const float* dagg_t, const float* dagg_s,
+                    const float* dh_in, const int32_t* dh_map, float dh_scale, float* dh, float* dlogits,
+                    void* stream);
+
+/* Refinement aggregation (matris/model/interaction_block.py:246-262):
+ * agg[n] = sum_{r in target segment n} h[r] * s[r]; s[r] = env[emap[r]] (atom graph, src == NULL)
+ * or env[src[r]] * env[n] (line graph). */
+int mb_seg_smooth_sum_fwd(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* emap, const int32_t* src,
+                          int32_t idx_stride, const float* env, const float* h, float* agg, void* stream);
+/* per row: dh[r] (+)= dagg[tgt[r]] * s[r]   (accumulate != 0: add to existing dh) */
+int mb_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
+                               const int32_t* emap, const float* env, const float* dagg, float* dh,
+                               int32_t accumulate, void* stream);
+/* gradient w.r.t. env.  Atom graph (src_ptr == NULL): denv[u] = sum over the two directed rows e of
+ * bond u of dagg[tgt[e]]*h[e]  (u2d / rev give the rows).  Line graph: denv[n] = sum_{r in tgt segment n}
+ * dagg[n]*h[r]*env[src[r]] + sum_{r in src segment n} dagg[tgt[r]]*h[r]*env[tgt[r]]. */
+int mb_seg_smooth_sum_bwd_env(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* src_ptr,
+                              const int32_t* src_perm, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
+                              const int32_t* u2d, const int32_t* rev, const float* env, const float* h,
+                              const float* dagg, float* denv, void* stream);
+
+/* directed -> bond mean with residual (aggregate(..., average=True) over directed2undirected,
+ * matris/model/interaction_block.py:123, 270-273): out[u] = 0.5*(y[u2d[u]] + y[rev[u2d[u]]]) + res_w*res[u] */
+int mb_pair_mean_res(int32_t n_bonds, const int32_t* u2d, const int32_t* rev, const float* y, const float* res,
+                     const float* res_w, float* out, void* stream);
+/* y = a*x (elementwise per channel weight a[128]) ; accumulate != 0: y += a*x */
+int mb_scale_rows(int64_t n_rows, const float* x, const float* a, float* y, int32_t accumulate, void* stream);
+
+/* K <= 16 linear layers (edge_linear1 / learnable_envelope: K=7, angle_embedding: K=16;
+ * matris/model/feature_embed.py:105-106,176, matris/model/interaction_block.py:213-215):
+ * y[R,128] = x[R,K] @ W[128,K]^T and dx[R,K] (+)= dy[R,128] @ W */
+int mb_small_linear_fwd(int64_t n_rows, int32_t k, const float* x, const float* w, float* y, void* stream);
+int mb_small_linear_bwd(int64_t n_rows, int32_t k, const float* dy, const float* w, float* dx, int32_t accumulate,
+                        void* stream);
+
+/* LayerNorm(128, eps=1e-5, affine) of the bond embedding (matris/model/feature_embed.py:113,140) */
+int mb_layernorm_fwd(int64_t n_rows, const float* x, const float* w, const float* b, float* y, void* stream);
+int mb_layernorm_bwd(int64_t n_rows, const float* x, const float* w, const float* dy, float* dx, void* stream);
+/* RMSNorm(128, eps = float32 epsilon, affine) (readout_norm, matris/model/model.py:167,216) */
+int mb_rmsnorm_fwd(int64_t n_rows, const float* x, const float* w, float* y, void* stream);
+int mb_rmsnorm_bwd(int64_t n_rows, const float* x, const float* w, const float* dy, float* dx, void* stream);
+
+/* embedding lookup: y[r] = table[idx[r] + offset] (nn.Embedding, matris/model/feature_embed.py:37) */
+int mb_embedding(int64_t n_rows, const int32_t* idx, int32_t offset, const float* table, float* y, void* stream);
+
+/* Final projection of the heads: out[r] = SiLU(z[r, 0:k]) . w + b ; optional |.| (magmom,
+ * matris/model/readout.py:131) ; energy head: summed per structure through atom_ptr in mb_energy_sum. */
+int mb_head_dot_fwd(int64_t n_rows, int32_t k, const float* z, const float* w, const float* b, int32_t take_abs,
+                    float* out, void* stream);
+/* dz[r, c] = seed[seed_map[r]] * w[c] * silu'(z[r, c])   (seed: upstream gradient per structure) */
+int mb_head_dot_bwd(int64_t n_rows, int32_t k, const float* z, const float* w, const float* seed,
+                    const int32_t* seed_map, float* dz, void* stream);
+/* dz = dy * d/dz SiLU(z), element-wise on [n_rows,128]: the reference's fused SiLU backward
+ * (matris/model/op/fused_silu_op.py:5-13,32-43; matris/model/op/src/kernel/fused_silu_bwd.cu:5-25) */
+int mb_silu_bwd(int64_t n_rows, const float* dy, const float* z, float* dz, void* stream);
+/* per-structure sum of per-atom energies (GraphPooling, matris/model/functions.py:340-365) */
+int mb_segment_sum_scalar(int32_t n_seg, const int32_t* seg_ptr, const float* x, float* out, void* stream);
+
+/* ------------------------------------------------------------------ geometry and bases
+ * Edge vectors of process_graphs (matris/model/processgraph.py:87, 192-199), float32:
+ * v = r_c - (r_n + image @ L), d = |v|, u = v/d; cart = frac32 @ lattice32 is computed by the caller. */
+int mb_edge_geometry_fwd(int64_t n_edges, const float* cart, const float* lattice, const int32_t* atom_struct,
+                         const int32_t* center, const int32_t* neighbor, const int32_t* image, float* vec,
+                         float* len, float* unit, void* stream);
+/* Backward of the above plus the conservative head (matris/model/readout.py:202-224): from dE/dlen [E] and
+ * dE/dunit [E,3] form g_e = dE/dv_e, then dE/dr_i = sum_{e:c=i} g_e - sum_{e:c=i} g_rev(e) (no atomics) and
+ * per-atom virial partials, reduced per structure into dE/dstrain = sym(sum_e v_e (x) g_e) [B,3,3]. */
+int mb_edge_geometry_bwd(int32_t n_atoms, int32_t n_struct, int64_t n_edges, const int32_t* edge_ptr,
+                         const int32_t* atom_ptr,
+                         const int32_t* rev, const float* vec, const float* len, const float* unit,
+                         const float* dlen, const float* dunit, float* g_edge, float* dcart, float* virial_atom,
+                         float* dstrain, void* stream);
+
+/* Bessel * polynomial envelope, both cutoffs at once (matris/model/basis_function.py:8-50, 162-186):
+ * per bond u with d = len[u2d[u]]: rbf_a[u,7] (cutoff ca, frequencies fa) and rbf_b[u,7] (cb, fb). */
+int mb_bessel_fwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* freq_a, float cut_a,
+                  const float* freq_b, float cut_b, int32_t p, float* rbf_a, float* rbf_b, void* stream);
+/* dlen[u2d[u]] += d(rbf_a)/dd . drbf_a + d(rbf_b)/dd . drbf_b */
+int mb_bessel_bwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* freq_a, float cut_a,
+                  const float* freq_b, float cut_b, int32_t p, const float* drbf_a, const float* drbf_b,
+                  float* dlen, void* stream);
+
+/* Angle basis of ThreebodyEmbedding + SphericalExpansion (matris/model/feature_embed.py:183-197,
+ * matris/model/basis_function.py:222-338): x = (u_a . u_b)(1-1e-6), theta = acos x, 16 = 4 radial orders x 4
+ * roots of spherical Bessel functions at |u_b|/cutoff times real m=0 harmonics of cos(theta). */
+int mb_angle_basis_fwd(int64_t n_trip, const int32_t* line_graph, const float* unit, float factor, float cutoff,
+                       float* basis, void* stream);
+/* dunit[tDE] += ..., dunit[sDE] += ... (atomic) from dbasis [T,16] */
+int mb_angle_basis_bwd(int64_t n_trip, const int32_t* line_graph, const float* unit, float factor, float cutoff,
+                       const float* dbasis, float* dunit, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MATRIS_B200_H */

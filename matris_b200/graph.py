@@ -1,0 +1,338 @@
+"""Structure -> radius graph / bond graph / line graph on the GPU.
+
+Host-side mirror of the reference's graph package: ``GraphConverter`` and
+``RadiusGraph`` keep the names, arguments and error behaviour of
+matris/graph/converter.py:22-129 and matris/graph/radiusgraph.py:17-113, but
+the work (neighbour search, edge pairing, triplet enumeration; reference:
+pymatgen's get_neighbor_list + create_graph.c + line_graph_adjacency_list) runs
+in CUDA for a whole batch of structures at once through the C ABI.
+
+Structures are accepted duck-typed: pymatgen-like (``.lattice.matrix``,
+``.frac_coords``, sites with ``.specie.Z``), ASE-like (``get_cell``,
+``get_positions``, ``get_atomic_numbers``) or plain ``(numbers, cart, lattice)``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+from torch import nn
+
+from . import _lib
+
+datatype = torch.float32
+
+
+# ------------------------------------------------------------------ input handling
+def as_arrays(structure) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Return (numbers int64 [N], cart float64 [N,3], lattice float64 [3,3])."""
+    if hasattr(structure, "lattice") and hasattr(structure.lattice, "matrix"):  # pymatgen-like
+        lattice = np.asarray(structure.lattice.matrix, dtype=np.float64)
+        if hasattr(structure, "cart_coords"):
+            cart = np.asarray(structure.cart_coords, dtype=np.float64)
+        else:
+            cart = np.asarray(structure.frac_coords, dtype=np.float64) @ lattice
+        numbers = np.asarray([site.specie.Z for site in structure], dtype=np.int64)
+    elif hasattr(structure, "get_positions"):  # ASE-like
+        lattice = np.asarray(structure.get_cell(), dtype=np.float64).reshape(3, 3)
+        cart = np.asarray(structure.get_positions(), dtype=np.float64)
+        numbers = np.asarray(structure.get_atomic_numbers(), dtype=np.int64)
+    elif hasattr(structure, "numbers") and hasattr(structure, "cart"):
+        numbers, cart, lattice = structure.numbers, structure.cart, structure.lattice
+    else:
+        numbers, cart, lattice = structure
+    numbers = np.ascontiguousarray(numbers, dtype=np.int64).reshape(-1)
+    cart = np.ascontiguousarray(cart, dtype=np.float64).reshape(-1, 3)
+    lattice = np.ascontiguousarray(lattice, dtype=np.float64).reshape(3, 3)
+    if len(numbers) != len(cart):
+        raise ValueError("numbers and positions differ in length")
+    return numbers, cart, lattice
+
+
+def _formula(numbers: np.ndarray) -> str:
+    z, n = np.unique(numbers, return_counts=True)
+    return " ".join(f"Z{int(a)}:{int(b)}" for a, b in zip(z, n))
+
+
+def cell_grid(lattice: np.ndarray, n_atoms: np.ndarray, cutoff: float) -> tuple[np.ndarray, int]:
+    """Per-structure cell grid for the neighbour search: cells per axis (each cell at
+    least ``cutoff`` wide where the cell allows it), search half-width in cells, and
+    the first global cell index.  lattice [B,3,3], n_atoms [B] -> int32 [B,8], n_cells."""
+    a, b, c = lattice[:, 0], lattice[:, 1], lattice[:, 2]
+    vol = np.abs(np.einsum("bi,bi->b", a, np.cross(b, c)))
+    if (vol <= 0).any():
+        raise ValueError("singular lattice")
+    width = np.stack([vol / np.linalg.norm(np.cross(b, c), axis=1),
+                      vol / np.linalg.norm(np.cross(c, a), axis=1),
+                      vol / np.linalg.norm(np.cross(a, b), axis=1)], axis=1)
+    g = np.maximum(1, np.floor(width / cutoff)).astype(np.int64)
+    # never more cells than a few per atom (huge vacuum boxes would waste memory)
+    cap = 4 * n_atoms.astype(np.int64) + 8
+    for _ in range(64):
+        over = g.prod(axis=1) > cap
+        if not over.any():
+            break
+        k = g.argmax(axis=1)
+        rows = np.nonzero(over)[0]
+        g[rows, k[rows]] = np.maximum(1, g[rows, k[rows]] // 2)
+    s = np.maximum(1, np.ceil(cutoff * g / width - 1e-12)).astype(np.int64)
+    cells = g.prod(axis=1)
+    base = np.concatenate([[0], np.cumsum(cells)[:-1]])
+    grid = np.zeros((len(lattice), 8), dtype=np.int32)
+    grid[:, 0:3], grid[:, 3:6], grid[:, 6] = g, s, base
+    if cells.sum() > 2**31 - 2:
+        raise ValueError("cell grid too large")
+    return grid, int(cells.sum())
+
+
+# ------------------------------------------------------------------ batched graph
+class BatchedGraph:
+    """Device-resident graph of a batch of structures (all indices global)."""
+
+    def __init__(self):
+        self.n_atoms = self.n_struct = self.n_edges = self.n_bonds = self.n_triplets = 0
+
+    @property
+    def device(self):
+        return self.cart32.device
+
+    def structure_slices(self):
+        """Host index ranges of every structure: atoms, directed edges, bonds, triplets."""
+        if getattr(self, "_slices", None) is None:
+            ap = self.atom_ptr_host
+            ep = self.edge_ptr.cpu().numpy()[ap]
+            first = self.u2d.cpu().numpy()
+            bp = np.searchsorted(first, ep)
+            tp = self.trip_ptr.cpu().numpy()[bp]
+            self._slices = (ap, ep, bp, tp)
+        return self._slices
+
+
+def _i32(n, device):
+    return torch.empty(max(int(n), 1), dtype=torch.int32, device=device)
+
+
+def build_batched_graph(numbers: Sequence[np.ndarray], carts: Sequence[np.ndarray], lattices: Sequence[np.ndarray],
+                        cutoff: float = 6.0, line_cutoff: float = 4.0, device="cuda", tol: float = 1e-8,
+                        stream=None) -> BatchedGraph:
+    """Build atom graph, bond graph and line graph for a batch of structures on ``device``."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise _lib.MbError("matris_b200 builds graphs on a CUDA device only (no CPU path)")
+    lib = _lib.load()
+    n_per = np.asarray([len(z) for z in numbers], dtype=np.int64)
+    if (n_per <= 0).any():
+        raise ValueError("empty structure")
+    n_struct, n_atoms = len(n_per), int(n_per.sum())
+    atom_ptr = np.concatenate([[0], np.cumsum(n_per)]).astype(np.int32)
+    cart = np.concatenate(carts).astype(np.float64, copy=False)
+    lattice = np.stack(lattices).astype(np.float64, copy=False)
+    inv = np.linalg.inv(lattice)
+    atom_struct = np.repeat(np.arange(n_struct, dtype=np.int32), n_per)
+    grid, n_cells = cell_grid(lattice, n_per, float(cutoff))
+    # float32 model inputs exactly as the reference derives them (converter.py:82-83, processgraph.py:87)
+    frac32 = np.einsum("ni,nij->nj", cart, inv[atom_struct]).astype(np.float32)
+    lat32 = lattice.astype(np.float32)
+    cart32 = np.einsum("ni,nij->nj", frac32, lat32[atom_struct]).astype(np.float32)
+    vol32 = np.einsum("bi,bi->b", lat32[:, 0], np.cross(lat32[:, 1], lat32[:, 2])).astype(np.float32)
+
+    with torch.cuda.device(device):
+        st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+
+        def up(x):
+            return torch.from_numpy(np.ascontiguousarray(x)).to(device, non_blocking=True)
+
+        g = BatchedGraph()
+        g.n_atoms, g.n_struct = n_atoms, n_struct
+        g.cutoff, g.line_cutoff = float(cutoff), float(line_cutoff)
+        g.atoms_per_graph = [int(x) for x in n_per]
+        g.atom_ptr_host = atom_ptr
+        g.numbers_host = np.concatenate(numbers).astype(np.int64)
+        g.cart64_host, g.lattice64_host = cart, lattice
+        g.cart64, g.lattice64, d_inv = up(cart), up(lattice), up(inv)
+        g.atom_struct, g.atom_ptr, d_grid = up(atom_struct), up(atom_ptr), up(grid)
+        g.numbers = up(g.numbers_host.astype(np.int32))
+        g.cart32, g.lattice32, g.volume = up(cart32), up(lat32), up(vol32)
+        g.frac32_host = frac32
+
+        m = _lib.MbGraph()
+        m.n_atoms, m.n_struct, m.n_cells = n_atoms, n_struct, n_cells
+        m.cutoff, m.line_cutoff, m.tol = float(cutoff), float(line_cutoff), float(tol)
+        m.cart, m.lattice, m.inv_lattice = g.cart64.data_ptr(), g.lattice64.data_ptr(), d_inv.data_ptr()
+        m.atom_struct, m.grid = g.atom_struct.data_ptr(), d_grid.data_ptr()
+        keep = [d_inv, d_grid]
+        scr = dict(cell_ptr=_i32(n_cells + 1, device), cell_fill=_i32(n_cells, device), cell_atoms=_i32(n_atoms, device),
+                   atom_cell=_i32(4 * n_atoms, device), atom_wrap=_i32(4 * n_atoms, device), status=_i32(8, device),
+                   scan_tmp=_i32(lib.mb_graph_scan_tmp_len(max(n_atoms, n_cells)), device))
+        g.edge_ptr = _i32(n_atoms + 1, device)
+        for k, v in scr.items():
+            setattr(m, k, v.data_ptr())
+        m.edge_ptr = g.edge_ptr.data_ptr()
+        _lib.call("mb_graph_count_edges", C.byref(m), st)
+        ne = int(m.n_edges)
+        if ne <= 0 or ne % 2:
+            raise _lib.MbError(f"graph build produced {ne} directed edges")
+        scr2 = dict(scan_tmp=_i32(lib.mb_graph_scan_tmp_len(ne), device),
+                    key_unsorted=torch.empty(ne, dtype=torch.int64, device=device),
+                    dist_unsorted=torch.empty(ne, dtype=torch.float64, device=device),
+                    key=torch.empty(ne, dtype=torch.int64, device=device),
+                    atom_counts=_i32(2 * n_atoms, device), edge_rank=_i32(2 * ne + 2, device),
+                    bond_counts=_i32(ne + 4, device), edge_flag=torch.empty(ne, dtype=torch.uint8, device=device))
+        for k, v in scr2.items():
+            setattr(m, k, v.data_ptr())
+        g.center, g.neighbor, g.image = _i32(ne, device), _i32(ne, device), _i32(3 * ne, device).view(ne, 3)
+        g.dist64 = torch.empty(ne, dtype=torch.float64, device=device)
+        g.rev, g.d2u, g.u2d = _i32(ne, device), _i32(ne, device), _i32(ne // 2, device)
+        g.trip_ptr, g.trip_src_ptr = _i32(ne // 2 + 1, device), _i32(ne // 2 + 1, device)
+        for k in ("center", "neighbor", "image", "rev", "d2u", "u2d", "trip_ptr", "trip_src_ptr"):
+            setattr(m, k, getattr(g, k).data_ptr())
+        m.dist = g.dist64.data_ptr()
+        _lib.call("mb_graph_build_edges", C.byref(m), st)
+        g.n_edges, g.n_bonds, nt = ne, int(m.n_bonds), int(m.n_triplets)
+        g.n_triplets = nt
+        g.line_graph = _i32(5 * nt, device).view(-1, 5)[:nt]
+        g.trip_src_perm = _i32(nt, device)[:nt]
+        if nt:
+            m.line_graph, m.trip_src_perm = g.line_graph.data_ptr(), g.trip_src_perm.data_ptr()
+            _lib.call("mb_graph_build_triplets", C.byref(m), st)
+            # column-major copy: each of (centre atom, target bond, target DE, source bond, source DE) contiguous
+            g.lg_cols = g.line_graph.t().contiguous()
+        else:
+            g.lg_cols = torch.empty(5, 0, dtype=torch.int32, device=device)
+        torch.cuda.current_stream().synchronize()  # scratch tensors go out of scope here
+        del keep, scr, scr2
+    return g
+
+
+# ------------------------------------------------------------------ reference-compatible value type
+class RadiusGraph:
+    """One structure's graph with the reference's field names
+    (matris/graph/radiusgraph.py:17-113).  Instances produced by
+    ``GraphConverter`` also carry the device-resident batch they were built in
+    (``_batch`` / ``_index``), which is what the model consumes."""
+
+    def __init__(self, graph_id=None, mp_id=None, composition=None, atomic_number=None, atom_frac_coord=None,
+                 lattice=None, neighbor_image=None, atom_graph=None, atom_graph_cutoff=6.0, line_graph=None,
+                 line_graph_cutoff=4.0, directed2undirected=None, undirected2directed=None):
+        self.graph_id, self.mp_id, self.composition = graph_id, mp_id, composition
+        self.atomic_number, self.atom_frac_coord, self.lattice = atomic_number, atom_frac_coord, lattice
+        self.neighbor_image, self.atom_graph, self.line_graph = neighbor_image, atom_graph, line_graph
+        self.atom_graph_cutoff, self.line_graph_cutoff = atom_graph_cutoff, line_graph_cutoff
+        self.directed2undirected, self.undirected2directed = directed2undirected, undirected2directed
+        self._batch, self._index, self._source = None, 0, None
+        assert len(directed2undirected) == 2 * len(undirected2directed), (
+            f"Number of directed indices ({len(directed2undirected)}) != "
+            f"2 * number of undirected indices ({2 * len(undirected2directed)})!")
+
+    _TENSORS = ("atomic_number", "atom_frac_coord", "lattice", "neighbor_image", "atom_graph", "line_graph",
+                "directed2undirected", "undirected2directed")
+
+    def to(self, device="cpu") -> "RadiusGraph":
+        d = self.to_dict()
+        for k in self._TENSORS:
+            d[k] = d[k].to(device)
+        out = RadiusGraph(**d)
+        out._batch, out._index, out._source = self._batch, self._index, self._source
+        return out
+
+    def to_dict(self) -> dict[str, Any]:
+        return {k: getattr(self, k) for k in ("graph_id", "mp_id", "composition", "atomic_number", "atom_frac_coord",
+                                               "lattice", "neighbor_image", "atom_graph", "atom_graph_cutoff",
+                                               "line_graph", "line_graph_cutoff", "directed2undirected",
+                                               "undirected2directed")}
+
+    def save(self, fname=None, save_dir=".") -> str:
+        name = fname or (f"{self.graph_id}.pt" if self.graph_id is not None else f"{self.composition}.pt")
+        path = os.path.join(save_dir, name)
+        torch.save({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.to_dict().items()}, path)
+        return path
+
+    @classmethod
+    def from_file(cls, file_name: str) -> "RadiusGraph":
+        return cls.from_dict(torch.load(file_name))
+
+    @classmethod
+    def from_dict(cls, dic: dict[str, Any]) -> "RadiusGraph":
+        return RadiusGraph(**dic)
+
+    def source_arrays(self):
+        """(numbers, cart, lattice) this graph was built from; falls back to the float32 fields."""
+        if self._source is not None:
+            return self._source
+        lat = self.lattice.detach().cpu().double().numpy()
+        return (self.atomic_number.detach().cpu().numpy().astype(np.int64),
+                self.atom_frac_coord.detach().cpu().double().numpy() @ lat, lat)
+
+    def __repr__(self) -> str:
+        return (f"RadiusGraph(composition={self.composition!r}, atom_graph_cutoff={self.atom_graph_cutoff}, "
+                f"line_graph_cutoff={self.line_graph_cutoff}, n_atoms={len(self.atomic_number)}, "
+                f"atom_graph_len={len(self.atom_graph)}, line_graph_len={len(self.line_graph)})")
+
+
+def split_batch(batch: BatchedGraph, sources=None, graph_ids=None) -> list[RadiusGraph]:
+    """Per-structure RadiusGraph views (local indices, reference layout) of a batch."""
+    ap, ep, bp, tp = batch.structure_slices()
+    out = []
+    frac = torch.from_numpy(batch.frac32_host).to(batch.device)
+    for b in range(batch.n_struct):
+        a0, a1, e0, e1, u0, u1, t0, t1 = ap[b], ap[b + 1], ep[b], ep[b + 1], bp[b], bp[b + 1], tp[b], tp[b + 1]
+        lg = batch.line_graph[t0:t1].clone()
+        if len(lg):
+            lg -= torch.tensor([a0, u0, e0, u0, e0], dtype=torch.int32, device=batch.device)
+        rg = RadiusGraph(
+            graph_id=None if graph_ids is None else graph_ids[b], mp_id=None,
+            composition=_formula(batch.numbers_host[a0:a1]),
+            atomic_number=batch.numbers[a0:a1], atom_frac_coord=frac[a0:a1], lattice=batch.lattice32[b],
+            neighbor_image=batch.image[e0:e1].to(datatype),
+            atom_graph=torch.stack([batch.center[e0:e1] - a0, batch.neighbor[e0:e1] - a0], dim=1),
+            atom_graph_cutoff=batch.cutoff, line_graph=lg, line_graph_cutoff=batch.line_cutoff,
+            directed2undirected=batch.d2u[e0:e1] - u0, undirected2directed=batch.u2d[u0:u1] - e0)
+        rg._batch, rg._index = batch, b
+        rg._source = (batch.numbers_host[a0:a1], batch.cart64_host[a0:a1], batch.lattice64_host[b])
+        out.append(rg)
+    return out
+
+
+class GraphConverter(nn.Module):
+    """Convert a structure to a RadiusGraph (matris/graph/converter.py:22-129) on the GPU."""
+
+    def __init__(self, atom_graph_cutoff: float = 6, line_graph_cutoff: float = 4, verbose: bool = False,
+                 device: str | None = None) -> None:
+        super().__init__()
+        self.atom_graph_cutoff = atom_graph_cutoff
+        self.line_graph_cutoff = atom_graph_cutoff if line_graph_cutoff is None else line_graph_cutoff
+        self.algorithm = "cuda"
+        self.device = device
+        if verbose:
+            print(self)
+
+    def __repr__(self) -> str:
+        return (f"GraphConverter(algorithm={self.algorithm!r}, atom_graph_cutoff={self.atom_graph_cutoff}, "
+                f"line_graph_cutoff={self.line_graph_cutoff})")
+
+    def _device(self):
+        return torch.device(self.device if self.device is not None else "cuda")
+
+    def batch(self, structures) -> BatchedGraph:
+        """Graphs of many structures in one pass (the batched entry the model uses)."""
+        arrays = [as_arrays(s) for s in structures]
+        return build_batched_graph([a[0] for a in arrays], [a[1] for a in arrays], [a[2] for a in arrays],
+                                   self.atom_graph_cutoff, self.line_graph_cutoff, self._device())
+
+    def forward(self, structure, graph_id=None, mp_id=None) -> RadiusGraph:
+        """Convert one structure; raises ValueError for an isolated atom like the reference."""
+        rg = split_batch(self.batch([structure]), graph_ids=[graph_id])[0]
+        rg.mp_id = mp_id
+        return rg
+
+    def as_dict(self) -> dict[str, float]:
+        return {"atom_graph_cutoff": self.atom_graph_cutoff, "line_graph_cutoff": self.line_graph_cutoff,
+                "algorithm": self.algorithm}
+
+    @classmethod
+    def from_dict(cls, dict) -> "GraphConverter":
+        dict = {k: v for k, v in dict.items() if k != "algorithm"}
+        return GraphConverter(**dict)

@@ -1,0 +1,602 @@
+"""MatRIS energy / force / stress / magmom evaluation on B200.
+
+Host-side mirror of the reference's ``MatRIS`` module
+(matris/model/model.py:30-317): same constructor arguments, ``config``,
+``state_dict`` key names, ``from_dict`` / ``load`` checkpoint interface,
+``graph_converter`` attribute and ``forward(graphs, task, is_training)`` result
+dictionary.  All arithmetic runs in the CUDA kernels behind the C ABI; the
+sub-blocks are ``torch.autograd.Function``s whose backward passes are
+hand-written kernel sequences (data gradients only: weights are frozen at
+inference), so forces = -dE/dr and stress = (1/V) dE/d(strain) come out of
+``torch.autograd.grad`` exactly as in the reference's conservative head
+(matris/model/readout.py:202-224).
+
+Memory policy: a sub-block keeps only its inputs for the backward pass and
+recomputes its internals there (the reference does the same above 60,000
+triplets, matris/model/interaction_block.py:15, 400-403).
+"""
+from __future__ import annotations
+
+import os
+from collections.abc import Sequence
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+from torch import nn
+from torch.autograd.function import once_differentiable
+
+from . import ops
+from .graph import BatchedGraph, GraphConverter, RadiusGraph, build_batched_graph, as_arrays
+from .ops import B, OUT_ADD, OUT_ATOMIC, OUT_STORE, S, gemm
+from .weights import BUFFER_KEYS, check_supported, full_config, random_state_dict, schema
+
+GPA_PER_EV_A3 = 160.21766208  # matris/model/readout.py:215
+D = 128
+
+
+# ------------------------------------------------------------------ packed parameters
+def _pack_gated(get, prefix, dev):
+    """GatedMLP weights in kernel layout: first layers of core|gate stacked to
+    [256,K], second layers stacked to [256,128], plus the transposes the backward
+    GEMMs contract with."""
+    c, g = prefix + "mlp_core.layers.", prefix + "mlp_gate.layers."
+    w1 = torch.cat([get(c + "0.weight"), get(g + "0.weight")], 0).contiguous()
+    w2 = torch.cat([get(c + "3.weight"), get(g + "3.weight")], 0).contiguous()
+    return SimpleNamespace(
+        w1=w1, b1=torch.cat([get(c + "0.bias"), get(g + "0.bias")]).contiguous(),
+        w2=w2, b2=torch.cat([get(c + "3.bias"), get(g + "3.bias")]).contiguous(),
+        w1t=w1.t().contiguous(),                                                  # [K,256]
+        w2t=torch.cat([get(c + "3.weight").t(), get(g + "3.weight").t()], 0).contiguous(),  # [256,128]
+        nc=get(prefix + "core_norm.weight").contiguous(), ng=get(prefix + "gate_norm.weight").contiguous(),
+        k=w1.shape[1])
+
+
+def _pack_ffn(get, prefix):
+    w1, w2 = get(prefix + "layers.0.weight").contiguous(), get(prefix + "layers.3.weight").contiguous()
+    return SimpleNamespace(w1=w1, w2=w2, w1t=w1.t().contiguous(), w2t=w2.t().contiguous())
+
+
+def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
+    def get(k):
+        return sd[k].detach().to(device=device, dtype=torch.float32)
+
+    P = SimpleNamespace()
+    P.emb_table = get("atom_embedding.embedding.weight").contiguous()
+    P.emb_w = get("atom_embedding.atom_swish_layer.linear.weight").contiguous()
+    e = "edge_embedding."
+    P.freq2, P.freq3 = get(e + "pairwise_rbf_expansion.frequencies").contiguous(), get(
+        e + "threebody_rbf_expansion.frequencies").contiguous()
+    P.e_w1 = get(e + "edge_linear1.weight").contiguous()
+    P.e_w2 = get(e + "edge_linear2.weight").contiguous()
+    P.e_w3 = get(e + "swish_layer.linear.weight").contiguous()
+    P.e_w2t, P.e_w3t = P.e_w2.t().contiguous(), P.e_w3.t().contiguous()
+    P.e_lnw, P.e_lnb = get(e + "edge_init_norm.weight").contiguous(), get(e + "edge_init_norm.bias").contiguous()
+    t = "three_body_embedding."
+    P.sph_factor = float(sd[t + "expansion.factor"])
+    P.t_wa = get(t + "angle_embedding.weight").contiguous()
+    P.t_wb = get(t + "swish_layer.linear.weight").contiguous()
+    P.t_wbt = P.t_wb.t().contiguous()
+    P.layers = []
+    for i in range(int(cfg["num_layers"])):
+        L = SimpleNamespace()
+        for gname in ("atom", "line"):
+            p = f"interaction_block.{i}.attn_block_{gname}_graph."
+            A = SimpleNamespace(node=_pack_gated(get, p + "node_nonlinear_update.", device),
+                                edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
+                                wn=get(p + "node_res_weight").reshape(-1).contiguous(),
+                                we=get(p + "edge_res_weight").reshape(-1).contiguous())
+            A.wst = torch.cat([get(p + "source_weight_linear.weight"), get(p + "target_weight_linear.weight")],
+                              0).contiguous()         # [256,128]
+            A.wstt = A.wst.t().contiguous()           # [128,256]
+            setattr(L, "attn_" + gname, A)
+            p = f"interaction_block.{i}.refine_block_{gname}_graph."
+            R = SimpleNamespace(edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
+                                nffn=_pack_ffn(get, p + "node_FFN."), effn=_pack_ffn(get, p + "edge_FFN."),
+                                wenv=get(p + "learnable_envelope.weight").contiguous(),
+                                wn=get(p + "node_res_weight").reshape(-1).contiguous(),
+                                we=get(p + "edge_res_weight").reshape(-1).contiguous())
+            setattr(L, "refine_" + gname, R)
+        P.layers.append(L)
+    P.out_norm = get("readout_norm.weight").contiguous()
+    h = "energy_head.energy_head.layers."
+    P.h_w0, P.h_b0 = get(h + "0.weight").contiguous(), get(h + "0.bias").contiguous()
+    P.h_w3, P.h_b3 = get(h + "3.weight").contiguous(), get(h + "3.bias").contiguous()
+    P.h_w0t, P.h_w3t = P.h_w0.t().contiguous(), P.h_w3.t().contiguous()
+    P.h_w6, P.h_b6 = get(h + "6.weight").reshape(-1).contiguous(), get(h + "6.bias").contiguous()
+    m = "magmom_head.magmom_head.layers."
+    P.m_w0, P.m_b0 = get(m + "0.weight").contiguous(), get(m + "0.bias").contiguous()
+    P.m_w3, P.m_b3 = get(m + "3.weight").reshape(-1).contiguous(), get(m + "3.bias").contiguous()
+    return P
+
+
+# ------------------------------------------------------------------ row graphs
+def row_graphs(g: BatchedGraph):
+    """The two message-passing graphs in the form the kernels take: rows grouped by
+    target node (tgt_ptr), the source-side grouping as a permutation."""
+    if getattr(g, "_row_graphs", None) is None:
+        atom = SimpleNamespace(is_atom=True, n_rows=g.n_edges, n_nodes=g.n_atoms, n_edge_rows=g.n_bonds,
+                               tgt=g.center, src=g.neighbor, ctr=None, tgt_ptr=g.edge_ptr, src_ptr=g.edge_ptr,
+                               src_perm=g.rev, emap=g.d2u, u2d=g.u2d, rev=g.rev)
+        line = None
+        if g.n_triplets:
+            c = g.lg_cols
+            line = SimpleNamespace(is_atom=False, n_rows=g.n_triplets, n_nodes=g.n_bonds, n_edge_rows=g.n_triplets,
+                                   ctr=c[0], tgt=c[1], src=c[3], tgt_ptr=g.trip_ptr, src_ptr=g.trip_src_ptr,
+                                   src_perm=g.trip_src_perm, emap=None, u2d=None, rev=None)
+        g._row_graphs = (atom, line)
+    return g._row_graphs
+
+
+# ------------------------------------------------------------------ gated MLP building block
+def gated_fwd(p, n_rows, srcs):
+    """z1 = X W1^T + b1 (core|gate, pre-activation), z2 = SiLU(z1) W2^T + b2 (pre-norm)."""
+    ref = srcs[0][0]
+    z1, z2 = ops.new(n_rows, 2 * D, ref), ops.new(n_rows, 2 * D, ref)
+    gemm(n_rows, [B(srcs, p.w1, w_row=D * j, bias=p.b1, bias_off=D * j, out=z1, out_col=D * j) for j in (0, 1)])
+    gemm(n_rows, [B([S(z1, None, D * j, 1)], p.w2, w_row=D * j, bias=p.b2, bias_off=D * j, out=z2, out_col=D * j)
+                  for j in (0, 1)])
+    return z1, z2
+
+
+def gated_bwd(p, n_rows, z1, z2, dh, dests):
+    """Backward through the gated MLP: dests[c] = (tensor, idx, mode) for K segment c."""
+    dz2 = ops.gate_bwd(z2, p.nc, p.ng, dh)
+    dz1 = torch.empty_like(z1)
+    gemm(n_rows, [B([S(dz2, None, D * j)], p.w2t, w_row=D * j, gate=z1, gate_col=D * j, out=dz1, out_col=D * j)
+                  for j in (0, 1)])
+    del dz2
+    blocks = [B([S(dz1, None, 0), S(dz1, None, D)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode)
+              for c, (t, idx, mode) in enumerate(dests) if t is not None]
+    gemm(n_rows, blocks)
+
+
+# ------------------------------------------------------------------ attention layer
+def _attn_forward(P, rg, node, edge):
+    R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
+    z1, z2 = gated_fwd(P.edge, R, [S(edge, rg.emap), S(node, rg.tgt), S(node, rg.src)])
+    if rg.is_atom:
+        h, _ = ops.gate_fwd(z2, P.edge.nc, P.edge.ng)
+        edge_out = ops.pair_mean_res(Ne, rg.u2d, rg.rev, h, edge, P.we)
+    else:
+        h, edge_out = ops.gate_fwd(z2, P.edge.nc, P.edge.ng, res=edge, res_w=P.we)
+    logits = ops.linear(edge, P.wst)                      # [Ne,256]: source | target logits
+    agg_t, agg_s, stats = ops.seg_attn_fwd(Nn, rg.tgt_ptr, rg.src_ptr, rg.src_perm, rg.emap, logits, h)
+    z1n, z2n = gated_fwd(P.node, Nn, [S(node), S(agg_t), S(agg_s)])
+    _, node_out = ops.gate_fwd(z2n, P.node.nc, P.node.ng, want_h=False, res=node, res_w=P.wn)
+    return node_out, edge_out, (z1, z2, h, logits, agg_t, agg_s, stats, z1n, z2n)
+
+
+class AttentionFn(torch.autograd.Function):
+    """Graph_Attention_Layer.forward (matris/model/interaction_block.py:87-143)."""
+
+    @staticmethod
+    def forward(ctx, node, edge, P, rg):
+        node, edge = node.contiguous(), edge.contiguous()
+        node_out, edge_out, _ = _attn_forward(P, rg, node, edge)
+        ctx.save_for_backward(node, edge)
+        ctx.P, ctx.rg = P, rg
+        return node_out, edge_out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_node_out, d_edge_out):
+        node, edge = ctx.saved_tensors
+        P, rg = ctx.P, ctx.rg
+        R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
+        d_node_out, d_edge_out = d_node_out.contiguous(), d_edge_out.contiguous()
+        _, _, (z1, z2, h, logits, agg_t, agg_s, stats, z1n, z2n) = _attn_forward(P, rg, node, edge)
+        # node update
+        d_node = ops.scale_rows(d_node_out, P.wn)
+        dagg_t, dagg_s = ops.new(Nn, D, node), ops.new(Nn, D, node)
+        gated_bwd(P.node, Nn, z1n, z2n, d_node_out,
+                  [(d_node, None, OUT_ADD), (dagg_t, None, OUT_STORE), (dagg_s, None, OUT_STORE)])
+        del z1n, z2n
+        # softmax-weighted aggregation
+        dh, dlogits = ops.seg_attn_bwd(rg.tgt, rg.src, rg.emap, logits, h, agg_t, agg_s, stats, dagg_t, dagg_s,
+                                       d_edge_out, rg.emap, 0.5 if rg.is_atom else 1.0)
+        del logits, h, agg_t, agg_s, stats, dagg_t, dagg_s
+        # edge update
+        d_edge = ops.scale_rows(d_edge_out, P.we)
+        emode = OUT_ATOMIC if rg.is_atom else OUT_ADD
+        gated_bwd(P.edge, R, z1, z2, dh,
+                  [(d_edge, rg.emap, emode), (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)])
+        del z1, z2, dh
+        gemm(R, [B([S(dlogits, None, 0), S(dlogits, None, D)], P.wstt, out=d_edge, out_idx=rg.emap, mode=emode)])
+        return d_node, d_edge, None, None
+
+
+# ------------------------------------------------------------------ refinement layer
+def _refine_forward(P, rg, node, edge, rbf, atom_feat):
+    R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
+    if rg.is_atom:
+        srcs = [S(edge, rg.emap), S(node, rg.tgt), S(node, rg.src)]
+    else:
+        srcs = [S(edge), S(atom_feat, rg.ctr), S(node, rg.tgt), S(node, rg.src)]
+    z1, z2 = gated_fwd(P.edge, R, srcs)
+    h, _ = ops.gate_fwd(z2, P.edge.nc, P.edge.ng)
+    env = ops.small_linear_fwd(rbf, P.wenv)               # [bonds,128]
+    agg = ops.seg_smooth_sum_fwd(Nn, rg.tgt_ptr, rg.emap, None if rg.is_atom else rg.src, env, h)
+    zn = ops.linear(agg, P.nffn.w1)
+    node_out = ops.linear(zn, P.nffn.w2, in_act=1, res=node, res_w=P.wn)
+    ze = ops.linear(h, P.effn.w1)
+    if rg.is_atom:
+        y = ops.linear(ze, P.effn.w2, in_act=1)
+        edge_out = ops.pair_mean_res(Ne, rg.u2d, rg.rev, y, edge, P.we)
+    else:
+        edge_out = ops.linear(ze, P.effn.w2, in_act=1, res=edge, res_w=P.we)
+    return node_out, edge_out, (z1, z2, h, env, zn, ze)
+
+
+class RefineFn(torch.autograd.Function):
+    """Refinement.forward (matris/model/interaction_block.py:218-278)."""
+
+    @staticmethod
+    def forward(ctx, node, edge, rbf, atom_feat, P, rg):
+        node, edge, rbf = node.contiguous(), edge.contiguous(), rbf.contiguous()
+        if atom_feat is not None:
+            atom_feat = atom_feat.contiguous()
+        node_out, edge_out, _ = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+        ctx.save_for_backward(node, edge, rbf, atom_feat)
+        ctx.P, ctx.rg = P, rg
+        return node_out, edge_out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_node_out, d_edge_out):
+        node, edge, rbf, atom_feat = ctx.saved_tensors
+        P, rg = ctx.P, ctx.rg
+        R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
+        d_node_out, d_edge_out = d_node_out.contiguous(), d_edge_out.contiguous()
+        _, _, (z1, z2, h, env, zn, ze) = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+        # node FFN
+        d_node = ops.scale_rows(d_node_out, P.wn)
+        dzn = ops.linear(d_node_out, P.nffn.w2t, gate=zn)
+        dagg = ops.linear(dzn, P.nffn.w1t)
+        del zn, dzn
+        # edge FFN (atom graph: the mean over the two directions is a gather * 0.5)
+        if rg.is_atom:
+            dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze, scale=0.5, idx=rg.emap)
+        else:
+            dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze)
+        dh = ops.linear(dze, P.effn.w1t)
+        del ze, dze
+        # smoothed aggregation
+        src = None if rg.is_atom else rg.src
+        ops.seg_smooth_sum_bwd_rows(rg.tgt, src, rg.emap, env, dagg, dh, accumulate=True)
+        denv = ops.seg_smooth_sum_bwd_env(env.shape[0], rg.tgt_ptr, None if rg.is_atom else rg.src_ptr, rg.src_perm,
+                                          rg.tgt, src if src is not None else rg.src, rg.u2d, rg.rev, env, h, dagg)
+        d_rbf = ops.small_linear_bwd(denv, P.wenv)
+        del env, denv, dagg, h
+        # gated MLP
+        d_edge = ops.scale_rows(d_edge_out, P.we)
+        if rg.is_atom:
+            d_atom = None
+            dests = [(d_edge, rg.emap, OUT_ATOMIC), (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
+        else:
+            d_atom = torch.zeros_like(atom_feat)
+            dests = [(d_edge, None, OUT_ADD), (d_atom, rg.ctr, OUT_ATOMIC), (d_node, rg.tgt, OUT_ATOMIC),
+                     (d_node, rg.src, OUT_ATOMIC)]
+        gated_bwd(P.edge, R, z1, z2, dh, dests)
+        return d_node, d_edge, d_rbf, d_atom, None, None
+
+
+# ------------------------------------------------------------------ geometry, embeddings, readout
+class EdgeGeometryFn(torch.autograd.Function):
+    """Edge vectors / lengths / unit vectors and their adjoint: forces and virial
+    (matris/model/processgraph.py:169-199, matris/model/readout.py:202-224).  ``strain`` is the
+    zero strain leaf; the forward value does not depend on it, its gradient is sym(sum v (x) dE/dv)."""
+
+    @staticmethod
+    def forward(ctx, cart, strain, g):
+        vec, length, unit = ops.edge_geometry_fwd(cart.contiguous(), g.lattice32, g.atom_struct, g.center, g.neighbor,
+                                                  g.image)
+        ctx.save_for_backward(vec, length, unit)
+        ctx.g, ctx.has_strain = g, strain is not None
+        ctx.mark_non_differentiable(vec)
+        return length, unit, vec
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dlen, dunit, _dvec):
+        vec, length, unit = ctx.saved_tensors
+        g = ctx.g
+        dcart, dstrain, _ = ops.edge_geometry_bwd(g.n_atoms, g.n_struct, g.edge_ptr, g.atom_ptr, g.rev, vec, length,
+                                                  unit, dlen.contiguous(), dunit.contiguous())
+        return dcart, (dstrain if ctx.has_strain else None), None
+
+
+def _edge_embed_forward(P, g, length, cfg):
+    rbf2, rbf3 = ops.bessel_fwd(g.u2d, length, P.freq2, cfg["pairwise_cutoff"], P.freq3, cfg["three_body_cutoff"],
+                                cfg["envelope_exponent"])
+    e1 = ops.small_linear_fwd(rbf2, P.e_w1)
+    e2 = ops.linear(e1, P.e_w2)
+    # both directed copies of a bond carry the same row, so their mean is the row itself:
+    # the expand-to-directed / average-back pair of the reference is the identity here
+    e3 = ops.layernorm_fwd(e2, P.e_lnw, P.e_lnb)
+    return rbf2, rbf3, e2, e3
+
+
+class EdgeEmbedFn(torch.autograd.Function):
+    """EdgeBasisEmbedding.forward (matris/model/feature_embed.py:114-148)."""
+
+    @staticmethod
+    def forward(ctx, length, P, g, cfg):
+        length = length.contiguous()
+        rbf2, rbf3, _, e3 = _edge_embed_forward(P, g, length, cfg)
+        edge = ops.linear(e3, P.e_w3, out_act=1)
+        ctx.save_for_backward(length)
+        ctx.P, ctx.g, ctx.cfg = P, g, cfg
+        return edge, rbf2, rbf3
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_edge, d_rbf2, d_rbf3):
+        (length,) = ctx.saved_tensors
+        P, g, cfg = ctx.P, ctx.g, ctx.cfg
+        _, _, e2, e3 = _edge_embed_forward(P, g, length, cfg)
+        z = ops.linear(e3, P.e_w3)
+        dz = ops.silu_bwd(d_edge.contiguous(), z)
+        de3 = ops.linear(dz, P.e_w3t)
+        de2 = ops.layernorm_bwd(e2, P.e_lnw, de3)
+        de1 = ops.linear(de2, P.e_w2t)
+        d2 = d_rbf2.contiguous().clone()
+        ops.small_linear_bwd(de1, P.e_w1, d2, accumulate=True)
+        dlen = ops.bessel_bwd(g.u2d, length, P.freq2, cfg["pairwise_cutoff"], P.freq3, cfg["three_body_cutoff"],
+                              cfg["envelope_exponent"], d2, d_rbf3.contiguous())
+        return dlen, None, None, None
+
+
+class AngleEmbedFn(torch.autograd.Function):
+    """ThreebodyEmbedding.forward (matris/model/feature_embed.py:183-203)."""
+
+    @staticmethod
+    def forward(ctx, unit, P, g, cfg):
+        unit = unit.contiguous()
+        basis = ops.angle_basis_fwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"])
+        t1 = ops.small_linear_fwd(basis, P.t_wa)
+        trip = ops.linear(t1, P.t_wb, out_act=1)
+        ctx.save_for_backward(unit)
+        ctx.P, ctx.g, ctx.cfg = P, g, cfg
+        return trip
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_trip):
+        (unit,) = ctx.saved_tensors
+        P, g, cfg = ctx.P, ctx.g, ctx.cfg
+        basis = ops.angle_basis_fwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"])
+        t1 = ops.small_linear_fwd(basis, P.t_wa)
+        z = ops.linear(t1, P.t_wb)
+        del basis, t1
+        dz = ops.silu_bwd(d_trip.contiguous(), z)
+        dt1 = ops.linear(dz, P.t_wbt)
+        del z, dz
+        dbasis = ops.small_linear_bwd(dt1, P.t_wa)
+        dunit = ops.angle_basis_bwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"], dbasis)
+        return dunit, None, None, None
+
+
+class EnergyFn(torch.autograd.Function):
+    """readout_norm + EnergyHead + per-structure sum (matris/model/model.py:216-218,
+    matris/model/readout.py:66-75).  Also returns the normalised features for the magmom head."""
+
+    @staticmethod
+    def forward(ctx, node, P, g):
+        node = node.contiguous()
+        nn_ = ops.rmsnorm_fwd(node, P.out_norm)
+        z1 = ops.linear(nn_, P.h_w0, bias=P.h_b0)
+        z2 = ops.linear(z1, P.h_w3, bias=P.h_b3, in_act=1)
+        e_atom = ops.head_dot_fwd(z2, P.h_w6, P.h_b6)
+        energy = ops.segment_sum_scalar(g.n_struct, g.atom_ptr, e_atom)
+        ctx.save_for_backward(node)
+        ctx.P, ctx.g = P, g
+        ctx.mark_non_differentiable(nn_)
+        return energy, nn_
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_energy, _d_nn):
+        (node,) = ctx.saved_tensors
+        P, g = ctx.P, ctx.g
+        nn_ = ops.rmsnorm_fwd(node, P.out_norm)
+        z1 = ops.linear(nn_, P.h_w0, bias=P.h_b0)
+        z2 = ops.linear(z1, P.h_w3, bias=P.h_b3, in_act=1)
+        dz2 = ops.head_dot_bwd(z2, P.h_w6, d_energy.contiguous(), g.atom_struct)
+        dz1 = ops.linear(dz2, P.h_w3t, gate=z1)
+        dnn = ops.linear(dz1, P.h_w0t)
+        return ops.rmsnorm_bwd(node, P.out_norm, dnn), None, None
+
+
+# ------------------------------------------------------------------ the module
+class _Node(nn.Module):
+    """Anonymous container so that parameters sit under the reference's dotted key names."""
+
+
+class MatRIS(nn.Module):
+    """Drop-in for the reference's ``MatRIS`` (matris/model/model.py:30-317)."""
+
+    def __init__(self, num_layers: int = 6, node_feat_dim: int = 128, edge_feat_dim: int = 128,
+                 three_body_feat_dim: int = 128, mlp_hidden_dims=(128, 128), dropout: float = 0.0,
+                 use_bias: bool = False, distance_expansion: str = "Bessel", three_body_expansion: str = "SH",
+                 num_radial: int = 7, num_angular: int = 7, max_l: int = 4, max_n: int = 4,
+                 envelope_exponent: int = 8, graph_conv_mlp: str = "GateMLP", activation_type: str = "silu",
+                 norm_type: str = "rms", pairwise_cutoff: float = 6, three_body_cutoff: float = 4,
+                 use_smoothed_for_delta_edge: bool = False, learnable_basis: bool = True, is_intensive: bool = True,
+                 is_conservation: bool = True, reference_energy: str | None = None, seed: int = 0):
+        super().__init__()
+        self.config = {k: v for k, v in locals().items() if k not in ("self", "__class__", "seed")}
+        cfg = full_config(self.config)
+        check_supported(cfg)
+        if use_smoothed_for_delta_edge:
+            raise NotImplementedError("use_smoothed_for_delta_edge=True is not implemented")
+        self.is_intensive = is_intensive
+        self.graph_converter = GraphConverter(atom_graph_cutoff=pairwise_cutoff, line_graph_cutoff=three_body_cutoff)
+        for key, value in random_state_dict(cfg, seed=seed).items():
+            self._register(key, value, buffer=key in BUFFER_KEYS, trainable=not key.startswith("reference_energy"))
+        self._packed = None
+        self._packed_device = None
+        self.last_batch = None
+
+    # -- parameter tree -------------------------------------------------------------------
+    def _register(self, key, value, buffer, trainable):
+        mod = self
+        parts = key.split(".")
+        for p in parts[:-1]:
+            if not hasattr(mod, p):
+                mod.add_module(p, _Node())
+            mod = getattr(mod, p)
+        if buffer:
+            mod.register_buffer(parts[-1], value.clone())
+        else:
+            mod.register_parameter(parts[-1], nn.Parameter(value.clone(), requires_grad=False))
+
+    def get_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def _apply(self, fn, *a, **k):
+        self._packed = None
+        return super()._apply(fn, *a, **k)
+
+    def load_state_dict(self, state_dict, strict: bool = True, **kw):
+        self._packed = None
+        return super().load_state_dict(state_dict, strict=strict, **kw)
+
+    def packed(self, device):
+        if self._packed is None or self._packed_device != device:
+            self._packed = pack_parameters(self.state_dict(), full_config(self.config), device)
+            self._packed_device = device
+        return self._packed
+
+    @property
+    def device(self):
+        return next(self.parameters()).device
+
+    # -- checkpoint interface ---------------------------------------------------------------
+    @classmethod
+    def from_dict(cls, dct: dict):
+        model = MatRIS(**dct["config"])
+        model.load_state_dict(dct["state_dict"])
+        return model
+
+    @classmethod
+    def load(cls, model_name: str = "matris_10m_oam", device: str | None = None, path: str | None = None):
+        """Load a checkpoint ``{"config", "state_dict"}``.  ``model_name`` resolves to
+        ``~/.cache/matris/MatRIS_10M_{OAM,MP}.pth.tar`` exactly like the reference
+        (matris/model/model.py:262-317); ``path`` (an extension) names the file directly."""
+        if path is None:
+            model_name = model_name.lower()
+            supported = ["matris_10m_oam", "matris_10m_mp"]
+            if os.path.isfile(model_name):
+                path = model_name
+            elif model_name not in supported:
+                raise ValueError(f"Unsupported model_name: {model_name}. Supported models are: {supported}")
+            else:
+                files = {"matris_10m_oam": "MatRIS_10M_OAM.pth.tar", "matris_10m_mp": "MatRIS_10M_MP.pth.tar"}
+                urls = {"matris_10m_oam": "https://figshare.com/ndownloader/files/59142728",
+                        "matris_10m_mp": "https://figshare.com/ndownloader/files/59143058"}
+                cache_dir = os.path.expanduser("~/.cache/matris")
+                os.makedirs(cache_dir, exist_ok=True)
+                path = os.path.join(cache_dir, files[model_name])
+                if not os.path.exists(path):
+                    print(f"Checkpoint not found, downloading to {path} ...")
+                    torch.hub.download_url_to_file(urls[model_name], path)
+        if device is None:
+            device = "cuda"
+        ckpt = torch.load(path, map_location=torch.device("cpu"), weights_only=False)
+        model = MatRIS.from_dict(ckpt).to(device)
+        print(f"Loading {model_name} successfully, running on {device}.")
+        return model
+
+    # -- evaluation -------------------------------------------------------------------------
+    def _as_batch(self, graphs) -> BatchedGraph:
+        if isinstance(graphs, BatchedGraph):
+            return graphs
+        if isinstance(graphs, RadiusGraph):
+            graphs = [graphs]
+        graphs = list(graphs)
+        if not graphs:
+            raise ValueError("no graphs")
+        b0 = getattr(graphs[0], "_batch", None)
+        if (b0 is not None and len(graphs) == b0.n_struct and b0.device == self.device
+                and all(getattr(g, "_batch", None) is b0 and g._index == i for i, g in enumerate(graphs))):
+            return b0
+        arrays = [g.source_arrays() if isinstance(g, RadiusGraph) else as_arrays(g) for g in graphs]
+        return build_batched_graph([a[0] for a in arrays], [a[1] for a in arrays], [a[2] for a in arrays],
+                                   self.config["pairwise_cutoff"], self.config["three_body_cutoff"], self.device)
+
+    def forward(self, graphs: Sequence[RadiusGraph] | BatchedGraph, task: str = "ef", is_training: bool = False):
+        """Same result dictionary as the reference's ``MatRIS.forward`` (model.py:183-250): ``e`` [B] energy per
+        atom including the reference energy, ``f`` tuple of [n_i,3], ``s`` list of [3,3] in GPa, ``m`` list of
+        [n_i], ``atoms_per_graph``, ``ref_energy``.  ``graphs`` may also be a ``BatchedGraph``."""
+        if is_training:
+            raise NotImplementedError("matris_b200 evaluates frozen models only (no parameter gradients)")
+        if self.device.type != "cuda":
+            raise RuntimeError("matris_b200 runs on a CUDA device only: move the model with .to('cuda')")
+        g = self._as_batch(graphs)
+        self.last_batch = g
+        with torch.cuda.device(self.device):
+            return self._evaluate(g, task)
+
+    def _evaluate(self, g: BatchedGraph, task: str):
+        cfg = self.config
+        P = self.packed(self.device)
+        atom_rg, line_rg = row_graphs(g)
+        want_f, want_s = "f" in task, "s" in task
+        need_grad = want_f or want_s
+        out = {}
+        with torch.set_grad_enabled(need_grad):
+            cart = g.cart32.detach().clone().requires_grad_(need_grad)
+            strain = None
+            if want_s:
+                strain = torch.zeros(g.n_struct, 3, 3, dtype=torch.float32, device=cart.device, requires_grad=True)
+            length, unit, _ = EdgeGeometryFn.apply(cart, strain, g)
+            node = ops.linear(ops.embedding(g.numbers, -1, P.emb_table), P.emb_w, out_act=1)
+            edge, rbf2, rbf3 = EdgeEmbedFn.apply(length, P, g, cfg)
+            trip = AngleEmbedFn.apply(unit, P, g, cfg) if line_rg is not None else None
+            for L in P.layers:
+                e_att, t_att = edge, trip
+                if trip is not None:
+                    e_att, t_att = AttentionFn.apply(edge, trip, L.attn_line, line_rg)
+                n_att, e_att = AttentionFn.apply(node, e_att, L.attn_atom, atom_rg)
+                e_upd, t_upd = edge, trip
+                if trip is not None:
+                    e_upd, t_upd = RefineFn.apply(e_att, t_att, rbf3, n_att, L.refine_line, line_rg)
+                node, edge = RefineFn.apply(n_att, e_upd, rbf2, None, L.refine_atom, atom_rg)
+                trip = t_upd
+            energy, node_n = EnergyFn.apply(node, P, g)
+            if need_grad:
+                leaves = [cart] + ([strain] if want_s else [])
+                grads = torch.autograd.grad(energy.sum(), leaves)
+                if want_f:
+                    out["f"] = torch.split(-grads[0], g.atoms_per_graph)
+                if want_s:
+                    scale = (GPA_PER_EV_A3 / g.volume).view(-1, 1, 1)
+                    out["s"] = list(torch.unbind(grads[-1] * scale, dim=0))
+        energy = energy.detach()
+        if "m" in task:
+            zm = ops.linear(node_n, P.m_w0, bias=P.m_b0)
+            out["m"] = list(torch.split(ops.head_dot_fwd(zm, P.m_w3, P.m_b3, take_abs=True), g.atoms_per_graph))
+        apg = torch.tensor(g.atoms_per_graph, dtype=torch.int32, device=energy.device)
+        out["e"] = energy / apg if self.is_intensive else energy
+        out["atoms_per_graph"] = apg
+        ref = 0
+        if cfg["reference_energy"] is not None:
+            ref = self._reference_energy(g)
+        out["e"] = out["e"] + ref
+        out["ref_energy"] = ref
+        return out
+
+    def _reference_energy(self, g: BatchedGraph):
+        """AtomRef.forward (matris/model/reference_energy.py:34-55): composition-weighted table sum, float32."""
+        table = self.state_dict()["reference_energy.fc.weight"].detach().cpu().numpy().reshape(-1).astype(np.float32)
+        comp = np.zeros((g.n_struct, 94), dtype=np.float32)
+        np.add.at(comp, (np.repeat(np.arange(g.n_struct), g.atoms_per_graph), g.numbers_host - 1), 1.0)
+        if self.is_intensive:
+            comp = comp / np.asarray(g.atoms_per_graph, dtype=np.float32)[:, None]
+        return torch.from_numpy(comp @ table).to(self.device)
+
+    # -- convenience ------------------------------------------------------------------------
+    def predict(self, structures, task: str = "efsm"):
+        """Evaluate a list of structures (any accepted structure type) as one batch."""
+        return self.forward(self.graph_converter.batch(structures), task=task)

@@ -1,0 +1,257 @@
+"""Thin Python wrappers over the C-ABI kernels (device pointers in, nothing computed here).
+
+Tensors are float32 / int32, contiguous, on the current CUDA device.  Every
+wrapper launches on torch's current stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import OUT_ADD, OUT_ATOMIC, OUT_STORE, call, ptr  # noqa: F401
+
+D = 128
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def new(rows, cols, like, zero=False):
+    f = torch.zeros if zero else torch.empty
+    return f((int(rows), int(cols)), dtype=torch.float32, device=like.device)
+
+
+# ------------------------------------------------------------------ GEMM descriptors
+def S(t, idx=None, col=0, act=0):
+    """One 128-wide K segment: rows of ``t`` (optionally gathered by ``idx``), columns col..col+127."""
+    return (t, idx, col, act)
+
+
+def B(srcs, W, w_row=0, bias=None, bias_off=0, gate=None, gate_col=0, out_act=0, res=None, res_col=0, res_w=None,
+      out=None, out_idx=None, out_col=0, mode=OUT_STORE, scale=1.0):
+    """One 128-column output block (see mb_colblock)."""
+    return dict(srcs=srcs, W=W, w_row=w_row, bias=bias, bias_off=bias_off, gate=gate, gate_col=gate_col,
+                out_act=out_act, res=res, res_col=res_col, res_w=res_w, out=out, out_idx=out_idx, out_col=out_col,
+                mode=mode, scale=scale)
+
+
+def gemm(n_rows: int, blocks: list[dict]) -> None:
+    if n_rows == 0:
+        return
+    d = _lib.MbGemmDesc()
+    d.n_rows, d.n_blocks = int(n_rows), len(blocks)
+    for j, b in enumerate(blocks):
+        cb = d.blk[j]
+        cb.n_src, cb.out_act = len(b["srcs"]), int(b["out_act"])
+        for s, (t, idx, col, act) in enumerate(b["srcs"]):
+            assert t.dtype == torch.float32 and t.stride(-1) == 1
+            cb.src[s].ptr, cb.src[s].idx = t.data_ptr(), ptr(idx)
+            cb.src[s].ld, cb.src[s].col, cb.src[s].act = t.stride(0), int(col), int(act)
+        W = b["W"]
+        assert W.dim() == 2 and W.stride(1) == 1 and W.shape[1] >= D * len(b["srcs"])
+        cb.W, cb.ldw = W.data_ptr() + 4 * W.stride(0) * int(b["w_row"]), W.stride(0)
+        cb.bias = None if b["bias"] is None else b["bias"].data_ptr() + 4 * int(b["bias_off"])
+        if b["gate"] is not None:
+            cb.gate, cb.ld_gate, cb.col_gate = b["gate"].data_ptr(), b["gate"].stride(0), int(b["gate_col"])
+        if b["res"] is not None:
+            cb.res, cb.ld_res, cb.col_res = b["res"].data_ptr(), b["res"].stride(0), int(b["res_col"])
+            cb.res_w = ptr(b["res_w"])
+        out = b["out"]
+        cb.out, cb.out_idx, cb.ld_out, cb.col_out = out.data_ptr(), ptr(b["out_idx"]), out.stride(0), int(b["out_col"])
+        cb.mode, cb.out_scale = int(b["mode"]), float(b["scale"])
+    call("mb_gemm", C.byref(d), _stream())
+
+
+def linear(x, W, bias=None, out_act=0, in_act=0, gate=None, res=None, res_w=None, scale=1.0, idx=None, out=None):
+    """y[R,128*nb] = epilogue(x[R,128*ns] @ W^T): plain dense layer built on gemm()."""
+    n_rows = x.shape[0] if idx is None else idx.shape[0]
+    n_out, k = W.shape
+    assert n_out % D == 0 and k % D == 0
+    if out is None:
+        out = new(n_rows, n_out, x)
+    srcs = [S(x, idx, D * s, in_act) for s in range(k // D)]
+    gemm(n_rows, [B(srcs, W, w_row=D * j, bias=bias, bias_off=D * j, gate=gate, gate_col=D * j, out_act=out_act,
+                    res=res, res_col=D * j, res_w=res_w, out=out, out_col=D * j, scale=scale)
+                  for j in range(n_out // D)])
+    return out
+
+
+# ------------------------------------------------------------------ row-wise kernels
+def gate_fwd(z, wc, wg, want_h=True, res=None, res_w=None):
+    n = z.shape[0]
+    h = new(n, D, z) if want_h else None
+    out2 = new(n, D, z) if res is not None else None
+    call("mb_gate_fwd", n, ptr(z), ptr(wc), ptr(wg), ptr(h), ptr(res), ptr(res_w), ptr(out2), _stream())
+    return h, out2
+
+
+def gate_bwd(z, wc, wg, dh):
+    dz = torch.empty_like(z)
+    call("mb_gate_bwd", z.shape[0], ptr(z), ptr(wc), ptr(wg), ptr(dh), ptr(dz), _stream())
+    return dz
+
+
+def seg_attn_fwd(n_nodes, tgt_ptr, src_ptr, src_perm, emap, logits, h):
+    agg_t, agg_s, stats = new(n_nodes, D, h), new(n_nodes, D, h), new(n_nodes, 4 * D, h)
+    call("mb_seg_attn_fwd", n_nodes, ptr(tgt_ptr), ptr(src_ptr), ptr(src_perm), ptr(emap), ptr(logits), ptr(h),
+         ptr(agg_t), ptr(agg_s), ptr(stats), _stream())
+    return agg_t, agg_s, stats
+
+
+def seg_attn_bwd(tgt, src, emap, logits, h, agg_t, agg_s, stats, dagg_t, dagg_s, dh_in, dh_map, dh_scale):
+    n = h.shape[0]
+    dh, dlogits = new(n, D, h), new(n, 2 * D, h)
+    call("mb_seg_attn_bwd", n, ptr(tgt), ptr(src), 1, ptr(emap), ptr(logits), ptr(h), ptr(agg_t), ptr(agg_s),
+         ptr(stats), ptr(dagg_t), ptr(dagg_s), ptr(dh_in), ptr(dh_map), float(dh_scale), ptr(dh), ptr(dlogits),
+         _stream())
+    return dh, dlogits
+
+
+def seg_smooth_sum_fwd(n_nodes, tgt_ptr, emap, src, env, h):
+    agg = new(n_nodes, D, h)
+    call("mb_seg_smooth_sum_fwd", n_nodes, ptr(tgt_ptr), ptr(emap), ptr(src), 1, ptr(env), ptr(h), ptr(agg), _stream())
+    return agg
+
+
+def seg_smooth_sum_bwd_rows(tgt, src, emap, env, dagg, dh, accumulate=True):
+    call("mb_seg_smooth_sum_bwd_rows", dh.shape[0], ptr(tgt), ptr(src), 1, ptr(emap), ptr(env), ptr(dagg), ptr(dh),
+         int(accumulate), _stream())
+
+
+def seg_smooth_sum_bwd_env(n_nodes, tgt_ptr, src_ptr, src_perm, tgt, src, u2d, rev, env, h, dagg):
+    denv = new(n_nodes, D, h)
+    call("mb_seg_smooth_sum_bwd_env", n_nodes, ptr(tgt_ptr), ptr(src_ptr), ptr(src_perm), ptr(tgt), ptr(src), 1,
+         ptr(u2d), ptr(rev), ptr(env), ptr(h), ptr(dagg), ptr(denv), _stream())
+    return denv
+
+
+def pair_mean_res(n_bonds, u2d, rev, y, res=None, res_w=None):
+    out = new(n_bonds, D, y)
+    call("mb_pair_mean_res", n_bonds, ptr(u2d), ptr(rev), ptr(y), ptr(res), ptr(res_w), ptr(out), _stream())
+    return out
+
+
+def scale_rows(x, a, y=None, accumulate=False):
+    if y is None:
+        y = torch.empty_like(x)
+    call("mb_scale_rows", x.shape[0], ptr(x), ptr(a), ptr(y), int(accumulate), _stream())
+    return y
+
+
+def small_linear_fwd(x, w):
+    y = new(x.shape[0], D, x)
+    call("mb_small_linear_fwd", x.shape[0], x.shape[1], ptr(x), ptr(w), ptr(y), _stream())
+    return y
+
+
+def small_linear_bwd(dy, w, dx=None, accumulate=False):
+    k = w.shape[1]
+    if dx is None:
+        dx = new(dy.shape[0], k, dy)
+    call("mb_small_linear_bwd", dy.shape[0], k, ptr(dy), ptr(w), ptr(dx), int(accumulate), _stream())
+    return dx
+
+
+def layernorm_fwd(x, w, b):
+    y = torch.empty_like(x)
+    call("mb_layernorm_fwd", x.shape[0], ptr(x), ptr(w), ptr(b), ptr(y), _stream())
+    return y
+
+
+def layernorm_bwd(x, w, dy):
+    dx = torch.empty_like(x)
+    call("mb_layernorm_bwd", x.shape[0], ptr(x), ptr(w), ptr(dy), ptr(dx), _stream())
+    return dx
+
+
+def rmsnorm_fwd(x, w):
+    y = torch.empty_like(x)
+    call("mb_rmsnorm_fwd", x.shape[0], ptr(x), ptr(w), ptr(y), _stream())
+    return y
+
+
+def rmsnorm_bwd(x, w, dy):
+    dx = torch.empty_like(x)
+    call("mb_rmsnorm_bwd", x.shape[0], ptr(x), ptr(w), ptr(dy), ptr(dx), _stream())
+    return dx
+
+
+def embedding(idx, offset, table):
+    y = new(idx.shape[0], D, table)
+    call("mb_embedding", idx.shape[0], ptr(idx), int(offset), ptr(table), ptr(y), _stream())
+    return y
+
+
+def head_dot_fwd(z, w, b, take_abs=False):
+    out = torch.empty(z.shape[0], dtype=torch.float32, device=z.device)
+    call("mb_head_dot_fwd", z.shape[0], z.shape[1], ptr(z), ptr(w), ptr(b), int(take_abs), ptr(out), _stream())
+    return out
+
+
+def head_dot_bwd(z, w, seed=None, seed_map=None):
+    dz = torch.empty_like(z)
+    call("mb_head_dot_bwd", z.shape[0], z.shape[1], ptr(z), ptr(w), ptr(seed), ptr(seed_map), ptr(dz), _stream())
+    return dz
+
+
+def silu_bwd(dy, z):
+    dz = torch.empty_like(z)
+    call("mb_silu_bwd", z.shape[0], ptr(dy), ptr(z), ptr(dz), _stream())
+    return dz
+
+
+def segment_sum_scalar(n_seg, seg_ptr, x):
+    out = torch.empty(n_seg, dtype=torch.float32, device=x.device)
+    call("mb_segment_sum_scalar", n_seg, ptr(seg_ptr), ptr(x), ptr(out), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ geometry and bases
+def edge_geometry_fwd(cart, lattice, atom_struct, center, neighbor, image):
+    ne = center.shape[0]
+    vec, unit = new(ne, 3, cart), new(ne, 3, cart)
+    length = torch.empty(ne, dtype=torch.float32, device=cart.device)
+    call("mb_edge_geometry_fwd", ne, ptr(cart), ptr(lattice), ptr(atom_struct), ptr(center), ptr(neighbor),
+         ptr(image), ptr(vec), ptr(length), ptr(unit), _stream())
+    return vec, length, unit
+
+
+def edge_geometry_bwd(n_atoms, n_struct, edge_ptr, atom_ptr, rev, vec, length, unit, dlen, dunit):
+    ne = rev.shape[0]
+    g = new(ne, 3, vec)
+    dcart, virial_atom, dstrain = new(n_atoms, 3, vec), new(n_atoms, 9, vec), new(n_struct, 9, vec)
+    call("mb_edge_geometry_bwd", n_atoms, n_struct, ne, ptr(edge_ptr), ptr(atom_ptr), ptr(rev), ptr(vec), ptr(length),
+         ptr(unit), ptr(dlen), ptr(dunit), ptr(g), ptr(dcart), ptr(virial_atom), ptr(dstrain), _stream())
+    return dcart, dstrain.view(n_struct, 3, 3), g
+
+
+def bessel_fwd(u2d, length, fa, ca, fb, cb, p):
+    nb = u2d.shape[0]
+    ra, rb = new(nb, 7, length), new(nb, 7, length)
+    call("mb_bessel_fwd", nb, ptr(u2d), ptr(length), ptr(fa), float(ca), ptr(fb), float(cb), int(p), ptr(ra), ptr(rb),
+         _stream())
+    return ra, rb
+
+
+def bessel_bwd(u2d, length, fa, ca, fb, cb, p, dra, drb):
+    dlen = torch.zeros_like(length)
+    call("mb_bessel_bwd", u2d.shape[0], ptr(u2d), ptr(length), ptr(fa), float(ca), ptr(fb), float(cb), int(p),
+         ptr(dra), ptr(drb), ptr(dlen), _stream())
+    return dlen
+
+
+def angle_basis_fwd(line_graph, unit, factor, cutoff):
+    nt = line_graph.shape[0]
+    basis = new(nt, 16, unit)
+    call("mb_angle_basis_fwd", nt, ptr(line_graph), ptr(unit), float(factor), float(cutoff), ptr(basis), _stream())
+    return basis
+
+
+def angle_basis_bwd(line_graph, unit, factor, cutoff, dbasis):
+    dunit = torch.zeros_like(unit)
+    call("mb_angle_basis_bwd", line_graph.shape[0], ptr(line_graph), ptr(unit), float(factor), float(cutoff),
+         ptr(dbasis), ptr(dunit), _stream())
+    return dunit

@@ -1,0 +1,101 @@
+"""CPU: the shared library builds, loads, exports every symbol the header declares,
+and the ctypes signatures agree with the header's parameter lists."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from matris_b200 import _lib, build
+
+HEADER = os.path.join(ROOT, "include", "matris_b200.h")
+
+
+def _declarations():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    decls = {}
+    for m in re.finditer(r"\b(int|size_t|const char\*)\s+(mb_\w+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S):
+        args = m.group(3).strip()
+        n = 0 if args in ("", "void") else len([a for a in args.split(",") if a.strip()])
+        decls[m.group(2)] = (m.group(1), n, args)
+    return decls
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.load()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    decls = _declarations()
+    assert len(decls) >= 30
+    for name in decls:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+
+
+def test_ctypes_signatures_match_header(lib):
+    decls = _declarations()
+    bound = dict(_lib._SIGNATURES)
+    bound.update({k: v[1] for k, v in _lib._OTHER.items()})
+    assert set(bound) == set(decls), set(bound) ^ set(decls)
+    for name, argtypes in bound.items():
+        ret, n, args = decls[name]
+        assert len(argtypes) == n, f"{name}: header has {n} parameters, binding has {len(argtypes)}"
+        # integer / float / pointer kinds agree position by position
+        for a, t in zip([x.strip() for x in args.split(",")] if n else [], argtypes):
+            is_ptr = "*" in a
+            if is_ptr:
+                assert t in (ctypes.c_void_p,) or hasattr(t, "contents") or t is ctypes.c_char_p, (name, a, t)
+            elif a.startswith("float"):
+                assert t is ctypes.c_float, (name, a, t)
+            elif a.startswith("int64_t"):
+                assert t is ctypes.c_int64, (name, a, t)
+            elif a.startswith("int32_t") or a.startswith("int "):
+                assert t in (ctypes.c_int32, ctypes.c_int), (name, a, t)
+
+
+def test_struct_layouts_match_header():
+    """Compile a tiny C program against the header and compare sizeof/offsetof."""
+    import subprocess
+    import tempfile
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "matris_b200.h"
+int main(void) {
+  printf("%zu %zu %zu %zu\n", sizeof(mb_graph), sizeof(mb_src), sizeof(mb_colblock), sizeof(mb_gemm_desc));
+  printf("%zu %zu %zu %zu\n", offsetof(mb_graph, cart), offsetof(mb_graph, edge_ptr), offsetof(mb_graph, trip_src_perm),
+         offsetof(mb_graph, tol));
+  printf("%zu %zu %zu %zu %zu\n", offsetof(mb_colblock, W), offsetof(mb_colblock, gate), offsetof(mb_colblock, res),
+         offsetof(mb_colblock, out), offsetof(mb_colblock, out_scale));
+  return 0;
+}
+'''
+    with tempfile.TemporaryDirectory() as d:
+        open(os.path.join(d, "t.c"), "w").write(src)
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), os.path.join(d, "t.c"), "-o",
+                               os.path.join(d, "t")])
+        out = subprocess.check_output([os.path.join(d, "t")], text=True).split()
+    got = [int(x) for x in out]
+    G, S, B, D = _lib.MbGraph, _lib.MbSrc, _lib.MbColBlock, _lib.MbGemmDesc
+    want = [ctypes.sizeof(G), ctypes.sizeof(S), ctypes.sizeof(B), ctypes.sizeof(D),
+            G.cart.offset, G.edge_ptr.offset, G.trip_src_perm.offset, G.tol.offset,
+            B.W.offset, B.gate.offset, B.res.offset, B.out.offset, B.out_scale.offset]
+    assert got == want
+
+
+def test_version_and_status_strings(lib):
+    assert lib.mb_version() == 1
+    assert lib.mb_status_string(0) == b"ok"
+    assert b"isolated" in lib.mb_status_string(5)
+    assert lib.mb_graph_scan_tmp_len(10_000_000) > 10_000_000 // 2048
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(_lib.MbError):
+        _lib.load()

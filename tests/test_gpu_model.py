@@ -1,0 +1,182 @@
+"""GPU: sub-block and end-to-end E/F/S/M parity.
+
+Sub-blocks are compared with the oracle's functions (forward and data gradients);
+whole evaluations with the committed results of the reference's own float32 run,
+inside the gates  |dE| <= 1e-5 eV/atom, |dF| <= 1e-4 eV/A, |dS| <= 1e-5 eV/A^3,
+|dm| <= 1e-4 mu_B."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, GPA, TOL, load_golden
+from gpu_util import dev, report
+from matris_b200 import workloads
+from matris_b200.weights import full_config, random_checkpoint
+
+pytestmark = pytest.mark.gpu
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).float()
+
+
+@pytest.fixture(scope="module")
+def setup():
+    from matris_b200.graph import build_batched_graph
+    from matris_b200.model import pack_parameters, row_graphs
+    crystals = [workloads.demo_pu4si6(), workloads.random_crystals(2, seed=21)[1]]
+    g = build_batched_graph([c.numbers for c in crystals], [c.cart for c in crystals], [c.lattice for c in crystals])
+    ck = random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=3, jitter=0.1)
+    P = pack_parameters(ck["state_dict"], full_config(ck["config"]), g.cart32.device)
+    return g, ck, P, row_graphs(g)
+
+
+def _oracle_dicts(g):
+    lg = g.line_graph.cpu().long()
+    atom = dict(source_index=g.neighbor.cpu().long(), target_index=g.center.cpu().long())
+    line = dict(atom_list=lg[:, 0], target_index=lg[:, 1], source_index=lg[:, 3])
+    return atom, line, g.d2u.cpu().long()
+
+
+@pytest.mark.parametrize("which", ["atom", "line"])
+def test_attention_layer_forward_backward(setup, which):
+    from matris_b200.model import AttentionFn
+    from oracle.model import _P, attention_layer
+    g, ck, P, (atom_rg, line_rg) = setup
+    atom_d, line_d, d2u = _oracle_dicts(g)
+    sd = {k: v.double() for k, v in ck["state_dict"].items()}
+    if which == "atom":
+        rg, gd, emap, nn_, ne = atom_rg, atom_d, d2u, g.n_atoms, g.n_bonds
+    else:
+        rg, gd, emap, nn_, ne = line_rg, line_d, None, g.n_bonds, g.n_triplets
+    node, edge = rnd(nn_, 128, seed=1), rnd(ne, 128, seed=2)
+    dn, de = rnd(nn_, 128, seed=3), rnd(ne, 128, seed=4)
+    N, E = node.double().requires_grad_(True), edge.double().requires_grad_(True)
+    rn, re_ = attention_layer(_P(sd, f"interaction_block.0.attn_block_{which}_graph."), N, E, gd, emap)
+    gn, ge = torch.autograd.grad((rn * dn.double()).sum() + (re_ * de.double()).sum(), [N, E])
+    n_in, e_in = dev(node).requires_grad_(True), dev(edge).requires_grad_(True)
+    on, oe = AttentionFn.apply(n_in, e_in, getattr(P.layers[0], "attn_" + which), rg)
+    report(f"attention[{which}] node", on, rn, 3e-5)
+    report(f"attention[{which}] edge", oe, re_, 3e-5)
+    dn_, de_ = torch.autograd.grad([on, oe], [n_in, e_in], [dev(dn), dev(de)])
+    report(f"attention[{which}] d node", dn_, gn, 2e-4)
+    report(f"attention[{which}] d edge", de_, ge, 2e-4)
+
+
+@pytest.mark.parametrize("which", ["atom", "line"])
+def test_refinement_layer_forward_backward(setup, which):
+    from matris_b200.model import RefineFn
+    from oracle.model import _P, refinement_layer
+    g, ck, P, (atom_rg, line_rg) = setup
+    atom_d, line_d, d2u = _oracle_dicts(g)
+    sd = {k: v.double() for k, v in ck["state_dict"].items()}
+    rbf = rnd(g.n_bonds, 7, seed=5, scale=0.3)
+    if which == "atom":
+        rg, gd, emap, nn_, ne, af = atom_rg, atom_d, d2u, g.n_atoms, g.n_bonds, None
+    else:
+        rg, gd, emap, nn_, ne, af = line_rg, line_d, None, g.n_bonds, g.n_triplets, rnd(g.n_atoms, 128, seed=6)
+    node, edge = rnd(nn_, 128, seed=1), rnd(ne, 128, seed=2)
+    dn, de = rnd(nn_, 128, seed=3), rnd(ne, 128, seed=4)
+    N, E, Rb = node.double().requires_grad_(True), edge.double().requires_grad_(True), rbf.double().requires_grad_(True)
+    A = None if af is None else af.double().requires_grad_(True)
+    rn, re_ = refinement_layer(_P(sd, f"interaction_block.0.refine_block_{which}_graph."), N, E, Rb, gd, emap, A)
+    leaves = [N, E, Rb] + ([A] if A is not None else [])
+    grads = torch.autograd.grad((rn * dn.double()).sum() + (re_ * de.double()).sum(), leaves)
+    n_in, e_in, r_in = dev(node).requires_grad_(True), dev(edge).requires_grad_(True), dev(rbf).requires_grad_(True)
+    a_in = None if af is None else dev(af).requires_grad_(True)
+    on, oe = RefineFn.apply(n_in, e_in, r_in, a_in, getattr(P.layers[0], "refine_" + which), rg)
+    report(f"refine[{which}] node", on, rn, 3e-5)
+    report(f"refine[{which}] edge", oe, re_, 3e-5)
+    mine = torch.autograd.grad([on, oe], [n_in, e_in, r_in] + ([a_in] if a_in is not None else []), [dev(dn), dev(de)])
+    for name, a, b in zip(["node", "edge", "rbf", "atom"], mine, grads):
+        report(f"refine[{which}] d {name}", a, b, 2e-4)
+
+
+def _evaluate(ck, crystals, task):
+    from matris_b200 import MatRIS
+    model = MatRIS.from_dict(ck).to("cuda")
+    out = model.predict(crystals, task)
+    res = {"e": out["e"].cpu().double().numpy(), "ref_energy": out["ref_energy"].cpu().double().numpy()}
+    if "f" in out:
+        res["f"] = torch.cat(list(out["f"])).cpu().double().numpy()
+    if "s" in out:
+        res["s"] = torch.stack(out["s"]).cpu().double().numpy()
+    if "m" in out:
+        res["m"] = torch.cat(out["m"]).cpu().double().numpy()
+    return res, out, model
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_end_to_end_matches_reference(case):
+    meta, crystals, z = load_golden(case)
+    ck = random_checkpoint(dict(num_layers=meta["num_layers"], reference_energy=meta["reference_energy"]),
+                           seed=meta["seed"], jitter=meta["jitter"])
+    res, out, _ = _evaluate(ck, crystals, meta["task"])
+    report(f"e2e[{case}] E (eV/atom)", res["e"], z["ref32_e"], TOL["e"])
+    report(f"e2e[{case}] F (eV/A)", res["f"], z["ref32_f"], TOL["f"])
+    report(f"e2e[{case}] S (eV/A^3)", res["s"] / GPA, z["ref32_s"] / GPA, TOL["s"])
+    if "m" in meta["task"]:
+        report(f"e2e[{case}] M (mu_B)", res["m"], z["ref32_m"], TOL["m"])
+    report(f"e2e[{case}] reference energy", res["ref_energy"], z["ref32_ref_energy"], 1e-6)
+    # tighter, relative check against the reference's float64 run (random-init forces are small)
+    fmax = np.abs(z["ref64_f"]).max()
+    if fmax > 1e-4:
+        report(f"e2e[{case}] F relative to fp64", res["f"], z["ref64_f"], 2e-3, rel=True)
+    # result dictionary layout of MatRIS.forward
+    assert out["atoms_per_graph"].dtype == torch.int32 and len(out["f"]) == len(crystals)
+    assert out["s"][0].shape == (3, 3) and out["f"][0].shape == (len(crystals[0].numbers), 3)
+
+
+def test_tasks_and_keys():
+    meta, crystals, z = load_golden("pu4si6_L2")
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0, jitter=0.1)
+    for task, keys in (("e", {"e"}), ("em", {"e", "m"}), ("ef", {"e", "f"}), ("efs", {"e", "f", "s"})):
+        res, out, _ = _evaluate(ck, crystals, task)
+        assert set(out) == keys | {"atoms_per_graph", "ref_energy"}
+        report(f"task={task} E", res["e"], z["ref32_e"], TOL["e"])
+
+
+def test_batch_equals_single_structures():
+    crystals = workloads.random_crystals(4, seed=5)
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=1)
+    batch, _, model = _evaluate(ck, crystals, "efs")
+    ofs = 0
+    for b, cr in enumerate(crystals):
+        single, _, _ = _evaluate(ck, [cr], "efs")
+        n = len(cr.numbers)
+        report(f"batch-vs-single E[{b}]", batch["e"][b:b + 1], single["e"], 2e-6)
+        report(f"batch-vs-single F[{b}]", batch["f"][ofs:ofs + n], single["f"], 2e-6)
+        report(f"batch-vs-single S[{b}]", batch["s"][b] / GPA, single["s"][0] / GPA, 2e-7)
+        ofs += n
+
+
+def test_forces_are_energy_derivatives():
+    """Finite differences of the CUDA energy against the CUDA forces (no oracle involved)."""
+    from matris_b200 import MatRIS
+    from matris_b200.workloads import Crystal
+    cr = workloads.demo_pu4si6()
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=2)
+    model = MatRIS.from_dict(ck).to("cuda")
+    out = model.predict([cr], "ef")
+    f = out["f"][0].cpu().double().numpy()
+    n = len(cr.numbers)
+    h = 2e-2
+    for (i, k) in ((0, 0), (5, 2)):
+        e = []
+        for sgn in (+1, -1):
+            cart = cr.cart.copy()
+            cart[i, k] += sgn * h
+            e.append(float(model.predict([Crystal(cr.numbers, cart, cr.lattice)], "e")["e"][0]) * n)
+        fd = -(e[0] - e[1]) / (2 * h)
+        assert abs(fd - f[i, k]) < 5e-3 * max(1.0, abs(f[i, k])) + 2e-3, (fd, f[i, k])
+
+
+def test_state_dict_roundtrip_and_from_dict():
+    from matris_b200 import MatRIS
+    ck = random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=4)
+    model = MatRIS.from_dict(ck)
+    assert list(model.state_dict().keys()) == list(ck["state_dict"].keys())
+    assert model.config["num_layers"] == 1 and model.is_intensive
+    with pytest.raises(RuntimeError):
+        model([workloads.demo_pu4si6()])  # still on CPU: no fallback

@@ -1,0 +1,309 @@
+"""GPU: every kernel behind the C ABI against plain PyTorch (CPU, float64 where the
+formula allows) evaluations of the reference's expressions (oracle.model)."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from gpu_util import dev, report
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from matris_b200 import ops as o
+    return o
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).float()
+
+
+# ---------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("n_rows", [1, 77, 128, 1000])
+def test_gemm_plain_and_bias_act(ops, n_rows):
+    x, W, b = rnd(n_rows, 256, seed=1), rnd(256, 256, seed=2, scale=0.1), rnd(256, seed=3)
+    y = ops.linear(dev(x), dev(W), bias=dev(b), out_act=1)
+    report(f"gemm bias+silu R={n_rows}", y, F.silu(F.linear(x.double(), W.double(), b.double())), 2e-5)
+    y = ops.linear(dev(x), dev(W), in_act=1)
+    report(f"gemm silu-on-load R={n_rows}", y, F.linear(F.silu(x.double()), W.double()), 2e-5)
+
+
+def test_gemm_gathered_concat_four_segments(ops):
+    R, n1, n2 = 700, 90, 40
+    e, node, atom = rnd(R, 128, seed=4), rnd(n1, 128, seed=5), rnd(n2, 128, seed=6)
+    g = torch.Generator().manual_seed(0)
+    tgt, src, ctr = (torch.randint(0, n1, (R,), generator=g), torch.randint(0, n1, (R,), generator=g),
+                     torch.randint(0, n2, (R,), generator=g))
+    W, b = rnd(256, 512, seed=7, scale=0.05), rnd(256, seed=8)
+    out = torch.empty(R, 256, device="cuda")
+    de, dn, da = dev(e), dev(node), dev(atom)
+    srcs = [ops.S(de), ops.S(da, dev(ctr, torch.int32)), ops.S(dn, dev(tgt, torch.int32)), ops.S(dn, dev(src, torch.int32))]
+    dW, db = dev(W), dev(b)
+    ops.gemm(R, [ops.B(srcs, dW, w_row=128 * j, bias=db, bias_off=128 * j, out=out, out_col=128 * j) for j in (0, 1)])
+    x = torch.cat([e, atom[ctr], node[tgt], node[src]], 1).double()
+    report("gemm gather-cat K=512", out, F.linear(x, W.double(), b.double()), 3e-5)
+
+
+def test_gemm_gate_residual_scale(ops):
+    R = 300
+    x, W, z, res, rw = rnd(R, 128, seed=1), rnd(128, 128, seed=2, scale=0.1), rnd(R, 128, seed=3), rnd(R, 128, seed=4), rnd(128, seed=5)
+    y = ops.linear(dev(x), dev(W), gate=dev(z), scale=0.5)
+    zz = z.double().requires_grad_(True)
+    (sg,) = torch.autograd.grad(F.silu(zz).sum(), zz)
+    report("gemm * silu'(gate) * 0.5", y, F.linear(x.double(), W.double()) * sg * 0.5, 2e-5)
+    y = ops.linear(dev(x), dev(W), res=dev(res), res_w=dev(rw))
+    report("gemm + w*res", y, F.linear(x.double(), W.double()) + rw.double() * res.double(), 2e-5)
+
+
+def test_gemm_scatter_modes(ops):
+    R, n = 900, 37
+    x, W = rnd(R, 256, seed=1), rnd(128, 256, seed=2, scale=0.1)
+    idx = torch.randint(0, n, (R,), generator=torch.Generator().manual_seed(1))
+    base = rnd(n, 128, seed=3)
+    out = dev(base.clone())
+    dx = dev(x)
+    ops.gemm(R, [ops.B([ops.S(dx, None, 0), ops.S(dx, None, 128)], dev(W), out=out, out_idx=dev(idx, torch.int32),
+                       mode=ops.OUT_ATOMIC)])
+    want = base.double().index_add_(0, idx, F.linear(x.double(), W.double()))
+    report("gemm atomic scatter-add", out, want, 1e-4)
+    base2 = rnd(R, 128, seed=4)
+    out2 = dev(base2.clone())
+    ops.gemm(R, [ops.B([ops.S(dx, None, 0), ops.S(dx, None, 128)], dev(W), out=out2, mode=ops.OUT_ADD)])
+    report("gemm accumulate", out2, base2.double() + F.linear(x.double(), W.double()), 3e-5)
+
+
+# ---------------------------------------------------------------- row-wise
+def _gate_ref(z, wc, wg):
+    c = F.rms_norm(z[:, :128], (128,), wc, torch.finfo(torch.float32).eps)
+    g = F.rms_norm(z[:, 128:], (128,), wg, torch.finfo(torch.float32).eps)
+    return F.silu(c) * torch.sigmoid(g)
+
+
+def test_gate_fwd_bwd(ops):
+    R = 333
+    z, wc, wg, dh, res, rw = rnd(R, 256, seed=1), 1 + 0.1 * rnd(128, seed=2), 1 + 0.1 * rnd(128, seed=3), rnd(R, 128, seed=4), rnd(R, 128, seed=5), rnd(128, seed=6)
+    h, out2 = ops.gate_fwd(dev(z), dev(wc), dev(wg), res=dev(res), res_w=dev(rw))
+    zz = z.double().requires_grad_(True)
+    ref = _gate_ref(zz, wc.double(), wg.double())
+    report("gate_fwd h", h, ref, 2e-6)
+    report("gate_fwd h + w*res", out2, ref + rw.double() * res.double(), 2e-6)
+    (dz_ref,) = torch.autograd.grad(ref, zz, dh.double())
+    report("gate_bwd dz", ops.gate_bwd(dev(z), dev(wc), dev(wg), dev(dh)), dz_ref, 5e-6)
+
+
+def _csr(seg, n):
+    order = torch.argsort(seg, stable=True)
+    ptr = torch.zeros(n + 1, dtype=torch.int64)
+    ptr[1:] = torch.cumsum(torch.bincount(seg, minlength=n), 0)
+    return order, ptr
+
+
+@pytest.mark.parametrize("with_emap", [False, True])
+def test_seg_attn_fwd_bwd(ops, with_emap):
+    from oracle.model import segment_softmax, segment_sum
+    R, Nn = 500, 40
+    g = torch.Generator().manual_seed(3)
+    tgt = torch.sort(torch.randint(0, Nn - 2, (R,), generator=g))[0]  # grouped by target; last nodes empty
+    src = torch.randint(0, Nn - 1, (R,), generator=g)
+    perm, sptr = _csr(src, Nn)
+    _, tptr = _csr(tgt, Nn)
+    Ne = 120 if with_emap else R
+    emap = torch.randint(0, Ne, (R,), generator=g) if with_emap else None
+    logits, h = rnd(Ne, 256, seed=1), rnd(R, 128, seed=2)
+    i32 = torch.int32
+    d = dict(tgt=dev(tgt, i32), src=dev(src, i32), tptr=dev(tptr, i32), sptr=dev(sptr, i32), perm=dev(perm, i32),
+             emap=None if emap is None else dev(emap, i32), lg=dev(logits), h=dev(h))
+    agg_t, agg_s, stats = ops.seg_attn_fwd(Nn, d["tptr"], d["sptr"], d["perm"], d["emap"], d["lg"], d["h"])
+    L = logits.double().requires_grad_(True)
+    H = h.double().requires_grad_(True)
+    lg_rows = L[emap] if with_emap else L
+    a_s, a_t = segment_softmax(lg_rows[:, :128], src), segment_softmax(lg_rows[:, 128:], tgt)
+    ref_s, ref_t = segment_sum(a_s * H, src, Nn), segment_sum(a_t * H, tgt, Nn)
+    report("seg_attn_fwd agg_t", agg_t, ref_t, 5e-6)
+    report("seg_attn_fwd agg_s", agg_s, ref_s, 5e-6)
+    dt, ds, dh_in = rnd(Nn, 128, seed=5), rnd(Nn, 128, seed=6), rnd(Ne if with_emap else R, 128, seed=7)
+    scale = 0.5 if with_emap else 1.0
+    extra = (dh_in.double()[emap] if with_emap else dh_in.double()) * scale
+    loss = (ref_t * dt.double()).sum() + (ref_s * ds.double()).sum() + (H * extra).sum()
+    dL, dH = torch.autograd.grad(loss, [L, H])
+    dh, dlg = ops.seg_attn_bwd(d["tgt"], d["src"], d["emap"], d["lg"], d["h"], agg_t, agg_s, stats, dev(dt), dev(ds),
+                               dev(dh_in), d["emap"], scale)
+    report("seg_attn_bwd dh", dh, dH, 1e-5)
+    if with_emap:  # per-row logits gradients are summed over rows sharing a logits row
+        dlg_sum = torch.zeros(Ne, 256, dtype=torch.float64).index_add_(0, emap, dlg.cpu().double())
+        report("seg_attn_bwd dlogits (summed)", dlg_sum, dL, 2e-5)
+    else:
+        report("seg_attn_bwd dlogits", dlg, dL, 1e-5)
+
+
+@pytest.mark.parametrize("line", [False, True])
+def test_seg_smooth_sum_fwd_bwd(ops, line):
+    R, Nn = 400, 30
+    g = torch.Generator().manual_seed(9)
+    i32 = torch.int32
+    h, dagg, dh0 = rnd(R, 128, seed=2), rnd(Nn, 128, seed=3), rnd(R, 128, seed=4)
+    if line:
+        tgt = torch.sort(torch.randint(0, Nn, (R,), generator=g))[0]
+        src = torch.randint(0, Nn, (R,), generator=g)
+        env = rnd(Nn, 128, seed=1)
+        u2d = rev = emap = None
+    else:  # atom graph: rows = directed edges in pairs, emap = bond of each edge
+        nb = R // 2
+        tgt = torch.sort(torch.randint(0, Nn, (R,), generator=g))[0]
+        src = torch.randint(0, Nn, (R,), generator=g)
+        pairing = torch.randperm(R, generator=g).view(nb, 2)
+        emap = torch.empty(R, dtype=torch.int64)
+        emap[pairing[:, 0]] = torch.arange(nb)
+        emap[pairing[:, 1]] = torch.arange(nb)
+        u2d, rev = pairing[:, 0].clone(), torch.empty(R, dtype=torch.int64)
+        rev[pairing[:, 0]], rev[pairing[:, 1]] = pairing[:, 1], pairing[:, 0]
+        env = rnd(nb, 128, seed=1)
+    perm, sptr = _csr(src, Nn)
+    _, tptr = _csr(tgt, Nn)
+    E, H = env.double().requires_grad_(True), h.double().requires_grad_(True)
+    s = E[src] * E[tgt] if line else E[emap]
+    ref = torch.zeros(Nn, 128, dtype=torch.float64).index_add_(0, tgt, H * s)
+    d_tgt, d_src = dev(tgt, i32), dev(src, i32)
+    d_emap = None if line else dev(emap, i32)
+    agg = ops.seg_smooth_sum_fwd(Nn, dev(tptr, i32), d_emap, d_src if line else None, dev(env), dev(h))
+    report(f"seg_smooth_sum_fwd line={line}", agg, ref, 1e-5)
+    dE, dH = torch.autograd.grad((ref * dagg.double()).sum(), [E, H])
+    dh = dev(dh0.clone())
+    ops.seg_smooth_sum_bwd_rows(d_tgt, d_src if line else None, d_emap, dev(env), dev(dagg), dh, accumulate=True)
+    report(f"seg_smooth_sum_bwd_rows line={line}", dh, dh0.double() + dH, 1e-5)
+    denv = ops.seg_smooth_sum_bwd_env(env.shape[0], dev(tptr, i32), dev(sptr, i32) if line else None, dev(perm, i32),
+                                      d_tgt, d_src, None if line else dev(u2d, i32), None if line else dev(rev, i32),
+                                      dev(env), dev(h), dev(dagg))
+    report(f"seg_smooth_sum_bwd_env line={line}", denv, dE, 2e-5)
+
+
+def test_pair_mean_scale_small_linear_norms(ops):
+    nb = 150
+    g = torch.Generator().manual_seed(2)
+    pairing = torch.randperm(2 * nb, generator=g).view(nb, 2)
+    rev = torch.empty(2 * nb, dtype=torch.int64)
+    rev[pairing[:, 0]], rev[pairing[:, 1]] = pairing[:, 1], pairing[:, 0]
+    y, res, w = rnd(2 * nb, 128, seed=1), rnd(nb, 128, seed=2), rnd(128, seed=3)
+    out = ops.pair_mean_res(nb, dev(pairing[:, 0], torch.int32), dev(rev, torch.int32), dev(y), dev(res), dev(w))
+    report("pair_mean_res", out, 0.5 * (y[pairing[:, 0]] + y[pairing[:, 1]]).double() + w.double() * res.double(), 3e-6)
+    x = rnd(500, 128, seed=4)
+    report("scale_rows", ops.scale_rows(dev(x), dev(w)), x * w, 1e-7)
+    base = rnd(500, 128, seed=12)
+    acc = dev(base.clone())
+    ops.scale_rows(dev(x), dev(w), acc, accumulate=True)
+    report("scale_rows accumulate", acc, base + x * w, 2e-6)
+    for k in (7, 16):
+        xs, W, dy = rnd(500, k, seed=5), rnd(128, k, seed=6), rnd(500, 128, seed=7)
+        report(f"small_linear_fwd k={k}", ops.small_linear_fwd(dev(xs), dev(W)), F.linear(xs.double(), W.double()), 5e-6)
+        report(f"small_linear_bwd k={k}", ops.small_linear_bwd(dev(dy), dev(W)), dy.double() @ W.double(), 3e-5)
+        dx = dev(xs.clone())
+        ops.small_linear_bwd(dev(dy), dev(W), dx, accumulate=True)
+        report(f"small_linear_bwd acc k={k}", dx, xs.double() + dy.double() @ W.double(), 3e-5)
+    x, lw, lb, dy = rnd(300, 128, seed=8) * 3 + 1, 1 + 0.1 * rnd(128, seed=9), 0.1 * rnd(128, seed=10), rnd(300, 128, seed=11)
+    X = x.double().requires_grad_(True)
+    ref = F.layer_norm(X, (128,), lw.double(), lb.double(), 1e-5)
+    report("layernorm_fwd", ops.layernorm_fwd(dev(x), dev(lw), dev(lb)), ref, 3e-6)
+    report("layernorm_bwd", ops.layernorm_bwd(dev(x), dev(lw), dev(dy)), torch.autograd.grad(ref, X, dy.double())[0], 5e-6)
+    X = x.double().requires_grad_(True)
+    ref = F.rms_norm(X, (128,), lw.double(), torch.finfo(torch.float32).eps)
+    report("rmsnorm_fwd", ops.rmsnorm_fwd(dev(x), dev(lw)), ref, 3e-6)
+    report("rmsnorm_bwd", ops.rmsnorm_bwd(dev(x), dev(lw), dev(dy)), torch.autograd.grad(ref, X, dy.double())[0], 5e-6)
+
+
+def test_silu_bwd_matches_reference_formula(ops):
+    """grad * sigmoid(x) * (1 + x * (1 - sigmoid(x)))  (the reference's fused SiLU backward)."""
+    z, dy = rnd(257, 128, seed=1) * 4, rnd(257, 128, seed=2)
+    s = torch.sigmoid(z.double())
+    report("silu_bwd", ops.silu_bwd(dev(dy), dev(z)), dy.double() * s * (1 + z.double() * (1 - s)), 1e-6)
+
+
+def test_heads_embedding_segment_sum(ops):
+    n = 200
+    z, w, b = rnd(n, 256, seed=1), rnd(256, seed=2), rnd(1, seed=3)
+    report("head_dot_fwd |.| k=256", ops.head_dot_fwd(dev(z), dev(w), dev(b), True),
+           (F.silu(z.double()) @ w.double() + b.double()).abs(), 2e-5)
+    z1 = z[:, :128].contiguous()
+    Z = z1.double().requires_grad_(True)
+    seg = torch.sort(torch.randint(0, 5, (n,), generator=torch.Generator().manual_seed(0)))[0]
+    seed = rnd(5, seed=4)
+    e = F.silu(Z) @ w[:128].double() + b.double()
+    (dz,) = torch.autograd.grad((e * seed.double()[seg]).sum(), Z)
+    report("head_dot_bwd seeded", ops.head_dot_bwd(dev(z1), dev(w[:128].contiguous()), dev(seed), dev(seg, torch.int32)), dz, 1e-5)
+    _, ptr = _csr(seg, 5)
+    x = rnd(n, seed=5)
+    report("segment_sum_scalar", ops.segment_sum_scalar(5, dev(ptr, torch.int32), dev(x)),
+           torch.zeros(5, dtype=torch.float64).index_add_(0, seg, x.double()), 1e-5)
+    table, idx = rnd(94, 128, seed=6), torch.randint(1, 95, (n,), generator=torch.Generator().manual_seed(1))
+    report("embedding", ops.embedding(dev(idx, torch.int32), -1, dev(table)), table[idx - 1], 0.0)
+
+
+# ---------------------------------------------------------------- geometry and bases
+def test_bessel_fwd_bwd(ops):
+    from oracle.model import bessel
+    nb = 400
+    g = torch.Generator().manual_seed(4)
+    length = torch.rand(2 * nb, generator=g) * 5.2 + 0.8          # 0.8 .. 6.0 (beyond the 4 A cutoff too)
+    u2d = torch.randperm(2 * nb, generator=g)[:nb]
+    fa = torch.pi * torch.arange(1, 8).float() * (1 + 0.02 * rnd(7, seed=1))
+    fb = torch.pi * torch.arange(1, 8).float() * (1 + 0.02 * rnd(7, seed=2))
+    ra, rb = ops.bessel_fwd(dev(u2d, torch.int32), dev(length), dev(fa), 6.0, dev(fb), 4.0, 8)
+    Ld = length.double().requires_grad_(True)
+    ref_a, ref_b = bessel(Ld[u2d], fa.double(), 6.0, 8), bessel(Ld[u2d], fb.double(), 4.0, 8)
+    report("bessel_fwd rc=6", ra, ref_a, 3e-6)
+    report("bessel_fwd rc=4", rb, ref_b, 3e-6)
+    da, db = rnd(nb, 7, seed=3), rnd(nb, 7, seed=4)
+    (dl,) = torch.autograd.grad((ref_a * da.double()).sum() + (ref_b * db.double()).sum(), Ld)
+    report("bessel_bwd dlen", ops.bessel_bwd(dev(u2d, torch.int32), dev(length), dev(fa), 6.0, dev(fb), 4.0, 8, dev(da), dev(db)),
+           dl, 3e-5)
+
+
+def test_angle_basis_fwd_bwd(ops):
+    from oracle.model import spherical_basis
+    ne, nt = 60, 900
+    g = torch.Generator().manual_seed(5)
+    v = torch.randn(ne, 3, generator=g)
+    unit = (v / v.norm(dim=1, keepdim=True)).float()
+    lg = torch.zeros(nt, 5, dtype=torch.int64)
+    lg[:, 2], lg[:, 4] = torch.randint(0, ne, (nt,), generator=g), torch.randint(0, ne, (nt,), generator=g)
+    lg[:5, 4] = lg[:5, 2]                                         # collinear (theta = 0) rows
+    factor = float(np.sqrt(np.float32(2.0 / 216.0)))
+    basis = ops.angle_basis_fwd(dev(lg, torch.int32), dev(unit), factor, 6.0)
+    U = unit.double().requires_grad_(True)
+    ua, ub = U[lg[:, 2]], U[lg[:, 4]]
+    theta = torch.acos((ua * ub).sum(1) * (1 - 1e-6))
+    ref = spherical_basis(torch.norm(ub.detach(), dim=1), theta, torch.tensor(factor, dtype=torch.float64), 6.0)
+    report("angle_basis_fwd", basis, ref, 2e-6)
+    db = rnd(nt, 16, seed=1)
+    (dU,) = torch.autograd.grad((ref * db.double()).sum(), U)
+    # float32 evaluation of d cos(acos x)/dx loses digits near |x| -> 1 exactly as the reference's autograd does
+    report("angle_basis_bwd dunit", ops.angle_basis_bwd(dev(lg, torch.int32), dev(unit), factor, 6.0, dev(db)), dU, 2e-3, rel=True)
+
+
+def test_edge_geometry_fwd_bwd(ops):
+    from matris_b200.graph import build_batched_graph
+    from matris_b200 import workloads
+    crystals = workloads.random_crystals(3, seed=2)
+    g = build_batched_graph([c.numbers for c in crystals], [c.cart for c in crystals], [c.lattice for c in crystals])
+    vec, length, unit = ops.edge_geometry_fwd(g.cart32, g.lattice32, g.atom_struct, g.center, g.neighbor, g.image)
+    cart = g.cart32.cpu().double().requires_grad_(True)
+    lat = g.lattice32.cpu().double()
+    strain = torch.zeros(g.n_struct, 3, 3, dtype=torch.float64, requires_grad=True)
+    sym = 0.5 * (strain + strain.transpose(1, 2))
+    seg = g.atom_struct.cpu().long()
+    pos = cart + torch.einsum("be,bec->bc", cart, sym[seg])
+    latt = lat + lat @ sym
+    c, n, im = g.center.cpu().long(), g.neighbor.cpu().long(), g.image.cpu().double()
+    v = pos[c] - (pos[n] + torch.einsum("ek,ekc->ec", im, latt[seg[c]]))
+    d = v.norm(dim=1)
+    report("edge_geometry_fwd vec", vec, v, 5e-6)
+    report("edge_geometry_fwd len", length, d, 5e-6)
+    report("edge_geometry_fwd unit", unit, v / d[:, None], 1e-6)
+    dl, du = rnd(g.n_edges, seed=1), rnd(g.n_edges, 3, seed=2)
+    gc, gs = torch.autograd.grad((d * dl.double()).sum() + ((v / d[:, None]) * du.double()).sum(), [cart, strain])
+    dcart, dstrain, _ = ops.edge_geometry_bwd(g.n_atoms, g.n_struct, g.edge_ptr, g.atom_ptr, g.rev, vec, length, unit,
+                                              dev(dl), dev(du))
+    report("edge_geometry_bwd dcart", dcart, gc, 2e-4)
+    report("edge_geometry_bwd dstrain", dstrain, gs, 2e-3)
