@@ -136,12 +136,25 @@ def check(status: int, what: str) -> None:
     raise MbError(f"{what} failed with status {status} ({msg})")
 
 
+profile = None       # set to a list to record (name, start_event, end_event, meta) around every call
+profile_meta = None  # filled by the caller (e.g. algorithmic FLOPs of a GEMM) just before call()
+
+
 def call(name: str, *args) -> None:
     """Call an int-returning entry point and raise on a non-zero status."""
-    global launch_count
+    global launch_count, profile_meta
     lib = load()
     launch_count += 1
+    if profile is None:
+        check(getattr(lib, name)(*args), name)
+        return
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     check(getattr(lib, name)(*args), name)
+    e1.record()
+    profile.append((name, e0, e1, profile_meta))
+    profile_meta = None
 
 
 def ptr(t):

@@ -115,55 +115,77 @@ def _i32(n, device):
     return torch.empty(max(int(n), 1), dtype=torch.int32, device=device)
 
 
-def build_batched_graph(numbers: Sequence[np.ndarray], carts: Sequence[np.ndarray], lattices: Sequence[np.ndarray],
-                        cutoff: float = 6.0, line_cutoff: float = 4.0, device="cuda", tol: float = 1e-8,
-                        stream=None) -> BatchedGraph:
-    """Build atom graph, bond graph and line graph for a batch of structures on ``device``."""
-    device = torch.device(device)
-    if device.type != "cuda":
-        raise _lib.MbError("matris_b200 builds graphs on a CUDA device only (no CPU path)")
-    lib = _lib.load()
-    n_per = np.asarray([len(z) for z in numbers], dtype=np.int64)
-    if (n_per <= 0).any():
-        raise ValueError("empty structure")
-    n_struct, n_atoms = len(n_per), int(n_per.sum())
-    atom_ptr = np.concatenate([[0], np.cumsum(n_per)]).astype(np.int32)
-    cart = np.concatenate(carts).astype(np.float64, copy=False)
-    lattice = np.stack(lattices).astype(np.float64, copy=False)
-    inv = np.linalg.inv(lattice)
-    atom_struct = np.repeat(np.arange(n_struct, dtype=np.int32), n_per)
-    grid, n_cells = cell_grid(lattice, n_per, float(cutoff))
-    # float32 model inputs exactly as the reference derives them (converter.py:82-83, processgraph.py:87)
-    frac32 = np.einsum("ni,nij->nj", cart, inv[atom_struct]).astype(np.float32)
-    lat32 = lattice.astype(np.float32)
-    cart32 = np.einsum("ni,nij->nj", frac32, lat32[atom_struct]).astype(np.float32)
-    vol32 = np.einsum("bi,bi->b", lat32[:, 0], np.cross(lat32[:, 1], lat32[:, 2])).astype(np.float32)
+class HostBatch:
+    """Host-side (NumPy, pinned where it is copied from) description of a batch of structures."""
 
+    def __init__(self, numbers, carts, lattices, cutoff, pin=True):
+        n_per = np.asarray([len(z) for z in numbers], dtype=np.int64)
+        if len(n_per) == 0 or (n_per <= 0).any():
+            raise ValueError("empty structure")
+        self.n_struct, self.n_atoms = len(n_per), int(n_per.sum())
+        self.atoms_per_graph = [int(x) for x in n_per]
+        self.atom_ptr = np.concatenate([[0], np.cumsum(n_per)]).astype(np.int32)
+        self.numbers = np.concatenate(numbers).astype(np.int64)
+        self.cart = np.ascontiguousarray(np.concatenate(carts), dtype=np.float64)
+        self.lattice = np.ascontiguousarray(np.stack(lattices), dtype=np.float64)
+        inv = np.linalg.inv(self.lattice)
+        self.atom_struct = np.repeat(np.arange(self.n_struct, dtype=np.int32), n_per)
+        grid, self.n_cells = cell_grid(self.lattice, n_per, float(cutoff))
+        # float32 model inputs exactly as the reference derives them (converter.py:82-83, processgraph.py:87)
+        self.frac32 = np.einsum("ni,nij->nj", self.cart, inv[self.atom_struct]).astype(np.float32)
+        lat32 = self.lattice.astype(np.float32)
+        cart32 = np.einsum("ni,nij->nj", self.frac32, lat32[self.atom_struct]).astype(np.float32)
+        vol32 = np.einsum("bi,bi->b", lat32[:, 0], np.cross(lat32[:, 1], lat32[:, 2])).astype(np.float32)
+        # two staging buffers (one float64, one 32-bit) so that a batch is two host->device copies
+        f64 = np.concatenate([self.cart.ravel(), self.lattice.ravel(), inv.ravel()])
+        i32 = np.concatenate([self.atom_struct, self.atom_ptr, grid.ravel(), self.numbers.astype(np.int32),
+                              cart32.ravel().view(np.int32), lat32.ravel().view(np.int32), vol32.view(np.int32)])
+        self.f64, self.i32 = torch.from_numpy(f64), torch.from_numpy(i32)
+        if pin and torch.cuda.is_available():
+            self.f64, self.i32 = self.f64.pin_memory(), self.i32.pin_memory()
+        self.h2d_bytes = self.f64.numel() * 8 + self.i32.numel() * 4
+
+
+def upload(hb: HostBatch, cutoff, line_cutoff, device) -> BatchedGraph:
+    """Copy a HostBatch to the device (two copies) and slice it into named tensors."""
+    N, Bn = hb.n_atoms, hb.n_struct
+    f64, i32 = hb.f64.to(device, non_blocking=True), hb.i32.to(device, non_blocking=True)
+    g = BatchedGraph()
+    g.n_atoms, g.n_struct, g.n_cells = N, Bn, hb.n_cells
+    g.cutoff, g.line_cutoff = float(cutoff), float(line_cutoff)
+    g.atoms_per_graph, g.atom_ptr_host, g.numbers_host = hb.atoms_per_graph, hb.atom_ptr, hb.numbers
+    g.cart64_host, g.lattice64_host, g.frac32_host = hb.cart, hb.lattice, hb.frac32
+    g.cart64, g.lattice64, g.inv_lattice64 = f64[:3 * N].view(N, 3), f64[3 * N:3 * N + 9 * Bn].view(Bn, 3, 3), \
+        f64[3 * N + 9 * Bn:].view(Bn, 3, 3)
+    o = 0
+
+    def take(n, shape=None, as_float=False):
+        nonlocal o
+        t = i32[o:o + n]
+        o += n
+        if as_float:
+            t = t.view(torch.float32)
+        return t if shape is None else t.view(*shape)
+
+    g.atom_struct, g.atom_ptr, g.grid, g.numbers = take(N), take(Bn + 1), take(8 * Bn, (Bn, 8)), take(N)
+    g.cart32, g.lattice32, g.volume = take(3 * N, (N, 3), True), take(9 * Bn, (Bn, 3, 3), True), take(Bn, None, True)
+    g._staging = (f64, i32)
+    return g
+
+
+def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None) -> BatchedGraph:
+    """Run the three graph phases on the device-resident inputs of ``g`` (positions, lattices, cell grid)
+    and attach the outputs.  Can be called again after ``g.cart64`` changed on the device."""
+    lib = _lib.load()
+    device = g.cart64.device
+    n_atoms, n_struct, n_cells = g.n_atoms, g.n_struct, g.n_cells
     with torch.cuda.device(device):
         st = torch.cuda.current_stream().cuda_stream if stream is None else stream
-
-        def up(x):
-            return torch.from_numpy(np.ascontiguousarray(x)).to(device, non_blocking=True)
-
-        g = BatchedGraph()
-        g.n_atoms, g.n_struct = n_atoms, n_struct
-        g.cutoff, g.line_cutoff = float(cutoff), float(line_cutoff)
-        g.atoms_per_graph = [int(x) for x in n_per]
-        g.atom_ptr_host = atom_ptr
-        g.numbers_host = np.concatenate(numbers).astype(np.int64)
-        g.cart64_host, g.lattice64_host = cart, lattice
-        g.cart64, g.lattice64, d_inv = up(cart), up(lattice), up(inv)
-        g.atom_struct, g.atom_ptr, d_grid = up(atom_struct), up(atom_ptr), up(grid)
-        g.numbers = up(g.numbers_host.astype(np.int32))
-        g.cart32, g.lattice32, g.volume = up(cart32), up(lat32), up(vol32)
-        g.frac32_host = frac32
-
         m = _lib.MbGraph()
         m.n_atoms, m.n_struct, m.n_cells = n_atoms, n_struct, n_cells
-        m.cutoff, m.line_cutoff, m.tol = float(cutoff), float(line_cutoff), float(tol)
-        m.cart, m.lattice, m.inv_lattice = g.cart64.data_ptr(), g.lattice64.data_ptr(), d_inv.data_ptr()
-        m.atom_struct, m.grid = g.atom_struct.data_ptr(), d_grid.data_ptr()
-        keep = [d_inv, d_grid]
+        m.cutoff, m.line_cutoff, m.tol = g.cutoff, g.line_cutoff, float(tol)
+        m.cart, m.lattice, m.inv_lattice = g.cart64.data_ptr(), g.lattice64.data_ptr(), g.inv_lattice64.data_ptr()
+        m.atom_struct, m.grid = g.atom_struct.data_ptr(), g.grid.data_ptr()
         scr = dict(cell_ptr=_i32(n_cells + 1, device), cell_fill=_i32(n_cells, device), cell_atoms=_i32(n_atoms, device),
                    atom_cell=_i32(4 * n_atoms, device), atom_wrap=_i32(4 * n_atoms, device), status=_i32(8, device),
                    scan_tmp=_i32(lib.mb_graph_scan_tmp_len(max(n_atoms, n_cells)), device))
@@ -202,9 +224,22 @@ def build_batched_graph(numbers: Sequence[np.ndarray], carts: Sequence[np.ndarra
             g.lg_cols = g.line_graph.t().contiguous()
         else:
             g.lg_cols = torch.empty(5, 0, dtype=torch.int32, device=device)
-        torch.cuda.current_stream().synchronize()  # scratch tensors go out of scope here
-        del keep, scr, scr2
+        # the scratch tensors were used on this stream only, so the caching allocator may reuse them in order
+        del scr, scr2
+    g._row_graphs = g._slices = None
     return g
+
+
+def build_batched_graph(numbers: Sequence[np.ndarray], carts: Sequence[np.ndarray], lattices: Sequence[np.ndarray],
+                        cutoff: float = 6.0, line_cutoff: float = 4.0, device="cuda", tol: float = 1e-8,
+                        stream=None) -> BatchedGraph:
+    """Build atom graph, bond graph and line graph for a batch of structures on ``device``."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise _lib.MbError("matris_b200 builds graphs on a CUDA device only (no CPU path)")
+    hb = HostBatch(numbers, carts, lattices, cutoff)
+    with torch.cuda.device(device):
+        return build_on_device(upload(hb, cutoff, line_cutoff, device), tol, stream)
 
 
 # ------------------------------------------------------------------ reference-compatible value type

@@ -62,6 +62,9 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
         out = b["out"]
         cb.out, cb.out_idx, cb.ld_out, cb.col_out = out.data_ptr(), ptr(b["out_idx"]), out.stride(0), int(b["out_col"])
         cb.mode, cb.out_scale = int(b["mode"]), float(b["scale"])
+    if _lib.profile is not None:
+        _lib.profile_meta = dict(flops=sum(2.0 * n_rows * D * D * len(b["srcs"]) for b in blocks), rows=int(n_rows),
+                                 k=D * len(blocks[0]["srcs"]), n=D * len(blocks))
     call("mb_gemm", C.byref(d), _stream())
 
 
