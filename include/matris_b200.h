@@ -155,6 +155,12 @@ typedef struct mb_gemm_desc {
 } mb_gemm_desc;
 
 int mb_gemm(const mb_gemm_desc* desc, void* stream);
+/* Contraction core used by mb_gemm: 0 = tcgen05 tensor cores, kind::tf32 with a 3-term hi/lo operand split
+ * accumulated in fp32 TMEM (default); 1 = fp32 SIMT FMA (bit-faithful fp32, the cross-check). Process-wide. */
+int mb_set_gemm_mode(int mode);
+/* Synchronises the stream, returns and clears the tensor-core kernel's status word (bit 0: a bounded
+ * mbarrier wait expired and the affected tiles were not written). */
+int mb_gemm_status(int* status, void* stream);
 
 /* ------------------------------------------------------------------ row-wise model kernels
  * All feature tensors are float32 row-major with 128 channels unless noted.

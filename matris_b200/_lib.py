@@ -65,6 +65,8 @@ _SIGNATURES = {
     "mb_graph_build_edges": [C.POINTER(MbGraph), _vp],
     "mb_graph_build_triplets": [C.POINTER(MbGraph), _vp],
     "mb_gemm": [C.POINTER(MbGemmDesc), _vp],
+    "mb_set_gemm_mode": [C.c_int],
+    "mb_gemm_status": [C.POINTER(C.c_int), _vp],
     "mb_gate_fwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_gate_bwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_seg_attn_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],

@@ -258,3 +258,16 @@ def angle_basis_bwd(line_graph, unit, factor, cutoff, dbasis):
     call("mb_angle_basis_bwd", line_graph.shape[0], ptr(line_graph), ptr(unit), float(factor), float(cutoff),
          ptr(dbasis), ptr(dunit), _stream())
     return dunit
+
+
+# ------------------------------------------------------------------ GEMM core selection / status
+def set_gemm_mode(mode: str) -> None:
+    """'tcgen05' (default): tensor cores, 3-term TF32 split; 'simt': exact fp32 FMA cross-check."""
+    _lib.check(_lib.load().mb_set_gemm_mode({"tcgen05": 0, "simt": 1}[mode]), "mb_set_gemm_mode")
+
+
+def gemm_status() -> int:
+    """Synchronise and return (then clear) the tensor-core kernel's status word; 0 = no wait expired."""
+    st = C.c_int(0)
+    _lib.check(_lib.load().mb_gemm_status(C.byref(st), _stream()), "mb_gemm_status")
+    return st.value

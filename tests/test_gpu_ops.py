@@ -75,6 +75,37 @@ def test_gemm_scatter_modes(ops):
     report("gemm accumulate", out2, base2.double() + F.linear(x.double(), W.double()), 3e-5)
 
 
+def test_tensor_core_gemm_matches_fp32_simt(ops):
+    """tcgen05 3xTF32 against the exact-fp32 SIMT core on the same descriptors, all epilogue paths."""
+    R, n1 = 5000, 300
+    e, node = rnd(R, 128, seed=4) * 3, rnd(n1, 128, seed=5) * 3
+    g = torch.Generator().manual_seed(0)
+    tgt, src = torch.randint(0, n1, (R,), generator=g), torch.randint(0, n1, (R,), generator=g)
+    W, b, z, res, rw = rnd(256, 384, seed=7, scale=0.2), rnd(256, seed=8), rnd(R, 256, seed=9), rnd(R, 256, seed=10), rnd(128, seed=11)
+    de, dn, dW, db, dz, dres, drw = dev(e), dev(node), dev(W), dev(b), dev(z), dev(res), dev(rw)
+    it, is_ = dev(tgt, torch.int32), dev(src, torch.int32)
+    outs = {}
+    for mode in ("simt", "tcgen05"):
+        ops.set_gemm_mode(mode)
+        out = torch.zeros(R, 256, device="cuda")
+        acc = torch.zeros(n1, 128, device="cuda")
+        srcs = [ops.S(de, None, 0, 1), ops.S(dn, it), ops.S(dn, is_)]
+        ops.gemm(R, [ops.B(srcs, dW, w_row=128 * j, bias=db, bias_off=128 * j, gate=dz, gate_col=128 * j, res=dres,
+                           res_col=128 * j, res_w=drw, out=out, out_col=128 * j, scale=0.5) for j in (0, 1)])
+        ops.gemm(R, [ops.B(srcs, dW, out=acc, out_idx=it, mode=ops.OUT_ATOMIC)])
+        assert ops.gemm_status() == 0
+        outs[mode] = (out.cpu(), acc.cpu())
+    ops.set_gemm_mode("tcgen05")
+    report("tcgen05 vs simt: fused epilogue", outs["tcgen05"][0], outs["simt"][0], 3e-6)
+    report("tcgen05 vs simt: atomic scatter", outs["tcgen05"][1], outs["simt"][1], 3e-6)
+    x = torch.cat([torch.nn.functional.silu(e), node[tgt], node[src]], 1).double()
+    want = torch.nn.functional.linear(x, W.double(), b.double())
+    zz = z.double().requires_grad_(True)
+    (sg,) = torch.autograd.grad(torch.nn.functional.silu(zz).sum(), zz)
+    want = (want * sg + torch.cat([rw, rw]).double() * res.double()) * 0.5
+    report("tcgen05 vs float64", outs["tcgen05"][0], want, 3e-6)
+
+
 # ---------------------------------------------------------------- row-wise
 def _gate_ref(z, wc, wg):
     c = F.rms_norm(z[:, :128], (128,), wc, torch.finfo(torch.float32).eps)
