@@ -136,7 +136,9 @@ typedef struct mb_colblock {
   int32_t out_act;             /* 0 none, 1 SiLU */
   mb_src src[4];
   const float* W;              /* [128, K] row-major: weight rows of this column block */
-  int64_t ldw;                 /* row stride of W in floats (>= K) */
+  const float* W_hi;           /* tf32(W), same layout (tensor-core mode; NULL allowed in SIMT mode) */
+  const float* W_lo;           /* W - tf32(W), same layout */
+  int64_t ldw;                 /* row stride of W, W_hi, W_lo in floats (>= K) */
   const float* bias;           /* [128] or NULL */
   const float* gate;           /* optional pre-activation z: multiply by d/dz SiLU(z) */
   int64_t ld_gate; int32_t col_gate; int32_t pad0;

@@ -48,7 +48,7 @@ class MbSrc(C.Structure):
 class MbColBlock(C.Structure):
     _fields_ = [
         ("n_src", _i32), ("out_act", _i32), ("src", MbSrc * 4),
-        ("W", _vp), ("ldw", _i64), ("bias", _vp),
+        ("W", _vp), ("W_hi", _vp), ("W_lo", _vp), ("ldw", _i64), ("bias", _vp),
         ("gate", _vp), ("ld_gate", _i64), ("col_gate", _i32), ("pad0", _i32),
         ("res", _vp), ("res_w", _vp), ("ld_res", _i64), ("col_res", _i32), ("mode", _i32),
         ("out", _vp), ("out_idx", _vp), ("ld_out", _i64), ("col_out", _i32), ("out_scale", _f32),

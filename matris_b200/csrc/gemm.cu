@@ -171,29 +171,66 @@ static int gemm_validate(const mb_gemm_desc* desc) {
 // tcgen05 / TMEM core: the same GEMM on the 5th-generation tensor cores, fp32-accurate.
 //
 // kind::tf32 reads 19 of the 32 operand bits, so each operand is split into
-// hi = tf32(x) and lo = tf32(x - hi) and three MMAs per K step accumulate
+// hi = tf32(x) and lo = x - hi and three MMAs per K step accumulate
 // lo*hi + hi*lo + hi*hi in the fp32 TMEM accumulator (the dropped lo*lo term is
 // ~2^-22 relative): results sit at the fp32 rounding floor.
 //
-// One CTA = one 128x128 output tile, 128 threads.  Per K chunk of 32: all threads
-// gather/convert the A rows and the W rows into four 128x32 K-major tiles in the
-// 128-byte-swizzled canonical layout (hi/lo of A and of W), then one thread issues
-// 12 tcgen05.mma (4 K steps x 3 split terms) and commits them to an mbarrier.  The
-// next chunk's global loads are already in flight in registers.  Three CTAs are
-// resident per SM (64 KB of tiles + 128 TMEM columns each), so one CTA's MMAs
-// overlap the other CTAs' tile fills.  Epilogue: tcgen05.ld, one thread per row.
+// Shared-memory bandwidth is what bounds a 3-term tf32 product with both operands
+// in shared memory (every MMA re-reads a 4 KB A tile and a 4 KB W tile), so the A
+// operand lives in TENSOR MEMORY instead:
+//   * One CTA = one 128x128 output tile; 4 producer/epilogue warps + 1 control warp;
+//     256 TMEM columns per CTA (128 accumulator + 2 x (32 hi + 32 lo) A columns),
+//     two CTAs resident per SM.
+//   * Producer warp w owns rows 32w..32w+31 of the tile; thread t owns row t (= TMEM
+//     lane t).  The warp gathers its rows' 32-float K chunk with coalesced 128-byte
+//     row reads (through the optional index), transposes it through a swizzled
+//     shared-memory patch so that every thread holds its own row, applies the
+//     optional SiLU, splits into hi / lo and writes both with tcgen05.st into the A
+//     buffer of that chunk; the next chunk's loads are already in flight.
+//   * W tiles: hi / lo parts of the weights (split once by the caller: W_hi, W_lo)
+//     arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle, no cluster forms) into
+//     a 3-deep ring, two chunks ahead, completing on mbarrier transaction counts.
+//   * The control thread issues 12 tcgen05.mma per chunk (4 K steps x 3 split terms,
+//     A from TMEM, W from shared memory) and commits them to mbarriers that free the
+//     A buffer and the W slot.
+//   * Epilogue: tcgen05.ld (one thread per row) -> shared-memory staging -> coalesced
+//     row-wise bias / SiLU' gate / SiLU / residual / scale and store, accumulate or
+//     atomic scatter.
 // Every mbarrier wait is bounded; on expiry a status word is set and the kernel
 // finishes normally (TMEM is always released).
+#include <cuda.h>
+#include <stdio.h>
+#include <type_traits>
+
 namespace mb {
 
-constexpr int TC_THREADS = 128;
+constexpr int TC_THREADS = 160;                 // warps 0-3: producers + epilogue, warp 4: control
 constexpr int TC_BK = 32;                       // floats per K chunk = one 128-byte swizzle row
 constexpr int TC_TILE_BYTES = 128 * 128;        // 128 rows x 128 bytes
-constexpr int TC_SMEM_BYTES = 4 * TC_TILE_BYTES + 1024 /*alignment slack*/ + 64 /*barrier, tmem slot*/;
+constexpr int TC_W_SLOTS = 3;
+constexpr int TC_STAGE_LD = 132;                // floats per staged output row (128 + 4 padding)
+constexpr int TC_RING_BYTES = TC_W_SLOTS * 2 * TC_TILE_BYTES;  // 96 KB, reused as the epilogue staging area
+constexpr int TC_XPOSE_BYTES = 4 * 32 * 128;    // per producer warp: 32 rows x 128 bytes, chunk-swizzled
+constexpr int TC_SMEM_BYTES = TC_RING_BYTES + TC_XPOSE_BYTES + 128 /*barriers, tmem slot*/;
+constexpr uint32_t TC_TMEM_COLS = 256;
 constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
+static_assert(128 * TC_STAGE_LD * 4 <= TC_RING_BYTES, "staging area must fit in the W ring");
+
+struct alignas(64) TcMaps { CUtensorMap m[4][2]; };  // per column block: W_hi, W_lo
 
 __device__ int g_gemm_status = 0;  // bit 0: an mbarrier wait expired
+
+#ifdef MB_GEMM_TIMING  // diagnostic build only: per-phase clock64() totals of thread 0 (producer) and the control thread
+__device__ unsigned long long g_gemm_timing[16];
+#define MB_TDECL long long t_last = clock64(); long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define MB_T(slot) do { const long long _n = clock64(); tacc[slot] += _n - t_last; t_last = _n; } while (0)
+#define MB_TFLUSH(base, n) do { for (int _k = 0; _k < (n); ++_k) atomicAdd(&g_gemm_timing[(base) + _k], (unsigned long long)tacc[_k]); } while (0)
+#else
+#define MB_TDECL
+#define MB_T(slot)
+#define MB_TFLUSH(base, n)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -208,15 +245,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
   // K-major, SWIZZLE_128B: start address, LBO = 1 (unused), SBO = 1024 B between 8-row groups, version 1
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]^T, M = 128, N = 128, K = 8 (tf32)
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-               :: "r"(tmem_d), "l"(da), "l"(db), "r"(TC_IDESC), "r"(accumulate) : "memory");
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+               :: "r"(tmem_d), "r"(tmem_a), "l"(db), "r"(TC_IDESC), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ float to_tf32(float x) {
@@ -225,38 +270,62 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(r);
 }
 
-// write a float4 (4 consecutive K values of one row) as hi / lo into the swizzled tiles
-__device__ __forceinline__ void store_split(uint8_t* tile_hi, uint8_t* tile_lo, int row, int chunk, float4 v) {
-  const int off = (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
-  float4 h = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
-  float4 l = make_float4(to_tf32(v.x - h.x), to_tf32(v.y - h.y), to_tf32(v.z - h.z), to_tf32(v.w - h.w));
-  *reinterpret_cast<float4*>(tile_hi + off) = h;
-  *reinterpret_cast<float4*>(tile_lo + off) = l;
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 3) k_gemm_tc(const __grid_constant__ mb_gemm_desc d) {
-  const mb_colblock& cb = d.blk[blockIdx.y];
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* a_hi = smem;
-  uint8_t* a_lo = smem + TC_TILE_BYTES;
-  uint8_t* b_hi = smem + 2 * TC_TILE_BYTES;
-  uint8_t* b_lo = smem + 3 * TC_TILE_BYTES;
-  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + 4 * TC_TILE_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 4 * TC_TILE_BYTES + 16);
+#define MB_TMEM_ST32(taddr, v)                                                                                   \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                                   \
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "                        \
+               "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"                \
+               :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),      \
+                  "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),  \
+                  "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),           \
+                  "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]),           \
+                  "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory")
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int64_t row0 = (int64_t)blockIdx.x * 128;
-  const int lrow = tid >> 3, chunk = tid & 7;   // loader: rows lrow + 16 i (i = 0..7), 16-byte chunk `chunk`
+#define MB_TMEM_LD32(taddr, v)                                                                                   \
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                         \
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                         \
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"         \
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), \
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),        \
+                 "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),      \
+                 "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),      \
+                 "=r"(v[29]), "=r"(v[30]), "=r"(v[31]) : "r"(taddr) : "memory")
+
+__global__ void __launch_bounds__(TC_THREADS, 2)
+k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps maps) {
+  const int jb = (int)(blockIdx.x % (unsigned)d.n_blocks);  // column block (fastest: the blocks of a row tile share A in L2)
+  const int64_t row0 = (int64_t)(blockIdx.x / (unsigned)d.n_blocks) * 128;
+  const mb_colblock& cb = d.blk[jb];
+  extern __shared__ __align__(1024) uint8_t smem[];  // W ring (1024-byte aligned tiles) | transpose patches | barriers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_RING_BYTES + TC_XPOSE_BYTES);
+  // bars[0..1]: A buffer full (4 producer warps); bars[2..4]: W slot landed (TMA); bars[5..6]: MMAs of a chunk done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_RING_BYTES + TC_XPOSE_BYTES + 64);
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
+    return;
+  }
+  const uint32_t a_full = smem_u32(bars), w_full = smem_u32(bars + 2), mma_done = smem_u32(bars + 5);
+  const uint32_t ring = smem_u32(smem);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Descriptor fields are read once into registers: the descriptor sits in kernel-parameter memory that is
+  // indexed dynamically (column block), and re-reading it inside the loops costs a memory round trip each time.
+  const int64_t n_rows = d.n_rows;
   const int n_chunks = cb.n_src * (128 / TC_BK);
-  const uint32_t bar_addr = smem_u32(bar);
 
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_addr) : "memory");
+    mbar_init(a_full, 4); mbar_init(a_full + 8, 4);
+    mbar_init(w_full, 1); mbar_init(w_full + 8, 1); mbar_init(w_full + 16, 1);
+    mbar_init(mma_done, 1); mbar_init(mma_done + 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" :: "r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -264,113 +333,205 @@ __global__ void __launch_bounds__(TC_THREADS, 3) k_gemm_tc(const __grid_constant
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  const float* a_ptr[8];
-  int a_act = 0;
-  const float* b_ptr = cb.W + (int64_t)lrow * cb.ldw + chunk * 4;
-  const int64_t b_step = 16 * cb.ldw;
-  float4 a_reg[8], b_reg[8];
-
-  auto prefetch = [&](int c) {
-    if ((c & 3) == 0) {  // new 128-wide K segment: resolve the gathered row pointers
-      const mb_src& s = cb.src[c >> 2];
-      a_act = s.act;
+  if (warp == 4) {
+    // ------------------------------------------------------------ control thread: TMA + MMA issue
+    if (lane == 0) {
+      const CUtensorMap* map_hi = &maps.m[jb][0];
+      const CUtensorMap* map_lo = &maps.m[jb][1];
+      auto load_w = [&](int c) {  // W_hi / W_lo rows 0..127, K columns 32c..32c+31 -> ring slot c % 3
+        const int slot = c % TC_W_SLOTS;
+        const uint32_t bar = w_full + 8 * slot, dst = ring + (uint32_t)slot * 2 * TC_TILE_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
+        tma_load_2d(dst, map_hi, bar, c * TC_BK, 0);
+        tma_load_2d(dst + TC_TILE_BYTES, map_lo, bar, c * TC_BK, 0);
+      };
+      bool alive = true;
+      MB_TDECL;
+      load_w(0);
+      if (n_chunks > 1) load_w(1);
+      for (int c = 0; c < n_chunks; ++c) {
+        const int ab = c & 1, slot = c % TC_W_SLOTS;
+        if (alive) alive = mbar_wait(a_full + 8 * ab, (uint32_t)((c >> 1) & 1));
+        MB_T(0);
+        if (alive) alive = mbar_wait(w_full + 8 * slot, (uint32_t)((c / TC_W_SLOTS) & 1));
+        MB_T(1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t wb = ring + (uint32_t)slot * 2 * TC_TILE_BYTES;
+        const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
+        const uint32_t ta_hi = tmem_base + 128 + 64 * ab, ta_lo = ta_hi + 32;
+#ifndef MB_DBG_NO_MMA
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int64_t r = row0 + lrow + 16 * i;
-        if (r < d.n_rows) {
-          const int64_t sr = s.idx ? (int64_t)s.idx[r] : r;
-          a_ptr[i] = s.ptr + sr * s.ld + s.col + chunk * 4;
-        } else {
-          a_ptr[i] = nullptr;
+        for (int k = 0; k < 4; ++k) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
+          const uint64_t adv = (uint64_t)(2 * k);
+          umma_tf32_ts(tmem_base, ta_lo + 8 * k, dbh + adv, (c > 0 || k > 0) ? 1u : 0u);
+          umma_tf32_ts(tmem_base, ta_hi + 8 * k, dbl + adv, 1u);
+          umma_tf32_ts(tmem_base, ta_hi + 8 * k, dbh + adv, 1u);
         }
+#endif
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                     :: "r"(mma_done + 8 * ab) : "memory");
+        MB_T(2);
+        if (c + 2 < n_chunks) {  // slot (c+2) % 3 was read by chunk c-1: refill it once those MMAs are done
+          if (c > 0 && alive) alive = mbar_wait(mma_done + 8 * ((c - 1) & 1), (uint32_t)(((c - 1) >> 1) & 1));
+          load_w(c + 2);
+        }
+        MB_T(3);
       }
+      MB_TFLUSH(8, 4);
     }
-    const int kofs = (c & 3) * TC_BK;
+    return;
+  }
+
+  // -------------------------------------------------------------- producers: thread = row = TMEM lane
+  const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int lr = lane >> 3, lc = lane & 7;  // coalesced loads: 8 lanes read one row's 128 bytes, 4 rows per instruction
+  const uint32_t patch = smem_u32(smem + TC_RING_BYTES + warp * (32 * 128));
+  const float* a_ptr[8];
+  int32_t a_row[8];  // source row of each of this lane's 8 rows in the NEXT K segment (-1: past the end)
+  int a_act = 0;
+  float4 a_reg[8];
+  auto resolve_rows = [&](int seg) {  // issued a chunk before the segment starts, so the index loads are hidden
+    const int32_t* idx = cb.src[seg].idx;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (a_ptr[i]) v = ld4(a_ptr[i] + kofs);
-      a_reg[i] = v;
-      b_reg[i] = ld4(b_ptr + i * b_step + c * TC_BK);
+      const int64_t r = row0 + warp * 32 + lr + 4 * i;
+      a_row[i] = r < n_rows ? (idx ? idx[r] : (int32_t)(r - row0)) : -1;
     }
+  };
+  auto prefetch = [&](int c) {
+    if ((c & 3) == 0) {  // new 128-wide K segment: turn the resolved rows into pointers
+      const mb_src& s = cb.src[c >> 2];
+      a_act = s.act;
+      const float* base = s.ptr + s.col + lc * 4;
+      const int64_t ld = s.ld;
+      const bool gathered = s.idx != nullptr;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        a_ptr[i] = a_row[i] < 0 ? nullptr : base + (gathered ? (int64_t)a_row[i] : row0 + a_row[i]) * ld;
+    }
+    if ((c & 3) == 2 && (c >> 2) + 1 < cb.n_src) resolve_rows((c >> 2) + 1);
+    const int kofs = (c & 3) * TC_BK;
+#pragma unroll
+#ifdef MB_DBG_NO_LOAD
+    for (int i = 0; i < 8; ++i) a_reg[i] = make_float4(1.f, 2.f, 3.f, (float)kofs);
+#else
+    for (int i = 0; i < 8; ++i) a_reg[i] = a_ptr[i] ? ld4(a_ptr[i] + kofs) : make_float4(0.f, 0.f, 0.f, 0.f);
+#endif
   };
 
   bool alive = true;
+  MB_TDECL;
+  resolve_rows(0);
   prefetch(0);
+  MB_T(0);
   for (int c = 0; c < n_chunks; ++c) {
-    if (c > 0 && alive) alive = mbar_wait(bar_addr, (uint32_t)((c - 1) & 1));  // previous chunk's MMAs have read the tiles
-    const int act = a_act;
+    const int ab = c & 1;
+    // transpose: row (lr + 4i), 16-byte chunk lc -> patch[row][chunk ^ (row & 7)]; then every thread reads its own row
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float4 v = a_reg[i];
-      if (act) { v.x = silu_f(v.x); v.y = silu_f(v.y); v.z = silu_f(v.z); v.w = silu_f(v.w); }
-      store_split(a_hi, a_lo, lrow + 16 * i, chunk, v);
-      store_split(b_hi, b_lo, lrow + 16 * i, chunk, b_reg[i]);
+      const int row = lr + 4 * i;
+      const uint32_t addr = patch + row * 128 + ((lc ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "f"(a_reg[i].x), "f"(a_reg[i].y),
+                   "f"(a_reg[i].z), "f"(a_reg[i].w) : "memory");
     }
-    if (c + 1 < n_chunks) prefetch(c + 1);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA's async proxy
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t dah = umma_desc(smem_u32(a_hi)), dal = umma_desc(smem_u32(a_lo));
-      const uint64_t dbh = umma_desc(smem_u32(b_hi)), dbl = umma_desc(smem_u32(b_lo));
+    const int act = a_act;
+    if (c + 1 < n_chunks) prefetch(c + 1);  // a_reg was consumed by the stores above: start the next chunk's loads now
+    MB_T(1);
+    __syncwarp();
+    float x[32];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {  // 4 K steps of 8 tf32 = 32 bytes: advance the start address by 32 >> 4
-        const uint64_t adv = (uint64_t)(2 * k);
-        umma_tf32(tmem_base, dal + adv, dbh + adv, (c > 0 || k > 0) ? 1u : 0u);
-        umma_tf32(tmem_base, dah + adv, dbl + adv, 1u);
-        umma_tf32(tmem_base, dah + adv, dbh + adv, 1u);
-      }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_addr) : "memory");
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t addr = patch + lane * 128 + ((j ^ (lane & 7)) << 4);
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]), "=f"(x[4 * j + 2]),
+                   "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
     }
+    __syncwarp();
+    MB_T(2);
+    uint32_t hi[32], lo[32];
+    if (act) {  // branch once per chunk: the SiLU must not be evaluated (and discarded) on the plain path
+#pragma unroll
+      for (int q = 0; q < 32; ++q) x[q] = silu_f(x[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      const float h = to_tf32(x[q]);
+      hi[q] = __float_as_uint(h);
+      lo[q] = __float_as_uint(x[q] - h);
+    }
+    if (c >= 2 && alive) alive = mbar_wait(mma_done + 8 * ab, (uint32_t)(((c >> 1) - 1) & 1));  // A buffer ab is free again
+    MB_T(3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t ta = lane_base + 128 + 64 * ab;
+    MB_TMEM_ST32(ta, hi);
+    MB_TMEM_ST32(ta + 32, lo);
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(a_full + 8 * ab);
+    MB_T(4);
   }
-  if (alive) alive = mbar_wait(bar_addr, (uint32_t)((n_chunks - 1) & 1));
+  // all MMAs retire in order: the last chunk's commit covers the whole accumulator
+  if (alive) alive = mbar_wait(mma_done + 8 * ((n_chunks - 1) & 1), (uint32_t)(((n_chunks - 1) >> 1) & 1));
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  MB_T(5);
 
-  // ---- epilogue: thread tid owns output row row0 + tid (TMEM lane tid), 32 columns per tcgen05.ld
-  const int64_t r = row0 + tid;
-  const bool valid = alive && r < d.n_rows;
-  const int64_t dr = (valid && cb.out_idx) ? (int64_t)cb.out_idx[r] : r;
+  // -------------------------------------------------------------- epilogue
+  // (1) accumulator row -> staging (the W ring is idle: every TMA landed and every MMA retired)
+  float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll 1
   for (int cg = 0; cg < 4; ++cg) {
     uint32_t v[32];
-    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cg * 32);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
+    MB_TMEM_LD32(lane_base + (uint32_t)(cg * 32), v);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    if (!valid) continue;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const int col = cg * 32 + q * 4;
-      float o[4] = {__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
-                    __uint_as_float(v[4 * q + 3])};
-      if (cb.bias) {
-        const float4 bb = ld4(cb.bias + col);
-        o[0] += bb.x; o[1] += bb.y; o[2] += bb.z; o[3] += bb.w;
-      }
-      if (cb.gate) {
-        const float4 z = ld4(cb.gate + r * cb.ld_gate + cb.col_gate + col);
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<uint4*>(stage + tid * TC_STAGE_LD + cg * 32 + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+  }
+  MB_T(6);
+  // (2) warp w finishes rows w, w+4, ...: lane l owns columns 4l..4l+3, every global access is a full 512-byte row
+  const int col = lane * 4;
+  const float* const gate = cb.gate;
+  const float* const res = cb.res;
+  const int32_t* const out_idx = cb.out_idx;
+  float* const out = cb.out;
+  const int64_t ld_gate = cb.ld_gate, ld_res = cb.ld_res, ld_out = cb.ld_out;
+  const int gcol = cb.col_gate + col, rcol = cb.col_res + col, ocol = cb.col_out + col;
+  const int mode = cb.mode, out_act = cb.out_act;
+  const float sc = cb.out_scale;
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), resw4 = make_float4(1.f, 1.f, 1.f, 1.f);
+  if (cb.bias) bias4 = ld4(cb.bias + col);
+  if (res && cb.res_w) resw4 = ld4(cb.res_w + col);
+  if (!alive) return;
+  const int rows_here = (int)((n_rows - row0) < 128 ? (n_rows - row0) : 128);
+  auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
+#pragma unroll 4
+    for (int rr = warp; rr < rows_here; rr += 4) {
+      const int64_t gr = row0 + rr;
+      const float4 a = *reinterpret_cast<const float4*>(stage + rr * TC_STAGE_LD + col);
+      float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
+      if constexpr (decltype(has_gate)::value) {
+        const float4 z = ld4(gate + gr * ld_gate + gcol);
         o[0] *= silu_grad_f(z.x); o[1] *= silu_grad_f(z.y); o[2] *= silu_grad_f(z.z); o[3] *= silu_grad_f(z.w);
       }
-      if (cb.out_act) { o[0] = silu_f(o[0]); o[1] = silu_f(o[1]); o[2] = silu_f(o[2]); o[3] = silu_f(o[3]); }
-      if (cb.res) {
-        const float4 x = ld4(cb.res + r * cb.ld_res + cb.col_res + col);
-        float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (cb.res_w) w = ld4(cb.res_w + col);
-        o[0] = fmaf(w.x, x.x, o[0]); o[1] = fmaf(w.y, x.y, o[1]); o[2] = fmaf(w.z, x.z, o[2]); o[3] = fmaf(w.w, x.w, o[3]);
+      if constexpr (decltype(has_act)::value) {
+        o[0] = silu_f(o[0]); o[1] = silu_f(o[1]); o[2] = silu_f(o[2]); o[3] = silu_f(o[3]);
       }
-      const float sc = cb.out_scale;
+      if constexpr (decltype(has_res)::value) {
+        const float4 x = ld4(res + gr * ld_res + rcol);
+        o[0] = fmaf(resw4.x, x.x, o[0]); o[1] = fmaf(resw4.y, x.y, o[1]);
+        o[2] = fmaf(resw4.z, x.z, o[2]); o[3] = fmaf(resw4.w, x.w, o[3]);
+      }
       const float4 ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
-      float* dst = cb.out + dr * cb.ld_out + cb.col_out + col;
-      if (cb.mode == MB_OUT_STORE) {
+      const int64_t dr = out_idx ? (int64_t)out_idx[gr] : gr;
+      float* dst = out + dr * ld_out + ocol;
+      if (mode == MB_OUT_STORE) {
         *reinterpret_cast<float4*>(dst) = ov;
-      } else if (cb.mode == MB_OUT_ADD) {
+      } else if (mode == MB_OUT_ADD) {
         float4 p = ld4(dst);
         p.x += ov.x; p.y += ov.y; p.z += ov.z; p.w += ov.w;
         *reinterpret_cast<float4*>(dst) = p;
@@ -378,15 +539,71 @@ __global__ void __launch_bounds__(TC_THREADS, 3) k_gemm_tc(const __grid_constant
         atomicAdd(reinterpret_cast<float4*>(dst), ov);
       }
     }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" :: "r"(tmem_base) : "memory");
-  }
+  };
+  // the transcendental epilogue terms are compiled out of the variants that do not use them
+  using T = std::true_type;
+  using F = std::false_type;
+  if (gate) finish_rows(T{}, F{}, F{});                 // backward: * SiLU'(z)
+  else if (out_act && res) finish_rows(F{}, T{}, T{});
+  else if (out_act) finish_rows(F{}, T{}, F{});
+  else if (res) finish_rows(F{}, F{}, T{});
+  else finish_rows(F{}, F{}, F{});
+  MB_T(7);
+#ifdef MB_GEMM_TIMING
+  if (tid == 0) MB_TFLUSH(0, 8);
+#endif
 }
 
 static int g_gemm_mode = 0;  // 0: tcgen05 3xTF32, 1: fp32 SIMT
+
+// TMA descriptor of a [128, k] float32 weight block (row stride ldw), box 128 rows x 32 columns, 128-byte swizzle.
+// Encoding depends only on (address, stride, k), so descriptors are cached per host thread.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MB_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) return MB_ERR_CUDA;
+    encode = (EncodeTiledFn)fn;
+  }
+  static thread_local bool bound = false;
+  if (!bound) {  // the driver call below needs this thread to have the device's context current
+    MB_CUDA_CHECK(cudaFree(nullptr));
+    bound = true;
+  }
+  struct Key { const float* w; int64_t ld; int k; };
+  struct Entry { Key key; CUtensorMap map; };
+  constexpr int SLOTS = 1024;
+  static thread_local Entry* cache = nullptr;
+  if (!cache) cache = new Entry[SLOTS]();
+  const size_t hsh = ((reinterpret_cast<uintptr_t>(w) >> 4) * 0x9E3779B97F4A7C15ull + (uint64_t)k) >> 54;  // 10 bits
+  Entry& e = cache[hsh % SLOTS];
+  if (e.key.w == w && e.key.ld == ldw && e.key.k == k) {
+    *out = e.map;
+    return MB_OK;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)k, 128};
+  const cuuint64_t strides[1] = {(cuuint64_t)ldw * sizeof(float)};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(w), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char where[64];
+    snprintf(where, sizeof(where), "cuTensorMapEncodeTiled (CUresult %d)", (int)r);
+    set_cuda_error(cudaErrorInvalidValue, where);
+    return MB_ERR_CUDA;
+  }
+  e.key = Key{w, ldw, k};
+  e.map = *out;
+  return MB_OK;
+}
 
 }  // namespace mb
 
@@ -395,6 +612,16 @@ extern "C" int mb_set_gemm_mode(int mode) {
   mb::g_gemm_mode = mode;
   return MB_OK;
 }
+
+#ifdef MB_GEMM_TIMING
+extern "C" int mb_gemm_read_timing(unsigned long long* host16) {
+  unsigned long long zero[16] = {0};
+  MB_CUDA_CHECK(cudaDeviceSynchronize());
+  MB_CUDA_CHECK(cudaMemcpyFromSymbol(host16, mb::g_gemm_timing, sizeof(zero)));
+  MB_CUDA_CHECK(cudaMemcpyToSymbol(mb::g_gemm_timing, zero, sizeof(zero)));
+  return MB_OK;
+}
+#endif
 
 extern "C" int mb_gemm_status(int* status, void* stream_) {
   if (!status) return MB_ERR_INVALID;
@@ -410,9 +637,9 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
   if (rc) return rc;
   if (desc->n_rows == 0) return MB_OK;
   const long long gx = (desc->n_rows + 127) / 128;
-  if (gx > 0x7fffffffLL) return MB_ERR_OVERFLOW;
-  dim3 grid((unsigned)gx, (unsigned)desc->n_blocks);
+  if (gx * desc->n_blocks > 0x7fffffffLL) return MB_ERR_OVERFLOW;
   if (mb::g_gemm_mode == 1) {
+    dim3 grid((unsigned)gx, (unsigned)desc->n_blocks);
     mb::k_gemm<<<grid, mb::GEMM_THREADS, 0, (cudaStream_t)stream_>>>(*desc);
   } else {
     static bool configured = false;  // per process; the attribute is per device function and context
@@ -420,7 +647,16 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
       MB_CUDA_CHECK(cudaFuncSetAttribute(mb::k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, mb::TC_SMEM_BYTES));
       configured = true;
     }
-    mb::k_gemm_tc<<<grid, mb::TC_THREADS, mb::TC_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc);
+    mb::TcMaps maps;
+    for (int j = 0; j < desc->n_blocks; ++j) {
+      const mb_colblock& cb = desc->blk[j];
+      if (!cb.W_hi || !cb.W_lo) return MB_ERR_INVALID;
+      rc = mb::weight_map(cb.W_hi, cb.ldw, 128 * cb.n_src, &maps.m[j][0]);
+      if (rc) return rc;
+      rc = mb::weight_map(cb.W_lo, cb.ldw, 128 * cb.n_src, &maps.m[j][1]);
+      if (rc) return rc;
+    }
+    mb::k_gemm_tc<<<(unsigned)(gx * desc->n_blocks), mb::TC_THREADS, mb::TC_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
   }
   MB_LAUNCH_CHECK("k_gemm");
   return MB_OK;

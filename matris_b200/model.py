@@ -11,9 +11,10 @@ inference), so forces = -dE/dr and stress = (1/V) dE/d(strain) come out of
 ``torch.autograd.grad`` exactly as in the reference's conservative head
 (matris/model/readout.py:202-224).
 
-Memory policy: a sub-block keeps only its inputs for the backward pass and
-recomputes its internals there (the reference does the same above 60,000
-triplets, matris/model/interaction_block.py:15, 400-403).
+Memory policy: a sub-block always keeps its inputs for the backward pass.  Its
+internals are kept too while they fit in a fraction of the free device memory;
+beyond that they are recomputed in the backward pass (the reference switches to
+recomputation above 60,000 triplets, matris/model/interaction_block.py:15, 400-403).
 """
 from __future__ import annotations
 
@@ -43,18 +44,20 @@ def _pack_gated(get, prefix, dev):
     c, g = prefix + "mlp_core.layers.", prefix + "mlp_gate.layers."
     w1 = torch.cat([get(c + "0.weight"), get(g + "0.weight")], 0).contiguous()
     w2 = torch.cat([get(c + "3.weight"), get(g + "3.weight")], 0).contiguous()
+    SW = ops.SplitWeight
     return SimpleNamespace(
-        w1=w1, b1=torch.cat([get(c + "0.bias"), get(g + "0.bias")]).contiguous(),
-        w2=w2, b2=torch.cat([get(c + "3.bias"), get(g + "3.bias")]).contiguous(),
-        w1t=w1.t().contiguous(),                                                  # [K,256]
-        w2t=torch.cat([get(c + "3.weight").t(), get(g + "3.weight").t()], 0).contiguous(),  # [256,128]
+        w1=SW(w1), b1=torch.cat([get(c + "0.bias"), get(g + "0.bias")]).contiguous(),
+        w2=SW(w2), b2=torch.cat([get(c + "3.bias"), get(g + "3.bias")]).contiguous(),
+        w1t=SW(w1.t()),                                                           # [K,256]
+        w2t=SW(torch.cat([get(c + "3.weight").t(), get(g + "3.weight").t()], 0)),  # [256,128]
         nc=get(prefix + "core_norm.weight").contiguous(), ng=get(prefix + "gate_norm.weight").contiguous(),
         k=w1.shape[1])
 
 
 def _pack_ffn(get, prefix):
-    w1, w2 = get(prefix + "layers.0.weight").contiguous(), get(prefix + "layers.3.weight").contiguous()
-    return SimpleNamespace(w1=w1, w2=w2, w1t=w1.t().contiguous(), w2t=w2.t().contiguous())
+    w1, w2 = get(prefix + "layers.0.weight"), get(prefix + "layers.3.weight")
+    SW = ops.SplitWeight
+    return SimpleNamespace(w1=SW(w1), w2=SW(w2), w1t=SW(w1.t()), w2t=SW(w2.t()))
 
 
 def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
@@ -63,20 +66,21 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
 
     P = SimpleNamespace()
     P.emb_table = get("atom_embedding.embedding.weight").contiguous()
-    P.emb_w = get("atom_embedding.atom_swish_layer.linear.weight").contiguous()
+    SW = ops.SplitWeight
+    P.emb_w = SW(get("atom_embedding.atom_swish_layer.linear.weight"))
     e = "edge_embedding."
     P.freq2, P.freq3 = get(e + "pairwise_rbf_expansion.frequencies").contiguous(), get(
         e + "threebody_rbf_expansion.frequencies").contiguous()
     P.e_w1 = get(e + "edge_linear1.weight").contiguous()
-    P.e_w2 = get(e + "edge_linear2.weight").contiguous()
-    P.e_w3 = get(e + "swish_layer.linear.weight").contiguous()
-    P.e_w2t, P.e_w3t = P.e_w2.t().contiguous(), P.e_w3.t().contiguous()
+    P.e_w2 = SW(get(e + "edge_linear2.weight"))
+    P.e_w3 = SW(get(e + "swish_layer.linear.weight"))
+    P.e_w2t, P.e_w3t = P.e_w2.t(), P.e_w3.t()
     P.e_lnw, P.e_lnb = get(e + "edge_init_norm.weight").contiguous(), get(e + "edge_init_norm.bias").contiguous()
     t = "three_body_embedding."
     P.sph_factor = float(sd[t + "expansion.factor"])
     P.t_wa = get(t + "angle_embedding.weight").contiguous()
-    P.t_wb = get(t + "swish_layer.linear.weight").contiguous()
-    P.t_wbt = P.t_wb.t().contiguous()
+    P.t_wb = SW(get(t + "swish_layer.linear.weight"))
+    P.t_wbt = P.t_wb.t()
     P.layers = []
     for i in range(int(cfg["num_layers"])):
         L = SimpleNamespace()
@@ -86,9 +90,9 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
                                 edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
                                 wn=get(p + "node_res_weight").reshape(-1).contiguous(),
                                 we=get(p + "edge_res_weight").reshape(-1).contiguous())
-            A.wst = torch.cat([get(p + "source_weight_linear.weight"), get(p + "target_weight_linear.weight")],
-                              0).contiguous()         # [256,128]
-            A.wstt = A.wst.t().contiguous()           # [128,256]
+            A.wst = SW(torch.cat([get(p + "source_weight_linear.weight"), get(p + "target_weight_linear.weight")],
+                                 0))                  # [256,128]
+            A.wstt = A.wst.t()                        # [128,256]
             setattr(L, "attn_" + gname, A)
             p = f"interaction_block.{i}.refine_block_{gname}_graph."
             R = SimpleNamespace(edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
@@ -100,12 +104,12 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
         P.layers.append(L)
     P.out_norm = get("readout_norm.weight").contiguous()
     h = "energy_head.energy_head.layers."
-    P.h_w0, P.h_b0 = get(h + "0.weight").contiguous(), get(h + "0.bias").contiguous()
-    P.h_w3, P.h_b3 = get(h + "3.weight").contiguous(), get(h + "3.bias").contiguous()
-    P.h_w0t, P.h_w3t = P.h_w0.t().contiguous(), P.h_w3.t().contiguous()
+    P.h_w0, P.h_b0 = SW(get(h + "0.weight")), get(h + "0.bias").contiguous()
+    P.h_w3, P.h_b3 = SW(get(h + "3.weight")), get(h + "3.bias").contiguous()
+    P.h_w0t, P.h_w3t = P.h_w0.t(), P.h_w3.t()
     P.h_w6, P.h_b6 = get(h + "6.weight").reshape(-1).contiguous(), get(h + "6.bias").contiguous()
     m = "magmom_head.magmom_head.layers."
-    P.m_w0, P.m_b0 = get(m + "0.weight").contiguous(), get(m + "0.bias").contiguous()
+    P.m_w0, P.m_b0 = SW(get(m + "0.weight")), get(m + "0.bias").contiguous()
     P.m_w3, P.m_b3 = get(m + "3.weight").reshape(-1).contiguous(), get(m + "3.bias").contiguous()
     return P
 
@@ -117,13 +121,13 @@ def row_graphs(g: BatchedGraph):
     if getattr(g, "_row_graphs", None) is None:
         atom = SimpleNamespace(is_atom=True, n_rows=g.n_edges, n_nodes=g.n_atoms, n_edge_rows=g.n_bonds,
                                tgt=g.center, src=g.neighbor, ctr=None, tgt_ptr=g.edge_ptr, src_ptr=g.edge_ptr,
-                               src_perm=g.rev, emap=g.d2u, u2d=g.u2d, rev=g.rev)
+                               src_perm=g.rev, emap=g.d2u, u2d=g.u2d, rev=g.rev, keep=False)
         line = None
         if g.n_triplets:
             c = g.lg_cols
             line = SimpleNamespace(is_atom=False, n_rows=g.n_triplets, n_nodes=g.n_bonds, n_edge_rows=g.n_triplets,
                                    ctr=c[0], tgt=c[1], src=c[3], tgt_ptr=g.trip_ptr, src_ptr=g.trip_src_ptr,
-                                   src_perm=g.trip_src_perm, emap=None, u2d=None, rev=None)
+                                   src_perm=g.trip_src_perm, emap=None, u2d=None, rev=None, keep=False)
         g._row_graphs = (atom, line)
     return g._row_graphs
 
@@ -173,9 +177,10 @@ class AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, node, edge, P, rg):
         node, edge = node.contiguous(), edge.contiguous()
-        node_out, edge_out, _ = _attn_forward(P, rg, node, edge)
+        node_out, edge_out, inter = _attn_forward(P, rg, node, edge)
         ctx.save_for_backward(node, edge)
         ctx.P, ctx.rg = P, rg
+        ctx.inter = inter if (rg.keep and any(ctx.needs_input_grad)) else None
         return node_out, edge_out
 
     @staticmethod
@@ -185,7 +190,11 @@ class AttentionFn(torch.autograd.Function):
         P, rg = ctx.P, ctx.rg
         R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
         d_node_out, d_edge_out = d_node_out.contiguous(), d_edge_out.contiguous()
-        _, _, (z1, z2, h, logits, agg_t, agg_s, stats, z1n, z2n) = _attn_forward(P, rg, node, edge)
+        inter, ctx.inter = ctx.inter, None
+        if inter is None:  # internals were not kept: recompute them from the saved inputs
+            _, _, inter = _attn_forward(P, rg, node, edge)
+        z1, z2, h, logits, agg_t, agg_s, stats, z1n, z2n = inter
+        del inter
         # node update
         d_node = ops.scale_rows(d_node_out, P.wn)
         dagg_t, dagg_s = ops.new(Nn, D, node), ops.new(Nn, D, node)
@@ -236,9 +245,10 @@ class RefineFn(torch.autograd.Function):
         node, edge, rbf = node.contiguous(), edge.contiguous(), rbf.contiguous()
         if atom_feat is not None:
             atom_feat = atom_feat.contiguous()
-        node_out, edge_out, _ = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+        node_out, edge_out, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat)
         ctx.save_for_backward(node, edge, rbf, atom_feat)
         ctx.P, ctx.rg = P, rg
+        ctx.inter = inter if (rg.keep and any(ctx.needs_input_grad)) else None
         return node_out, edge_out
 
     @staticmethod
@@ -248,7 +258,11 @@ class RefineFn(torch.autograd.Function):
         P, rg = ctx.P, ctx.rg
         R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
         d_node_out, d_edge_out = d_node_out.contiguous(), d_edge_out.contiguous()
-        _, _, (z1, z2, h, env, zn, ze) = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+        inter, ctx.inter = ctx.inter, None
+        if inter is None:
+            _, _, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+        z1, z2, h, env, zn, ze = inter
+        del inter
         # node FFN
         d_node = ops.scale_rows(d_node_out, P.wn)
         dzn = ops.linear(d_node_out, P.nffn.w2t, gate=zn)
@@ -437,6 +451,7 @@ class MatRIS(nn.Module):
         self._packed = None
         self._packed_device = None
         self.last_batch = None
+        self.keep_activations = None  # None: decide per call from free memory; True / False: force
 
     # -- parameter tree -------------------------------------------------------------------
     def _register(self, key, value, buffer, trainable):
@@ -544,6 +559,14 @@ class MatRIS(nn.Module):
         atom_rg, line_rg = row_graphs(g)
         want_f, want_s = "f" in task, "s" in task
         need_grad = want_f or want_s
+        # bytes of sub-block internals over all layers: ~6.7 KB per triplet row and ~6.2 KB per directed edge
+        est = len(P.layers) * (6.7e3 * g.n_triplets + 6.2e3 * g.n_edges)
+        keep = self.keep_activations
+        if keep is None:
+            keep = est < 0.45 * torch.cuda.mem_get_info(self.device)[0]
+        atom_rg.keep = bool(keep)
+        if line_rg is not None:
+            line_rg.keep = bool(keep)
         out = {}
         with torch.set_grad_enabled(need_grad):
             cart = g.cart32.detach().clone().requires_grad_(need_grad)

@@ -25,6 +25,37 @@ def new(rows, cols, like, zero=False):
 
 
 # ------------------------------------------------------------------ GEMM descriptors
+class SplitWeight:
+    """A weight matrix [n_out, K] with its tensor-core operand split: ``hi`` = tf32-rounded values,
+    ``lo`` = w - hi (both float32, same layout).  ``w`` itself feeds the exact-fp32 SIMT core."""
+
+    __slots__ = ("w", "hi", "lo", "shape")
+
+    def __init__(self, w: torch.Tensor):
+        w = w.detach().contiguous()
+        bits = w.view(torch.int32)
+        hi = ((bits + 0x1000) & ~0x1FFF).view(torch.float32)  # round to nearest (ties away) at 10 mantissa bits
+        self.w, self.hi, self.lo, self.shape = w, hi.contiguous(), (w - hi).contiguous(), w.shape
+
+    def t(self) -> "SplitWeight":
+        return SplitWeight(self.w.t())
+
+
+_split_cache: dict = {}
+
+
+def as_split(W) -> SplitWeight:
+    if isinstance(W, SplitWeight):
+        return W
+    key = (W.data_ptr(), tuple(W.shape), W._version)
+    sw = _split_cache.get(key)
+    if sw is None:
+        if len(_split_cache) > 256:
+            _split_cache.clear()
+        sw = _split_cache[key] = SplitWeight(W)
+    return sw
+
+
 def S(t, idx=None, col=0, act=0):
     """One 128-wide K segment: rows of ``t`` (optionally gathered by ``idx``), columns col..col+127."""
     return (t, idx, col, act)
@@ -50,9 +81,12 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
             assert t.dtype == torch.float32 and t.stride(-1) == 1
             cb.src[s].ptr, cb.src[s].idx = t.data_ptr(), ptr(idx)
             cb.src[s].ld, cb.src[s].col, cb.src[s].act = t.stride(0), int(col), int(act)
-        W = b["W"]
+        sw = as_split(b["W"])
+        W = sw.w
         assert W.dim() == 2 and W.stride(1) == 1 and W.shape[1] >= D * len(b["srcs"])
-        cb.W, cb.ldw = W.data_ptr() + 4 * W.stride(0) * int(b["w_row"]), W.stride(0)
+        w_off = 4 * W.stride(0) * int(b["w_row"])
+        cb.W, cb.W_hi, cb.W_lo = W.data_ptr() + w_off, sw.hi.data_ptr() + w_off, sw.lo.data_ptr() + w_off
+        cb.ldw = W.stride(0)
         cb.bias = None if b["bias"] is None else b["bias"].data_ptr() + 4 * int(b["bias_off"])
         if b["gate"] is not None:
             cb.gate, cb.ld_gate, cb.col_gate = b["gate"].data_ptr(), b["gate"].stride(0), int(b["gate_col"])
@@ -71,6 +105,7 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
 def linear(x, W, bias=None, out_act=0, in_act=0, gate=None, res=None, res_w=None, scale=1.0, idx=None, out=None):
     """y[R,128*nb] = epilogue(x[R,128*ns] @ W^T): plain dense layer built on gemm()."""
     n_rows = x.shape[0] if idx is None else idx.shape[0]
+    W = as_split(W)
     n_out, k = W.shape
     assert n_out % D == 0 and k % D == 0
     if out is None:

@@ -1,0 +1,76 @@
+"""GPU: the application layer (calculator / relax / MD) on top of the CUDA path, without ASE."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GPA, load_golden
+from gpu_util import report
+from matris_b200 import workloads
+from matris_b200.weights import random_checkpoint
+
+pytestmark = pytest.mark.gpu
+
+
+def _atoms(cr):
+    from matris_b200.applications import SimpleAtoms
+    return SimpleAtoms(cr.numbers, cr.cart, cr.lattice)
+
+
+def test_calculator_results_match_reference_conversion():
+    """MatRISCalculator.calculate: total energy = e/atom * n, stress GPa -> eV/A^3 (base.py:108-122)."""
+    from matris_b200.applications import MatRISCalculator
+    meta, crystals, z = load_golden("pu4si6_L2")
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0, jitter=meta["jitter"])
+    calc = MatRISCalculator(model=ck, task="efsm", device="cuda")
+    atoms = _atoms(crystals[0])
+    calc.calculate(atoms)
+    n = len(crystals[0].numbers)
+    r = calc.results
+    report("calculator energy (eV)", np.array([r["energy"]]), z["ref32_e"] * n, 1e-5 * n)
+    report("calculator ref_energy (eV)", np.array([r["ref_energy"]]), z["ref32_ref_energy"] * n, 1e-5)
+    report("calculator forces", r["forces"], z["ref32_f"], 1e-4)
+    report("calculator stress (eV/A^3)", r["stress"], z["ref32_s"][0] / GPA, 1e-5)
+    report("calculator magmoms", r["magmoms"], z["ref32_m"], 1e-4)
+    assert r["stress"].shape == (3, 3) and set(r) >= {"energy", "forces", "stress", "magmoms", "ref_energy"}
+    calc2 = MatRISCalculator(model=calc.model, task="e", device="cuda")
+    calc2.calculate(atoms)
+    assert calc2.results["forces"] is None and calc2.results["stress"] is None
+
+
+def test_calculator_non_periodic_axis_gets_a_big_box():
+    from matris_b200.applications import MatRISCalculator, SimpleAtoms
+    ck = random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=0)
+    cr = workloads.cu_fcc(reps=(2, 2, 1))
+    atoms = SimpleAtoms(cr.numbers, cr.cart, cr.lattice, pbc=[True, True, False])
+    MatRISCalculator(model=ck, task="ef", device="cuda").calculate(atoms)
+    assert atoms.get_cell()[2, 2] > 100.0  # the cell of the caller's object is changed, as in the reference
+
+
+def test_nve_energy_conservation_and_langevin_runs():
+    from matris_b200.applications import MolecularDynamics
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)
+    from matris_b200 import MatRIS
+    model = MatRIS.from_dict(ck).to("cuda")
+    md = MolecularDynamics(_atoms(workloads.cu_fcc()), model=model, ensemble="nve", timestep=1.0,
+                           starting_temperature=300, task="ef", device="cuda")
+    e0 = md.atoms.get_potential_energy() + md.atoms.get_kinetic_energy()
+    md.run(20)
+    e1 = md.atoms.get_potential_energy() + md.atoms.get_kinetic_energy()
+    assert abs(e1 - e0) < 2e-3 * len(md.atoms), (e0, e1)
+    md2 = MolecularDynamics(_atoms(workloads.cu_fcc()), model=model, ensemble="nvt", thermostat="langevin",
+                            temperature=600, starting_temperature=600, timestep=1.0, task="efsm", device="cuda")
+    md2.run(5)
+    assert md2.steps_done == 5 and np.isfinite(md2.atoms.get_temperature())
+
+
+def test_relax_lowers_the_force():
+    from matris_b200.applications import StructOptimizer
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)
+    opt = StructOptimizer(model=ck, task="efs", optimizer="FIRE", device="cuda")
+    atoms = _atoms(workloads.demo_pu4si6())
+    opt.calculator.calculate(atoms)
+    f0 = np.abs(opt.calculator.results["forces"]).max()
+    out = opt.relax(atoms, fmax=1e-4, steps=15, verbose=False)
+    assert set(out) == {"final_structure", "trajectory"} and len(out["trajectory"]) >= 2
+    assert out["trajectory"].energies[-1] <= out["trajectory"].energies[0] + 1e-6
+    assert np.isfinite(f0)

@@ -180,3 +180,18 @@ def test_state_dict_roundtrip_and_from_dict():
     assert model.config["num_layers"] == 1 and model.is_intensive
     with pytest.raises(RuntimeError):
         model([workloads.demo_pu4si6()])  # still on CPU: no fallback
+
+
+def test_recompute_equals_kept_activations():
+    """The two memory policies (keep sub-block internals / recompute them in backward) agree."""
+    from matris_b200 import MatRIS
+    crystals = workloads.random_crystals(3, seed=9)
+    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=5)
+    model = MatRIS.from_dict(ck).to("cuda")
+    res = {}
+    for keep in (True, False):
+        model.keep_activations = keep
+        out = model.predict(crystals, "efs")
+        res[keep] = (torch.cat(list(out["f"])).cpu(), torch.stack(out["s"]).cpu())
+    report("keep vs recompute F", res[True][0], res[False][0], 2e-6)
+    report("keep vs recompute S", res[True][1] / GPA, res[False][1] / GPA, 2e-7)
