@@ -543,11 +543,9 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   // the transcendental epilogue terms are compiled out of the variants that do not use them
   using T = std::true_type;
   using F = std::false_type;
-  if (gate) finish_rows(T{}, F{}, F{});                 // backward: * SiLU'(z)
-  else if (out_act && res) finish_rows(F{}, T{}, T{});
-  else if (out_act) finish_rows(F{}, T{}, F{});
-  else if (res) finish_rows(F{}, F{}, T{});
-  else finish_rows(F{}, F{}, F{});
+  auto pick_res = [&](auto g, auto a) { if (res) finish_rows(g, a, T{}); else finish_rows(g, a, F{}); };
+  auto pick_act = [&](auto g) { if (out_act) pick_res(g, T{}); else pick_res(g, F{}); };
+  if (gate) pick_act(T{}); else pick_act(F{});
   MB_T(7);
 #ifdef MB_GEMM_TIMING
   if (tid == 0) MB_TFLUSH(0, 8);

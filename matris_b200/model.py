@@ -563,7 +563,9 @@ class MatRIS(nn.Module):
         est = len(P.layers) * (6.7e3 * g.n_triplets + 6.2e3 * g.n_edges)
         keep = self.keep_activations
         if keep is None:
-            keep = est < 0.45 * torch.cuda.mem_get_info(self.device)[0]
+            # memory the allocator can hand out: free on the device plus its own cached, unused blocks
+            reusable = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+            keep = est < 0.45 * (torch.cuda.mem_get_info(self.device)[0] + reusable)
         atom_rg.keep = bool(keep)
         if line_rg is not None:
             line_rg.keep = bool(keep)
