@@ -38,6 +38,8 @@ def make_workload(name: str, rank: int):
     from matris_b200 import workloads as w
     if name == "random256":
         return w.random_crystals(256, seed=1 + rank), "efs", "256 random crystals (8-64 atoms), seed 1+rank"
+    if name == "random64":  # small case for profiler captures (activations still exceed the L2)
+        return w.random_crystals(64, seed=1 + rank), "efs", "64 random crystals (8-64 atoms), seed 1+rank"
     if name == "perov512":
         return w.perovskites(512, seed=4 + rank), "efsm", "512 ABX3 2x2x2 perovskite cells (40 atoms)"
     if name == "cu32":
@@ -68,7 +70,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "500"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -170,6 +172,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="random256")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--keep", default="auto", choices=["auto", "on", "off"],
+                    help="keep sub-block internals for the backward pass (auto: when they fit in memory)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -193,6 +197,7 @@ def main():
     crystals, task, desc = make_workload(args.workload, rank)
     ck = random_checkpoint(dict(num_layers=NUM_LAYERS, reference_energy="mpa"), seed=0)
     model = MatRIS.from_dict(ck).to(device)
+    model.keep_activations = {"auto": None, "on": True, "off": False}[args.keep]
     cut, lcut = model.config["pairwise_cutoff"], model.config["three_body_cutoff"]
     n_atoms = sum(len(c.numbers) for c in crystals)
 
@@ -289,10 +294,14 @@ def main():
         peak_gb = float(peaks.get("hbm_gbs", 6650.0))
         src = "measured" if peaks else "fallback"
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
-        roofline = {"kernel": "k_gemm (mb_gemm)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
+        roofline = {"kernel": "k_gemm_tc (mb_gemm)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
                     "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": None, "peak_source": src + " bf16 sustained",
                     "launches": per["mb_gemm"][0], "avg_launch_ms": gemm_ms / per["mb_gemm"][0],
-                    "flops_per_step": gemm_flops, "note": "fp32 SIMT FMA core: tensor pipe idle"}
+                    "flops_per_step": gemm_flops, "tf32_issued_tflops": 3.0 * ach, "tf32_peak_measured_tflops": 1151.0,
+                    "frac_of_tf32_peak": 3.0 * ach / 1151.0,
+                    "note": "tcgen05 kind::tf32 with a 3-term operand split: 3 tensor FLOPs are issued per "
+                            "algorithmic FLOP; 1151 TFLOP/s = measured raw tcgen05.mma tf32 rate (64 cycles per "
+                            "M128 N128 K8 MMA x 148 SMs x 1.9 GHz)"}
         gms = sum(per[k][1] for k in per if k.startswith("mb_graph"))
         gbytes = 26.0 * g.n_edges + 20.0 * g.n_triplets + 16.0 * g.n_atoms
         roofline_graph = {"kernels": "mb_graph_* (3 phases)", "bound": "hbm", "achieved": gbytes / (gms * 1e-3) / 1e9,

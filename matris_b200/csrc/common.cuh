@@ -42,6 +42,14 @@ __device__ __forceinline__ float silu_grad_f(float x) {
   return s * (1.0f + x * (1.0f - s));
 }
 
+// Fast variants for the GEMM prologue / epilogue, where the transcendental cost is paid per operand element:
+// ex2.approx-based exponential and an approximate division (a few ulp each, far inside the fp32-tolerance gates).
+__device__ __forceinline__ float silu_fast_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_grad_fast_f(float x) {
+  const float s = __fdividef(1.0f, 1.0f + __expf(-x));
+  return s * (1.0f + x * (1.0f - s));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

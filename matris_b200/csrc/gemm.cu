@@ -450,7 +450,7 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
     uint32_t hi[32], lo[32];
     if (act) {  // branch once per chunk: the SiLU must not be evaluated (and discarded) on the plain path
 #pragma unroll
-      for (int q = 0; q < 32; ++q) x[q] = silu_f(x[q]);
+      for (int q = 0; q < 32; ++q) x[q] = silu_fast_f(x[q]);
     }
 #pragma unroll
     for (int q = 0; q < 32; ++q) {
@@ -516,10 +516,10 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
       float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
       if constexpr (decltype(has_gate)::value) {
         const float4 z = ld4(gate + gr * ld_gate + gcol);
-        o[0] *= silu_grad_f(z.x); o[1] *= silu_grad_f(z.y); o[2] *= silu_grad_f(z.z); o[3] *= silu_grad_f(z.w);
+        o[0] *= silu_grad_fast_f(z.x); o[1] *= silu_grad_fast_f(z.y); o[2] *= silu_grad_fast_f(z.z); o[3] *= silu_grad_fast_f(z.w);
       }
       if constexpr (decltype(has_act)::value) {
-        o[0] = silu_f(o[0]); o[1] = silu_f(o[1]); o[2] = silu_f(o[2]); o[3] = silu_f(o[3]);
+        o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
       }
       if constexpr (decltype(has_res)::value) {
         const float4 x = ld4(res + gr * ld_res + rcol);
