@@ -265,14 +265,14 @@ def main():
     d2h = sum(r.numel() * r.element_size() for r in res)
 
     # ---- one instrumented step: per-kernel device time (CUDA events on the launching stream)
-    roofline, roofline_graph, kernel_table = None, None, None
+    roofline, roofline_graph, kernel_table, gemm_shapes = None, None, None, None
     if rank == 0:
         torch.cuda.synchronize()
         _lib.profile = []
         step_resident()
         torch.cuda.synchronize()
         prof, _lib.profile = _lib.profile, None
-        per = {}
+        per, shapes = {}, {}
         gemm_flops, gemm_ms = 0.0, 0.0
         for name, a, b, meta in prof:
             ms = a.elapsed_time(b)
@@ -282,9 +282,15 @@ def main():
             if name == "mb_gemm":
                 gemm_flops += meta["flops"]
                 gemm_ms += ms
+                s = shapes.setdefault(f"rows={meta['rows']} K={meta['k']} N={meta['n']}", [0, 0.0, 0.0])
+                s[0] += 1
+                s[1] += ms
+                s[2] += meta["flops"]
         total_ms = sum(v[1] for v in per.values())
         kernel_table = {k: {"launches": v[0], "ms": round(v[1], 3), "share": round(v[1] / total_ms, 4)}
                         for k, v in sorted(per.items(), key=lambda kv: -kv[1][1])}
+        gemm_shapes = {k: {"launches": v[0], "ms": round(v[1], 3), "tflops": round(v[2] / (v[1] * 1e-3) / 1e12, 1)}
+                       for k, v in sorted(shapes.items(), key=lambda kv: -kv[1][1])[:10]}
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -332,6 +338,7 @@ def main():
                                                                "(each issues one or more kernels)",
                 "achieved_tflops_algorithmic": flops_per_eval(g, NUM_LAYERS) * world * args.steps / t_res / 1e12,
                 "roofline": roofline, "roofline_graph_build": roofline_graph, "kernels": kernel_table,
+                "gemm_shapes": gemm_shapes if rank == 0 else None,
                 "cpu_baseline": cpu_baseline}
         print(json.dumps(line), flush=True)
     if world > 1:
