@@ -30,6 +30,7 @@ extern "C" {
 #define MB_ERR_OVERFLOW 3  /* a count exceeds int32 or an image index exceeds +-127 */
 #define MB_ERR_UNPAIRED 4  /* a directed edge has no reverse edge (bond exactly on the cutoff) */
 #define MB_ERR_ISOLATED 5  /* an atom has no neighbour inside the cutoff */
+#define MB_ERR_TOO_LARGE 6 /* problem exceeds the fixed capacity of an allocation-free entry point */
 
 int mb_version(void);
 const char* mb_status_string(int status);
@@ -261,6 +262,37 @@ int mb_edge_geometry_bwd(int32_t n_atoms, int32_t n_struct, int64_t n_edges, con
                          const int32_t* rev, const float* vec, const float* len, const float* unit,
                          const float* dlen, const float* dunit, float* g_edge, float* dcart, float* virial_atom,
                          float* dstrain, void* stream);
+
+/* Allocation-free twin of mb_edge_geometry_bwd.  No counterpart in the reference: the reference reaches forces and
+ * stress through torch.autograd, which allocates freely.
+ *
+ * Who needs it: programs that bind this C ABI directly and own the whole device-memory budget themselves - a
+ * molecular-dynamics engine written in C, C++ or Fortran that carves all of its device memory up at start-up and
+ * then calls the force / virial reduction once per time step from its own integrator.  Such a caller has no
+ * caching allocator behind it; a cudaMalloc / cudaFree pair per step would synchronise the whole device each time
+ * (and can simply fail once the engine has handed out the rest of the memory), and inside its per-step callback it
+ * is often not allowed to allocate at all.  mb_edge_geometry_bwd needs two scratch arrays from the caller (the
+ * per-edge gradient and the per-atom virial partials); this entry takes them from a fixed array inside the library
+ * instead, so the caller passes inputs and outputs only.
+ *
+ * Limits and rules:
+ *  - at most MB_STATIC_MAX_EDGES directed edges and MB_STATIC_MAX_ATOMS atoms per call; larger problems are
+ *    rejected with MB_ERR_TOO_LARGE before anything is launched (use mb_edge_geometry_bwd for those);
+ *  - the array (3*MB_STATIC_MAX_EDGES + 9*MB_STATIC_MAX_ATOMS floats, about 7.1 MB) is part of the library image:
+ *    every GPU that loads the library holds it until the process exits;
+ *  - the first call on a device looks the array's device address up (with that device current) and remembers it;
+ *    make that first call during set-up, before any stream capture is started;
+ *  - it calls no cudaMalloc, cudaFree or other allocating routine;
+ *  - all calls share the one array and it keeps whatever the previous call left there.  Nothing has to start at
+ *    zero: each call overwrites every element it later reads.  Two calls that overlap on the GPU (different
+ *    streams, or different host threads without ordering) race on the array: serialise them.
+ * Same results as mb_edge_geometry_bwd (same kernels, same summation order). */
+#define MB_STATIC_MAX_EDGES (1 << 19)
+#define MB_STATIC_MAX_ATOMS (1 << 15)
+int mb_edge_geometry_bwd_static(int32_t n_atoms, int32_t n_struct, int64_t n_edges, const int32_t* edge_ptr,
+                                const int32_t* atom_ptr, const int32_t* rev, const float* vec, const float* len,
+                                const float* unit, const float* dlen, const float* dunit, float* dcart,
+                                float* dstrain, void* stream);
 
 /* Bessel * polynomial envelope, both cutoffs at once (matris/model/basis_function.py:8-50, 162-186):
  * per bond u with d = len[u2d[u]]: rbf_a[u,7] (cutoff ca, frequencies fa) and rbf_b[u,7] (cb, fb). */

@@ -89,6 +89,7 @@ _SIGNATURES = {
     "mb_segment_sum_scalar": [_i32, _vp, _vp, _vp, _vp],
     "mb_edge_geometry_fwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_edge_geometry_bwd": [_i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "mb_edge_geometry_bwd_static": [_i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_bessel_fwd": [_i32, _vp, _vp, _vp, _f32, _vp, _f32, _i32, _vp, _vp, _vp],
     "mb_bessel_bwd": [_i32, _vp, _vp, _vp, _f32, _vp, _f32, _i32, _vp, _vp, _vp, _vp],
     "mb_angle_basis_fwd": [_i64, _vp, _vp, _f32, _f32, _vp, _vp],

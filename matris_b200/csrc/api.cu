@@ -21,6 +21,7 @@ extern "C" const char* mb_status_string(int status) {
     case MB_ERR_OVERFLOW: return "count or periodic image index out of range";
     case MB_ERR_UNPAIRED: return "directed edge without a reverse edge";
     case MB_ERR_ISOLATED: return "isolated atom: no neighbour inside the cutoff";
+    case MB_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this allocation-free entry point";
     default: return "unknown status";
   }
 }

@@ -286,6 +286,58 @@ extern "C" int mb_edge_geometry_bwd(int32_t n_atoms, int32_t n_struct, int64_t n
   return MB_OK;
 }
 
+// ------------------------------------------------------------------ allocation-free force / virial reduction
+// Scratch for mb_edge_geometry_bwd_static: the per-edge gradient (3 floats per directed edge) followed by the
+// per-atom virial partials (9 floats per atom).  It is part of the library image, so every GPU that loads the
+// library holds these bytes until the process exits.
+static __device__ __align__(256) float g_static_scratch[3 * MB_STATIC_MAX_EDGES + 9 * MB_STATIC_MAX_ATOMS];
+
+// Host code must not hand `g_static_scratch` itself to a kernel: in host code that name is only a stand-in for
+// the symbol.  The device address is looked up once per device, with that device current.
+static float* static_scratch_address(int* status) {
+  constexpr int MAX_DEVICES = 64;
+  static float* address[MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    mb::set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice, "cudaGetDevice (static scratch)");
+    *status = MB_ERR_CUDA;
+    return nullptr;
+  }
+  if (!address[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      mb::set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(g_static_scratch)");
+      *status = MB_ERR_CUDA;
+      return nullptr;
+    }
+    address[dev] = p;
+  }
+  *status = MB_OK;
+  return address[dev];
+}
+
+extern "C" int mb_edge_geometry_bwd_static(int32_t n_atoms, int32_t n_struct, int64_t n_edges, const int32_t* edge_ptr,
+                                           const int32_t* atom_ptr, const int32_t* rev, const float* vec,
+                                           const float* len, const float* unit, const float* dlen, const float* dunit,
+                                           float* dcart, float* dstrain, void* stream) {
+  MB_REQUIRE(n_atoms > 0 && n_struct > 0 && n_edges > 0 && edge_ptr && atom_ptr && rev && vec && len && unit && dlen &&
+             dunit && dcart && dstrain);
+  if (n_edges > MB_STATIC_MAX_EDGES || n_atoms > MB_STATIC_MAX_ATOMS) return MB_ERR_TOO_LARGE;
+  int status = MB_OK;
+  float* scratch = static_scratch_address(&status);
+  if (!scratch) return status;
+  float* g_edge = scratch;                                  // [n_edges,3]  written in full by k_edge_grad before it is read
+  float* virial_atom = scratch + 3 * MB_STATIC_MAX_EDGES;   // [n_atoms,9]  written in full by k_atom_grad before it is read
+  k_edge_grad<<<grid1(n_edges), GEO_THREADS, 0, STREAM>>>(n_edges, len, unit, dlen, dunit, g_edge);
+  k_atom_grad<<<grid1((int64_t)n_atoms * 32), GEO_THREADS, 0, STREAM>>>(n_atoms, edge_ptr, rev, vec, g_edge, dcart,
+                                                                       virial_atom);
+  k_struct_virial<<<grid1((int64_t)n_struct * 32), GEO_THREADS, 0, STREAM>>>(n_struct, atom_ptr, virial_atom, dstrain);
+  MB_LAUNCH_CHECK("mb_edge_geometry_bwd_static");
+  return MB_OK;
+}
+
 extern "C" int mb_bessel_fwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* freq_a, float cut_a,
                              const float* freq_b, float cut_b, int32_t p, float* rbf_a, float* rbf_b, void* stream) {
   MB_REQUIRE(n_bonds >= 0 && u2d && len && freq_a && freq_b && rbf_a && rbf_b && p >= 1 && cut_a > 0 && cut_b > 0);
