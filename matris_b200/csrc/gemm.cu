@@ -182,14 +182,14 @@ static int gemm_validate(const mb_gemm_desc* desc) {
 //     256 TMEM columns per CTA (128 accumulator + 2 x (32 hi + 32 lo) A columns),
 //     two CTAs resident per SM.
 //   * Producer warp w owns rows 32w..32w+31 of the tile; thread t owns row t (= TMEM
-//     lane t).  The warp gathers its rows' 32-float K chunk with coalesced 128-byte
-//     row reads (through the optional index), transposes it through a swizzled
-//     shared-memory patch so that every thread holds its own row, applies the
-//     optional SiLU, splits into hi / lo and writes both with tcgen05.st into the A
-//     buffer of that chunk; the next chunk's loads are already in flight.
+//     lane t).  The warp gathers its rows' 32-float K chunk with cp.async (coalesced
+//     128-byte row reads through the optional index, three stages = two chunks in
+//     flight, no registers held) into a swizzled shared-memory patch, from which
+//     every thread reads its own row, applies the optional SiLU, splits into hi / lo
+//     and writes both with tcgen05.st into the A buffer of that chunk.
 //   * W tiles: hi / lo parts of the weights (split once by the caller: W_hi, W_lo)
 //     arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle, no cluster forms) into
-//     a 3-deep ring, two chunks ahead, completing on mbarrier transaction counts.
+//     a double buffer, completing on mbarrier transaction counts.
 //   * The control thread issues 12 tcgen05.mma per chunk (4 K steps x 3 split terms,
 //     A from TMEM, W from shared memory) and commits them to mbarriers that free the
 //     A buffer and the W slot.
@@ -207,15 +207,17 @@ namespace mb {
 constexpr int TC_THREADS = 160;                 // warps 0-3: producers + epilogue, warp 4: control
 constexpr int TC_BK = 32;                       // floats per K chunk = one 128-byte swizzle row
 constexpr int TC_TILE_BYTES = 128 * 128;        // 128 rows x 128 bytes
-constexpr int TC_W_SLOTS = 3;
+constexpr int TC_W_SLOTS = 2;
+constexpr int TC_A_STAGES = 3;                  // cp.async stages of the A gather, per producer warp
 constexpr int TC_STAGE_LD = 132;                // floats per staged output row (128 + 4 padding)
 constexpr int TC_RING_BYTES = TC_W_SLOTS * 2 * TC_TILE_BYTES;  // 96 KB, reused as the epilogue staging area
-constexpr int TC_XPOSE_BYTES = 4 * 32 * 128;    // per producer warp: 32 rows x 128 bytes, chunk-swizzled
+constexpr int TC_XPOSE_BYTES = 4 * TC_A_STAGES * 32 * 128;  // per producer warp and stage: 32 rows x 128 bytes, chunk-swizzled
 constexpr int TC_SMEM_BYTES = TC_RING_BYTES + TC_XPOSE_BYTES + 128 /*barriers, tmem slot*/;
 constexpr uint32_t TC_TMEM_COLS = 256;
 constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
-static_assert(128 * TC_STAGE_LD * 4 <= TC_RING_BYTES, "staging area must fit in the W ring");
+static_assert(128 * TC_STAGE_LD * 4 <= TC_RING_BYTES + TC_XPOSE_BYTES, "staging area must fit in ring + patches");
+static_assert(2 * (TC_SMEM_BYTES + 1024) <= 227 * 1024, "two CTAs per SM");
 
 struct alignas(64) TcMaps { CUtensorMap m[4][2]; };  // per column block: W_hi, W_lo
 
@@ -302,7 +304,7 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   const mb_colblock& cb = d.blk[jb];
   extern __shared__ __align__(1024) uint8_t smem[];  // W ring (1024-byte aligned tiles) | transpose patches | barriers
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_RING_BYTES + TC_XPOSE_BYTES);
-  // bars[0..1]: A buffer full (4 producer warps); bars[2..4]: W slot landed (TMA); bars[5..6]: MMAs of a chunk done
+  // bars[0..1]: A buffer full (4 producer warps); bars[2..3]: W slot landed (TMA); bars[5..6]: MMAs of a chunk done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_RING_BYTES + TC_XPOSE_BYTES + 64);
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
@@ -317,16 +319,76 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   const int64_t n_rows = d.n_rows;
   const int n_chunks = cb.n_src * (128 / TC_BK);
 
-  if (tid == 0) {
-    mbar_init(a_full, 4); mbar_init(a_full + 8, 4);
-    mbar_init(w_full, 1); mbar_init(w_full + 8, 1); mbar_init(w_full + 16, 1);
-    mbar_init(mma_done, 1); mbar_init(mma_done + 8, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
+  // Producer state: thread = row = TMEM lane; declared before the set-up barrier so that the first two chunks'
+  // gathers are already in flight while the control warp initialises barriers and allocates tensor memory.
+  const int lr = lane >> 3, lc = lane & 7;  // coalesced loads: 8 lanes read one row's 128 bytes, 4 rows per instruction
+  const uint32_t patch0 = smem_u32(smem + TC_RING_BYTES + (warp & 3) * (TC_A_STAGES * 32 * 128));
+  const float* a_ptr[8];
+  int32_t a_row[8];  // source row of each of this lane's 8 rows in the NEXT K segment (-1: past the end)
+  const int n_src = cb.n_src;
+  const float* const dummy_src = cb.src[0].ptr;  // valid address for zero-length copies of rows past the end
+  auto resolve_rows = [&](int seg) {  // issued well before the segment starts, so the index loads are hidden
+    const int32_t* idx = cb.src[seg].idx;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int64_t r = row0 + warp * 32 + lr + 4 * i;
+      a_row[i] = r < n_rows ? (idx ? idx[r] : (int32_t)(r - row0)) : -1;
+    }
+  };
+  // Asynchronous gather of chunk c: 8 lanes copy one row's 128 bytes (4 rows per instruction) straight into the
+  // chunk-swizzled patch of stage c % 3: row (lr + 4i), 16-byte chunk lc -> patch[row][lc ^ (row & 7)].
+  auto gather = [&](int c) {
+    if ((c & 3) == 0) {  // new 128-wide K segment: turn the resolved rows into pointers
+      const mb_src& s = cb.src[c >> 2];
+      const float* base = s.ptr + s.col + lc * 4;
+      const int64_t ld = s.ld;
+      const bool gathered = s.idx != nullptr;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        a_ptr[i] = a_row[i] < 0 ? nullptr : base + (gathered ? (int64_t)a_row[i] : row0 + a_row[i]) * ld;
+    }
+    if ((c & 3) == 1 && (c >> 2) + 1 < n_src) resolve_rows((c >> 2) + 1);
+    const int kofs = (c & 3) * TC_BK;
+    const uint32_t patch = patch0 + (uint32_t)(c % TC_A_STAGES) * (32 * 128);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = lr + 4 * i;
+      const uint32_t dst = patch + row * 128 + ((lc ^ (row & 7)) << 4);
+      const float* src = a_ptr[i] ? a_ptr[i] + kofs : dummy_src;
+      const int bytes = a_ptr[i] ? 16 : 0;  // 0: nothing is read, the 16 destination bytes are zero-filled
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const CUtensorMap* const map_hi = &maps.m[jb][0];
+  const CUtensorMap* const map_lo = &maps.m[jb][1];
+  auto load_w = [&](int c) {  // W_hi / W_lo rows 0..127, K columns 32c..32c+31 -> ring slot c & 1
+    const int slot = c % TC_W_SLOTS;
+    const uint32_t bar = w_full + 8 * slot, dst = ring + (uint32_t)slot * 2 * TC_TILE_BYTES;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
+    tma_load_2d(dst, map_hi, bar, c * TC_BK, 0);
+    tma_load_2d(dst + TC_TILE_BYTES, map_lo, bar, c * TC_BK, 0);
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_init(a_full, 4); mbar_init(a_full + 8, 4);
+      mbar_init(w_full, 1); mbar_init(w_full + 8, 1);
+      mbar_init(mma_done, 1); mbar_init(mma_done + 8, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      load_w(0);  // the first weight tiles travel while tensor memory is being allocated
+      if (n_chunks > 1) load_w(1);
+    }
+    __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  :: "r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else {
+    resolve_rows(0);
+    gather(0);
+    if (n_chunks > 1) gather(1); else asm volatile("cp.async.commit_group;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -336,27 +398,16 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   if (warp == 4) {
     // ------------------------------------------------------------ control thread: TMA + MMA issue
     if (lane == 0) {
-      const CUtensorMap* map_hi = &maps.m[jb][0];
-      const CUtensorMap* map_lo = &maps.m[jb][1];
-      auto load_w = [&](int c) {  // W_hi / W_lo rows 0..127, K columns 32c..32c+31 -> ring slot c % 3
-        const int slot = c % TC_W_SLOTS;
-        const uint32_t bar = w_full + 8 * slot, dst = ring + (uint32_t)slot * 2 * TC_TILE_BYTES;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
-        tma_load_2d(dst, map_hi, bar, c * TC_BK, 0);
-        tma_load_2d(dst + TC_TILE_BYTES, map_lo, bar, c * TC_BK, 0);
-      };
       bool alive = true;
       MB_TDECL;
-      load_w(0);
-      if (n_chunks > 1) load_w(1);
       for (int c = 0; c < n_chunks; ++c) {
-        const int ab = c & 1, slot = c % TC_W_SLOTS;
+        const int ab = c & 1;  // A buffer, W slot and completion barrier of this chunk
         if (alive) alive = mbar_wait(a_full + 8 * ab, (uint32_t)((c >> 1) & 1));
         MB_T(0);
-        if (alive) alive = mbar_wait(w_full + 8 * slot, (uint32_t)((c / TC_W_SLOTS) & 1));
+        if (alive) alive = mbar_wait(w_full + 8 * ab, (uint32_t)((c >> 1) & 1));
         MB_T(1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t wb = ring + (uint32_t)slot * 2 * TC_TILE_BYTES;
+        const uint32_t wb = ring + (uint32_t)ab * 2 * TC_TILE_BYTES;
         const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
         const uint32_t ta_hi = tmem_base + 128 + 64 * ab, ta_lo = ta_hi + 32;
 #ifndef MB_DBG_NO_MMA
@@ -371,8 +422,8 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                      :: "r"(mma_done + 8 * ab) : "memory");
         MB_T(2);
-        if (c + 2 < n_chunks) {  // slot (c+2) % 3 was read by chunk c-1: refill it once those MMAs are done
-          if (c > 0 && alive) alive = mbar_wait(mma_done + 8 * ((c - 1) & 1), (uint32_t)(((c - 1) >> 1) & 1));
+        if (c + 2 < n_chunks) {  // this chunk's W slot is refilled as soon as its MMAs have retired
+          if (alive) alive = mbar_wait(mma_done + 8 * ab, (uint32_t)((c >> 1) & 1));
           load_w(c + 2);
         }
         MB_T(3);
@@ -384,60 +435,21 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
 
   // -------------------------------------------------------------- producers: thread = row = TMEM lane
   const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const int lr = lane >> 3, lc = lane & 7;  // coalesced loads: 8 lanes read one row's 128 bytes, 4 rows per instruction
-  const uint32_t patch = smem_u32(smem + TC_RING_BYTES + warp * (32 * 128));
-  const float* a_ptr[8];
-  int32_t a_row[8];  // source row of each of this lane's 8 rows in the NEXT K segment (-1: past the end)
-  int a_act = 0;
-  float4 a_reg[8];
-  auto resolve_rows = [&](int seg) {  // issued a chunk before the segment starts, so the index loads are hidden
-    const int32_t* idx = cb.src[seg].idx;
+  int act_of_seg[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int64_t r = row0 + warp * 32 + lr + 4 * i;
-      a_row[i] = r < n_rows ? (idx ? idx[r] : (int32_t)(r - row0)) : -1;
-    }
-  };
-  auto prefetch = [&](int c) {
-    if ((c & 3) == 0) {  // new 128-wide K segment: turn the resolved rows into pointers
-      const mb_src& s = cb.src[c >> 2];
-      a_act = s.act;
-      const float* base = s.ptr + s.col + lc * 4;
-      const int64_t ld = s.ld;
-      const bool gathered = s.idx != nullptr;
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        a_ptr[i] = a_row[i] < 0 ? nullptr : base + (gathered ? (int64_t)a_row[i] : row0 + a_row[i]) * ld;
-    }
-    if ((c & 3) == 2 && (c >> 2) + 1 < cb.n_src) resolve_rows((c >> 2) + 1);
-    const int kofs = (c & 3) * TC_BK;
-#pragma unroll
-#ifdef MB_DBG_NO_LOAD
-    for (int i = 0; i < 8; ++i) a_reg[i] = make_float4(1.f, 2.f, 3.f, (float)kofs);
-#else
-    for (int i = 0; i < 8; ++i) a_reg[i] = a_ptr[i] ? ld4(a_ptr[i] + kofs) : make_float4(0.f, 0.f, 0.f, 0.f);
-#endif
-  };
+  for (int sgm = 0; sgm < 4; ++sgm) act_of_seg[sgm] = sgm < cb.n_src ? cb.src[sgm].act : 0;
 
   bool alive = true;
   MB_TDECL;
-  resolve_rows(0);
-  prefetch(0);
   MB_T(0);
   for (int c = 0; c < n_chunks; ++c) {
     const int ab = c & 1;
-    // transpose: row (lr + 4i), 16-byte chunk lc -> patch[row][chunk ^ (row & 7)]; then every thread reads its own row
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int row = lr + 4 * i;
-      const uint32_t addr = patch + row * 128 + ((lc ^ (row & 7)) << 4);
-      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "f"(a_reg[i].x), "f"(a_reg[i].y),
-                   "f"(a_reg[i].z), "f"(a_reg[i].w) : "memory");
-    }
-    const int act = a_act;
-    if (c + 1 < n_chunks) prefetch(c + 1);  // a_reg was consumed by the stores above: start the next chunk's loads now
+    // stage (c+2) % 3 was last read for chunk c-1, and the __syncwarp that closed that chunk orders those reads
+    if (c + 2 < n_chunks) gather(c + 2); else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 2;" ::: "memory");  // chunk c's copies of this lane have landed
+    __syncwarp();                                          // ... and so have the other lanes'
     MB_T(1);
-    __syncwarp();
+    const uint32_t patch = patch0 + (uint32_t)(c % TC_A_STAGES) * (32 * 128);
     float x[32];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -445,10 +457,9 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
       asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]), "=f"(x[4 * j + 2]),
                    "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
     }
-    __syncwarp();
     MB_T(2);
     uint32_t hi[32], lo[32];
-    if (act) {  // branch once per chunk: the SiLU must not be evaluated (and discarded) on the plain path
+    if (act_of_seg[c >> 2]) {  // branch once per chunk: the SiLU must not be evaluated (and discarded) on the plain path
 #pragma unroll
       for (int q = 0; q < 32; ++q) x[q] = silu_fast_f(x[q]);
     }
@@ -466,7 +477,7 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
     MB_TMEM_ST32(ta + 32, lo);
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncwarp();
+    __syncwarp();  // all lanes have read their patch rows: the stage may be overwritten two chunks from now
     if (lane == 0) mbar_arrive(a_full + 8 * ab);
     MB_T(4);
   }
@@ -508,35 +519,51 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   if (res && cb.res_w) resw4 = ld4(cb.res_w + col);
   if (!alive) return;
   const int rows_here = (int)((n_rows - row0) < 128 ? (n_rows - row0) : 128);
+  // Rows are finished eight at a time per warp: all global reads of a batch (gate, residual, scatter index, old
+  // value) are issued before the first dependent use, so eight rows' latencies overlap instead of adding up.
+  constexpr int RB = 8;
   auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
-#pragma unroll 4
-    for (int rr = warp; rr < rows_here; rr += 4) {
-      const int64_t gr = row0 + rr;
-      const float4 a = *reinterpret_cast<const float4*>(stage + rr * TC_STAGE_LD + col);
-      float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
-      if constexpr (decltype(has_gate)::value) {
-        const float4 z = ld4(gate + gr * ld_gate + gcol);
-        o[0] *= silu_grad_fast_f(z.x); o[1] *= silu_grad_fast_f(z.y); o[2] *= silu_grad_fast_f(z.z); o[3] *= silu_grad_fast_f(z.w);
+#pragma unroll 1
+    for (int r0 = warp; r0 < rows_here; r0 += 4 * RB) {
+      float4 z[RB], x[RB];
+      int64_t dr[RB];
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int rr = r0 + 4 * i;
+        const bool valid = rr < rows_here;
+        const int64_t gr = row0 + (valid ? rr : r0);
+        if constexpr (decltype(has_gate)::value) z[i] = ld4(gate + gr * ld_gate + gcol);
+        if constexpr (decltype(has_res)::value) x[i] = ld4(res + gr * ld_res + rcol);
+        dr[i] = out_idx ? (int64_t)out_idx[gr] : gr;
       }
-      if constexpr (decltype(has_act)::value) {
-        o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
-      }
-      if constexpr (decltype(has_res)::value) {
-        const float4 x = ld4(res + gr * ld_res + rcol);
-        o[0] = fmaf(resw4.x, x.x, o[0]); o[1] = fmaf(resw4.y, x.y, o[1]);
-        o[2] = fmaf(resw4.z, x.z, o[2]); o[3] = fmaf(resw4.w, x.w, o[3]);
-      }
-      const float4 ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
-      const int64_t dr = out_idx ? (int64_t)out_idx[gr] : gr;
-      float* dst = out + dr * ld_out + ocol;
-      if (mode == MB_OUT_STORE) {
-        *reinterpret_cast<float4*>(dst) = ov;
-      } else if (mode == MB_OUT_ADD) {
-        float4 p = ld4(dst);
-        p.x += ov.x; p.y += ov.y; p.z += ov.z; p.w += ov.w;
-        *reinterpret_cast<float4*>(dst) = p;
-      } else {
-        atomicAdd(reinterpret_cast<float4*>(dst), ov);
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int rr = r0 + 4 * i;
+        if (rr >= rows_here) break;
+        const float4 a = *reinterpret_cast<const float4*>(stage + rr * TC_STAGE_LD + col);
+        float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
+        if constexpr (decltype(has_gate)::value) {
+          o[0] *= silu_grad_fast_f(z[i].x); o[1] *= silu_grad_fast_f(z[i].y);
+          o[2] *= silu_grad_fast_f(z[i].z); o[3] *= silu_grad_fast_f(z[i].w);
+        }
+        if constexpr (decltype(has_act)::value) {
+          o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
+        }
+        if constexpr (decltype(has_res)::value) {
+          o[0] = fmaf(resw4.x, x[i].x, o[0]); o[1] = fmaf(resw4.y, x[i].y, o[1]);
+          o[2] = fmaf(resw4.z, x[i].z, o[2]); o[3] = fmaf(resw4.w, x[i].w, o[3]);
+        }
+        const float4 ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
+        float* dst = out + dr[i] * ld_out + ocol;
+        if (mode == MB_OUT_STORE) {
+          *reinterpret_cast<float4*>(dst) = ov;
+        } else if (mode == MB_OUT_ADD) {
+          float4 p = ld4(dst);
+          p.x += ov.x; p.y += ov.y; p.z += ov.z; p.w += ov.w;
+          *reinterpret_cast<float4*>(dst) = p;
+        } else {
+          atomicAdd(reinterpret_cast<float4*>(dst), ov);
+        }
       }
     }
   };
