@@ -215,7 +215,8 @@ constexpr int TC_XPOSE_BYTES = 4 * TC_A_STAGES * 32 * 128;  // per producer warp
 constexpr int TC_SMEM_BYTES = TC_RING_BYTES + TC_XPOSE_BYTES + 128 /*barriers, tmem slot*/;
 constexpr uint32_t TC_TMEM_COLS = 256;
 constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;     // polls per wait; each may park for up to TC_WAIT_HINT_NS
+constexpr uint32_t TC_WAIT_HINT_NS = 4000;
 static_assert(128 * TC_STAGE_LD * 4 <= TC_RING_BYTES + TC_XPOSE_BYTES, "staging area must fit in ring + patches");
 static_assert(2 * (TC_SMEM_BYTES + 1024) <= 227 * 1024, "two CTAs per SM");
 
@@ -224,11 +225,13 @@ struct alignas(64) TcMaps { CUtensorMap m[4][2]; };  // per column block: W_hi, 
 __device__ int g_gemm_status = 0;  // bit 0: an mbarrier wait expired
 
 #ifdef MB_GEMM_TIMING  // diagnostic build only: per-phase clock64() totals of thread 0 (producer) and the control thread
-__device__ unsigned long long g_gemm_timing[16];
-#define MB_TDECL long long t_last = clock64(); long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+__device__ unsigned long long g_gemm_timing[32];
+#define MB_TSTART const long long t_kernel0 = clock64()
+#define MB_TDECL long long t_last = t_kernel0; long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define MB_T(slot) do { const long long _n = clock64(); tacc[slot] += _n - t_last; t_last = _n; } while (0)
 #define MB_TFLUSH(base, n) do { for (int _k = 0; _k < (n); ++_k) atomicAdd(&g_gemm_timing[(base) + _k], (unsigned long long)tacc[_k]); } while (0)
 #else
+#define MB_TSTART
 #define MB_TDECL
 #define MB_T(slot)
 #define MB_TFLUSH(base, n)
@@ -236,11 +239,17 @@ __device__ unsigned long long g_gemm_timing[16];
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Bounded wait.  The suspend-time hint lets the hardware park the thread until the phase completes (or the hint runs
+// out) instead of re-issuing the poll: waiting warps then leave the issue slots to the warps that convert and store.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  // fast path: a phase that has already completed is seen by one non-blocking test
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  if (ok) return true;
   for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
     if (ok) return true;
   }
   atomicOr(&g_gemm_status, 1);
@@ -287,6 +296,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                   "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]),           \
                   "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory")
 
+#define MB_TMEM_ST16(taddr, v)                                                                                   \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                   \
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                        \
+               :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),      \
+                  "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),  \
+                  "r"(v[15]) : "memory")
+
 #define MB_TMEM_LD32(taddr, v)                                                                                   \
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                         \
                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                         \
@@ -299,6 +315,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 
 __global__ void __launch_bounds__(TC_THREADS, 2)
 k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps maps) {
+  MB_TSTART;
   const int jb = (int)(blockIdx.x % (unsigned)d.n_blocks);  // column block (fastest: the blocks of a row tile share A in L2)
   const int64_t row0 = (int64_t)(blockIdx.x / (unsigned)d.n_blocks) * 128;
   const mb_colblock& cb = d.blk[jb];
@@ -579,7 +596,9 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
 #endif
 }
 
-static int g_gemm_mode = 0;  // 0: tcgen05 3xTF32, 1: fp32 SIMT
+#include "gemm_persistent.cuh"
+
+static int g_gemm_mode = 0;  // 0: persistent tcgen05 3xTF32, 1: fp32 SIMT, 2: one-tile-per-CTA tcgen05 3xTF32
 
 // TMA descriptor of a [128, k] float32 weight block (row stride ldw), box 128 rows x 32 columns, 128-byte swizzle.
 // Encoding depends only on (address, stride, k), so descriptors are cached per host thread.
@@ -633,17 +652,25 @@ static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out) {
 }  // namespace mb
 
 extern "C" int mb_set_gemm_mode(int mode) {
-  if (mode != 0 && mode != 1) return MB_ERR_INVALID;
+  if (mode < 0 || mode > 2) return MB_ERR_INVALID;
   mb::g_gemm_mode = mode;
   return MB_OK;
 }
 
 #ifdef MB_GEMM_TIMING
 extern "C" int mb_gemm_read_timing(unsigned long long* host16) {
-  unsigned long long zero[16] = {0};
+  unsigned long long zero[32] = {0};
   MB_CUDA_CHECK(cudaDeviceSynchronize());
   MB_CUDA_CHECK(cudaMemcpyFromSymbol(host16, mb::g_gemm_timing, sizeof(zero)));
   MB_CUDA_CHECK(cudaMemcpyToSymbol(mb::g_gemm_timing, zero, sizeof(zero)));
+  return MB_OK;
+}
+#endif
+
+#ifdef MB_GEMM_TRACE
+extern "C" int mb_gemm_read_trace(long long* host) {
+  MB_CUDA_CHECK(cudaDeviceSynchronize());
+  MB_CUDA_CHECK(cudaMemcpyFromSymbol(host, mb::g_trace, sizeof(long long) * 8 * 128));
   return MB_OK;
 }
 #endif
@@ -668,8 +695,13 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
     mb::k_gemm<<<grid, mb::GEMM_THREADS, 0, (cudaStream_t)stream_>>>(*desc);
   } else {
     static bool configured = false;  // per process; the attribute is per device function and context
+    static int n_sm = 0;
     if (!configured) {
       MB_CUDA_CHECK(cudaFuncSetAttribute(mb::k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, mb::TC_SMEM_BYTES));
+      MB_CUDA_CHECK(cudaFuncSetAttribute(mb::k_gemm_ps, cudaFuncAttributeMaxDynamicSharedMemorySize, mb::PS_SMEM_BYTES));
+      int dev = 0;
+      MB_CUDA_CHECK(cudaGetDevice(&dev));
+      MB_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
       configured = true;
     }
     mb::TcMaps maps;
@@ -681,7 +713,13 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
       rc = mb::weight_map(cb.W_lo, cb.ldw, 128 * cb.n_src, &maps.m[j][1]);
       if (rc) return rc;
     }
-    mb::k_gemm_tc<<<(unsigned)(gx * desc->n_blocks), mb::TC_THREADS, mb::TC_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
+    const long long n_tiles = gx * desc->n_blocks;
+    if (mb::g_gemm_mode == 0) {
+      const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
+      mb::k_gemm_ps<<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
+    } else {
+      mb::k_gemm_tc<<<(unsigned)n_tiles, mb::TC_THREADS, mb::TC_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
+    }
   }
   MB_LAUNCH_CHECK("k_gemm");
   return MB_OK;

@@ -1,0 +1,442 @@
+// Persistent tcgen05 GEMM (included by gemm.cu inside namespace mb, after the tcgen05 / TMA / mbarrier helpers).
+//
+// Same contract and arithmetic as k_gemm_tc (gathered, K-concatenated A operand; 3xTF32 with fp32 accumulation in
+// tensor memory; bias / SiLU' gate / SiLU / residual / scale epilogue with store, accumulate or atomic scatter), but
+// one CTA per SM walks over many 128x128 output tiles, so that the three stages of a tile run concurrently on
+// DIFFERENT tiles instead of one after the other:
+//
+//   warps 0-7   producers.  Warp w owns rows 32(w&3).. of the tile (= its TMEM lane quarter); warps 0-3 take the even
+//               32-float K chunks, warps 4-7 the odd ones.  A chunk is gathered with cp.async (coalesced 128-byte row
+//               reads through the optional index, two stages per warp) into a swizzled shared-memory patch, read back
+//               one row per thread, passed through the optional SiLU, split into tf32 hi / lo and written with
+//               tcgen05.st into one of FOUR A buffers in tensor memory.
+//   warp 13     TMA (one thread): streams W_hi / W_lo tiles into a 3-slot ring, up to three chunks ahead and across
+//               tile boundaries.
+//   warp 12     MMA (one thread): issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor
+//               memory) into one of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot
+//               free) and, after a tile's last chunk, "accumulator full".
+//   warps 8-11  epilogue.  Warp e drains rows 32e.. of the finished accumulator (tcgen05.ld) into its own swizzled
+//               staging patch, releases the accumulator at once, and then finishes its 32 rows with fully coalesced
+//               512-byte row accesses while the tensor cores already work on the next tile.
+//
+// Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64b (hi | lo).
+// Shared memory: W ring 96 KB | producer patches 64 KB | epilogue staging 64 KB | barriers | descriptor copy.
+// Every mbarrier wait is bounded; on expiry a status word is set, the role stops waiting and runs to the common exit,
+// where tensor memory is released.
+
+#ifdef MB_GEMM_TRACE
+__device__ long long g_trace[8][128];
+#define MB_TRACE(row, g) do { if (blockIdx.x == 0 && (g) >= 200 && (g) < 328) g_trace[row][(g) - 200] = clock64(); } while (0)
+#else
+#define MB_TRACE(row, g)
+#endif
+constexpr int PS_THREADS = 448;
+constexpr int PS_W_SLOTS = 3;
+constexpr int PS_RING_BYTES = PS_W_SLOTS * 2 * TC_TILE_BYTES;
+constexpr int PS_PATCH_BYTES = 8 * 2 * 32 * 128;
+constexpr int PS_STAGE_BYTES = 4 * 32 * 512;
+constexpr int PS_BAR_OFF = PS_RING_BYTES + PS_PATCH_BYTES + PS_STAGE_BYTES;
+constexpr int PS_DESC_OFF = PS_BAR_OFF + 256;
+constexpr int PS_SMEM_BYTES = PS_DESC_OFF + (int)((sizeof(mb_gemm_desc) + 15) / 16 * 16);
+constexpr uint32_t PS_TMEM_COLS = 512;
+static_assert(PS_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
+
+__global__ void __launch_bounds__(PS_THREADS, 1)
+k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ TcMaps maps) {
+  MB_TSTART;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PS_BAR_OFF);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + PS_BAR_OFF + 128);
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
+    return;
+  }
+  // barriers: a_full[4] (count 4 warps) | chunk_done[4] | w_full[3] | d_full[2] | d_free[2] (count 4 warps)
+  const uint32_t a_full = smem_u32(bars), chunk_done = smem_u32(bars + 4), w_full = smem_u32(bars + 8);
+  const uint32_t d_full = smem_u32(bars + 11), d_free = smem_u32(bars + 13);
+  const uint32_t ring = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // The descriptor is indexed dynamically (column block, K segment) all through the kernel.  From kernel-parameter
+  // memory every such read is a round trip through the memory system; from this shared-memory copy it is not.
+  const mb_gemm_desc& d = *reinterpret_cast<const mb_gemm_desc*>(smem + PS_DESC_OFF);
+  {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(&d_param);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(smem + PS_DESC_OFF);
+    for (int i = tid; i < (int)(sizeof(mb_gemm_desc) / 4); i += PS_THREADS) dst[i] = src[i];
+  }
+  __syncthreads();
+  const int64_t n_rows = d.n_rows;
+  const int n_blocks = d.n_blocks;
+  // Tiles are numbered row tile * n_blocks + column block; this CTA takes tiles blockIdx.x, + gridDim.x, ...  Every
+  // role walks that sequence as a (row tile, column block) pair advanced by (step_rt, step_jb): no division in loops.
+  const int n_row_tiles = (int)((n_rows + 127) >> 7);
+  const int first_rt = (int)(blockIdx.x / (unsigned)n_blocks), first_jb = (int)(blockIdx.x % (unsigned)n_blocks);
+  const int step_rt = (int)(gridDim.x / (unsigned)n_blocks), step_jb = (int)(gridDim.x % (unsigned)n_blocks);
+  auto next_tile = [&](int& rt, int& jb) {
+    jb += step_jb;
+    rt += step_rt;
+    if (jb >= n_blocks) { jb -= n_blocks; ++rt; }
+  };
+
+  // ---- producer state
+  const int par = (warp >> 2) & 1, quarter = warp & 3;
+  const int lr = lane >> 3, lc = lane & 7;  // 8 lanes read one row's 128 bytes, 4 rows per instruction
+  // row (lr + 4i), 16-byte chunk lc -> patch[row][lc ^ (row & 7)]; (row & 7) is lr for even i and lr + 4 for odd i
+  const uint32_t patch0 = smem_u32(smem + PS_RING_BYTES + (warp & 7) * (2 * 32 * 128));
+  const uint32_t dst_even = patch0 + lr * 128 + ((lc ^ lr) << 4), dst_odd = patch0 + lr * 128 + ((lc ^ (lr | 4)) << 4);
+  const float* a_ptr[8];  // this lane's 8 row pointers in the current K segment, at this warp's first chunk
+  int32_t a_row[8];       // source rows of the NEXT segment (looked up one chunk ahead, so the index loads are hidden)
+  int g_rt = first_rt, g_jb = first_jb;  // gather iterator: the next chunk this warp will request
+  int g_seg = 0, g_nsrc = d.blk[first_jb].n_src, g_cnt = 0;
+  bool g_second = false;
+  // Rows past the end of the matrix are clamped to the last row: their products land in accumulator rows that the
+  // epilogue never writes, and every copy stays a plain 16-byte one.
+  auto resolve_rows = [&](int rt, int jb, int seg) {
+    const int64_t row0 = (int64_t)rt * 128;
+    const int32_t* idx = d.blk[jb].src[seg].idx;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int64_t r = row0 + quarter * 32 + lr + 4 * i;
+      r = r < n_rows ? r : n_rows - 1;
+      a_row[i] = idx ? idx[r] : (int32_t)(r - row0);
+    }
+  };
+#define MB_CP16(dst, off, src, soff)                                                                    \
+  asm volatile("cp.async.cg.shared.global [%0 + %1], [%2 + %3], 16;" :: "r"(dst), "n"(off), "l"(src), "n"(soff) : "memory")
+  auto gather_next = [&]() {
+    if (g_rt >= n_row_tiles) {
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
+    const uint32_t st = (uint32_t)(g_cnt & 1) * (32 * 128);
+    const uint32_t de = dst_even + st, dq = dst_odd + st;
+    if (!g_second) {  // first of this warp's two chunks in the segment: rows -> pointers (chunk par of the segment)
+      const mb_src& s = d.blk[g_jb].src[g_seg];
+      const float* base = s.ptr + s.col + lc * 4 + par * TC_BK;
+      const int64_t ld = s.ld;
+      const int64_t row0 = s.idx ? 0 : (int64_t)g_rt * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a_ptr[i] = base + (row0 + a_row[i]) * ld;
+#ifndef MB_DBG_NO_A
+      MB_CP16(de, 0, a_ptr[0], 0);    MB_CP16(dq, 512, a_ptr[1], 0);  MB_CP16(de, 1024, a_ptr[2], 0); MB_CP16(dq, 1536, a_ptr[3], 0);
+      MB_CP16(de, 2048, a_ptr[4], 0); MB_CP16(dq, 2560, a_ptr[5], 0); MB_CP16(de, 3072, a_ptr[6], 0); MB_CP16(dq, 3584, a_ptr[7], 0);
+#endif
+    } else {          // chunk par + 2 of the segment: 64 floats further along every row
+#ifndef MB_DBG_NO_A
+      MB_CP16(de, 0, a_ptr[0], 256);    MB_CP16(dq, 512, a_ptr[1], 256);  MB_CP16(de, 1024, a_ptr[2], 256); MB_CP16(dq, 1536, a_ptr[3], 256);
+      MB_CP16(de, 2048, a_ptr[4], 256); MB_CP16(dq, 2560, a_ptr[5], 256); MB_CP16(de, 3072, a_ptr[6], 256); MB_CP16(dq, 3584, a_ptr[7], 256);
+#endif
+      if (++g_seg == g_nsrc) {  // on to the next tile
+        g_seg = 0;
+        next_tile(g_rt, g_jb);
+        if (g_rt < n_row_tiles) g_nsrc = d.blk[g_jb].n_src;
+      }
+      if (g_rt < n_row_tiles) resolve_rows(g_rt, g_jb, g_seg);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    ++g_cnt;
+    g_second = !g_second;
+  };
+
+  if (warp == 12) {
+    if (lane == 0) {
+      for (int b = 0; b < 4; ++b) { mbar_init(a_full + 8 * b, 4); mbar_init(chunk_done + 8 * b, 1); }
+      for (int b = 0; b < 3; ++b) mbar_init(w_full + 8 * b, 1);
+      for (int b = 0; b < 2; ++b) { mbar_init(d_full + 8 * b, 1); mbar_init(d_free + 8 * b, 4); }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(tmem_slot)), "r"(PS_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else if (warp < 8) {
+    resolve_rows(first_rt, first_jb, 0);
+    gather_next();
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 12) {
+    // ---------------------------------------------------------------- control thread: TMA + MMA issue
+    if (lane == 0) {
+      bool alive = true;
+      MB_TDECL;
+      uint32_t g = 0;  // chunks issued so far (all tiles); a multiple of 4 at every tile start
+      int k = 0;
+      for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
+        const int acc = k & 1;
+        const uint32_t d_tmem = tmem_base + 128u * acc;
+        const int nch = d.blk[jb].n_src * 4;
+        for (int c = 0; c < nch; ++c, ++g) {
+          const uint32_t ab = g & 3, slot = g % PS_W_SLOTS;
+          MB_TRACE(0, g);
+          if (alive) alive = mbar_wait(a_full + 8 * ab, (g >> 2) & 1);
+          MB_TRACE(1, g);
+          MB_T(0);
+#ifdef MB_DBG_NO_W
+          if (g < PS_W_SLOTS)
+#endif
+          if (alive) alive = mbar_wait(w_full + 8 * slot, (g / PS_W_SLOTS) & 1);
+          MB_T(1);
+          if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
+          MB_T(2);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t wb = ring + slot * 2 * TC_TILE_BYTES;
+          const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
+          const uint32_t ta_hi = tmem_base + 256 + 64 * ab, ta_lo = ta_hi + 32;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
+            const uint64_t adv = (uint64_t)(2 * kk);
+#ifdef MB_DBG_NO_MMA
+            continue;
+#endif
+#ifndef MB_DBG_ONE_MMA
+            umma_tf32_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (c > 0 || kk > 0) ? 1u : 0u);
+            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
+#endif
+            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                       :: "r"(chunk_done + 8 * ab) : "memory");
+          if (c == nch - 1)
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(d_full + 8 * acc) : "memory");
+          MB_TRACE(2, g);
+          MB_T(3);
+        }
+      }
+      MB_TFLUSH(8, 4);
+    }
+  } else if (warp == 13) {
+    // ---------------------------------------------------------------- TMA thread: W_hi / W_lo tiles, up to 3 chunks ahead
+    if (lane == 0) {
+      bool alive = true;
+      uint32_t w_g = 0;
+      for (int rt = first_rt, jb = first_jb; rt < n_row_tiles && alive; next_tile(rt, jb)) {
+        const int nch = d.blk[jb].n_src * 4;
+        for (int c = 0; c < nch && alive; ++c, ++w_g) {
+          const uint32_t slot = w_g % PS_W_SLOTS;
+          // the slot was last read by chunk w_g - 3
+          if (w_g >= PS_W_SLOTS) alive = mbar_wait(chunk_done + 8 * ((w_g - PS_W_SLOTS) & 3), ((w_g - PS_W_SLOTS) >> 2) & 1);
+          if (!alive) break;
+#ifdef MB_DBG_NO_W
+          if (w_g >= PS_W_SLOTS) continue;
+#endif
+          const uint32_t bar = w_full + 8 * slot, dst = ring + slot * 2 * TC_TILE_BYTES;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
+          tma_load_2d(dst, &maps.m[jb][0], bar, c * TC_BK, 0);
+          tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, c * TC_BK, 0);
+        }
+      }
+      if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
+        for (uint32_t i = w_g >= PS_W_SLOTS ? w_g - PS_W_SLOTS : 0; i < w_g; ++i)
+          mbar_wait(w_full + 8 * (i % PS_W_SLOTS), (i / PS_W_SLOTS) & 1);
+      }
+    }
+  } else if (warp >= 8) {
+    // ---------------------------------------------------------------- epilogue warps
+    const int e = warp - 8;  // TMEM lane quarter and row quarter of the tile
+    uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 512);
+    const uint32_t stage_u = smem_u32(stage);
+    const uint32_t lane_base = tmem_base + ((uint32_t)(e * 32) << 16);
+    const int col = lane * 4;
+    bool alive = true;
+    MB_TDECL;
+    int k = 0;
+    for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
+      const int acc = k & 1;
+      const int64_t row0 = (int64_t)rt * 128 + e * 32;  // first row of this warp
+      const mb_colblock& cb = d.blk[jb];
+      const float* const gate = cb.gate;
+      const float* const res = cb.res;
+      const int32_t* const out_idx = cb.out_idx;
+      float* const out = cb.out;
+      const int64_t ld_gate = cb.ld_gate, ld_res = cb.ld_res, ld_out = cb.ld_out;
+      const int gcol = cb.col_gate + col, rcol = cb.col_res + col, ocol = cb.col_out + col;
+      const int mode = cb.mode, out_act = cb.out_act;
+      const float sc = cb.out_scale;
+      float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), resw4 = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (cb.bias) bias4 = ld4(cb.bias + col);
+      if (res && cb.res_w) resw4 = ld4(cb.res_w + col);
+      const int64_t left = n_rows - row0;
+      const int rows_here = left >= 32 ? 32 : (left > 0 ? (int)left : 0);
+      // the rows this warp will read in the epilogue are pulled into L2 while the tile is still being multiplied
+      if (gate || res) {
+        const int r = lane >> 2, part = lane & 3;  // 8 rows x four 128-byte lines per pass
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const int rr = p * 8 + r;
+          if (rr < rows_here) {
+            if (gate) asm volatile("prefetch.global.L2 [%0];" :: "l"(gate + (row0 + rr) * ld_gate + cb.col_gate + part * 32));
+            if (res) asm volatile("prefetch.global.L2 [%0];" :: "l"(res + (row0 + rr) * ld_res + cb.col_res + part * 32));
+          }
+        }
+      }
+      if (alive) alive = mbar_wait(d_full + 8 * acc, (uint32_t)((k >> 1) & 1));
+      alive = __all_sync(0xffffffffu, alive);
+      MB_T(0);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // (1) accumulator row (thread = row) -> staging; 16-byte chunk ch of row r sits at position ch ^ r
+#pragma unroll 1
+      for (int cg = 0; cg < 4; ++cg) {
+        uint32_t v[32];
+        MB_TMEM_LD32(lane_base + 128u * acc + (uint32_t)(cg * 32), v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t addr = stage_u + lane * 512 + (((cg * 8 + q) ^ lane) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                       :: "r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3]) : "memory");
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the tensor cores may overwrite this accumulator now
+      MB_T(1);
+      if (!alive) continue;
+      // (2) rows in batches of eight: all global reads of a batch are issued before their first use
+      constexpr int RB = 8;
+      const float* const gate0 = gate ? gate + row0 * ld_gate + gcol : nullptr;
+      const float* const res0 = res ? res + row0 * ld_res + rcol : nullptr;
+      float* const out0 = out + (out_idx ? 0 : row0 * ld_out) + ocol;
+      const float4 bsc = make_float4(bias4.x * sc, bias4.y * sc, bias4.z * sc, bias4.w * sc);
+      auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
+        constexpr bool plain = !decltype(has_gate)::value && !decltype(has_act)::value && !decltype(has_res)::value;
+#pragma unroll 1
+        for (int r0 = 0; r0 < rows_here; r0 += RB) {
+          float4 z[RB], x[RB];
+          int32_t dr[RB];
+#pragma unroll
+          for (int i = 0; i < RB; ++i) {
+            const int rr = r0 + i < rows_here ? r0 + i : r0;
+            if constexpr (decltype(has_gate)::value) z[i] = ld4(gate0 + rr * ld_gate);
+            if constexpr (decltype(has_res)::value) x[i] = ld4(res0 + rr * ld_res);
+            dr[i] = out_idx ? out_idx[row0 + rr] : rr;
+          }
+#pragma unroll
+          for (int i = 0; i < RB; ++i) {
+            const int rr = r0 + i;
+            float4 a;
+            const uint32_t addr = stage_u + rr * 512 + ((lane ^ rr) << 4);
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "r"(addr) : "memory");
+            float4 ov;
+            if constexpr (plain) {
+              ov = make_float4(fmaf(a.x, sc, bsc.x), fmaf(a.y, sc, bsc.y), fmaf(a.z, sc, bsc.z), fmaf(a.w, sc, bsc.w));
+            } else {
+              float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
+              if constexpr (decltype(has_gate)::value) {
+                o[0] *= silu_grad_fast_f(z[i].x); o[1] *= silu_grad_fast_f(z[i].y);
+                o[2] *= silu_grad_fast_f(z[i].z); o[3] *= silu_grad_fast_f(z[i].w);
+              }
+              if constexpr (decltype(has_act)::value) {
+                o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
+              }
+              if constexpr (decltype(has_res)::value) {
+                o[0] = fmaf(resw4.x, x[i].x, o[0]); o[1] = fmaf(resw4.y, x[i].y, o[1]);
+                o[2] = fmaf(resw4.z, x[i].z, o[2]); o[3] = fmaf(resw4.w, x[i].w, o[3]);
+              }
+              ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
+            }
+            float* dst = out0 + dr[i] * ld_out;
+            if (rr < rows_here) {
+              // accumulate = one reduction at the memory side: the same single fp32 addition as read-add-write
+              // when nobody else touches the row, without the read's round trip
+              if (mode == MB_OUT_STORE) *reinterpret_cast<float4*>(dst) = ov;
+              else atomicAdd(reinterpret_cast<float4*>(dst), ov);
+            }
+          }
+        }
+      };
+      using T = std::true_type;
+      using F = std::false_type;
+      auto pick_res = [&](auto g_, auto a_) { if (res) finish_rows(g_, a_, T{}); else finish_rows(g_, a_, F{}); };
+      auto pick_act = [&](auto g_) { if (out_act) pick_res(g_, T{}); else pick_res(g_, F{}); };
+      if (gate) pick_act(T{}); else pick_act(F{});
+      __syncwarp();  // the staging patch is rewritten by the next tile
+      MB_T(2);
+    }
+#ifdef MB_GEMM_TIMING
+    if (warp == 8 && lane == 0) MB_TFLUSH(16, 3);
+#endif
+  } else {
+    // ---------------------------------------------------------------- producers: thread = row = TMEM lane
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    bool alive = true;
+    MB_TDECL;
+    MB_T(0);
+    uint32_t g = 0;
+    int n = 0;  // chunks this warp has converted
+    for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb)) {
+      const mb_colblock& cb = d.blk[jb];
+      const int nch = cb.n_src * 4;
+      int act_mask = 0;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) act_mask |= (s < cb.n_src && cb.src[s].act) ? (1 << s) : 0;
+      for (int c = par; c < nch; c += 2, ++n) {
+        const uint32_t gi = g + c, ab = gi & 3;
+        gather_next();  // into the stage read one chunk ago; the __syncwarp that closed that chunk orders the reads
+        MB_T(5);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this chunk's copies of this lane have landed
+        MB_T(6);
+        __syncwarp();                                          // ... and so have the other lanes'
+        MB_T(1);
+        const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
+        const bool act = (act_mask >> (c >> 2)) & 1;  // branch once per chunk: no SiLU is evaluated on the plain path
+        const uint32_t ta = lane_base + 256 + 64 * ab;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // two halves of 16 floats keep the live registers of the split low
+          float x[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t addr = patch + lane * 128 + (((4 * h + j) ^ (lane & 7)) << 4);
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]),
+                         "=f"(x[4 * j + 2]), "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
+          }
+          if (act) {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) x[q] = silu_fast_f(x[q]);
+          }
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {  // hi = x cut to tf32's 10 mantissa bits, lo = the exact remainder
+            hi[q] = __float_as_uint(x[q]) & 0xFFFFE000u;
+            lo[q] = __float_as_uint(x[q] - __uint_as_float(hi[q]));
+          }
+          if (h == 0) {
+            MB_T(2);
+            if (quarter == 0 && lane == 0) MB_TRACE(3, gi);
+            if (gi >= 4 && alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);  // A buffer ab is free again
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (quarter == 0 && lane == 0) MB_TRACE(4, gi);
+            MB_T(3);
+          }
+          MB_TMEM_ST16(ta + 16 * h, hi);
+          MB_TMEM_ST16(ta + 32 + 16 * h, lo);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();  // all lanes have read their patch rows and written their A rows
+        if (lane == 0) mbar_arrive(a_full + 8 * ab);
+        if (quarter == 0 && lane == 0) MB_TRACE(5, gi);
+        MB_T(4);
+      }
+      g += (uint32_t)nch;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#ifdef MB_GEMM_TIMING
+    if (tid == 0) MB_TFLUSH(0, 8);
+#endif
+  }
+
+  // ------------------------------------------------------------------ common exit: release tensor memory
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 12) {
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(PS_TMEM_COLS) : "memory");
+  }
+}

@@ -297,8 +297,9 @@ def angle_basis_bwd(line_graph, unit, factor, cutoff, dbasis):
 
 # ------------------------------------------------------------------ GEMM core selection / status
 def set_gemm_mode(mode: str) -> None:
-    """'tcgen05' (default): tensor cores, 3-term TF32 split; 'simt': exact fp32 FMA cross-check."""
-    _lib.check(_lib.load().mb_set_gemm_mode({"tcgen05": 0, "simt": 1}[mode]), "mb_set_gemm_mode")
+    """'tcgen05' (default): persistent tensor-core kernel, 3-term TF32 split; 'simt': exact fp32 FMA cross-check;
+    'tcgen05_tile': the one-tile-per-CTA tensor-core kernel (same arithmetic as the default)."""
+    _lib.check(_lib.load().mb_set_gemm_mode({"tcgen05": 0, "simt": 1, "tcgen05_tile": 2}[mode]), "mb_set_gemm_mode")
 
 
 def gemm_status() -> int:

@@ -85,7 +85,7 @@ def test_tensor_core_gemm_matches_fp32_simt(ops):
     de, dn, dW, db, dz, dres, drw = dev(e), dev(node), dev(W), dev(b), dev(z), dev(res), dev(rw)
     it, is_ = dev(tgt, torch.int32), dev(src, torch.int32)
     outs = {}
-    for mode in ("simt", "tcgen05"):
+    for mode in ("simt", "tcgen05", "tcgen05_tile"):
         ops.set_gemm_mode(mode)
         out = torch.zeros(R, 256, device="cuda")
         acc = torch.zeros(n1, 128, device="cuda")
@@ -98,6 +98,8 @@ def test_tensor_core_gemm_matches_fp32_simt(ops):
     ops.set_gemm_mode("tcgen05")
     report("tcgen05 vs simt: fused epilogue", outs["tcgen05"][0], outs["simt"][0], 1e-5)
     report("tcgen05 vs simt: atomic scatter", outs["tcgen05"][1], outs["simt"][1], 1e-5)
+    report("tcgen05_tile vs simt: fused epilogue", outs["tcgen05_tile"][0], outs["simt"][0], 1e-5)
+    report("tcgen05_tile vs simt: atomic scatter", outs["tcgen05_tile"][1], outs["simt"][1], 1e-5)
     x = torch.cat([torch.nn.functional.silu(e), node[tgt], node[src]], 1).double()
     want = torch.nn.functional.linear(x, W.double(), b.double())
     zz = z.double().requires_grad_(True)
