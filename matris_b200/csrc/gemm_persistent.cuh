@@ -10,14 +10,15 @@
 //               reads through the optional index, two stages per warp) into a swizzled shared-memory patch, read back
 //               one row per thread, passed through the optional SiLU, split into tf32 hi / lo and written with
 //               tcgen05.st into one of FOUR A buffers in tensor memory.
-//   warp 13     TMA (one thread): streams W_hi / W_lo tiles into a 3-slot ring, up to three chunks ahead and across
+//   warp 17     TMA (one thread): streams W_hi / W_lo tiles into a 3-slot ring, up to three chunks ahead and across
 //               tile boundaries.
-//   warp 12     MMA (one thread): issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor
+//   warp 16     MMA (one thread): issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor
 //               memory) into one of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot
 //               free) and, after a tile's last chunk, "accumulator full".
-//   warps 8-11  epilogue.  Warp e drains rows 32e.. of the finished accumulator (tcgen05.ld) into its own swizzled
-//               staging patch, releases the accumulator at once, and then finishes its 32 rows with fully coalesced
-//               512-byte row accesses while the tensor cores already work on the next tile.
+//   warps 8-15  epilogue.  Warp 8 + e drains rows 32 (e & 3).., columns 64 (e >> 2).. of the finished accumulator
+//               (tcgen05.ld) into its own swizzled staging patch, releases the accumulator at once, and then finishes
+//               its 32 x 64 block with coalesced 256-byte row accesses while the tensor cores already work on the
+//               next tile.
 //
 // Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64b (hi | lo).
 // Shared memory: W ring 96 KB | producer patches 64 KB | epilogue staging 64 KB | barriers | descriptor copy.
@@ -30,7 +31,8 @@ __device__ long long g_trace[8][128];
 #else
 #define MB_TRACE(row, g)
 #endif
-constexpr int PS_THREADS = 448;
+constexpr int PS_THREADS = 576;          // 18 warps
+constexpr int PS_MMA_WARP = 16, PS_TMA_WARP = 17;
 constexpr int PS_W_SLOTS = 3;
 constexpr int PS_RING_BYTES = PS_W_SLOTS * 2 * TC_TILE_BYTES;
 constexpr int PS_PATCH_BYTES = 8 * 2 * 32 * 128;
@@ -138,11 +140,11 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     g_second = !g_second;
   };
 
-  if (warp == 12) {
+  if (warp == PS_MMA_WARP) {
     if (lane == 0) {
       for (int b = 0; b < 4; ++b) { mbar_init(a_full + 8 * b, 4); mbar_init(chunk_done + 8 * b, 1); }
       for (int b = 0; b < 3; ++b) mbar_init(w_full + 8 * b, 1);
-      for (int b = 0; b < 2; ++b) { mbar_init(d_full + 8 * b, 1); mbar_init(d_free + 8 * b, 4); }
+      for (int b = 0; b < 2; ++b) { mbar_init(d_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8); }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -159,7 +161,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 12) {
+  if (warp == PS_MMA_WARP) {
     // ---------------------------------------------------------------- control thread: TMA + MMA issue
     if (lane == 0) {
       bool alive = true;
@@ -210,7 +212,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       }
       MB_TFLUSH(8, 4);
     }
-  } else if (warp == 13) {
+  } else if (warp == PS_TMA_WARP) {
     // ---------------------------------------------------------------- TMA thread: W_hi / W_lo tiles, up to 3 chunks ahead
     if (lane == 0) {
       bool alive = true;
@@ -238,17 +240,19 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     }
   } else if (warp >= 8) {
     // ---------------------------------------------------------------- epilogue warps
-    const int e = warp - 8;  // TMEM lane quarter and row quarter of the tile
-    uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 512);
+    // Warp 8 + e drains rows 32 (e & 3).. (its TMEM lane quarter), columns 64 (e >> 2).. of the accumulator.
+    const int e = warp - 8, quarter_e = e & 3, half = e >> 2;
+    uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 256);  // 32 rows x 256 bytes, swizzled
     const uint32_t stage_u = smem_u32(stage);
-    const uint32_t lane_base = tmem_base + ((uint32_t)(e * 32) << 16);
-    const int col = lane * 4;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter_e * 32) << 16) + (uint32_t)(half * 64);
+    const int sub = lane >> 4, ch = lane & 15;  // finishing: 16 lanes cover one row's 256 bytes, two rows per instruction
+    const int col = half * 64 + ch * 4;
     bool alive = true;
     MB_TDECL;
     int k = 0;
     for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
       const int acc = k & 1;
-      const int64_t row0 = (int64_t)rt * 128 + e * 32;  // first row of this warp
+      const int64_t row0 = (int64_t)rt * 128 + quarter_e * 32;  // first row of this warp
       const mb_colblock& cb = d.blk[jb];
       const float* const gate = cb.gate;
       const float* const res = cb.res;
@@ -265,13 +269,13 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       const int rows_here = left >= 32 ? 32 : (left > 0 ? (int)left : 0);
       // the rows this warp will read in the epilogue are pulled into L2 while the tile is still being multiplied
       if (gate || res) {
-        const int r = lane >> 2, part = lane & 3;  // 8 rows x four 128-byte lines per pass
+        const int part = lane & 1;  // 16 rows x two 128-byte lines per pass
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          const int rr = p * 8 + r;
+        for (int p = 0; p < 2; ++p) {
+          const int rr = p * 16 + (lane >> 1);
           if (rr < rows_here) {
-            if (gate) asm volatile("prefetch.global.L2 [%0];" :: "l"(gate + (row0 + rr) * ld_gate + cb.col_gate + part * 32));
-            if (res) asm volatile("prefetch.global.L2 [%0];" :: "l"(res + (row0 + rr) * ld_res + cb.col_res + part * 32));
+            if (gate) asm volatile("prefetch.global.L2 [%0];" :: "l"(gate + (row0 + rr) * ld_gate + cb.col_gate + half * 64 + part * 32));
+            if (res) asm volatile("prefetch.global.L2 [%0];" :: "l"(res + (row0 + rr) * ld_res + cb.col_res + half * 64 + part * 32));
           }
         }
       }
@@ -279,15 +283,15 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       alive = __all_sync(0xffffffffu, alive);
       MB_T(0);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // (1) accumulator row (thread = row) -> staging; 16-byte chunk ch of row r sits at position ch ^ r
+      // (1) accumulator row (thread = row) -> staging; 16-byte chunk c of row r sits at position c ^ (r & 15)
 #pragma unroll 1
-      for (int cg = 0; cg < 4; ++cg) {
+      for (int cg = 0; cg < 2; ++cg) {
         uint32_t v[32];
         MB_TMEM_LD32(lane_base + 128u * acc + (uint32_t)(cg * 32), v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          const uint32_t addr = stage_u + lane * 512 + (((cg * 8 + q) ^ lane) << 4);
+          const uint32_t addr = stage_u + lane * 256 + (((cg * 8 + q) ^ (lane & 15)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
                        :: "r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3]) : "memory");
         }
@@ -297,8 +301,9 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the tensor cores may overwrite this accumulator now
       MB_T(1);
       if (!alive) continue;
-      // (2) rows in batches of eight: all global reads of a batch are issued before their first use
-      constexpr int RB = 8;
+      // (2) two rows per instruction, in batches of four instructions: all global reads of a batch are issued
+      //     before their first use
+      constexpr int RB = 4;
       const float* const gate0 = gate ? gate + row0 * ld_gate + gcol : nullptr;
       const float* const res0 = res ? res + row0 * ld_res + rcol : nullptr;
       float* const out0 = out + (out_idx ? 0 : row0 * ld_out) + ocol;
@@ -306,22 +311,22 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
         constexpr bool plain = !decltype(has_gate)::value && !decltype(has_act)::value && !decltype(has_res)::value;
 #pragma unroll 1
-        for (int r0 = 0; r0 < rows_here; r0 += RB) {
-          float4 z[RB], x[RB];
+        for (int r0 = 0; r0 < rows_here; r0 += 2 * RB) {
+          float4 z[RB], x[RB], av[RB];
           int32_t dr[RB];
 #pragma unroll
           for (int i = 0; i < RB; ++i) {
-            const int rr = r0 + i < rows_here ? r0 + i : r0;
+            const int rq = r0 + 2 * i + sub;
+            const int rr = rq < rows_here ? rq : r0;
             if constexpr (decltype(has_gate)::value) z[i] = ld4(gate0 + rr * ld_gate);
             if constexpr (decltype(has_res)::value) x[i] = ld4(res0 + rr * ld_res);
             dr[i] = out_idx ? out_idx[row0 + rr] : rr;
+            av[i] = *reinterpret_cast<const float4*>(stage + rq * 256 + ((ch ^ (rq & 15)) << 4));
           }
 #pragma unroll
           for (int i = 0; i < RB; ++i) {
-            const int rr = r0 + i;
-            float4 a;
-            const uint32_t addr = stage_u + rr * 512 + ((lane ^ rr) << 4);
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "r"(addr) : "memory");
+            const int rq = r0 + 2 * i + sub;
+            const float4 a = av[i];
             float4 ov;
             if constexpr (plain) {
               ov = make_float4(fmaf(a.x, sc, bsc.x), fmaf(a.y, sc, bsc.y), fmaf(a.z, sc, bsc.z), fmaf(a.w, sc, bsc.w));
@@ -341,7 +346,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
               ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
             }
             float* dst = out0 + dr[i] * ld_out;
-            if (rr < rows_here) {
+            if (rq < rows_here) {
               // accumulate = one reduction at the memory side: the same single fp32 addition as read-add-write
               // when nobody else touches the row, without the read's round trip
               if (mode == MB_OUT_STORE) *reinterpret_cast<float4*>(dst) = ov;
@@ -434,7 +439,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   // ------------------------------------------------------------------ common exit: release tensor memory
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 12) {
+  if (warp == PS_MMA_WARP) {
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(PS_TMEM_COLS) : "memory");
