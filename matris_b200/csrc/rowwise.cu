@@ -89,24 +89,70 @@ __global__ void k_seg_attn_fwd(int n_nodes, const int32_t* __restrict__ tgt_ptr,
                                const float* __restrict__ logits, const float* __restrict__ h,
                                float* __restrict__ agg_t, float* __restrict__ agg_s, float* __restrict__ stats) {
   MB_ROW_PROLOGUE(n_nodes)
+  constexpr int NB = 8;  // rows in flight per warp: their index and data loads are issued together
 #pragma unroll
   for (int side = 0; side < 2; ++side) {
     const int32_t* ptr = side == 0 ? tgt_ptr : src_ptr;
     const int q0 = ptr[row], q1 = ptr[row + 1];
     const int lcol = side == 0 ? 128 : 0;
+    auto rows_of = [&](int q, int64_t (&r)[NB], int64_t (&er)[NB]) {
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const int qq = q + i < q1 ? q + i : q1 - 1;
+        r[i] = side == 0 ? qq : src_perm[qq];
+      }
+#pragma unroll
+      for (int i = 0; i < NB; ++i) er[i] = emap ? emap[r[i]] : r[i];
+    };
     float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    for (int q = q0; q < q1; ++q) {
-      const int64_t r = side == 0 ? q : src_perm[q];
-      const int64_t er = emap ? emap[r] : r;
-      mx = max4(mx, ld4(logits + er * 256 + lcol + c));
-    }
     float4 s = zero4(), acc = zero4();
-    for (int q = q0; q < q1; ++q) {
-      const int64_t r = side == 0 ? q : src_perm[q];
-      const int64_t er = emap ? emap[r] : r;
-      const float4 e = exp4(sub4(ld4(logits + er * 256 + lcol + c), mx));
-      s = add4(s, e);
-      acc = fma4(e, ld4(h + r * 128 + c), acc);
+    if (q1 - q0 <= NB) {  // the common case: the whole segment is held in registers, every row is read once
+      if (q1 > q0) {
+        int64_t r[NB], er[NB];
+        rows_of(q0, r, er);
+        float4 x[NB], hv[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i) x[i] = ld4(logits + er[i] * 256 + lcol + c);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) hv[i] = ld4(h + r[i] * 128 + c);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) mx = max4(mx, x[i]);  // rows past the end repeat the last one
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+          if (q0 + i < q1) {
+            const float4 e = exp4(sub4(x[i], mx));
+            s = add4(s, e);
+            acc = fma4(e, hv[i], acc);
+          }
+        }
+      }
+    } else {
+      for (int q = q0; q < q1; q += NB) {
+        int64_t r[NB], er[NB];
+        rows_of(q, r, er);
+        float4 x[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i) x[i] = ld4(logits + er[i] * 256 + lcol + c);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) mx = max4(mx, x[i]);
+      }
+      for (int q = q0; q < q1; q += NB) {
+        int64_t r[NB], er[NB];
+        rows_of(q, r, er);
+        float4 x[NB], hv[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i) x[i] = ld4(logits + er[i] * 256 + lcol + c);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) hv[i] = ld4(h + r[i] * 128 + c);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+          if (q + i < q1) {
+            const float4 e = exp4(sub4(x[i], mx));
+            s = add4(s, e);
+            acc = fma4(e, hv[i], acc);
+          }
+        }
+      }
     }
     float4 inv = zero4();
     if (q1 > q0) inv = make_float4(1.f / s.x, 1.f / s.y, 1.f / s.z, 1.f / s.w);
