@@ -58,31 +58,79 @@ def flops_per_eval(g, layers):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML read-only queries from a thread of
+    this process (no child process competing for the driver), every 100 ms; nvidia-smi as a fallback."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index: int):
-        self.proc, self.lines, self.index = None, [], index
+        self.index, self.proc, self.thread, self.stop = index, None, None, threading.Event()
+        self.sm, self.mx, self.reasons, self.source = [], [], set(), None
+
+    def _nvml_handle(self):
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll_nvml(self, pynvml, handle):
+        while not self.stop.is_set():
+            try:
+                self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                self.mx.append(float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                bits = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                for name, bit in self.REASON_BITS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self.stop.wait(0.1)
+
+    def _poll_smi(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.proc.stdout:
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                self.sm.append(float(p[0]))
+                self.mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[3:7]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(name)
 
     def __enter__(self):
+        try:
+            pynvml, handle = self._nvml_handle()
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._poll_nvml, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            pass
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "500"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.source = "nvidia-smi"
+            self.thread = threading.Thread(target=self._poll_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
     def __exit__(self, *a):
+        self.stop.set()
         if self.proc is not None:
             time.sleep(0.25)
             self.proc.terminate()
@@ -90,26 +138,14 @@ class ClockSampler:
                 self.proc.wait(timeout=2)
             except Exception:
                 pass
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            p = [x.strip() for x in line.split(",")]
-            if len(p) < 7:
-                continue
-            try:
-                sm.append(float(p[0]))
-                mx.append(float(p[1]))
-            except ValueError:
-                continue
-            for name, v in zip(names, p[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": self.source}
+        return {"sm_mhz": float(np.median(self.sm)), "sm_max_mhz": float(max(self.mx)), "reasons": sorted(self.reasons),
+                "samples": len(self.sm), "source": self.source}
 
 
 def cpu_oracle_rate(crystals, task, budget_s=20.0, max_structs=16, threads=None):
@@ -254,11 +290,12 @@ def main():
 
     step_e2e()
     barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        res = step_e2e()
-    ev1.record()
-    barrier()
+    with ClockSampler(local_rank) as clocks_e2e:
+        ev0.record()
+        for _ in range(args.steps):
+            res = step_e2e()
+        ev1.record()
+        barrier()
     t_e2e = torch.tensor([ev0.elapsed_time(ev1) * 1e-3], device=device)
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
@@ -274,7 +311,7 @@ def main():
         torch.cuda.synchronize()
         prof, _lib.profile = _lib.profile, None
         per, shapes = {}, {}
-        gemm_flops, gemm_ms = 0.0, 0.0
+        gemm_flops, gemm_ms, gemm_bytes = 0.0, 0.0, 0.0
         for name, a, b, meta in prof:
             ms = a.elapsed_time(b)
             d = per.setdefault(name, [0, 0.0])
@@ -283,6 +320,7 @@ def main():
             if name == "mb_gemm":
                 gemm_flops += meta["flops"]
                 gemm_ms += ms
+                gemm_bytes += 4.0 * meta["rows"] * (meta["k"] + meta["n"])  # A rows read once + output rows written
                 s = shapes.setdefault(f"rows={meta['rows']} K={meta['k']} N={meta['n']}", [0, 0.0, 0.0])
                 s[0] += 1
                 s[1] += ms
@@ -301,8 +339,12 @@ def main():
         peak_gb = float(peaks.get("hbm_gbs", 6650.0))
         src = "measured" if peaks else "fallback"
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
-        roofline = {"kernel": "k_gemm_tc (mb_gemm)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": None, "peak_source": src + " bf16 sustained",
+        # DRAM traffic per launch: ncu measured 0.906 x (A read + output write) on a captured K=384 N=256 launch of
+        # 151,552 rows (profiles/k_gemm_ps.md); scaled here to the average launch of the step by its rows x (K + N).
+        roofline = {"kernel": "k_gemm_ps (mb_gemm)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
+                    "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.906 * gemm_bytes / per["mb_gemm"][0],
+                    "traffic_note": "bytes per average launch, scaled from one ncu capture by rows x (K + N)",
+                    "peak_source": src + " bf16 sustained",
                     "launches": per["mb_gemm"][0], "avg_launch_ms": gemm_ms / per["mb_gemm"][0],
                     "flops_per_step": gemm_flops, "tf32_issued_tflops": 3.0 * ach, "tf32_peak_measured_tflops": 1151.0,
                     "frac_of_tf32_peak": 3.0 * ach / 1151.0,
@@ -331,7 +373,7 @@ def main():
                            "atoms_per_rank": n_atoms, "directed_edges": g.n_edges, "triplets": g.n_triplets,
                            "l2": "per-step working set (>1 GB of activations) exceeds the 126 MB L2",
                            "parallelism": f"structures sharded, {world} rank(s), result gather only"},
-                "clocks": clocks.summary(),
+                "clocks": clocks.summary(), "clocks_e2e": clocks_e2e.summary(),
                 "e2e": {"value": atoms_total * args.steps / t_e2e, "unit": "atoms*evals/s",
                         "h2d_bytes_per_step": hb.h2d_bytes, "d2h_bytes_per_step": d2h,
                         "ms_per_step": 1e3 * t_e2e / args.steps},
