@@ -563,9 +563,13 @@ class MatRIS(nn.Module):
         est = len(P.layers) * (6.7e3 * g.n_triplets + 6.2e3 * g.n_edges)
         keep = self.keep_activations
         if keep is None:
-            # memory the allocator can hand out: free on the device plus its own cached, unused blocks
-            reusable = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
-            keep = est < 0.45 * (torch.cuda.mem_get_info(self.device)[0] + reusable)
+            # memory the allocator can hand out: free on the device plus its own cached, unused blocks.  The driver
+            # query costs milliseconds, so a small evaluation (under a tenth of the last answer) reuses that answer.
+            free = getattr(self, "_free_bytes", None)
+            if free is None or est > 0.1 * free:
+                reusable = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+                free = self._free_bytes = torch.cuda.mem_get_info(self.device)[0] + reusable
+            keep = est < 0.45 * free
         atom_rg.keep = bool(keep)
         if line_rg is not None:
             line_rg.keep = bool(keep)

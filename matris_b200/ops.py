@@ -6,6 +6,7 @@ wrapper launches on torch's current stream.
 from __future__ import annotations
 
 import ctypes as C
+import struct
 
 import torch
 
@@ -15,7 +16,13 @@ from ._lib import OUT_ADD, OUT_ATOMIC, OUT_STORE, call, ptr  # noqa: F401
 D = 128
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """Raw handle of torch's current stream on the current device (the stream every entry point launches on)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -69,37 +76,49 @@ def B(srcs, W, w_row=0, bias=None, bias_off=0, gate=None, gate_col=0, out_act=0,
                 mode=mode, scale=scale)
 
 
+# Byte layout of mb_colblock / mb_gemm_desc (little endian, every member naturally aligned; checked against the
+# ctypes mirror at import).  The descriptor is packed with one struct call per column block: filling the ctypes
+# mirror field by field costs more host time than a small launch takes on the device.
+_BLK_FMT = struct.Struct("<ii" + "QQqii" * 4 + "QQQqQ" + "Qqii" + "QQqii" + "QQqif")
+_HDR_FMT = struct.Struct("<qii")
+_BLK_OFF, _BLK_SIZE, _DESC_SIZE = _lib.MbGemmDesc.blk.offset, C.sizeof(_lib.MbColBlock), C.sizeof(_lib.MbGemmDesc)
+assert _BLK_FMT.size == _BLK_SIZE and _HDR_FMT.size == _BLK_OFF and _DESC_SIZE == _BLK_OFF + 4 * _BLK_SIZE
+_NO_SRC = (0, 0, 0, 0, 0)
+
+
 def gemm(n_rows: int, blocks: list[dict]) -> None:
     if n_rows == 0:
         return
-    d = _lib.MbGemmDesc()
-    d.n_rows, d.n_blocks = int(n_rows), len(blocks)
+    buf = bytearray(_DESC_SIZE)
+    _HDR_FMT.pack_into(buf, 0, int(n_rows), len(blocks), 0)
     for j, b in enumerate(blocks):
-        cb = d.blk[j]
-        cb.n_src, cb.out_act = len(b["srcs"]), int(b["out_act"])
-        for s, (t, idx, col, act) in enumerate(b["srcs"]):
+        srcs = b["srcs"]
+        flat = []
+        for t, idx, col, act in srcs:
             assert t.dtype == torch.float32 and t.stride(-1) == 1
-            cb.src[s].ptr, cb.src[s].idx = t.data_ptr(), ptr(idx)
-            cb.src[s].ld, cb.src[s].col, cb.src[s].act = t.stride(0), int(col), int(act)
+            flat += (t.data_ptr(), 0 if idx is None else idx.data_ptr(), t.stride(0), int(col), int(act))
+        for _ in range(4 - len(srcs)):
+            flat += _NO_SRC
         sw = as_split(b["W"])
         W = sw.w
-        assert W.dim() == 2 and W.stride(1) == 1 and W.shape[1] >= D * len(b["srcs"])
-        w_off = 4 * W.stride(0) * int(b["w_row"])
-        cb.W, cb.W_hi, cb.W_lo = W.data_ptr() + w_off, sw.hi.data_ptr() + w_off, sw.lo.data_ptr() + w_off
-        cb.ldw = W.stride(0)
-        cb.bias = None if b["bias"] is None else b["bias"].data_ptr() + 4 * int(b["bias_off"])
-        if b["gate"] is not None:
-            cb.gate, cb.ld_gate, cb.col_gate = b["gate"].data_ptr(), b["gate"].stride(0), int(b["gate_col"])
-        if b["res"] is not None:
-            cb.res, cb.ld_res, cb.col_res = b["res"].data_ptr(), b["res"].stride(0), int(b["res_col"])
-            cb.res_w = ptr(b["res_w"])
-        out = b["out"]
-        cb.out, cb.out_idx, cb.ld_out, cb.col_out = out.data_ptr(), ptr(b["out_idx"]), out.stride(0), int(b["out_col"])
-        cb.mode, cb.out_scale = int(b["mode"]), float(b["scale"])
+        ldw = W.stride(0)
+        assert W.dim() == 2 and W.stride(1) == 1 and W.shape[1] >= D * len(srcs)
+        w_off = 4 * ldw * int(b["w_row"])
+        bias, gate, res, res_w, out, out_idx = b["bias"], b["gate"], b["res"], b["res_w"], b["out"], b["out_idx"]
+        _BLK_FMT.pack_into(
+            buf, _BLK_OFF + j * _BLK_SIZE, len(srcs), int(b["out_act"]), *flat,
+            W.data_ptr() + w_off, sw.hi.data_ptr() + w_off, sw.lo.data_ptr() + w_off, ldw,
+            0 if bias is None else bias.data_ptr() + 4 * int(b["bias_off"]),
+            0 if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0),
+            0 if gate is None else int(b["gate_col"]), 0,
+            0 if res is None else res.data_ptr(), 0 if res is None or res_w is None else res_w.data_ptr(),
+            0 if res is None else res.stride(0), 0 if res is None else int(b["res_col"]), int(b["mode"]),
+            out.data_ptr(), 0 if out_idx is None else out_idx.data_ptr(), out.stride(0), int(b["out_col"]),
+            float(b["scale"]))
     if _lib.profile is not None:
         _lib.profile_meta = dict(flops=sum(2.0 * n_rows * D * D * len(b["srcs"]) for b in blocks), rows=int(n_rows),
                                  k=D * len(blocks[0]["srcs"]), n=D * len(blocks))
-    call("mb_gemm", C.byref(d), _stream())
+    call("mb_gemm", C.byref(_lib.MbGemmDesc.from_buffer(buf)), _stream())
 
 
 def linear(x, W, bias=None, out_act=0, in_act=0, gate=None, res=None, res_w=None, scale=1.0, idx=None, out=None):

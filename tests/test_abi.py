@@ -99,3 +99,39 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.MbError):
         _lib.load()
+
+
+def test_gemm_descriptor_packing_matches_ctypes_mirror(monkeypatch):
+    """ops.gemm packs mb_gemm_desc with struct; every field must land where the ctypes mirror (and the header) put it."""
+    import torch
+
+    from matris_b200 import _lib, ops
+
+    captured = {}
+    monkeypatch.setattr(ops, "call", lambda name, *a: captured.update(name=name, desc=bytes(a[0]._obj)))
+    monkeypatch.setattr(ops, "_stream", lambda: 0)
+
+    class FakeSplit:
+        def __init__(self, w):
+            self.w, self.hi, self.lo, self.shape = w, w.clone(), w.clone(), w.shape
+
+    monkeypatch.setattr(ops, "as_split", lambda w: w if isinstance(w, FakeSplit) else FakeSplit(w))
+    x, idx, W = torch.randn(300, 256), torch.arange(300, dtype=torch.int32), FakeSplit(torch.randn(256, 384))
+    out, g, r, rw, bias = torch.empty(300, 256), torch.randn(300, 256), torch.randn(300, 256), torch.randn(128), torch.randn(256)
+    ops.gemm(300, [ops.B([ops.S(x, None, 0, 1), ops.S(x, idx, 128, 0), ops.S(x, idx, 0, 0)], W, w_row=128 * j, bias=bias,
+                         bias_off=128 * j, gate=g, gate_col=128 * j, res=r, res_col=128 * j, res_w=rw, out=out,
+                         out_idx=idx, out_col=128 * j, mode=ops.OUT_ATOMIC, scale=0.5, out_act=1) for j in (0, 1)])
+    assert captured["name"] == "mb_gemm"
+    d = _lib.MbGemmDesc.from_buffer_copy(captured["desc"])
+    assert (d.n_rows, d.n_blocks) == (300, 2)
+    for j in (0, 1):
+        cb = d.blk[j]
+        assert (cb.n_src, cb.out_act, cb.mode) == (3, 1, ops.OUT_ATOMIC) and abs(cb.out_scale - 0.5) < 1e-9
+        assert (cb.src[0].ptr, cb.src[0].idx or 0, cb.src[0].ld, cb.src[0].col, cb.src[0].act) == (x.data_ptr(), 0, 256, 0, 1)
+        assert (cb.src[1].idx, cb.src[1].col, cb.src[1].act) == (idx.data_ptr(), 128, 0) and not cb.src[3].ptr
+        off = 4 * 384 * 128 * j
+        assert (cb.W, cb.W_hi, cb.W_lo, cb.ldw) == (W.w.data_ptr() + off, W.hi.data_ptr() + off, W.lo.data_ptr() + off, 384)
+        assert cb.bias == bias.data_ptr() + 512 * j
+        assert (cb.gate, cb.ld_gate, cb.col_gate) == (g.data_ptr(), 256, 128 * j)
+        assert (cb.res, cb.res_w, cb.ld_res, cb.col_res) == (r.data_ptr(), rw.data_ptr(), 256, 128 * j)
+        assert (cb.out, cb.out_idx, cb.ld_out, cb.col_out) == (out.data_ptr(), idx.data_ptr(), 256, 128 * j)
