@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Throughput of the E/F/S evaluation path: atoms*evals/s on a batch of random crystals.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload random256|perov512|cu32|fe16k|lipscl]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload random256|perov512|cu32|fe16k|lipscl] [--md-steps N]
 
 Workload (default): 256 random periodic crystals, 8-64 atoms each, seed 1 (+ rank), task
 "efs", MatRIS with 10 interaction blocks and seeded random-init weights.  One step =
@@ -207,6 +207,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="random256")
+    ap.add_argument("--md-steps", type=int, default=None,
+                    help="with --workload lipscl: Langevin MD steps to time (default 200; 0 skips the MD leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--keep", default="auto", choices=["auto", "on", "off"],
                     help="keep sub-block internals for the backward pass (auto: when they fit in memory)")
@@ -364,6 +366,27 @@ def main():
                         "sample": f"first {info['structures']} structures ({info['atoms']} atoms) of the workload as "
                                   f"one batch, {info['reps']} repetitions, {info['seconds']:.1f}s of CPU work"}
 
+    # ---- MD leg (4,096-atom cell only): the public MolecularDynamics driver, Langevin NVT at 600 K, dt = 1 fs,
+    # friction 0.01 / fs, Maxwell-Boltzmann start, one efsm evaluation per step (graph rebuilt every step)
+    md = None
+    md_steps = args.md_steps if args.md_steps is not None else (200 if args.workload == "lipscl" else 0)
+    if rank == 0 and world == 1 and args.workload == "lipscl" and md_steps > 0:
+        from matris_b200.applications import MolecularDynamics
+
+        dyn = MolecularDynamics(crystals[0], model=model, ensemble="nvt", thermostat="langevin", temperature=600,
+                                starting_temperature=600, timestep=1.0, friction=0.01, task="efsm", device="cuda",
+                                seed=2)
+        dyn.run(3)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        dyn.run(md_steps)
+        torch.cuda.synchronize()
+        t_md = time.perf_counter() - t0
+        md = {"metric": "md_steps_per_s", "value": md_steps / t_md, "steps": md_steps, "ms_per_step": 1e3 * t_md / md_steps,
+              "atoms": n_atoms, "setup": "Langevin (BAOAB) NVT 600 K, dt 1 fs, friction 0.01/fs, efsm every step, "
+                                         "host-driven loop (positions H2D, forces D2H each step)",
+              "temperature_K_end": float(dyn.atoms.get_temperature())}
+
     if rank == 0:
         value = atoms_total * args.steps / t_res
         line = {"metric": METRIC, "value": value, "unit": "atoms*evals/s", "n_gpus": world, "steps": args.steps,
@@ -383,6 +406,8 @@ def main():
                 "roofline": roofline, "roofline_graph_build": roofline_graph, "kernels": kernel_table,
                 "gemm_shapes": gemm_shapes if rank == 0 else None,
                 "cpu_baseline": cpu_baseline}
+        if md is not None:
+            line["md"] = md
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
