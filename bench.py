@@ -367,7 +367,7 @@ def main():
                                   f"one batch, {info['reps']} repetitions, {info['seconds']:.1f}s of CPU work"}
 
     # ---- MD leg (4,096-atom cell only): the public MolecularDynamics driver, Langevin NVT at 600 K, dt = 1 fs,
-    # friction 0.01 / fs, Maxwell-Boltzmann start, one efsm evaluation per step (graph rebuilt every step)
+    # friction 0.01 / fs, Maxwell-Boltzmann start, one efsm evaluation per step (graph rebuilt every step on the device)
     md = None
     md_steps = args.md_steps if args.md_steps is not None else (200 if args.workload == "lipscl" else 0)
     if rank == 0 and world == 1 and args.workload == "lipscl" and md_steps > 0:
@@ -384,7 +384,7 @@ def main():
         t_md = time.perf_counter() - t0
         md = {"metric": "md_steps_per_s", "value": md_steps / t_md, "steps": md_steps, "ms_per_step": 1e3 * t_md / md_steps,
               "atoms": n_atoms, "setup": "Langevin (BAOAB) NVT 600 K, dt 1 fs, friction 0.01/fs, efsm every step, "
-                                         "host-driven loop (positions H2D, forces D2H each step)",
+                                         "integrator state and graph rebuild on the device (MolecularDynamics device_resident=True)",
               "temperature_K_end": float(dyn.atoms.get_temperature())}
 
     if rank == 0:

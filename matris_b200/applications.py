@@ -313,8 +313,10 @@ class MolecularDynamics:
                  taut: float | None = None, taup: float | None = None, bulk_modulus: float | None = None,
                  trajectory=None, logfile: str | None = None, loginterval: int = 1,
                  crystal_feas_logfile: str | None = None, append_trajectory: bool = False, task: str = "efs",
-                 device: str | None = "cuda", friction: float = 0.01, seed: int = 0) -> None:
+                 device: str | None = "cuda", friction: float = 0.01, seed: int = 0,
+                 device_resident: bool = True) -> None:
         self.ensemble, self.thermostat = ensemble, thermostat
+        self.device_resident, self.seed = bool(device_resident), int(seed)
         self.temperature, self.timestep, self.friction = temperature, timestep, friction
         self.trajectory, self.logfile, self.loginterval = trajectory, logfile, loginterval
         self.crystal_feas_logfile = crystal_feas_logfile
@@ -416,6 +418,9 @@ class MolecularDynamics:
             if obs is not None:
                 obs.save(self.crystal_feas_logfile)
             return
+        if self.device_resident and bool(np.all(self.atoms.get_pbc())):
+            self._run_on_device(steps)
+            return
         a = self.atoms
         dt = self.timestep * FS
         m = a.get_masses()[:, None]
@@ -435,6 +440,55 @@ class MolecularDynamics:
             f = a.get_forces()
             a.set_momenta(p + 0.5 * dt * f)
             self.steps_done += 1
+
+    def _run_on_device(self, steps: int) -> None:
+        """The built-in integrators with the whole state on the GPU (an extension: the reference's loop,
+        md.py:297-310, goes through the host every step).  Positions (fp64), momenta and forces stay in device
+        memory; each step updates the batch's positions in place, rebuilds the graph there and evaluates the
+        model; nothing is copied to the host until the run ends.  The thermostat noise comes from a torch CUDA
+        generator seeded with ``seed + steps_done``, so a trajectory differs from the host loop's in its noise
+        only."""
+        import torch
+
+        from .graph import build_on_device
+
+        a, calc = self.atoms, self.atoms.calc
+        model, task = calc.model, calc.task
+        if "f" not in task:
+            raise ValueError("molecular dynamics needs forces: the task must contain 'f'")
+        numbers, cart, lattice = as_arrays(a)
+        g = model.graph_converter.batch([Crystal(numbers, cart, lattice)])
+        dev = g.cart64.device
+        dt = self.timestep * FS
+        x = g.cart64.clone()
+        p = torch.as_tensor(a.get_momenta(), dtype=torch.float64, device=dev)
+        m = torch.as_tensor(a.get_masses(), dtype=torch.float64, device=dev)[:, None]
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(self.seed + self.steps_done)
+        if self._mode == "langevin":  # BAOAB splitting; friction is given per fs
+            c1 = float(np.exp(-self.friction * self.timestep))
+            c2 = torch.sqrt((1.0 - c1 * c1) * KB * self.temperature * m)
+        out = model(g, task=task)
+        f = out["f"][0].to(torch.float64)
+        for _ in range(steps):
+            p = p + 0.5 * dt * f
+            if self._mode == "langevin":
+                x = x + 0.5 * dt * p / m
+                p = c1 * p + c2 * torch.randn(p.shape, dtype=torch.float64, device=dev, generator=gen)
+                x = x + 0.5 * dt * p / m
+            else:
+                x = x + dt * p / m
+            g.cart64.copy_(x)
+            g.cart32.copy_(x)
+            build_on_device(g)
+            out = model(g, task=task)
+            f = out["f"][0].to(torch.float64)
+            p = p + 0.5 * dt * f
+            self.steps_done += 1
+        a.set_positions(x.cpu().numpy())
+        a.set_momenta(p.cpu().numpy())
+        n_atoms = len(numbers) if model.is_intensive else 1
+        calc.results.update(energy=out["e"][0].detach().cpu().numpy() * n_atoms, forces=f.cpu().numpy().astype(np.float32))
 
     def set_atoms(self, atoms) -> None:
         calculator = self.atoms.calc

@@ -63,6 +63,23 @@ def test_nve_energy_conservation_and_langevin_runs():
     assert md2.steps_done == 5 and np.isfinite(md2.atoms.get_temperature())
 
 
+def test_device_resident_nve_follows_the_host_loop():
+    """Velocity Verlet has no noise: the loop with its state on the GPU must retrace the host-driven loop."""
+    from matris_b200 import MatRIS
+    from matris_b200.applications import MolecularDynamics
+    model = MatRIS.from_dict(random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)).to("cuda")
+    runs = []
+    for resident in (False, True):
+        md = MolecularDynamics(_atoms(workloads.cu_fcc()), model=model, ensemble="nve", timestep=1.0,
+                               starting_temperature=300, task="ef", device="cuda", seed=5, device_resident=resident)
+        md.run(10)
+        md.run(5)  # a second call continues from the stored state
+        assert md.steps_done == 15
+        runs.append((md.atoms.get_positions(), md.atoms.get_momenta()))
+    report("device-resident NVE positions vs host loop", torch.tensor(runs[1][0]), torch.tensor(runs[0][0]), 1e-6)
+    report("device-resident NVE momenta vs host loop", torch.tensor(runs[1][1]), torch.tensor(runs[0][1]), 1e-5)
+
+
 def test_relax_lowers_the_force():
     from matris_b200.applications import StructOptimizer
     ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)
