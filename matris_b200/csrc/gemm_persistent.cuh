@@ -53,8 +53,10 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
     return;
   }
-  // barriers: a_full[4] (count 4 warps) | chunk_done[4] | w_full[3] | d_full[2] | d_free[2] (count 4 warps)
-  const uint32_t a_full = smem_u32(bars), chunk_done = smem_u32(bars + 4), w_full = smem_u32(bars + 8);
+  // barriers: ready[4] (chunk g & 3: 4 producer warps + the TMA thread's expect_tx arrival) | chunk_done[4] |
+  //           d_full[2] | d_free[2] (8 epilogue warps).  One wait per chunk for the MMA thread: every shared-memory
+  //           operation of that thread queues behind the data traffic of the other 17 warps.
+  const uint32_t ready = smem_u32(bars), chunk_done = smem_u32(bars + 4);
   const uint32_t d_full = smem_u32(bars + 11), d_free = smem_u32(bars + 13);
   const uint32_t ring = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -142,8 +144,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
 
   if (warp == PS_MMA_WARP) {
     if (lane == 0) {
-      for (int b = 0; b < 4; ++b) { mbar_init(a_full + 8 * b, 4); mbar_init(chunk_done + 8 * b, 1); }
-      for (int b = 0; b < 3; ++b) mbar_init(w_full + 8 * b, 1);
+      for (int b = 0; b < 4; ++b) { mbar_init(ready + 8 * b, 5); mbar_init(chunk_done + 8 * b, 1); }
       for (int b = 0; b < 2; ++b) { mbar_init(d_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8); }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -166,22 +167,21 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     if (lane == 0) {
       bool alive = true;
       MB_TDECL;
+      uint32_t nch_of = 0;  // chunks per tile of the (up to four) column blocks, a byte each: no descriptor read per tile
+      for (int j = 0; j < n_blocks; ++j) nch_of |= (uint32_t)(d.blk[j].n_src * 4) << (8 * j);
       uint32_t g = 0;  // chunks issued so far (all tiles); a multiple of 4 at every tile start
       int k = 0;
       for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
         const int acc = k & 1;
         const uint32_t d_tmem = tmem_base + 128u * acc;
-        const int nch = d.blk[jb].n_src * 4;
+        const int nch = (int)((nch_of >> (8 * jb)) & 0xffu);
+        MB_TRACE(6, g);
         for (int c = 0; c < nch; ++c, ++g) {
           const uint32_t ab = g & 3, slot = g % PS_W_SLOTS;
           MB_TRACE(0, g);
-          if (alive) alive = mbar_wait(a_full + 8 * ab, (g >> 2) & 1);
+          if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);  // A rows stored and W tiles landed
           MB_TRACE(1, g);
           MB_T(0);
-#ifdef MB_DBG_NO_W
-          if (g < PS_W_SLOTS)
-#endif
-          if (alive) alive = mbar_wait(w_full + 8 * slot, (g / PS_W_SLOTS) & 1);
           MB_T(1);
           if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
           MB_T(2);
@@ -203,6 +203,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
           }
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                        :: "r"(chunk_done + 8 * ab) : "memory");
+          MB_TRACE(7, g);
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(d_full + 8 * acc) : "memory");
@@ -224,10 +225,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
           // the slot was last read by chunk w_g - 3
           if (w_g >= PS_W_SLOTS) alive = mbar_wait(chunk_done + 8 * ((w_g - PS_W_SLOTS) & 3), ((w_g - PS_W_SLOTS) >> 2) & 1);
           if (!alive) break;
-#ifdef MB_DBG_NO_W
-          if (w_g >= PS_W_SLOTS) continue;
-#endif
-          const uint32_t bar = w_full + 8 * slot, dst = ring + slot * 2 * TC_TILE_BYTES;
+          const uint32_t bar = ready + 8 * (w_g & 3), dst = ring + slot * 2 * TC_TILE_BYTES;
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
           tma_load_2d(dst, &maps.m[jb][0], bar, c * TC_BK, 0);
           tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, c * TC_BK, 0);
@@ -235,7 +233,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       }
       if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
         for (uint32_t i = w_g >= PS_W_SLOTS ? w_g - PS_W_SLOTS : 0; i < w_g; ++i)
-          mbar_wait(w_full + 8 * (i % PS_W_SLOTS), (i / PS_W_SLOTS) & 1);
+          mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
       }
     }
   } else if (warp >= 8) {
@@ -424,7 +422,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();  // all lanes have read their patch rows and written their A rows
-        if (lane == 0) mbar_arrive(a_full + 8 * ab);
+        if (lane == 0) mbar_arrive(ready + 8 * ab);
         if (quarter == 0 && lane == 0) MB_TRACE(5, gi);
         MB_T(4);
       }
