@@ -128,6 +128,16 @@ class TrajectoryObserver:
         return self.atoms.get_potential_energy()
 
     def save(self, filename: str) -> None:
+        """Pickle of the recorded lists (base.py:163-175); a name ending in ``.xyz`` / ``.extxyz`` writes the frames
+        as extended XYZ instead (an extension)."""
+        if str(filename).endswith((".xyz", ".extxyz")):
+            from .io import write_extxyz
+            numbers = self.atoms.get_atomic_numbers()
+            frames = [SimpleAtoms(numbers, p, c) for p, c in zip(self.atom_positions, self.cells)]
+            results = [dict(energy=e, forces=f, stress=s, magmoms=m)
+                       for e, f, s, m in zip(self.energies, self.forces, self.stresses, self.magmoms)]
+            write_extxyz(filename, frames, results=results)
+            return
         out = {"energy": self.energies, "forces": self.forces, "stresses": self.stresses, "magmoms": self.magmoms,
                "atom_positions": self.atom_positions, "cell": self.cells,
                "atomic_number": self.atoms.get_atomic_numbers()}
@@ -440,6 +450,8 @@ class MolecularDynamics:
             f = a.get_forces()
             a.set_momenta(p + 0.5 * dt * f)
             self.steps_done += 1
+            if self._logs_now():
+                self._log_frame(a, dict(a.calc.results))
 
     def _run_on_device(self, steps: int) -> None:
         """The built-in integrators with the whole state on the GPU (an extension: the reference's loop,
@@ -485,10 +497,23 @@ class MolecularDynamics:
             f = out["f"][0].to(torch.float64)
             p = p + 0.5 * dt * f
             self.steps_done += 1
+            if self._logs_now():  # the only host copies inside the loop, every ``loginterval`` steps
+                frame = SimpleAtoms(numbers, x.cpu().numpy(), lattice, momenta=p.cpu().numpy())
+                n_at = len(numbers) if model.is_intensive else 1
+                self._log_frame(frame, dict(energy=out["e"][0].detach().cpu().numpy() * n_at, forces=f.cpu().numpy()))
         a.set_positions(x.cpu().numpy())
         a.set_momenta(p.cpu().numpy())
         n_atoms = len(numbers) if model.is_intensive else 1
         calc.results.update(energy=out["e"][0].detach().cpu().numpy() * n_atoms, forces=f.cpu().numpy().astype(np.float32))
+
+    def _logs_now(self) -> bool:
+        return (self.dyn is None and isinstance(self.trajectory, str) and self.loginterval > 0
+                and self.steps_done % self.loginterval == 0)
+
+    def _log_frame(self, atoms, results) -> None:
+        """Built-in integrators: append a frame to the extended-XYZ file named by ``trajectory``."""
+        from .io import write_extxyz
+        write_extxyz(self.trajectory, atoms, append=True, results=results)
 
     def set_atoms(self, atoms) -> None:
         calculator = self.atoms.calc

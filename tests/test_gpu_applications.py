@@ -80,6 +80,23 @@ def test_device_resident_nve_follows_the_host_loop():
     report("device-resident NVE momenta vs host loop", torch.tensor(runs[1][1]), torch.tensor(runs[0][1]), 1e-5)
 
 
+def test_md_writes_an_extxyz_trajectory(tmp_path):
+    from matris_b200 import MatRIS
+    from matris_b200.applications import MolecularDynamics
+    from matris_b200.io import read_extxyz
+    model = MatRIS.from_dict(random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=0)).to("cuda")
+    for resident in (True, False):
+        path = str(tmp_path / f"traj_{int(resident)}.xyz")
+        md = MolecularDynamics(_atoms(workloads.cu_fcc()), model=model, ensemble="nve", timestep=1.0,
+                               starting_temperature=300, task="ef", device="cuda", trajectory=path, loginterval=2,
+                               device_resident=resident)
+        md.run(6)
+        frames = read_extxyz(path)
+        assert len(frames) == 3 and len(frames[-1]) == 32
+        np.testing.assert_allclose(frames[-1].positions, md.atoms.get_positions(), atol=1e-8)
+        assert "forces" in frames[-1].arrays and "energy" in frames[-1].info
+
+
 def test_relax_lowers_the_force():
     from matris_b200.applications import StructOptimizer
     ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)
