@@ -159,7 +159,10 @@ typedef struct mb_gemm_desc {
 
 int mb_gemm(const mb_gemm_desc* desc, void* stream);
 /* Contraction core used by mb_gemm: 0 = tcgen05 tensor cores, kind::tf32 with a 3-term hi/lo operand split
- * accumulated in fp32 TMEM (default); 1 = fp32 SIMT FMA (bit-faithful fp32, the cross-check). Process-wide. */
+ * accumulated in fp32 TMEM, persistent kernel with one CTA per SM (default); 1 = fp32 SIMT FMA (bit-faithful fp32,
+ * the cross-check); 2 = the same tensor-core arithmetic as 0 in a one-tile-per-CTA kernel. Process-wide.
+ * MB_OUT_ADD is performed as one memory-side fp32 addition per element in mode 0 (read-add-write in modes 1, 2):
+ * identical results as long as no other kernel writes the output rows concurrently. */
 int mb_set_gemm_mode(int mode);
 /* Synchronises the stream, returns and clears the tensor-core kernel's status word (bit 0: a bounded
  * mbarrier wait expired and the affected tiles were not written). */
