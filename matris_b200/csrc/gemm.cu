@@ -427,7 +427,6 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
         const uint32_t wb = ring + (uint32_t)ab * 2 * TC_TILE_BYTES;
         const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
         const uint32_t ta_hi = tmem_base + 128 + 64 * ab, ta_lo = ta_hi + 32;
-#ifndef MB_DBG_NO_MMA
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
           const uint64_t adv = (uint64_t)(2 * k);
@@ -435,7 +434,6 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
           umma_tf32_ts(tmem_base, ta_hi + 8 * k, dbl + adv, 1u);
           umma_tf32_ts(tmem_base, ta_hi + 8 * k, dbh + adv, 1u);
         }
-#endif
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                      :: "r"(mma_done + 8 * ab) : "memory");
         MB_T(2);
@@ -663,14 +661,6 @@ extern "C" int mb_gemm_read_timing(unsigned long long* host16) {
   MB_CUDA_CHECK(cudaDeviceSynchronize());
   MB_CUDA_CHECK(cudaMemcpyFromSymbol(host16, mb::g_gemm_timing, sizeof(zero)));
   MB_CUDA_CHECK(cudaMemcpyToSymbol(mb::g_gemm_timing, zero, sizeof(zero)));
-  return MB_OK;
-}
-#endif
-
-#ifdef MB_GEMM_TRACE
-extern "C" int mb_gemm_read_trace(long long* host) {
-  MB_CUDA_CHECK(cudaDeviceSynchronize());
-  MB_CUDA_CHECK(cudaMemcpyFromSymbol(host, mb::g_trace, sizeof(long long) * 8 * 128));
   return MB_OK;
 }
 #endif

@@ -25,12 +25,6 @@
 // Every mbarrier wait is bounded; on expiry a status word is set, the role stops waiting and runs to the common exit,
 // where tensor memory is released.
 
-#ifdef MB_GEMM_TRACE
-__device__ long long g_trace[8][128];
-#define MB_TRACE(row, g) do { if (blockIdx.x == 0 && (g) >= 200 && (g) < 328) g_trace[row][(g) - 200] = clock64(); } while (0)
-#else
-#define MB_TRACE(row, g)
-#endif
 constexpr int PS_THREADS = 576;          // 18 warps
 constexpr int PS_MMA_WARP = 16, PS_TMA_WARP = 17;
 constexpr int PS_W_SLOTS = 3;
@@ -121,15 +115,11 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       const int64_t row0 = s.idx ? 0 : (int64_t)g_rt * 128;
 #pragma unroll
       for (int i = 0; i < 8; ++i) a_ptr[i] = base + (row0 + a_row[i]) * ld;
-#ifndef MB_DBG_NO_A
       MB_CP16(de, 0, a_ptr[0], 0);    MB_CP16(dq, 512, a_ptr[1], 0);  MB_CP16(de, 1024, a_ptr[2], 0); MB_CP16(dq, 1536, a_ptr[3], 0);
       MB_CP16(de, 2048, a_ptr[4], 0); MB_CP16(dq, 2560, a_ptr[5], 0); MB_CP16(de, 3072, a_ptr[6], 0); MB_CP16(dq, 3584, a_ptr[7], 0);
-#endif
     } else {          // chunk par + 2 of the segment: 64 floats further along every row
-#ifndef MB_DBG_NO_A
       MB_CP16(de, 0, a_ptr[0], 256);    MB_CP16(dq, 512, a_ptr[1], 256);  MB_CP16(de, 1024, a_ptr[2], 256); MB_CP16(dq, 1536, a_ptr[3], 256);
       MB_CP16(de, 2048, a_ptr[4], 256); MB_CP16(dq, 2560, a_ptr[5], 256); MB_CP16(de, 3072, a_ptr[6], 256); MB_CP16(dq, 3584, a_ptr[7], 256);
-#endif
       if (++g_seg == g_nsrc) {  // on to the next tile
         g_seg = 0;
         next_tile(g_rt, g_jb);
@@ -175,12 +165,9 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         const int acc = k & 1;
         const uint32_t d_tmem = tmem_base + 128u * acc;
         const int nch = (int)((nch_of >> (8 * jb)) & 0xffu);
-        MB_TRACE(6, g);
         for (int c = 0; c < nch; ++c, ++g) {
           const uint32_t ab = g & 3, slot = g % PS_W_SLOTS;
-          MB_TRACE(0, g);
           if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);  // A rows stored and W tiles landed
-          MB_TRACE(1, g);
           MB_T(0);
           MB_T(1);
           if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
@@ -192,22 +179,15 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
             const uint64_t adv = (uint64_t)(2 * kk);
-#ifdef MB_DBG_NO_MMA
-            continue;
-#endif
-#ifndef MB_DBG_ONE_MMA
             umma_tf32_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (c > 0 || kk > 0) ? 1u : 0u);
             umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
-#endif
             umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
           }
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                        :: "r"(chunk_done + 8 * ab) : "memory");
-          MB_TRACE(7, g);
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(d_full + 8 * acc) : "memory");
-          MB_TRACE(2, g);
           MB_T(3);
         }
       }
@@ -410,10 +390,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
           }
           if (h == 0) {
             MB_T(2);
-            if (quarter == 0 && lane == 0) MB_TRACE(3, gi);
             if (gi >= 4 && alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);  // A buffer ab is free again
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (quarter == 0 && lane == 0) MB_TRACE(4, gi);
             MB_T(3);
           }
           MB_TMEM_ST16(ta + 16 * h, hi);
@@ -423,7 +401,6 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();  // all lanes have read their patch rows and written their A rows
         if (lane == 0) mbar_arrive(ready + 8 * ab);
-        if (quarter == 0 && lane == 0) MB_TRACE(5, gi);
         MB_T(4);
       }
       g += (uint32_t)nch;
