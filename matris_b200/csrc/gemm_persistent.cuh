@@ -5,32 +5,34 @@
 // one CTA per SM walks over many 128x128 output tiles, so that the three stages of a tile run concurrently on
 // DIFFERENT tiles instead of one after the other:
 //
-//   warps 0-7   producers.  Warp w owns rows 32(w&3).. of the tile (= its TMEM lane quarter); warps 0-3 take the even
-//               32-float K chunks, warps 4-7 the odd ones.  A chunk is gathered with cp.async (coalesced 128-byte row
+//   warps 2-9   producers.  A warp owns rows 32 (warp & 3).. of the tile (= its TMEM lane quarter); the first four
+//               take the even 32-float K chunks, the other four the odd ones.  A chunk is gathered with cp.async (coalesced 128-byte row
 //               reads through the optional index, two stages per warp) into a swizzled shared-memory patch, read back
 //               one row per thread, passed through the optional SiLU, split into tf32 hi / lo and written with
 //               tcgen05.st into one of FOUR A buffers in tensor memory.
-//   warp 17     TMA (one thread): streams W_hi / W_lo tiles into a 3-slot ring, up to three chunks ahead and across
-//               tile boundaries.
-//   warp 16     MMA (one thread): issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor
+//   warp 1      TMA (one thread): streams W_hi / W_lo tiles into a 4-slot ring, up to four chunks ahead and across
+//               tile boundaries; a column block with K = 128 is loaded once and stays (its four chunks = the ring).
+//   warp 0      MMA (one thread): issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor
 //               memory) into one of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot
 //               free) and, after a tile's last chunk, "accumulator full".
-//   warps 8-15  epilogue.  Warp 8 + e drains rows 32 (e & 3).., columns 64 (e >> 2).. of the finished accumulator
-//               (tcgen05.ld) into its own swizzled staging patch, releases the accumulator at once, and then finishes
-//               its 32 x 64 block with coalesced 256-byte row accesses while the tensor cores already work on the
-//               next tile.
+//   warps 10-17 epilogue.  Warp 10 + e reads rows 32 (warp & 3).., columns 64 (e >> 2).. of the finished accumulator into
+//               registers (tcgen05.ld), releases the accumulator at once, and then finishes its 32 x 64 block through
+//               a small swizzled patch with coalesced 128-byte row segments while the tensor cores already work on
+//               the next tile.
 //
 // Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64b (hi | lo).
-// Shared memory: W ring 96 KB | producer patches 64 KB | epilogue staging 64 KB | barriers | descriptor copy.
+// Shared memory: W ring 4 x 32 KB | producer patches 64 KB | epilogue patches 32 KB | barriers | descriptor copy.
 // Every mbarrier wait is bounded; on expiry a status word is set, the role stops waiting and runs to the common exit,
 // where tensor memory is released.
 
 constexpr int PS_THREADS = 576;          // 18 warps
-constexpr int PS_MMA_WARP = 16, PS_TMA_WARP = 17;
-constexpr int PS_W_SLOTS = 3;
+constexpr int PS_MMA_WARP = 0, PS_TMA_WARP = 1, PS_PROD_WARP0 = 2, PS_EPI_WARP0 = 10;
+// The two issuing warps come first: the warp schedulers favour the oldest (lowest-numbered) eligible warp, and the
+// MMA thread's few instructions per chunk must not queue behind the sixteen data-moving warps.
+constexpr int PS_W_SLOTS = 4;
 constexpr int PS_RING_BYTES = PS_W_SLOTS * 2 * TC_TILE_BYTES;
 constexpr int PS_PATCH_BYTES = 8 * 2 * 32 * 128;
-constexpr int PS_STAGE_BYTES = 4 * 32 * 512;
+constexpr int PS_STAGE_BYTES = 8 * 32 * 128;   // per epilogue warp: 32 rows x 32 columns, swizzled
 constexpr int PS_BAR_OFF = PS_RING_BYTES + PS_PATCH_BYTES + PS_STAGE_BYTES;
 constexpr int PS_DESC_OFF = PS_BAR_OFF + 256;
 constexpr int PS_SMEM_BYTES = PS_DESC_OFF + (int)((sizeof(mb_gemm_desc) + 15) / 16 * 16);
@@ -70,6 +72,9 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   const int n_row_tiles = (int)((n_rows + 127) >> 7);
   const int first_rt = (int)(blockIdx.x / (unsigned)n_blocks), first_jb = (int)(blockIdx.x % (unsigned)n_blocks);
   const int step_rt = (int)(gridDim.x / (unsigned)n_blocks), step_jb = (int)(gridDim.x % (unsigned)n_blocks);
+  // When every tile of this CTA belongs to the same column block and that block has a single 128-wide K segment,
+  // its four W chunks fill the four ring slots once and stay there for the whole kernel.
+  const bool w_resident = step_jb == 0 && d.blk[first_jb].n_src == 1;
   auto next_tile = [&](int& rt, int& jb) {
     jb += step_jb;
     rt += step_rt;
@@ -77,10 +82,11 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   };
 
   // ---- producer state
-  const int par = (warp >> 2) & 1, quarter = warp & 3;
+  const int pw = (warp - PS_PROD_WARP0) & 7;  // producer index 0-7 (meaningful in producer warps only)
+  const int par = pw >> 2, quarter = warp & 3;  // chunk parity set; TMEM lane quarter = warp id mod 4
   const int lr = lane >> 3, lc = lane & 7;  // 8 lanes read one row's 128 bytes, 4 rows per instruction
   // row (lr + 4i), 16-byte chunk lc -> patch[row][lc ^ (row & 7)]; (row & 7) is lr for even i and lr + 4 for odd i
-  const uint32_t patch0 = smem_u32(smem + PS_RING_BYTES + (warp & 7) * (2 * 32 * 128));
+  const uint32_t patch0 = smem_u32(smem + PS_RING_BYTES + pw * (2 * 32 * 128));
   const uint32_t dst_even = patch0 + lr * 128 + ((lc ^ lr) << 4), dst_odd = patch0 + lr * 128 + ((lc ^ (lr | 4)) << 4);
   const float* a_ptr[8];  // this lane's 8 row pointers in the current K segment, at this warp's first chunk
   int32_t a_row[8];       // source rows of the NEXT segment (looked up one chunk ahead, so the index loads are hidden)
@@ -143,7 +149,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  :: "r"(smem_u32(tmem_slot)), "r"(PS_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  } else if (warp < 8) {
+  } else if (warp >= PS_PROD_WARP0 && warp < PS_EPI_WARP0) {
     resolve_rows(first_rt, first_jb, 0);
     gather_next();
   }
@@ -153,29 +159,37 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == PS_MMA_WARP) {
-    // ---------------------------------------------------------------- control thread: TMA + MMA issue
-    if (lane == 0) {
-      bool alive = true;
-      MB_TDECL;
-      uint32_t nch_of = 0;  // chunks per tile of the (up to four) column blocks, a byte each: no descriptor read per tile
-      for (int j = 0; j < n_blocks; ++j) nch_of |= (uint32_t)(d.blk[j].n_src * 4) << (8 * j);
-      uint32_t g = 0;  // chunks issued so far (all tiles); a multiple of 4 at every tile start
-      int k = 0;
-      for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
-        const int acc = k & 1;
-        const uint32_t d_tmem = tmem_base + 128u * acc;
-        const int nch = (int)((nch_of >> (8 * jb)) & 0xffu);
-        for (int c = 0; c < nch; ++c, ++g) {
-          const uint32_t ab = g & 3, slot = g % PS_W_SLOTS;
-          if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);  // A rows stored and W tiles landed
-          MB_T(0);
-          MB_T(1);
-          if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
-          MB_T(2);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t wb = ring + slot * 2 * TC_TILE_BYTES;
-          const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
-          const uint32_t ta_hi = tmem_base + 256 + 64 * ab, ta_lo = ta_hi + 32;
+    // ---------------------------------------------------------------- MMA warp
+    // The whole warp runs the loop and computes the (warp-uniform) addresses and descriptors; one elected lane issues
+    // the tcgen05 instructions.  Their operands must sit in uniform registers: computed by a single lane inside a
+    // divergent branch they would each be moved there one by one in front of every MMA, which costs more than the MMA.
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
+    bool alive = true;
+    MB_TDECL;
+    uint32_t nch_of = 0;  // chunks per tile of the (up to four) column blocks, a byte each: no descriptor read per tile
+    for (int j = 0; j < n_blocks; ++j) nch_of |= (uint32_t)(d.blk[j].n_src * 4) << (8 * j);
+    nch_of = __shfl_sync(0xffffffffu, nch_of, 0);
+    uint32_t g = 0;  // chunks issued so far (all tiles); a multiple of 4 at every tile start
+    int k = 0;
+    for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
+      const int acc = k & 1;
+      const uint32_t d_tmem = tmem_u + 128u * acc;
+      const int nch = (int)((nch_of >> (8 * jb)) & 0xffu);
+      for (int c = 0; c < nch; ++c, ++g) {
+        const uint32_t ab = g & 3, slot = ab;  // A buffer and W slot of chunk g
+        if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);  // A rows stored and W tiles landed
+        MB_T(0);
+        if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
+        alive = __all_sync(0xffffffffu, alive);
+        MB_T(2);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t wb = ring_u + slot * 2 * TC_TILE_BYTES;
+        const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
+        const uint32_t ta_hi = tmem_u + 256 + 64 * ab, ta_lo = ta_hi + 32;
+        if (elected) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
             const uint64_t adv = (uint64_t)(2 * kk);
@@ -188,43 +202,51 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(d_full + 8 * acc) : "memory");
-          MB_T(3);
         }
+        __syncwarp();
+        MB_T(3);
       }
-      MB_TFLUSH(8, 4);
     }
+#ifdef MB_GEMM_TIMING
+    if (lane == 0) MB_TFLUSH(8, 4);
+#endif
   } else if (warp == PS_TMA_WARP) {
-    // ---------------------------------------------------------------- TMA thread: W_hi / W_lo tiles, up to 3 chunks ahead
+    // ---------------------------------------------------------------- TMA thread: W_hi / W_lo tiles, up to 4 chunks ahead
     if (lane == 0) {
       bool alive = true;
       uint32_t w_g = 0;
       for (int rt = first_rt, jb = first_jb; rt < n_row_tiles && alive; next_tile(rt, jb)) {
         const int nch = d.blk[jb].n_src * 4;
         for (int c = 0; c < nch && alive; ++c, ++w_g) {
-          const uint32_t slot = w_g % PS_W_SLOTS;
-          // the slot was last read by chunk w_g - 3
-          if (w_g >= PS_W_SLOTS) alive = mbar_wait(chunk_done + 8 * ((w_g - PS_W_SLOTS) & 3), ((w_g - PS_W_SLOTS) >> 2) & 1);
+          const uint32_t slot = w_g & 3;
+          // slot and barrier were last used by chunk w_g - 4
+          if (w_g >= 4) alive = mbar_wait(chunk_done + 8 * slot, ((w_g >> 2) - 1) & 1);
           if (!alive) break;
-          const uint32_t bar = ready + 8 * (w_g & 3), dst = ring + slot * 2 * TC_TILE_BYTES;
+          const uint32_t bar = ready + 8 * slot;
+          if (w_resident && w_g >= 4) {  // the chunk is in its slot already: only this thread's arrival is due
+            mbar_arrive(bar);
+            continue;
+          }
+          const uint32_t dst = ring + slot * 2 * TC_TILE_BYTES;
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
           tma_load_2d(dst, &maps.m[jb][0], bar, c * TC_BK, 0);
           tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, c * TC_BK, 0);
         }
       }
       if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
-        for (uint32_t i = w_g >= PS_W_SLOTS ? w_g - PS_W_SLOTS : 0; i < w_g; ++i)
-          mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
+        for (uint32_t i = w_g >= 4 ? w_g - 4 : 0; i < w_g; ++i) mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= PS_EPI_WARP0) {
     // ---------------------------------------------------------------- epilogue warps
-    // Warp 8 + e drains rows 32 (e & 3).. (its TMEM lane quarter), columns 64 (e >> 2).. of the accumulator.
-    const int e = warp - 8, quarter_e = e & 3, half = e >> 2;
-    uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 256);  // 32 rows x 256 bytes, swizzled
+    // Epilogue warp e drains rows 32 (warp & 3).. (its TMEM lane quarter), columns 64 (e >> 2).. of the accumulator, 32 columns
+    // at a time: tcgen05.ld (thread = row) -> 4 KB swizzled patch -> rows finished with 8 lanes per 128-byte row
+    // segment, four rows per instruction.
+    const int e = warp - PS_EPI_WARP0, quarter_e = warp & 3, half = e >> 2;
+    uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 128);
     const uint32_t stage_u = smem_u32(stage);
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter_e * 32) << 16) + (uint32_t)(half * 64);
-    const int sub = lane >> 4, ch = lane & 15;  // finishing: 16 lanes cover one row's 256 bytes, two rows per instruction
-    const int col = half * 64 + ch * 4;
+    const int sub = lane >> 3, ch = lane & 7;
     bool alive = true;
     MB_TDECL;
     int k = 0;
@@ -237,12 +259,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       const int32_t* const out_idx = cb.out_idx;
       float* const out = cb.out;
       const int64_t ld_gate = cb.ld_gate, ld_res = cb.ld_res, ld_out = cb.ld_out;
-      const int gcol = cb.col_gate + col, rcol = cb.col_res + col, ocol = cb.col_out + col;
       const int mode = cb.mode, out_act = cb.out_act;
       const float sc = cb.out_scale;
-      float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), resw4 = make_float4(1.f, 1.f, 1.f, 1.f);
-      if (cb.bias) bias4 = ld4(cb.bias + col);
-      if (res && cb.res_w) resw4 = ld4(cb.res_w + col);
       const int64_t left = n_rows - row0;
       const int rows_here = left >= 32 ? 32 : (left > 0 ? (int)left : 0);
       // the rows this warp will read in the epilogue are pulled into L2 while the tile is still being multiplied
@@ -261,88 +279,93 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       alive = __all_sync(0xffffffffu, alive);
       MB_T(0);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // (1) accumulator row (thread = row) -> staging; 16-byte chunk c of row r sits at position c ^ (r & 15)
-#pragma unroll 1
-      for (int cg = 0; cg < 2; ++cg) {
-        uint32_t v[32];
-        MB_TMEM_LD32(lane_base + 128u * acc + (uint32_t)(cg * 32), v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const uint32_t addr = stage_u + lane * 256 + (((cg * 8 + q) ^ (lane & 15)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                       :: "r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3]) : "memory");
-        }
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the tensor cores may overwrite this accumulator now
-      MB_T(1);
-      if (!alive) continue;
-      // (2) two rows per instruction, in batches of four instructions: all global reads of a batch are issued
-      //     before their first use
-      constexpr int RB = 4;
-      const float* const gate0 = gate ? gate + row0 * ld_gate + gcol : nullptr;
-      const float* const res0 = res ? res + row0 * ld_res + rcol : nullptr;
-      float* const out0 = out + (out_idx ? 0 : row0 * ld_out) + ocol;
-      const float4 bsc = make_float4(bias4.x * sc, bias4.y * sc, bias4.z * sc, bias4.w * sc);
-      auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
-        constexpr bool plain = !decltype(has_gate)::value && !decltype(has_act)::value && !decltype(has_res)::value;
-#pragma unroll 1
-        for (int r0 = 0; r0 < rows_here; r0 += 2 * RB) {
-          float4 z[RB], x[RB], av[RB];
-          int32_t dr[RB];
-#pragma unroll
-          for (int i = 0; i < RB; ++i) {
-            const int rq = r0 + 2 * i + sub;
-            const int rr = rq < rows_here ? rq : r0;
-            if constexpr (decltype(has_gate)::value) z[i] = ld4(gate0 + rr * ld_gate);
-            if constexpr (decltype(has_res)::value) x[i] = ld4(res0 + rr * ld_res);
-            dr[i] = out_idx ? out_idx[row0 + rr] : rr;
-            av[i] = *reinterpret_cast<const float4*>(stage + rq * 256 + ((ch ^ (rq & 15)) << 4));
-          }
-#pragma unroll
-          for (int i = 0; i < RB; ++i) {
-            const int rq = r0 + 2 * i + sub;
-            const float4 a = av[i];
-            float4 ov;
-            if constexpr (plain) {
-              ov = make_float4(fmaf(a.x, sc, bsc.x), fmaf(a.y, sc, bsc.y), fmaf(a.z, sc, bsc.z), fmaf(a.w, sc, bsc.w));
-            } else {
-              float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
-              if constexpr (decltype(has_gate)::value) {
-                o[0] *= silu_grad_fast_f(z[i].x); o[1] *= silu_grad_fast_f(z[i].y);
-                o[2] *= silu_grad_fast_f(z[i].z); o[3] *= silu_grad_fast_f(z[i].w);
-              }
-              if constexpr (decltype(has_act)::value) {
-                o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
-              }
-              if constexpr (decltype(has_res)::value) {
-                o[0] = fmaf(resw4.x, x[i].x, o[0]); o[1] = fmaf(resw4.y, x[i].y, o[1]);
-                o[2] = fmaf(resw4.z, x[i].z, o[2]); o[3] = fmaf(resw4.w, x[i].w, o[3]);
-              }
-              ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
-            }
-            float* dst = out0 + dr[i] * ld_out;
-            if (rq < rows_here) {
-              // accumulate = one reduction at the memory side: the same single fp32 addition as read-add-write
-              // when nobody else touches the row, without the read's round trip
-              if (mode == MB_OUT_STORE) *reinterpret_cast<float4*>(dst) = ov;
-              else atomicAdd(reinterpret_cast<float4*>(dst), ov);
-            }
-          }
-        }
-      };
       using T = std::true_type;
       using F = std::false_type;
-      auto pick_res = [&](auto g_, auto a_) { if (res) finish_rows(g_, a_, T{}); else finish_rows(g_, a_, F{}); };
-      auto pick_act = [&](auto g_) { if (out_act) pick_res(g_, T{}); else pick_res(g_, F{}); };
-      if (gate) pick_act(T{}); else pick_act(F{});
-      __syncwarp();  // the staging patch is rewritten by the next tile
+#pragma unroll 1
+      for (int pass = 0; pass < 2; ++pass) {
+        // (1) 32 rows x 32 columns -> patch; 16-byte chunk q of row r sits at position q ^ (r & 7)
+        {
+          uint32_t v[32];
+          MB_TMEM_LD32(lane_base + 128u * acc + 32u * pass, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t addr = stage_u + lane * 128 + ((q ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                         :: "r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3]) : "memory");
+          }
+        }
+        if (pass == 1) asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (pass == 1 && lane == 0) mbar_arrive(d_free + 8 * acc);  // the tensor cores may overwrite this accumulator now
+        if (!alive) continue;
+        // (2) four rows per instruction, in batches of four instructions: all global reads of a batch are issued
+        //     before their first use
+        const int col = half * 64 + pass * 32 + ch * 4;
+        float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), resw4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (cb.bias) bias4 = ld4(cb.bias + col);
+        if (res && cb.res_w) resw4 = ld4(cb.res_w + col);
+        const float* const gate0 = gate ? gate + row0 * ld_gate + cb.col_gate + col : nullptr;
+        const float* const res0 = res ? res + row0 * ld_res + cb.col_res + col : nullptr;
+        float* const out0 = out + (out_idx ? 0 : row0 * ld_out) + cb.col_out + col;
+        const float4 bsc = make_float4(bias4.x * sc, bias4.y * sc, bias4.z * sc, bias4.w * sc);
+        constexpr int RB = 4;
+        auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
+          constexpr bool plain = !decltype(has_gate)::value && !decltype(has_act)::value && !decltype(has_res)::value;
+#pragma unroll 1
+          for (int r0 = 0; r0 < rows_here; r0 += 4 * RB) {
+            float4 z[RB], x[RB], av[RB];
+            int32_t dr[RB];
+#pragma unroll
+            for (int i = 0; i < RB; ++i) {
+              const int rq = r0 + 4 * i + sub;
+              const int rr = rq < rows_here ? rq : r0;
+              if constexpr (decltype(has_gate)::value) z[i] = ld4(gate0 + rr * ld_gate);
+              if constexpr (decltype(has_res)::value) x[i] = ld4(res0 + rr * ld_res);
+              dr[i] = out_idx ? out_idx[row0 + rr] : rr;
+              av[i] = *reinterpret_cast<const float4*>(stage + rq * 128 + ((ch ^ (rq & 7)) << 4));
+            }
+#pragma unroll
+            for (int i = 0; i < RB; ++i) {
+              const int rq = r0 + 4 * i + sub;
+              const float4 a = av[i];
+              float4 ov;
+              if constexpr (plain) {
+                ov = make_float4(fmaf(a.x, sc, bsc.x), fmaf(a.y, sc, bsc.y), fmaf(a.z, sc, bsc.z), fmaf(a.w, sc, bsc.w));
+              } else {
+                float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
+                if constexpr (decltype(has_gate)::value) {
+                  o[0] *= silu_grad_fast_f(z[i].x); o[1] *= silu_grad_fast_f(z[i].y);
+                  o[2] *= silu_grad_fast_f(z[i].z); o[3] *= silu_grad_fast_f(z[i].w);
+                }
+                if constexpr (decltype(has_act)::value) {
+                  o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
+                }
+                if constexpr (decltype(has_res)::value) {
+                  o[0] = fmaf(resw4.x, x[i].x, o[0]); o[1] = fmaf(resw4.y, x[i].y, o[1]);
+                  o[2] = fmaf(resw4.z, x[i].z, o[2]); o[3] = fmaf(resw4.w, x[i].w, o[3]);
+                }
+                ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
+              }
+              float* dst = out0 + dr[i] * ld_out;
+              if (rq < rows_here) {
+                // accumulate = one reduction at the memory side: the same single fp32 addition as read-add-write
+                // when nobody else touches the row, without the read's round trip
+                if (mode == MB_OUT_STORE) *reinterpret_cast<float4*>(dst) = ov;
+                else atomicAdd(reinterpret_cast<float4*>(dst), ov);
+              }
+            }
+          }
+        };
+        auto pick_res = [&](auto g_, auto a_) { if (res) finish_rows(g_, a_, T{}); else finish_rows(g_, a_, F{}); };
+        auto pick_act = [&](auto g_) { if (out_act) pick_res(g_, T{}); else pick_res(g_, F{}); };
+        if (gate) pick_act(T{}); else pick_act(F{});
+        __syncwarp();  // the patch is rewritten by the next pass / tile
+      }
       MB_T(2);
     }
 #ifdef MB_GEMM_TIMING
-    if (warp == 8 && lane == 0) MB_TFLUSH(16, 3);
+    if (warp == PS_EPI_WARP0 && lane == 0) MB_TFLUSH(16, 3);
 #endif
   } else {
     // ---------------------------------------------------------------- producers: thread = row = TMEM lane
@@ -407,7 +430,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #ifdef MB_GEMM_TIMING
-    if (tid == 0) MB_TFLUSH(0, 8);
+    if (warp == PS_PROD_WARP0 && lane == 0) MB_TFLUSH(0, 8);
 #endif
   }
 
