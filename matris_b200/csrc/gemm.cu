@@ -704,7 +704,18 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
       if (rc) return rc;
     }
     const long long n_tiles = gx * desc->n_blocks;
-    if (mb::g_gemm_mode == 0) {
+    // the persistent kernel's epilogue uses 32-byte accesses; operands aligned to 16 bytes only take the tile kernel
+    bool wide_ok = true;
+    for (int j = 0; j < desc->n_blocks; ++j) {
+      const mb_colblock& cb = desc->blk[j];
+      auto ok32 = [](const void* p, int64_t ld, int col) {
+        return (reinterpret_cast<uintptr_t>(p) & 31) == 0 && (ld & 7) == 0 && (col & 7) == 0;
+      };
+      wide_ok = wide_ok && ok32(cb.out, cb.ld_out, cb.col_out) && (!cb.gate || ok32(cb.gate, cb.ld_gate, cb.col_gate)) &&
+                (!cb.res || ok32(cb.res, cb.ld_res, cb.col_res)) && (!cb.bias || ok32(cb.bias, 0, 0)) &&
+                (!cb.res_w || ok32(cb.res_w, 0, 0));
+    }
+    if (mb::g_gemm_mode == 0 && wide_ok) {
       const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
       mb::k_gemm_ps<<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
     } else {

@@ -16,14 +16,24 @@
 //               memory) into one of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot
 //               free) and, after a tile's last chunk, "accumulator full".
 //   warps 10-17 epilogue.  Warp 10 + e reads rows 32 (warp & 3).., columns 64 (e >> 2).. of the finished accumulator into
-//               registers (tcgen05.ld), releases the accumulator at once, and then finishes its 32 x 64 block through
-//               a small swizzled patch with coalesced 128-byte row segments while the tensor cores already work on
-//               the next tile.
+//               registers (tcgen05.ld, thread = row), releases the accumulator, and finishes its rows there with
+//               256-bit global loads / stores (a full 32-byte sector per thread) while the tensor cores already work
+//               on the next tile.
 //
 // Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64b (hi | lo).
 // Shared memory: W ring 4 x 32 KB | producer patches 64 KB | epilogue patches 32 KB | barriers | descriptor copy.
 // Every mbarrier wait is bounded; on expiry a status word is set, the role stops waiting and runs to the common exit,
 // where tensor memory is released.
+
+// 256-bit global accesses (one full 32-byte sector per thread)
+__device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
+  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(p));
+}
+__device__ __forceinline__ void st8(float* p, const float (&v)[8]) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               :: "l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
 
 constexpr int PS_THREADS = 576;          // 18 warps
 constexpr int PS_MMA_WARP = 0, PS_TMA_WARP = 1, PS_PROD_WARP0 = 2, PS_EPI_WARP0 = 10;
@@ -32,7 +42,7 @@ constexpr int PS_MMA_WARP = 0, PS_TMA_WARP = 1, PS_PROD_WARP0 = 2, PS_EPI_WARP0 
 constexpr int PS_W_SLOTS = 4;
 constexpr int PS_RING_BYTES = PS_W_SLOTS * 2 * TC_TILE_BYTES;
 constexpr int PS_PATCH_BYTES = 8 * 2 * 32 * 128;
-constexpr int PS_STAGE_BYTES = 8 * 32 * 128;   // per epilogue warp: 32 rows x 32 columns, swizzled
+constexpr int PS_STAGE_BYTES = 8 * 32 * 128;   // per epilogue warp: 32 rows x 32 columns (scatter / accumulate modes only)
 constexpr int PS_BAR_OFF = PS_RING_BYTES + PS_PATCH_BYTES + PS_STAGE_BYTES;
 constexpr int PS_DESC_OFF = PS_BAR_OFF + 256;
 constexpr int PS_SMEM_BYTES = PS_DESC_OFF + (int)((sizeof(mb_gemm_desc) + 15) / 16 * 16);
@@ -211,157 +221,210 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     if (lane == 0) MB_TFLUSH(8, 4);
 #endif
   } else if (warp == PS_TMA_WARP) {
-    // ---------------------------------------------------------------- TMA thread: W_hi / W_lo tiles, up to 4 chunks ahead
-    if (lane == 0) {
-      bool alive = true;
-      uint32_t w_g = 0;
-      for (int rt = first_rt, jb = first_jb; rt < n_row_tiles && alive; next_tile(rt, jb)) {
-        const int nch = d.blk[jb].n_src * 4;
-        for (int c = 0; c < nch && alive; ++c, ++w_g) {
-          const uint32_t slot = w_g & 3;
-          // slot and barrier were last used by chunk w_g - 4
-          if (w_g >= 4) alive = mbar_wait(chunk_done + 8 * slot, ((w_g >> 2) - 1) & 1);
-          if (!alive) break;
-          const uint32_t bar = ready + 8 * slot;
+    // ---------------------------------------------------------------- TMA warp: W_hi / W_lo tiles, up to 4 chunks ahead
+    // (warp-uniform loop, one elected lane issues: same reason as in the MMA warp)
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
+    bool alive = true;
+    uint32_t w_g = 0;
+    for (int rt = first_rt, jb = first_jb; rt < n_row_tiles && alive; next_tile(rt, jb)) {
+      const int nch = __shfl_sync(0xffffffffu, d.blk[jb].n_src * 4, 0);
+      for (int c = 0; c < nch && alive; ++c, ++w_g) {
+        const uint32_t slot = w_g & 3;
+        // slot and barrier were last used by chunk w_g - 4
+        if (w_g >= 4) alive = mbar_wait(chunk_done + 8 * slot, ((w_g >> 2) - 1) & 1);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
+        const uint32_t bar = ready + 8 * slot;
+        if (elected) {
           if (w_resident && w_g >= 4) {  // the chunk is in its slot already: only this thread's arrival is due
             mbar_arrive(bar);
-            continue;
+          } else {
+            const uint32_t dst = ring_u + slot * 2 * TC_TILE_BYTES;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
+            tma_load_2d(dst, &maps.m[jb][0], bar, c * TC_BK, 0);
+            tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, c * TC_BK, 0);
           }
-          const uint32_t dst = ring + slot * 2 * TC_TILE_BYTES;
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
-          tma_load_2d(dst, &maps.m[jb][0], bar, c * TC_BK, 0);
-          tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, c * TC_BK, 0);
         }
+        __syncwarp();
       }
-      if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
-        for (uint32_t i = w_g >= 4 ? w_g - 4 : 0; i < w_g; ++i) mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
-      }
+    }
+    if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
+      for (uint32_t i = w_g >= 4 ? w_g - 4 : 0; i < w_g; ++i) mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
     }
   } else if (warp >= PS_EPI_WARP0) {
     // ---------------------------------------------------------------- epilogue warps
-    // Epilogue warp e drains rows 32 (warp & 3).. (its TMEM lane quarter), columns 64 (e >> 2).. of the accumulator, 32 columns
-    // at a time: tcgen05.ld (thread = row) -> 4 KB swizzled patch -> rows finished with 8 lanes per 128-byte row
-    // segment, four rows per instruction.
+    // Epilogue warp e finishes rows 32 (warp & 3).. (its TMEM lane quarter), columns 64 (e >> 2).. of the accumulator
+    // straight from the tcgen05.ld layout: thread = row, 32 columns per load, global accesses of 32 bytes (one full
+    // sector) per thread with 256-bit loads and stores.  No shared-memory staging: every sector is still written
+    // exactly once, and the row's sixteen sectors merge in L2.
     const int e = warp - PS_EPI_WARP0, quarter_e = warp & 3, half = e >> 2;
-    uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 128);
-    const uint32_t stage_u = smem_u32(stage);
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter_e * 32) << 16) + (uint32_t)(half * 64);
-    const int sub = lane >> 3, ch = lane & 7;
     bool alive = true;
     MB_TDECL;
     int k = 0;
     for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
       const int acc = k & 1;
-      const int64_t row0 = (int64_t)rt * 128 + quarter_e * 32;  // first row of this warp
+      const int64_t row = (int64_t)rt * 128 + quarter_e * 32 + lane;  // this thread's row
+      const bool valid = row < n_rows;
+      const int64_t rowc = valid ? row : n_rows - 1;
       const mb_colblock& cb = d.blk[jb];
-      const float* const gate = cb.gate;
-      const float* const res = cb.res;
-      const int32_t* const out_idx = cb.out_idx;
-      float* const out = cb.out;
-      const int64_t ld_gate = cb.ld_gate, ld_res = cb.ld_res, ld_out = cb.ld_out;
+      const int c0 = half * 64;
+      const float* const gate = cb.gate ? cb.gate + rowc * cb.ld_gate + cb.col_gate + c0 : nullptr;
+      const float* const res = cb.res ? cb.res + rowc * cb.ld_res + cb.col_res + c0 : nullptr;
+      const float* const bias = cb.bias ? cb.bias + c0 : nullptr;
+      const float* const res_w = (cb.res && cb.res_w) ? cb.res_w + c0 : nullptr;
+      const int64_t dr = cb.out_idx ? (int64_t)cb.out_idx[rowc] : rowc;
+      float* const out = cb.out + dr * cb.ld_out + cb.col_out + c0;
       const int mode = cb.mode, out_act = cb.out_act;
       const float sc = cb.out_scale;
-      const int64_t left = n_rows - row0;
-      const int rows_here = left >= 32 ? 32 : (left > 0 ? (int)left : 0);
-      // the rows this warp will read in the epilogue are pulled into L2 while the tile is still being multiplied
-      if (gate || res) {
-        const int part = lane & 1;  // 16 rows x two 128-byte lines per pass
-#pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          const int rr = p * 16 + (lane >> 1);
-          if (rr < rows_here) {
-            if (gate) asm volatile("prefetch.global.L2 [%0];" :: "l"(gate + (row0 + rr) * ld_gate + cb.col_gate + half * 64 + part * 32));
-            if (res) asm volatile("prefetch.global.L2 [%0];" :: "l"(res + (row0 + rr) * ld_res + cb.col_res + half * 64 + part * 32));
-          }
-        }
+      // the row segments this thread will read are pulled into L2 while the tile is still being multiplied
+      if (gate) {
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(gate));
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(gate + 32));
+      }
+      if (res) {
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(res));
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(res + 32));
       }
       if (alive) alive = mbar_wait(d_full + 8 * acc, (uint32_t)((k >> 1) & 1));
       alive = __all_sync(0xffffffffu, alive);
       MB_T(0);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      using T = std::true_type;
-      using F = std::false_type;
+      auto finish = [&](auto has_gate, auto has_act, auto has_res) {
 #pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-        // (1) 32 rows x 32 columns -> patch; 16-byte chunk q of row r sits at position q ^ (r & 7)
-        {
+        for (int cg = 0; cg < 2; ++cg) {
           uint32_t v[32];
-          MB_TMEM_LD32(lane_base + 128u * acc + 32u * pass, v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          MB_TMEM_LD32(lane_base + 128u * acc + 32u * cg, v);
+          // the gate values of these 32 columns are requested before the accumulator load is waited for, all four
+          // 32-byte pieces at once: one memory latency per 32 columns instead of four
+          float z[decltype(has_gate)::value ? 4 : 1][8];
+          if constexpr (decltype(has_gate)::value) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const uint32_t addr = stage_u + lane * 128 + ((q ^ (lane & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                         :: "r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3]) : "memory");
+            for (int j = 0; j < 4; ++j) ld8(gate + cg * 32 + j * 8, z[j]);
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (cg == 1) {  // the accumulator is in registers: the tensor cores may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_free + 8 * acc);
+          }
+          if (!alive) continue;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = cg * 32 + j * 8;
+            float o[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) o[q] = __uint_as_float(v[8 * j + q]);
+            if (bias) {  // same address in every lane: a broadcast load
+              float bv[8];
+              ld8(bias + c, bv);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) o[q] += bv[q];
+            }
+            if constexpr (decltype(has_gate)::value) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) o[q] *= silu_grad_fast_f(z[j][q]);
+            }
+            if constexpr (decltype(has_act)::value) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) o[q] = silu_fast_f(o[q]);
+            }
+            if constexpr (decltype(has_res)::value) {
+              float x[8];
+              ld8(res + c, x);
+              if (res_w) {
+                float w[8];
+                ld8(res_w + c, w);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) o[q] = fmaf(w[q], x[q], o[q]);
+              } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) o[q] += x[q];
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) o[q] *= sc;
+            if (valid) {
+              st8(out + c, o);
+            }
           }
         }
-        if (pass == 1) asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (pass == 1 && lane == 0) mbar_arrive(d_free + 8 * acc);  // the tensor cores may overwrite this accumulator now
-        if (!alive) continue;
-        // (2) four rows per instruction, in batches of four instructions: all global reads of a batch are issued
-        //     before their first use
-        const int col = half * 64 + pass * 32 + ch * 4;
-        float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), resw4 = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (cb.bias) bias4 = ld4(cb.bias + col);
-        if (res && cb.res_w) resw4 = ld4(cb.res_w + col);
-        const float* const gate0 = gate ? gate + row0 * ld_gate + cb.col_gate + col : nullptr;
-        const float* const res0 = res ? res + row0 * ld_res + cb.col_res + col : nullptr;
-        float* const out0 = out + (out_idx ? 0 : row0 * ld_out) + cb.col_out + col;
-        const float4 bsc = make_float4(bias4.x * sc, bias4.y * sc, bias4.z * sc, bias4.w * sc);
-        constexpr int RB = 4;
-        auto finish_rows = [&](auto has_gate, auto has_act, auto has_res) {
-          constexpr bool plain = !decltype(has_gate)::value && !decltype(has_act)::value && !decltype(has_res)::value;
+      };
+      // Scatter / accumulate modes go through a 4 KB swizzled patch instead, 32 columns at a time, so that eight lanes
+      // cover one row's 128 contiguous bytes: the memory-side reductions then arrive as four 128-byte requests per
+      // instruction, not as 32 requests of 16 bytes (which the direct layout would give).
+      auto finish_reduce = [&]() {
+        uint8_t* const stage = smem + PS_RING_BYTES + PS_PATCH_BYTES + e * (32 * 128);
+        const uint32_t stage_u = smem_u32(stage);
+        const int sub = lane >> 3, ch = lane & 7;
+        const int64_t row0 = (int64_t)rt * 128 + quarter_e * 32;
+        const int64_t left = n_rows - row0;
+        const int rows_here = left >= 32 ? 32 : (left > 0 ? (int)left : 0);
 #pragma unroll 1
-          for (int r0 = 0; r0 < rows_here; r0 += 4 * RB) {
-            float4 z[RB], x[RB], av[RB];
-            int32_t dr[RB];
+        for (int pass = 0; pass < 2; ++pass) {
+          {
+            uint32_t v[32];
+            MB_TMEM_LD32(lane_base + 128u * acc + 32u * pass, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < RB; ++i) {
+            for (int q = 0; q < 8; ++q) {  // 16-byte chunk q of row r sits at position q ^ (r & 7)
+              const uint32_t addr = stage_u + lane * 128 + ((q ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                           :: "r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3]) : "memory");
+            }
+          }
+          if (pass == 1) asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (pass == 1 && lane == 0) mbar_arrive(d_free + 8 * acc);
+          if (!alive) continue;
+          const int col = c0 + pass * 32 + ch * 4;  // column within the 128-wide block
+          float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), resw4 = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (cb.bias) bias4 = ld4(cb.bias + col);
+          if (cb.res && cb.res_w) resw4 = ld4(cb.res_w + col);
+#pragma unroll 1
+          for (int r0 = 0; r0 < rows_here; r0 += 16) {
+            float4 av[4];
+            int64_t drow[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
               const int rq = r0 + 4 * i + sub;
-              const int rr = rq < rows_here ? rq : r0;
-              if constexpr (decltype(has_gate)::value) z[i] = ld4(gate0 + rr * ld_gate);
-              if constexpr (decltype(has_res)::value) x[i] = ld4(res0 + rr * ld_res);
-              dr[i] = out_idx ? out_idx[row0 + rr] : rr;
+              const int64_t gr = row0 + (rq < rows_here ? rq : r0);
+              drow[i] = cb.out_idx ? (int64_t)cb.out_idx[gr] : gr;
               av[i] = *reinterpret_cast<const float4*>(stage + rq * 128 + ((ch ^ (rq & 7)) << 4));
             }
 #pragma unroll
-            for (int i = 0; i < RB; ++i) {
+            for (int i = 0; i < 4; ++i) {
               const int rq = r0 + 4 * i + sub;
-              const float4 a = av[i];
-              float4 ov;
-              if constexpr (plain) {
-                ov = make_float4(fmaf(a.x, sc, bsc.x), fmaf(a.y, sc, bsc.y), fmaf(a.z, sc, bsc.z), fmaf(a.w, sc, bsc.w));
-              } else {
-                float o[4] = {a.x + bias4.x, a.y + bias4.y, a.z + bias4.z, a.w + bias4.w};
-                if constexpr (decltype(has_gate)::value) {
-                  o[0] *= silu_grad_fast_f(z[i].x); o[1] *= silu_grad_fast_f(z[i].y);
-                  o[2] *= silu_grad_fast_f(z[i].z); o[3] *= silu_grad_fast_f(z[i].w);
-                }
-                if constexpr (decltype(has_act)::value) {
-                  o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]);
-                }
-                if constexpr (decltype(has_res)::value) {
-                  o[0] = fmaf(resw4.x, x[i].x, o[0]); o[1] = fmaf(resw4.y, x[i].y, o[1]);
-                  o[2] = fmaf(resw4.z, x[i].z, o[2]); o[3] = fmaf(resw4.w, x[i].w, o[3]);
-                }
-                ov = make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc);
+              const int64_t gr = row0 + (rq < rows_here ? rq : r0);
+              float o[4] = {av[i].x + bias4.x, av[i].y + bias4.y, av[i].z + bias4.z, av[i].w + bias4.w};
+              if (cb.gate) {
+                const float4 z = ld4(cb.gate + gr * cb.ld_gate + cb.col_gate + col);
+                o[0] *= silu_grad_fast_f(z.x); o[1] *= silu_grad_fast_f(z.y); o[2] *= silu_grad_fast_f(z.z); o[3] *= silu_grad_fast_f(z.w);
               }
-              float* dst = out0 + dr[i] * ld_out;
-              if (rq < rows_here) {
-                // accumulate = one reduction at the memory side: the same single fp32 addition as read-add-write
-                // when nobody else touches the row, without the read's round trip
-                if (mode == MB_OUT_STORE) *reinterpret_cast<float4*>(dst) = ov;
-                else atomicAdd(reinterpret_cast<float4*>(dst), ov);
+              if (out_act) { o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]); }
+              if (cb.res) {
+                const float4 x = ld4(cb.res + gr * cb.ld_res + cb.col_res + col);
+                o[0] = fmaf(resw4.x, x.x, o[0]); o[1] = fmaf(resw4.y, x.y, o[1]); o[2] = fmaf(resw4.z, x.z, o[2]); o[3] = fmaf(resw4.w, x.w, o[3]);
               }
+              // accumulate = one reduction at the memory side: the same single fp32 addition as read-add-write
+              // when nobody else touches the row, without the read's round trip
+              if (rq < rows_here)
+                atomicAdd(reinterpret_cast<float4*>(cb.out + drow[i] * cb.ld_out + cb.col_out + col),
+                          make_float4(o[0] * sc, o[1] * sc, o[2] * sc, o[3] * sc));
             }
           }
-        };
-        auto pick_res = [&](auto g_, auto a_) { if (res) finish_rows(g_, a_, T{}); else finish_rows(g_, a_, F{}); };
-        auto pick_act = [&](auto g_) { if (out_act) pick_res(g_, T{}); else pick_res(g_, F{}); };
-        if (gate) pick_act(T{}); else pick_act(F{});
-        __syncwarp();  // the patch is rewritten by the next pass / tile
-      }
+          __syncwarp();  // the patch is rewritten by the next pass / tile
+        }
+      };
+      using T = std::true_type;
+      using F = std::false_type;
+      auto pick_res = [&](auto g_, auto a_) { if (res) finish(g_, a_, T{}); else finish(g_, a_, F{}); };
+      auto pick_act = [&](auto g_) { if (out_act) pick_res(g_, T{}); else pick_res(g_, F{}); };
+      if (mode != MB_OUT_STORE) finish_reduce();
+      else if (gate) pick_act(T{});
+      else pick_act(F{});
       MB_T(2);
     }
 #ifdef MB_GEMM_TIMING
