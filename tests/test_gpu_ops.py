@@ -75,6 +75,27 @@ def test_gemm_scatter_modes(ops):
     report("gemm accumulate", out2, base2.double() + F.linear(x.double(), W.double()), 3e-5)
 
 
+def test_gemm_large_mixed_direct_and_gathered_sources(ops):
+    """Many tiles per CTA of the persistent kernel with a mix of un-indexed and gathered A sources, a ragged last
+    tile and a column offset, against the fp32 SIMT core."""
+    R, n1 = 20000 + 37, 700
+    x, node = rnd(R, 256, seed=21) * 2, rnd(n1, 128, seed=22) * 2
+    g = torch.Generator().manual_seed(3)
+    idx = torch.randint(0, n1, (R,), generator=g)
+    W, b = rnd(256, 384, seed=23, scale=0.2), rnd(256, seed=24)
+    dx, dn, dW, db, di = dev(x), dev(node), dev(W), dev(b), dev(idx, torch.int32)
+    outs = {}
+    for mode in ("simt", "tcgen05"):
+        ops.set_gemm_mode(mode)
+        out = torch.zeros(R, 256, device="cuda")
+        srcs = [ops.S(dx, None, 128, 1), ops.S(dn, di), ops.S(dx, None, 0)]
+        ops.gemm(R, [ops.B(srcs, dW, w_row=128 * j, bias=db, bias_off=128 * j, out=out, out_col=128 * j) for j in (0, 1)])
+        assert ops.gemm_status() == 0
+        outs[mode] = out.cpu()
+    ops.set_gemm_mode("tcgen05")
+    report("tcgen05 (direct + gathered A, 157 tiles) vs simt", outs["tcgen05"], outs["simt"], 1e-5)
+
+
 def test_tensor_core_gemm_matches_fp32_simt(ops):
     """tcgen05 3xTF32 against the exact-fp32 SIMT core on the same descriptors, all epilogue paths."""
     R, n1 = 5000, 300
