@@ -167,6 +167,10 @@ int mb_set_gemm_mode(int mode);
 /* Synchronises the stream, returns and clears the tensor-core kernel's status word (bit 0: a bounded
  * mbarrier wait expired and the affected tiles were not written). */
 int mb_gemm_status(int* status, void* stream);
+/* The same status word copied to `host_status` (pinned host memory) in stream order, without synchronising and
+ * without clearing it: a caller that launches evaluation after evaluation reads the word of the previous one
+ * when it starts the next, at no cost.  No counterpart in the reference (its kernels have no bounded waits). */
+int mb_gemm_status_async(int* host_status, void* stream);
 
 /* ------------------------------------------------------------------ row-wise model kernels
  * All feature tensors are float32 row-major with 128 channels unless noted.

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "mb_gemm": [C.POINTER(MbGemmDesc), _vp],
     "mb_set_gemm_mode": [C.c_int],
     "mb_gemm_status": [C.POINTER(C.c_int), _vp],
+    "mb_gemm_status_async": [_vp, _vp],
     "mb_gate_fwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_gate_bwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_seg_attn_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],

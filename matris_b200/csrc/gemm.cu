@@ -674,6 +674,13 @@ extern "C" int mb_gemm_status(int* status, void* stream_) {
   return MB_OK;
 }
 
+extern "C" int mb_gemm_status_async(int* host_status, void* stream_) {
+  if (!host_status) return MB_ERR_INVALID;
+  MB_CUDA_CHECK(cudaMemcpyFromSymbolAsync(host_status, mb::g_gemm_status, sizeof(int), 0, cudaMemcpyDeviceToHost,
+                                          (cudaStream_t)stream_));
+  return MB_OK;
+}
+
 extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
   int rc = gemm_validate(desc);
   if (rc) return rc;

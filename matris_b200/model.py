@@ -28,6 +28,7 @@ from torch import nn
 from torch.autograd.function import once_differentiable
 
 from . import ops
+from ._lib import MbError
 from .graph import BatchedGraph, GraphConverter, RadiusGraph, build_batched_graph, as_arrays
 from .ops import B, OUT_ADD, OUT_ATOMIC, OUT_STORE, S, gemm
 from .weights import BUFFER_KEYS, check_supported, full_config, random_state_dict, schema
@@ -551,7 +552,18 @@ class MatRIS(nn.Module):
         g = self._as_batch(graphs)
         self.last_batch = g
         with torch.cuda.device(self.device):
-            return self._evaluate(g, task)
+            # The GEMM kernels bound every wait and raise a status word instead of hanging.  The word of the previous
+            # evaluation was copied to pinned memory in stream order; it is read here, so a failure surfaces at the
+            # latest one call later and costs no synchronisation.
+            flag = getattr(self, "_gemm_flag", None)
+            if flag is None:
+                flag = self._gemm_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+            elif int(flag[0]) != 0:
+                raise MbError(f"a tensor-core GEMM wait expired in an earlier evaluation (status {int(flag[0])}); "
+                              "its results were invalid")
+            out = self._evaluate(g, task)
+            ops.gemm_status_async(flag)
+            return out
 
     def _evaluate(self, g: BatchedGraph, task: str):
         cfg = self.config

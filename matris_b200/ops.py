@@ -321,6 +321,12 @@ def set_gemm_mode(mode: str) -> None:
     _lib.check(_lib.load().mb_set_gemm_mode({"tcgen05": 0, "simt": 1, "tcgen05_tile": 2}[mode]), "mb_set_gemm_mode")
 
 
+def gemm_status_async(pinned_int32: torch.Tensor) -> None:
+    """Enqueue a copy of the tensor-core kernels' status word into a pinned int32 tensor (no synchronisation)."""
+    assert pinned_int32.dtype == torch.int32 and pinned_int32.is_pinned()
+    call("mb_gemm_status_async", pinned_int32.data_ptr(), _stream())
+
+
 def gemm_status() -> int:
     """Synchronise and return (then clear) the tensor-core kernel's status word; 0 = no wait expired."""
     st = C.c_int(0)

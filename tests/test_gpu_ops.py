@@ -96,6 +96,15 @@ def test_gemm_large_mixed_direct_and_gathered_sources(ops):
     report("tcgen05 (direct + gathered A, 157 tiles) vs simt", outs["tcgen05"], outs["simt"], 1e-5)
 
 
+def test_status_word_copy_in_stream_order(ops):
+    flag = torch.full((1,), 7, dtype=torch.int32).pin_memory()
+    x, W = dev(rnd(300, 128, seed=1)), dev(rnd(128, 128, seed=2))
+    ops.linear(x, W)
+    ops.gemm_status_async(flag)
+    torch.cuda.synchronize()
+    assert int(flag[0]) == 0 and ops.gemm_status() == 0
+
+
 def test_tensor_core_gemm_matches_fp32_simt(ops):
     """tcgen05 3xTF32 against the exact-fp32 SIMT core on the same descriptors, all epilogue paths."""
     R, n1 = 5000, 300
