@@ -86,7 +86,12 @@ class MatRISCalculator(_AseCalculator):
             atoms.set_cell(cell, scale_atoms=False)
         numbers, cart, lattice = as_arrays(atoms)
         out = self.model.predict([Crystal(numbers, cart, lattice)], task=self.task)
-        n_atoms = len(numbers) if self.model.is_intensive else 1
+        self.store_output(out, len(numbers))
+
+    def store_output(self, out: dict, n_atoms_in_structure: int) -> None:
+        """Fill ``results`` from a model output dictionary (the last structure of the batch), with the reference's
+        unit conversions (base.py:115-122)."""
+        n_atoms = n_atoms_in_structure if self.model.is_intensive else 1
         get = lambda k: out[k][-1].detach().cpu().numpy() if k in out else None  # noqa: E731  (last structure)
         ref = out["ref_energy"]
         ref = ref[-1].detach().cpu().numpy() if hasattr(ref, "detach") else np.float32(ref)
@@ -195,8 +200,18 @@ class SimpleAtoms:
     def get_velocities(self): return self.momenta / self.masses[:, None]
     def __len__(self): return len(self.numbers)
 
+    def _state_key(self):
+        return (self.positions.tobytes(), self.cell.tobytes(), self.numbers.tobytes(), self.pbc.tobytes())
+
+    def mark_results_current(self) -> None:
+        """Declare ``calc.results`` valid for the present positions / cell (used by the device-resident drivers)."""
+        self._cache_key, self._cache_calc = self._state_key(), self.calc
+
     def _results(self):
-        self.calc.calculate(self)
+        # one evaluation per geometry: energy, forces, stress and magmoms of the same state share it
+        if getattr(self, "_cache_calc", None) is not self.calc or getattr(self, "_cache_key", None) != self._state_key():
+            self.calc.calculate(self)
+            self.mark_results_current()  # after calculate(): it may have enlarged the cell of a non-periodic axis
         return self.calc.results
 
     def get_potential_energy(self): return float(self._results()["energy"])
@@ -229,7 +244,10 @@ class StructOptimizer:
             atoms = SimpleAtoms(numbers, cart, lattice)
         atoms.calc = self.calculator
         obs = TrajectoryObserver(atoms)
-        fire_relax(atoms, fmax=fmax, steps=steps, observer=obs, interval=loginterval, verbose=verbose)
+        relax_fn = fire_relax
+        if kwargs.get("device_resident", True) and isinstance(atoms, SimpleAtoms) and bool(np.all(atoms.get_pbc())):
+            relax_fn = fire_relax_device
+        relax_fn(atoms, fmax=fmax, steps=steps, observer=obs, interval=loginterval, verbose=verbose)
         obs()
         if save_path is not None:
             obs.save(save_path)
@@ -309,6 +327,69 @@ def fire_relax(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, f_inc=1
         if norm > max_step:
             step *= max_step / norm
         atoms.set_positions(atoms.get_positions() + step)
+    return steps
+
+
+def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, f_inc=1.1, f_dec=0.5, alpha0=0.1,
+                      f_alpha=0.99, max_step=0.2, observer=None, interval=1, verbose=False):
+    """``fire_relax`` with positions, velocities and forces kept on the GPU (an extension; the reference's loop,
+    relax.py:116-123, goes through ASE on the host).  Per step the positions of the device-resident batch are updated
+    in place, the graph is rebuilt on the device and the model evaluated; three scalars (max force, F.v and the
+    norms) come back to the host for the FIRE decisions, and the full state only when the observer logs."""
+    import torch
+
+    from .graph import build_on_device
+
+    calc = atoms.calc
+    model, task = calc.model, calc.task
+    numbers, cart, lattice = as_arrays(atoms)
+    g = model.graph_converter.batch([Crystal(numbers, cart, lattice)])
+    x = g.cart64.clone()
+    v = torch.zeros_like(x)
+    alpha, n_pos = alpha0, 0
+
+    def push_state(out):
+        atoms.set_positions(x.cpu().numpy())
+        calc.store_output(out, len(numbers))
+        atoms.mark_results_current()
+
+    it, out = 0, None
+    for it in range(steps):
+        if it > 0:
+            g.cart64.copy_(x)
+            g.cart32.copy_(x)
+            build_on_device(g)
+        out = model(g, task=task)
+        f = out["f"][0].to(torch.float64)
+        stats = torch.stack([(f * f).sum(dim=1).max().sqrt(), (f * v).sum(), f.norm(), v.norm()]).tolist()
+        fnorm, p, f_len, v_len = stats
+        if observer is not None and it % interval == 0:
+            push_state(out)
+            observer()
+        if verbose:
+            print(f"FIRE {it:4d}  E={float(out['e'][0]) * (len(numbers) if model.is_intensive else 1):.6f}  fmax={fnorm:.5f}")
+        if fnorm < fmax:
+            push_state(out)
+            return it
+        if p > 0:
+            v = (1 - alpha) * v + (alpha * v_len / max(f_len, 1e-30)) * f
+            if n_pos > n_min:
+                dt, alpha = min(dt * f_inc, dt_max), alpha * f_alpha
+            n_pos += 1
+        else:
+            v = torch.zeros_like(v)
+            alpha, dt, n_pos = alpha0, dt * f_dec, 0
+        v = v + dt * f
+        step = dt * v
+        norm = float((step * step).sum(dim=1).max().sqrt())
+        if norm > max_step:
+            step = step * (max_step / norm)
+        x = x + step
+    # the loop ended on the step limit: evaluate the final positions so that the stored results match them
+    g.cart64.copy_(x)
+    g.cart32.copy_(x)
+    build_on_device(g)
+    push_state(model(g, task=task))
     return steps
 
 
@@ -499,12 +580,13 @@ class MolecularDynamics:
             self.steps_done += 1
             if self._logs_now():  # the only host copies inside the loop, every ``loginterval`` steps
                 frame = SimpleAtoms(numbers, x.cpu().numpy(), lattice, momenta=p.cpu().numpy())
-                n_at = len(numbers) if model.is_intensive else 1
-                self._log_frame(frame, dict(energy=out["e"][0].detach().cpu().numpy() * n_at, forces=f.cpu().numpy()))
+                calc.store_output(out, len(numbers))
+                self._log_frame(frame, dict(calc.results))
         a.set_positions(x.cpu().numpy())
         a.set_momenta(p.cpu().numpy())
-        n_atoms = len(numbers) if model.is_intensive else 1
-        calc.results.update(energy=out["e"][0].detach().cpu().numpy() * n_atoms, forces=f.cpu().numpy().astype(np.float32))
+        calc.store_output(out, len(numbers))
+        if hasattr(a, "mark_results_current"):
+            a.mark_results_current()
 
     def _logs_now(self) -> bool:
         return (self.dyn is None and isinstance(self.trajectory, str) and self.loginterval > 0

@@ -108,3 +108,30 @@ def test_relax_lowers_the_force():
     assert set(out) == {"final_structure", "trajectory"} and len(out["trajectory"]) >= 2
     assert out["trajectory"].energies[-1] <= out["trajectory"].energies[0] + 1e-6
     assert np.isfinite(f0)
+
+
+def test_device_resident_fire_follows_the_host_loop_and_evaluates_once_per_step():
+    """FIRE with its state on the GPU retraces the host loop; with result caching one geometry costs one evaluation
+    whichever of energy / forces / stress / magmoms the observer asks for."""
+    from matris_b200 import MatRIS
+    from matris_b200.applications import StructOptimizer
+    model = MatRIS.from_dict(random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)).to("cuda")
+    finals = []
+    for resident in (False, True):
+        opt = StructOptimizer(model=model, task="efsm", optimizer="FIRE", device="cuda")
+        calls = {"n": 0}
+        inner = model._evaluate
+
+        def counting(g, task, _inner=inner, _calls=calls):
+            _calls["n"] += 1
+            return _inner(g, task)
+
+        model._evaluate = counting
+        try:
+            out = opt.relax(_atoms(workloads.demo_pu4si6()), fmax=1e-6, steps=6, verbose=False, device_resident=resident)
+        finally:
+            model._evaluate = inner
+        assert len(out["trajectory"]) == 7 and calls["n"] == 7, (len(out["trajectory"]), calls["n"])
+        finals.append((out["final_structure"].get_positions(), np.array(out["trajectory"].energies, dtype=float)))
+    report("device-resident FIRE positions vs host loop", torch.tensor(finals[1][0]), torch.tensor(finals[0][0]), 1e-6)
+    report("device-resident FIRE energies vs host loop", torch.tensor(finals[1][1]), torch.tensor(finals[0][1]), 1e-5)
