@@ -575,13 +575,17 @@ class MatRIS(nn.Module):
         est = len(P.layers) * (6.7e3 * g.n_triplets + 6.2e3 * g.n_edges)
         keep = self.keep_activations
         if keep is None:
-            # memory the allocator can hand out: free on the device plus its own cached, unused blocks.  The driver
-            # query costs milliseconds, so a small evaluation (under a tenth of the last answer) reuses that answer.
-            free = getattr(self, "_free_bytes", None)
-            if free is None or est > 0.1 * free:
-                reusable = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
-                free = self._free_bytes = torch.cuda.mem_get_info(self.device)[0] + reusable
-            keep = est < 0.45 * free
+            # Memory the allocator can hand out = device total - what lives outside this allocator - what it has
+            # allocated.  The driver query behind the middle term costs milliseconds (during which the GPU idles at
+            # the start of an evaluation), so it is refreshed every 64th call only; the last term is a counter.
+            st = getattr(self, "_mem_state", None)
+            if st is None:
+                st = self._mem_state = {"calls": 0, "total": 0, "outside": 0}
+            if st["calls"] % 64 == 0:
+                free, total = torch.cuda.mem_get_info(self.device)
+                st["total"], st["outside"] = total, total - free - torch.cuda.memory_reserved(self.device)
+            st["calls"] += 1
+            keep = est < 0.45 * (st["total"] - st["outside"] - torch.cuda.memory_allocated(self.device))
         atom_rg.keep = bool(keep)
         if line_rg is not None:
             line_rg.keep = bool(keep)
