@@ -450,6 +450,7 @@ class MatRIS(nn.Module):
         for key, value in random_state_dict(cfg, seed=seed).items():
             self._register(key, value, buffer=key in BUFFER_KEYS, trainable=not key.startswith("reference_energy"))
         self._packed = None
+        self._ref_table = None
         self._packed_device = None
         self.last_batch = None
         self.keep_activations = None  # None: decide per call from free memory; True / False: force
@@ -472,10 +473,12 @@ class MatRIS(nn.Module):
 
     def _apply(self, fn, *a, **k):
         self._packed = None
+        self._ref_table = None
         return super()._apply(fn, *a, **k)
 
     def load_state_dict(self, state_dict, strict: bool = True, **kw):
         self._packed = None
+        self._ref_table = None
         return super().load_state_dict(state_dict, strict=strict, **kw)
 
     def packed(self, device):
@@ -622,7 +625,7 @@ class MatRIS(nn.Module):
         if "m" in task:
             zm = ops.linear(node_n, P.m_w0, bias=P.m_b0)
             out["m"] = list(torch.split(ops.head_dot_fwd(zm, P.m_w3, P.m_b3, take_abs=True), g.atoms_per_graph))
-        apg = torch.tensor(g.atoms_per_graph, dtype=torch.int32, device=energy.device)
+        apg = g.atom_ptr[1:] - g.atom_ptr[:-1]  # atoms per structure, on the device (no host copy, no synchronisation)
         out["e"] = energy / apg if self.is_intensive else energy
         out["atoms_per_graph"] = apg
         ref = 0
@@ -634,12 +637,18 @@ class MatRIS(nn.Module):
 
     def _reference_energy(self, g: BatchedGraph):
         """AtomRef.forward (matris/model/reference_energy.py:34-55): composition-weighted table sum, float32."""
-        table = self.state_dict()["reference_energy.fc.weight"].detach().cpu().numpy().reshape(-1).astype(np.float32)
-        comp = np.zeros((g.n_struct, 94), dtype=np.float32)
-        np.add.at(comp, (np.repeat(np.arange(g.n_struct), g.atoms_per_graph), g.numbers_host - 1), 1.0)
+        # evaluated on the device from the batch's own index tensors: a host round trip here would synchronise the
+        # stream at the end of every evaluation
+        table = getattr(self, "_ref_table", None)
+        if table is None or table.device != g.numbers.device:
+            table = self._ref_table = (self.state_dict()["reference_energy.fc.weight"].detach().reshape(-1)
+                                       .to(device=g.numbers.device, dtype=torch.float32))
+        comp = torch.zeros(g.n_struct, table.numel(), dtype=torch.float32, device=table.device)
+        comp.index_put_((g.atom_struct.long(), (g.numbers - 1).long()),
+                        torch.ones(g.n_atoms, dtype=torch.float32, device=table.device), accumulate=True)
         if self.is_intensive:
-            comp = comp / np.asarray(g.atoms_per_graph, dtype=np.float32)[:, None]
-        return torch.from_numpy(comp @ table).to(self.device)
+            comp = comp / (g.atom_ptr[1:] - g.atom_ptr[:-1]).to(torch.float32)[:, None]
+        return comp @ table
 
     # -- convenience ------------------------------------------------------------------------
     def predict(self, structures, task: str = "efsm"):
