@@ -145,14 +145,22 @@ def gated_fwd(p, n_rows, srcs):
 
 
 def gated_bwd(p, n_rows, z1, z2, dh, dests):
-    """Backward through the gated MLP: dests[c] = (tensor, idx, mode) for K segment c."""
+    """Backward through the gated MLP: dests[c] = (tensor, idx, mode[, res, res_w]) for K segment c.  With ``res``
+    the block stores ``gemm + res_w * res`` (the residual branch's gradient joins in the epilogue instead of in a
+    separate scaling pass followed by an accumulate)."""
     dz2 = ops.gate_bwd(z2, p.nc, p.ng, dh)
     dz1 = torch.empty_like(z1)
     gemm(n_rows, [B([S(dz2, None, D * j)], p.w2t, w_row=D * j, gate=z1, gate_col=D * j, out=dz1, out_col=D * j)
                   for j in (0, 1)])
     del dz2
-    blocks = [B([S(dz1, None, 0), S(dz1, None, D)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode)
-              for c, (t, idx, mode) in enumerate(dests) if t is not None]
+    blocks = []
+    for c, dest in enumerate(dests):
+        t, idx, mode = dest[:3]
+        if t is None:
+            continue
+        res, res_w = (dest[3], dest[4]) if len(dest) > 3 else (None, None)
+        blocks.append(B([S(dz1, None, 0), S(dz1, None, D)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode,
+                        res=res, res_w=res_w))
     gemm(n_rows, blocks)
 
 
@@ -206,11 +214,16 @@ class AttentionFn(torch.autograd.Function):
         dh, dlogits = ops.seg_attn_bwd(rg.tgt, rg.src, rg.emap, logits, h, agg_t, agg_s, stats, dagg_t, dagg_s,
                                        d_edge_out, rg.emap, 0.5 if rg.is_atom else 1.0)
         del logits, h, agg_t, agg_s, stats, dagg_t, dagg_s
-        # edge update
-        d_edge = ops.scale_rows(d_edge_out, P.we)
+        # edge update (line graph: rows map one to one, so the residual gradient we * d_edge_out rides in the
+        # epilogue of the store; atom graph: two directed rows add into one bond row, so it is laid down first)
         emode = OUT_ATOMIC if rg.is_atom else OUT_ADD
-        gated_bwd(P.edge, R, z1, z2, dh,
-                  [(d_edge, rg.emap, emode), (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)])
+        if rg.is_atom:
+            d_edge = ops.scale_rows(d_edge_out, P.we)
+            edge_dest = (d_edge, rg.emap, OUT_ATOMIC)
+        else:
+            d_edge = torch.empty_like(d_edge_out)
+            edge_dest = (d_edge, None, OUT_STORE, d_edge_out, P.we)
+        gated_bwd(P.edge, R, z1, z2, dh, [edge_dest, (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)])
         del z1, z2, dh
         gemm(R, [B([S(dlogits, None, 0), S(dlogits, None, D)], P.wstt, out=d_edge, out_idx=rg.emap, mode=emode)])
         return d_node, d_edge, None, None
@@ -284,14 +297,15 @@ class RefineFn(torch.autograd.Function):
         d_rbf = ops.small_linear_bwd(denv, P.wenv)
         del env, denv, dagg, h
         # gated MLP
-        d_edge = ops.scale_rows(d_edge_out, P.we)
         if rg.is_atom:
             d_atom = None
+            d_edge = ops.scale_rows(d_edge_out, P.we)
             dests = [(d_edge, rg.emap, OUT_ATOMIC), (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
         else:
             d_atom = torch.zeros_like(atom_feat)
-            dests = [(d_edge, None, OUT_ADD), (d_atom, rg.ctr, OUT_ATOMIC), (d_node, rg.tgt, OUT_ATOMIC),
-                     (d_node, rg.src, OUT_ATOMIC)]
+            d_edge = torch.empty_like(d_edge_out)  # stored once: gemm + we * d_edge_out in the epilogue
+            dests = [(d_edge, None, OUT_STORE, d_edge_out, P.we), (d_atom, rg.ctr, OUT_ATOMIC),
+                     (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
         gated_bwd(P.edge, R, z1, z2, dh, dests)
         return d_node, d_edge, d_rbf, d_atom, None, None
 
