@@ -5,20 +5,23 @@
 // one CTA per SM walks over many 128x128 output tiles, so that the three stages of a tile run concurrently on
 // DIFFERENT tiles instead of one after the other:
 //
+//   warp 0      MMA.  The whole warp walks the chunk sequence with warp-uniform addresses and descriptors; one elected
+//               lane issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor memory) into one
+//               of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot free) and, after a
+//               tile's last chunk, "accumulator full".
+//   warp 1      TMA.  Same structure; the elected lane streams W_hi / W_lo tiles into a 4-slot ring, up to four chunks
+//               ahead and across tile boundaries; a column block with K = 128 is loaded once and stays (its four
+//               chunks = the ring).
 //   warps 2-9   producers.  A warp owns rows 32 (warp & 3).. of the tile (= its TMEM lane quarter); the first four
-//               take the even 32-float K chunks, the other four the odd ones.  A chunk is gathered with cp.async (coalesced 128-byte row
-//               reads through the optional index, two stages per warp) into a swizzled shared-memory patch, read back
-//               one row per thread, passed through the optional SiLU, split into tf32 hi / lo and written with
-//               tcgen05.st into one of FOUR A buffers in tensor memory.
-//   warp 1      TMA (one thread): streams W_hi / W_lo tiles into a 4-slot ring, up to four chunks ahead and across
-//               tile boundaries; a column block with K = 128 is loaded once and stays (its four chunks = the ring).
-//   warp 0      MMA (one thread): issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor
-//               memory) into one of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot
-//               free) and, after a tile's last chunk, "accumulator full".
-//   warps 10-17 epilogue.  Warp 10 + e reads rows 32 (warp & 3).., columns 64 (e >> 2).. of the finished accumulator into
-//               registers (tcgen05.ld, thread = row), releases the accumulator, and finishes its rows there with
-//               256-bit global loads / stores (a full 32-byte sector per thread) while the tensor cores already work
-//               on the next tile.
+//               take the even 32-float K chunks, the other four the odd ones.  A chunk is gathered with cp.async
+//               (coalesced 128-byte row reads through the optional index, two stages per warp) into a swizzled
+//               shared-memory patch, read back one row per thread, passed through the optional SiLU, split into tf32
+//               hi / lo and written with tcgen05.st into one of FOUR A buffers in tensor memory.
+//   warps 10-17 epilogue.  Epilogue warp e takes rows 32 (warp & 3).., columns 64 (e >> 2).. of the finished
+//               accumulator into registers (tcgen05.ld, thread = row), releases the accumulator, and finishes its
+//               rows there with 256-bit global loads / stores (a full 32-byte sector per thread) while the tensor
+//               cores already work on the next tile.  Scatter / accumulate modes go through a 4 KB patch per warp
+//               instead, so that their memory-side reductions leave as 128-byte row segments.
 //
 // Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64b (hi | lo).
 // Shared memory: W ring 4 x 32 KB | producer patches 64 KB | epilogue patches 32 KB | barriers | descriptor copy.
