@@ -365,6 +365,10 @@ def main():
         cpu_baseline = {"value": rate, "unit": "atoms*evals/s", "cores": info["threads"], "kind": "port",
                         "sample": f"first {info['structures']} structures ({info['atoms']} atoms) of the workload as "
                                   f"one batch, {info['reps']} repetitions, {info['seconds']:.1f}s of CPU work"}
+        rate1, info1 = cpu_oracle_rate(crystals, task, budget_s=8.0, max_structs=4, threads=1)
+        cpu_baseline["one_thread"] = {"value": rate1, "cores": 1,
+                                      "sample": f"first {info1['structures']} structures ({info1['atoms']} atoms), "
+                                                f"{info1['reps']} repetitions, {info1['seconds']:.1f}s of CPU work"}
 
     # ---- MD leg (4,096-atom cell only): the public MolecularDynamics driver, Langevin NVT at 600 K, dt = 1 fs,
     # friction 0.01 / fs, Maxwell-Boltzmann start, one efsm evaluation per step (graph rebuilt every step on the device)
