@@ -488,7 +488,12 @@ class MatRIS(nn.Module):
     def _apply(self, fn, *a, **k):
         self._packed = None
         self._ref_table = None
-        return super()._apply(fn, *a, **k)
+        out = super()._apply(fn, *a, **k)
+        # graphs are built where the weights live: a batch on another GPU would be read through peer pointers
+        # (or fault without peer access) by kernels launched on this one
+        dev = self.device
+        self.graph_converter.device = dev if dev.type == "cuda" else None
+        return out
 
     def load_state_dict(self, state_dict, strict: bool = True, **kw):
         self._packed = None
@@ -544,6 +549,10 @@ class MatRIS(nn.Module):
     # -- evaluation -------------------------------------------------------------------------
     def _as_batch(self, graphs) -> BatchedGraph:
         if isinstance(graphs, BatchedGraph):
+            if graphs.device != self.device:
+                raise ValueError(f"the batch lives on {graphs.device} but the model on {self.device}: build it with "
+                                 "model.graph_converter (which follows the model) or pass device= to "
+                                 "build_batched_graph")
             return graphs
         if isinstance(graphs, RadiusGraph):
             graphs = [graphs]

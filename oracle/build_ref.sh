@@ -4,7 +4,7 @@
 # reference tree into oracle/_ref/.  Outputs only; no reference source is copied.
 # Usage: oracle/build_ref.sh [reference_root]
 set -e
-REF="${1:-${MATRIS_REFERENCE_ROOT:-/root/reference}}"
+REF="${1:-${MATRIS_REFERENCE_ROOT:?set MATRIS_REFERENCE_ROOT or pass the reference root}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 [ -f "$REF/matris/graph/cygraph.c" ] || { echo "reference tree not found under $REF" >&2; exit 3; }
 mkdir -p "$HERE/_ref"

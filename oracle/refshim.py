@@ -14,7 +14,6 @@ import os
 import sys
 import types
 
-DEFAULT_REFERENCE_ROOT = os.environ.get("MATRIS_REFERENCE_ROOT", "/root/reference")
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
 
@@ -44,7 +43,9 @@ def import_reference(root: str | None = None):
     ``matris.graph.cygraph`` and ``ns.make_graph`` is the reference's C builder;
     otherwise ``ns.make_graph`` is None and only the legacy Python builder exists.
     """
-    root = root or DEFAULT_REFERENCE_ROOT
+    root = root or os.environ.get("MATRIS_REFERENCE_ROOT")
+    if not root:
+        raise ImportError("set MATRIS_REFERENCE_ROOT to a copy of the reference tree")
     if not os.path.isdir(os.path.join(root, "matris")):
         raise ImportError(f"reference tree not found under {root}")
     _install_stubs()

@@ -24,7 +24,8 @@ def load_golden(name):
     return meta, crystals, z
 
 
-GOLDEN_CASES = ["cu32_L10", "cu32_L2_jit", "cu32_ideal_L1", "random2_L2", "pu4si6_L2", "cu1_L1", "perov_L3"]
+GOLDEN_CASES = ["cu32_L10", "cu32_L2_jit", "cu32_ideal_L1", "random2_L2", "pu4si6_L2", "cu1_L1", "perov_L3",
+                "fe432_L2", "lipscl256_L2", "random8_L2", "democif_L2"]
 
 # tolerances of the evaluation path (energy eV/atom, force eV/A, stress eV/A^3, magmom mu_B)
 TOL = dict(e=1e-5, f=1e-4, s=1e-5, m=1e-4)

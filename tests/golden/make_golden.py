@@ -2,7 +2,9 @@
 
 Run where a copy of the reference tree exists (it is imported, never copied):
 
-    python tests/golden/make_golden.py [reference_root]
+    MATRIS_REFERENCE_ROOT=<reference tree> python tests/golden/make_golden.py [case ...]
+
+With case names only those cases are regenerated; without, all of them.
 
 For each case the structure comes from matris_b200.workloads (seeded), the
 neighbour list from oracle.neighbors (brute-force float64, standing in for
@@ -37,7 +39,22 @@ CASES = {
     "pu4si6_L2": (lambda: workloads.demo_pu4si6(), 2, "efsm", 0.1),
     "cu1_L1": (lambda: workloads.cu_fcc(reps=(1, 1, 1), sigma=0.0), 1, "efsm", 0.1),  # self-image bonds only... 4 atoms
     "perov_L3": (lambda: workloads.perovskites(1, seed=5)[0], 3, "efsm", 0.1),
+    # 432-atom BCC Fe: ~112k triplets, above the 60,000-triplet switch to torch.utils.checkpoint
+    # (matris/model/interaction_block.py:15, 400-403)
+    "fe432_L2": (lambda: workloads.fe_bcc(reps=(6, 6, 6)), 2, "efsm", 0.1),
+    "lipscl256_L2": (lambda: workloads.lipscl(n_atoms=256), 2, "efsm", 0.1),
+    # the first eight structures of the benchmark batch (the generator is sequential in its seed)
+    "random8_L2": (lambda: workloads.random_crystals(8, seed=1), 2, "efs", 0.1),
+    # the structure file the reference ships (example/cif_file/demo.cif; a copy sits beside this script)
+    "democif_L2": (lambda: demo_cif(), 2, "efsm", 0.1),
 }
+
+
+def demo_cif():
+    from matris_b200.io import read_cif
+    a = read_cif(os.path.join(HERE, "demo.cif"))
+    return workloads.Crystal(np.asarray(a.get_atomic_numbers(), dtype=np.int64), np.asarray(a.get_positions(), float),
+                             np.asarray(a.get_cell(), float))
 
 
 def reference_graph(ns, crystal, cutoff=6.0, line_cutoff=4.0):
@@ -78,8 +95,12 @@ def run_reference(ns, graphs, layers, task, jitter, double):
                                                 "atom_frac_coord": g.atom_frac_coord.double(),
                                                 "lattice": g.lattice.double(),
                                                 "neighbor_image": g.neighbor_image.double()}) for g in graphs]
+    pooled = []  # EnergyHead output: per-structure total energy before the division by atoms and before AtomRef
+    hook = model.energy_head.register_forward_hook(lambda m, a, k, o: pooled.append(o.detach()), with_kwargs=True)
     out = model(graphs, task=task)
-    res = {"e": out["e"].detach().double().numpy(), "ref_energy": out["ref_energy"].detach().double().numpy()}
+    hook.remove()
+    res = {"e": out["e"].detach().double().numpy(), "ref_energy": out["ref_energy"].detach().double().numpy(),
+           "e_model": (pooled[-1] / out["atoms_per_graph"]).double().numpy()}
     if "f" in out:
         res["f"] = torch.cat(list(out["f"])).detach().double().numpy()
     if "s" in out:
@@ -90,13 +111,19 @@ def run_reference(ns, graphs, layers, task, jitter, double):
 
 
 def main():
-    ns = import_reference(sys.argv[1] if len(sys.argv) > 1 else None)
+    ns = import_reference(os.environ.get("MATRIS_REFERENCE_ROOT"))
+    only = set(sys.argv[1:])
+    unknown = only - set(CASES)
+    if unknown:
+        raise SystemExit(f"unknown cases: {sorted(unknown)}")
     torch.set_num_threads(os.cpu_count() or 1)
     ref_model = ns.MatRIS(num_layers=2, reference_energy="mpa")
     with open(os.path.join(HERE, "schema.json"), "w") as f:
         json.dump({"num_layers": 2, "reference_energy": "mpa",
                    "keys": [[k, list(v.shape)] for k, v in ref_model.state_dict().items()]}, f, indent=0)
     for name, (factory, layers, task, jitter) in CASES.items():
+        if only and name not in only:
+            continue
         crystals = factory()
         if not isinstance(crystals, list):
             crystals = [crystals]

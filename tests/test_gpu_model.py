@@ -9,11 +9,14 @@ import pytest
 import torch
 
 from conftest import GOLDEN_CASES, GPA, TOL, load_golden
+from functools import partial
+
 from gpu_util import dev, report
 from matris_b200 import workloads
 from matris_b200.weights import full_config, random_checkpoint
 
 pytestmark = pytest.mark.gpu
+report_feat = partial(report, scaled=True)  # feature tensors: bound scales with the reference's magnitude
 
 
 def rnd(*shape, seed=0, scale=1.0):
@@ -57,11 +60,11 @@ def test_attention_layer_forward_backward(setup, which):
     gn, ge = torch.autograd.grad((rn * dn.double()).sum() + (re_ * de.double()).sum(), [N, E])
     n_in, e_in = dev(node).requires_grad_(True), dev(edge).requires_grad_(True)
     on, oe = AttentionFn.apply(n_in, e_in, getattr(P.layers[0], "attn_" + which), rg)
-    report(f"attention[{which}] node", on, rn, 3e-5)
-    report(f"attention[{which}] edge", oe, re_, 3e-5)
+    report_feat(f"attention[{which}] node", on, rn, 3e-5)
+    report_feat(f"attention[{which}] edge", oe, re_, 3e-5)
     dn_, de_ = torch.autograd.grad([on, oe], [n_in, e_in], [dev(dn), dev(de)])
-    report(f"attention[{which}] d node", dn_, gn, 2e-4)
-    report(f"attention[{which}] d edge", de_, ge, 2e-4)
+    report_feat(f"attention[{which}] d node", dn_, gn, 2e-4)
+    report_feat(f"attention[{which}] d edge", de_, ge, 2e-4)
 
 
 @pytest.mark.parametrize("which", ["atom", "line"])
@@ -86,16 +89,17 @@ def test_refinement_layer_forward_backward(setup, which):
     n_in, e_in, r_in = dev(node).requires_grad_(True), dev(edge).requires_grad_(True), dev(rbf).requires_grad_(True)
     a_in = None if af is None else dev(af).requires_grad_(True)
     on, oe = RefineFn.apply(n_in, e_in, r_in, a_in, getattr(P.layers[0], "refine_" + which), rg)
-    report(f"refine[{which}] node", on, rn, 3e-5)
-    report(f"refine[{which}] edge", oe, re_, 3e-5)
+    report_feat(f"refine[{which}] node", on, rn, 3e-5)
+    report_feat(f"refine[{which}] edge", oe, re_, 3e-5)
     mine = torch.autograd.grad([on, oe], [n_in, e_in, r_in] + ([a_in] if a_in is not None else []), [dev(dn), dev(de)])
     for name, a, b in zip(["node", "edge", "rbf", "atom"], mine, grads):
-        report(f"refine[{which}] d {name}", a, b, 2e-4)
+        report_feat(f"refine[{which}] d {name}", a, b, 2e-4)
 
 
-def _evaluate(ck, crystals, task):
+def _evaluate(ck, crystals, task, keep=None):
     from matris_b200 import MatRIS
     model = MatRIS.from_dict(ck).to("cuda")
+    model.keep_activations = keep
     out = model.predict(crystals, task)
     res = {"e": out["e"].cpu().double().numpy(), "ref_energy": out["ref_energy"].cpu().double().numpy()}
     if "f" in out:
@@ -107,22 +111,30 @@ def _evaluate(ck, crystals, task):
     return res, out, model
 
 
+@pytest.mark.parametrize("keep", [True, False], ids=["keep", "recompute"])
 @pytest.mark.parametrize("case", GOLDEN_CASES)
-def test_end_to_end_matches_reference(case):
+def test_end_to_end_matches_reference(case, keep):
+    """Whole evaluations against the reference's own float32 results; the gates are ABSOLUTE.  Both memory
+    policies run every case (the reference itself recomputes above 60,000 triplets; fe432_L2 is above that)."""
     meta, crystals, z = load_golden(case)
     ck = random_checkpoint(dict(num_layers=meta["num_layers"], reference_energy=meta["reference_energy"]),
                            seed=meta["seed"], jitter=meta["jitter"])
-    res, out, _ = _evaluate(ck, crystals, meta["task"])
-    report(f"e2e[{case}] E (eV/atom)", res["e"], z["ref32_e"], TOL["e"])
-    report(f"e2e[{case}] F (eV/A)", res["f"], z["ref32_f"], TOL["f"])
-    report(f"e2e[{case}] S (eV/A^3)", res["s"] / GPA, z["ref32_s"] / GPA, TOL["s"])
+    res, out, _ = _evaluate(ck, crystals, meta["task"], keep=keep)
+    tag = f"e2e[{case},{'keep' if keep else 'recompute'}]"
+    report(f"{tag} E (eV/atom)", res["e"], z["ref32_e"], TOL["e"])
+    # the model's own energy, before the (much larger) tabulated reference energy is added
+    report(f"{tag} E model part (eV/atom)", res["e"] - res["ref_energy"], z["ref32_e_model"], TOL["e"])
+    report(f"{tag} E model part vs fp64", res["e"] - res["ref_energy"], z["ref64_e_model"], TOL["e"])
+    report(f"{tag} F (eV/A)", res["f"], z["ref32_f"], TOL["f"])
+    report(f"{tag} S (eV/A^3)", res["s"] / GPA, z["ref32_s"] / GPA, TOL["s"])
     if "m" in meta["task"]:
-        report(f"e2e[{case}] M (mu_B)", res["m"], z["ref32_m"], TOL["m"])
-    report(f"e2e[{case}] reference energy", res["ref_energy"], z["ref32_ref_energy"], 1e-6)
-    # tighter, relative check against the reference's float64 run (random-init forces are small)
-    fmax = np.abs(z["ref64_f"]).max()
-    if fmax > 1e-4:
-        report(f"e2e[{case}] F relative to fp64", res["f"], z["ref64_f"], 2e-3, rel=True)
+        report(f"{tag} M (mu_B)", res["m"], z["ref32_m"], TOL["m"])
+    report(f"{tag} reference energy", res["ref_energy"], z["ref32_ref_energy"], 1e-6)
+    # tighter checks against the reference's float64 run, relative to the largest component (random-init forces are
+    # small, so the absolute gate alone is blunt), with a floor at the float32 rounding noise of the reference
+    # itself (forces that vanish by symmetry have nothing but that noise to compare)
+    report(f"{tag} F vs fp64 (2e-3 relative)", res["f"], z["ref64_f"], max(2e-3 * np.abs(z["ref64_f"]).max(), 1e-6))
+    report(f"{tag} S vs fp64 (2e-3 relative, GPa)", res["s"], z["ref64_s"], max(2e-3 * np.abs(z["ref64_s"]).max(), 1e-4))
     # result dictionary layout of MatRIS.forward
     assert out["atoms_per_graph"].dtype == torch.int32 and len(out["f"]) == len(crystals)
     assert out["s"][0].shape == (3, 3) and out["f"][0].shape == (len(crystals[0].numbers), 3)

@@ -5,7 +5,13 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from gpu_util import dev, report
+from functools import partial
+
+import gpu_util
+from gpu_util import dev
+
+# feature tensors: the bound scales with the reference's magnitude
+report = partial(gpu_util.report, scaled=True)
 
 pytestmark = pytest.mark.gpu
 

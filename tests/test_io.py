@@ -88,3 +88,18 @@ Cl1 Cl 0.5 0.5 0.5(2)
     p.write_text(p.read_text().replace(" 'x, y, z'", " 'x, y, z'\n '-x, -y, -z'"))
     with pytest.raises(ValueError):
         mio.read_cif(str(p))
+
+
+def test_reference_demo_cif_is_read():
+    """The structure file the reference ships (example/cif_file/demo.cif, Pu4Si6, P1; a copy sits in tests/golden):
+    10 sites, and the same arrays the committed golden case was generated from."""
+    import os
+
+    from conftest import GOLDEN, load_golden
+    a = mio.read_cif(os.path.join(GOLDEN, "demo.cif"))
+    assert list(a.get_atomic_numbers()) == [94] * 4 + [14] * 6
+    np.testing.assert_allclose(np.diag(a.get_cell()), [4.26022438, 7.16692875, 7.16692875], atol=1e-12)
+    _, crystals, _ = load_golden("democif_L2")
+    assert np.array_equal(crystals[0].numbers, a.get_atomic_numbers())
+    np.testing.assert_allclose(crystals[0].cart, a.get_positions(), atol=1e-12)
+    np.testing.assert_allclose(crystals[0].lattice, a.get_cell(), atol=1e-12)
