@@ -31,6 +31,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 NUM_LAYERS = 10
+GEMM_CALLS = ("mb_gemm", "mb_gated_mlp_fwd")  # the tensor-core entry points
 METRIC = "atoms*evals/s (efs, fp32-tol)"
 
 
@@ -319,11 +320,12 @@ def main():
             d = per.setdefault(name, [0, 0.0])
             d[0] += 1
             d[1] += ms
-            if name == "mb_gemm":
+            if name in GEMM_CALLS:
                 gemm_flops += meta["flops"]
                 gemm_ms += ms
-                gemm_bytes += 4.0 * meta["rows"] * (meta["k"] + meta["n"])  # A rows read once + output rows written
-                s = shapes.setdefault(f"rows={meta['rows']} K={meta['k']} N={meta['n']}", [0, 0.0, 0.0])
+                gemm_bytes += meta["bytes"]  # A rows read once + output rows written
+                tag = "gated " if meta.get("fused") else ""
+                s = shapes.setdefault(f"{tag}rows={meta['rows']} K={meta['k']} N={meta['n']}", [0, 0.0, 0.0])
                 s[0] += 1
                 s[1] += ms
                 s[2] += meta["flops"]
@@ -341,13 +343,14 @@ def main():
         peak_gb = float(peaks.get("hbm_gbs", 6650.0))
         src = "measured" if peaks else "fallback"
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
+        n_gemm = sum(per[k][0] for k in GEMM_CALLS if k in per)
         # DRAM traffic per launch: ncu measured 0.906 x (A read + output write) on a captured K=384 N=256 launch of
         # 151,552 rows (profiles/k_gemm_ps.md); scaled here to the average launch of the step by its rows x (K + N).
-        roofline = {"kernel": "k_gemm_ps (mb_gemm)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.906 * gemm_bytes / per["mb_gemm"][0],
+        roofline = {"kernel": "k_gemm_ps + k_gated_fwd (mb_gemm, mb_gated_mlp_fwd)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
+                    "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.906 * gemm_bytes / n_gemm,
                     "traffic_note": "bytes per average launch, scaled from one ncu capture by rows x (K + N)",
                     "peak_source": src + " bf16 sustained",
-                    "launches": per["mb_gemm"][0], "avg_launch_ms": gemm_ms / per["mb_gemm"][0],
+                    "launches": n_gemm, "avg_launch_ms": gemm_ms / n_gemm,
                     "flops_per_step": gemm_flops, "tf32_issued_tflops": 3.0 * ach, "tf32_peak_measured_tflops": 1151.0,
                     "frac_of_tf32_peak": 3.0 * ach / 1151.0,
                     "note": "tcgen05 kind::tf32 with a 3-term operand split: 3 tensor FLOPs are issued per "

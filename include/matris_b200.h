@@ -158,19 +158,73 @@ typedef struct mb_gemm_desc {
 } mb_gemm_desc;
 
 int mb_gemm(const mb_gemm_desc* desc, void* stream);
-/* Contraction core used by mb_gemm: 0 = tcgen05 tensor cores, kind::tf32 with a 3-term hi/lo operand split
- * accumulated in fp32 TMEM, persistent kernel with one CTA per SM (default); 1 = fp32 SIMT FMA (bit-faithful fp32,
- * the cross-check); 2 = the same tensor-core arithmetic as 0 in a one-tile-per-CTA kernel. Process-wide.
+/* Contraction core used by mb_gemm and mb_gated_mlp_fwd: 0 = tcgen05 tensor cores, kind::tf32 with a 3-term hi/lo
+ * operand split accumulated in fp32 TMEM, persistent kernels with one CTA per SM (default); 1 = fp32 SIMT FMA
+ * (bit-faithful fp32, the cross-check); 2 = the same tensor-core arithmetic as 0 in a one-tile-per-CTA kernel.
+ * A test knob: it is process-wide and not meant to be switched while other host threads launch.
  * MB_OUT_ADD is performed as one memory-side fp32 addition per element in mode 0 (read-add-write in modes 1, 2):
  * identical results as long as no other kernel writes the output rows concurrently. */
 int mb_set_gemm_mode(int mode);
-/* Synchronises the stream, returns and clears the tensor-core kernel's status word (bit 0: a bounded
- * mbarrier wait expired and the affected tiles were not written). */
+/* Status word of the tensor-core kernels on the CURRENT device (bit 0: a bounded mbarrier wait expired and the
+ * affected tiles were not written; bit 1: misaligned dynamic shared memory).  No counterpart in the reference (its
+ * kernels have no bounded waits).
+ *   mb_gemm_status        synchronises the stream, returns the word and clears it;
+ *   mb_gemm_status_async  copies the word to `host_status` (pinned host memory) in stream order, without
+ *                         synchronising and without clearing it: a caller that launches evaluation after
+ *                         evaluation reads the word of the previous one when it starts the next, at no cost;
+ *   mb_gemm_status_clear  zeroes the word in stream order (after an expiry has been reported). */
 int mb_gemm_status(int* status, void* stream);
-/* The same status word copied to `host_status` (pinned host memory) in stream order, without synchronising and
- * without clearing it: a caller that launches evaluation after evaluation reads the word of the previous one
- * when it starts the next, at no cost.  No counterpart in the reference (its kernels have no bounded waits). */
 int mb_gemm_status_async(int* host_status, void* stream);
+int mb_gemm_status_clear(void* stream);
+/* Self-test of the failure path above: launches one CTA that waits, with a limit of a few polls, on an mbarrier
+ * that nothing ever arrives at.  The wait runs out, the kernel sets bit 0 of the status word and returns through
+ * its normal exit; nothing faults, traps or hangs.  The next mb_gemm_status* call sees bit 0. */
+int mb_selftest_wait_expiry(void* stream);
+/* Timed issue rate of the tensor-core instruction the kernels above are built on: every SM runs `iters` batches of
+ * four M128 x N128 tcgen05.mma (kind 0: tf32, K = 8; kind 1: bf16, K = 16) on operands resident in tensor / shared
+ * memory; returns the elapsed time of the launch (CUDA events on `stream`, which is synchronised) and the number
+ * of SMs used, from which the caller derives TFLOP/s = 2 * 128 * 128 * K * 4 * iters * sms / ms.  This is the
+ * denominator the 3-pass tf32 GEMMs are judged against. */
+int mb_bench_mma_rate(int kind, int iters, float* elapsed_ms, int* n_sms, void* stream);
+
+/* ------------------------------------------------------------------ fused gated MLP (forward)
+ * GatedMLP.forward (matris/model/functions.py:245-311) as ONE kernel per call:
+ *   z1 = X W1^T + b1            X = up to four gathered 128-wide row segments (as in mb_gemm), W1 [256, K]:
+ *                               rows 0..127 the core branch's first layer, 128..255 the gate branch's
+ *   z2 = SiLU(z1) (.) W2^T + b2 W2 [256, 128]: rows 0..127 act on z1[:, :128] (core), 128..255 on z1[:, 128:] (gate)
+ *   h  = SiLU(RMSNorm(z2[:, :128]) * norm_core) * sigmoid(RMSNorm(z2[:, 128:]) * norm_gate)
+ *   out2 = h + res_w * res      (optional)
+ * Layer 1's accumulator never leaves tensor memory: it is read back, biased, passed through SiLU, split into
+ * tf32 hi / lo and stored as the A operand of layer 2 on chip; RMSNorm and the gate run in the epilogue of
+ * layer 2.  z1 / z2 are written only when the pointers are given (the backward pass wants them).  In GEMM
+ * modes 1 and 2 (see mb_set_gemm_mode) the same result is composed from mb_gemm and mb_gate_fwd, which needs
+ * z1 and z2 as scratch: they are required there. */
+typedef struct mb_gated_mlp {
+  int64_t n_rows;
+  int32_t n_src;               /* 1..4 ; K = 128 * n_src */
+  int32_t pad;
+  mb_src src[4];               /* src[].act is honoured (SiLU on load) */
+  const float* W1;             /* [256, K] row-major (SIMT mode) */
+  const float* W1_hi;          /* tf32(W1) */
+  const float* W1_lo;          /* W1 - tf32(W1) */
+  int64_t ldw1;                /* row stride of W1* in floats (>= K) */
+  const float* b1;             /* [256] or NULL */
+  const float* W2;             /* [256, 128] */
+  const float* W2_hi;
+  const float* W2_lo;
+  int64_t ldw2;                /* row stride of W2* in floats (>= 128) */
+  const float* b2;             /* [256] or NULL */
+  const float* norm_core;      /* [128] RMSNorm weights */
+  const float* norm_gate;      /* [128] */
+  float* z1; int64_t ld_z1;    /* optional [R, 256] */
+  float* z2; int64_t ld_z2;    /* optional [R, 256] */
+  float* h; int64_t ld_h;      /* optional [R, 128] (h or out2 must be given) */
+  const float* res;            /* [R, 128] rows, required with out2 */
+  const float* res_w;          /* [128] or NULL (= 1) */
+  int64_t ld_res;
+  float* out2; int64_t ld_out2;
+} mb_gated_mlp;
+int mb_gated_mlp_fwd(const mb_gated_mlp* desc, void* stream);
 
 /* ------------------------------------------------------------------ row-wise model kernels
  * All feature tensors are float32 row-major with 128 channels unless noted.

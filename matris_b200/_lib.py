@@ -59,6 +59,17 @@ class MbGemmDesc(C.Structure):
     _fields_ = [("n_rows", _i64), ("n_blocks", _i32), ("pad", _i32), ("blk", MbColBlock * 4)]
 
 
+class MbGatedMlp(C.Structure):
+    _fields_ = [
+        ("n_rows", _i64), ("n_src", _i32), ("pad", _i32), ("src", MbSrc * 4),
+        ("W1", _vp), ("W1_hi", _vp), ("W1_lo", _vp), ("ldw1", _i64), ("b1", _vp),
+        ("W2", _vp), ("W2_hi", _vp), ("W2_lo", _vp), ("ldw2", _i64), ("b2", _vp),
+        ("norm_core", _vp), ("norm_gate", _vp),
+        ("z1", _vp), ("ld_z1", _i64), ("z2", _vp), ("ld_z2", _i64), ("h", _vp), ("ld_h", _i64),
+        ("res", _vp), ("res_w", _vp), ("ld_res", _i64), ("out2", _vp), ("ld_out2", _i64),
+    ]
+
+
 # name -> argtypes (every function returns int status unless listed in _OTHER)
 _SIGNATURES = {
     "mb_graph_count_edges": [C.POINTER(MbGraph), _vp],
@@ -68,6 +79,10 @@ _SIGNATURES = {
     "mb_set_gemm_mode": [C.c_int],
     "mb_gemm_status": [C.POINTER(C.c_int), _vp],
     "mb_gemm_status_async": [_vp, _vp],
+    "mb_gemm_status_clear": [_vp],
+    "mb_selftest_wait_expiry": [_vp],
+    "mb_bench_mma_rate": [C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int), _vp],
+    "mb_gated_mlp_fwd": [C.POINTER(MbGatedMlp), _vp],
     "mb_gate_fwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_gate_bwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_seg_attn_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],

@@ -1,12 +1,11 @@
-"""Diagnostic (not part of the library's API): one `mb_gemm` launch shape, timed with CUDA events.
+"""Kernel micro-benchmark: one `mb_gemm` launch shape, timed with CUDA events.
 
-    python -m matris_b200.diag.gemm_case K N [act] [gate] [rows] [mode] [scatter]
+    python -m matris_b200.bench_gemm K N [act] [gate] [rows] [mode] [scatter]
 
 K: reduction width (a multiple of 128: K/128 concatenated sources), N: output width (a multiple of 128: N/128 column
 blocks), act: SiLU on load, gate: SiLU' gate in the epilogue, rows: default 151,552 (8 tiles per SM on 148 SMs),
 mode: tcgen05 (persistent kernel, default) | tcgen05_tile | simt; scatter: 0 plain store (default), 1 atomic
 scatter-add to rows/5 targets in sorted order (runs of five equal targets), 2 the same targets in random order.
-Used for the ncu captures under profiles/.
 """
 import sys
 

@@ -1,0 +1,465 @@
+// Fused gated MLP, forward (included by gemm.cu inside namespace mb, after gemm_persistent.cuh).
+//
+//   z1 = X W1^T + b1          [rows, 256] = core | gate pre-activations    (K = 128 n_src, gathered A as in k_gemm_ps)
+//   z2 = SiLU(z1) (.) W2^T + b2   per branch: [rows, 128] x [128, 128]
+//   h  = SiLU(RMSNorm(z2_core) w_core) * sigmoid(RMSNorm(z2_gate) w_gate)  (+ optional out2 = h + res_w * res)
+//
+// One persistent CTA per SM.  The unit of work is (128-row tile, branch); a CTA takes row tiles blockIdx.x,
+// + gridDim.x, ... and runs the core unit and then the gate unit of each.  A unit is two chained contractions on the
+// same tensor-memory accumulator (unit k uses accumulator k & 1):
+//
+//   L1(k)   12 or 16 K chunks of X against rows 128 j.. of W1  ->  D (128 x 128 fp32)
+//   mid(k)  the eight epilogue warps read D back (tcgen05.ld, thread = row), add b1, optionally write z1, apply SiLU,
+//           split into tf32 hi / lo and store the result as the A operand of layer 2 into the four A buffers
+//           (tcgen05.st): z1 never travels through shared or global memory on its way to layer 2
+//   L2(k)   4 K chunks against rows 128 j.. of W2, written over D (every column of D has been read by then)
+//   epi(k)  D -> registers, + b2, optional z2 store, RMSNorm (the two warps that share a row exchange their partial
+//           sums of squares through shared memory), then  core unit: c = SiLU(.) is parked in the output row;
+//           gate unit: the same thread reads c back, multiplies by sigmoid(.) and writes h / out2.
+//
+// The tensor pipe executes L1(0) L1(1) L2(0) L1(2) L2(1) ... L1(n-1) L2(n-2) L2(n-1): while it works on L1(k+1) the
+// epilogue warps drain unit k-1 and prepare unit k's layer-2 operand, so neither hand-off idles the tensor cores for
+// longer than one tcgen05.st + mbarrier round trip.  All roles walk that one chunk sequence (counter g): chunk g uses
+// A buffer g & 3 and W ring slot g & 3, exactly as in k_gemm_ps, and every phase has a multiple of four chunks.
+//
+// Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64 b (hi | lo).
+// Shared memory: W ring 4 x 32 KB | producer patches 64 KB | sums of squares 2 KB | barriers | descriptor copy.
+// Every mbarrier wait is bounded; on expiry the status word is set, the role stops waiting and runs to the common exit.
+
+struct alignas(64) GatedMaps { CUtensorMap w1[2]; CUtensorMap w2[2]; };  // hi, lo of W1 [256, K] and W2 [256, 128]
+
+constexpr int GP_THREADS = PS_THREADS;
+constexpr int GP_XSUM_OFF = PS_RING_BYTES + PS_PATCH_BYTES;
+constexpr int GP_BAR_OFF = GP_XSUM_OFF + 2 * 2 * 128 * 4;
+constexpr int GP_DESC_OFF = GP_BAR_OFF + 256;
+constexpr int GP_SMEM_BYTES = GP_DESC_OFF + (int)((sizeof(mb_gated_mlp) + 15) / 16 * 16);
+constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): float32 machine epsilon
+static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
+static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word");
+
+__device__ __forceinline__ float sigmoid_fast_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+__global__ void __launch_bounds__(GP_THREADS, 1)
+k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant__ GatedMaps maps) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GP_BAR_OFF);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 128);
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
+    return;
+  }
+  // barriers: ready[4] (4 storing warps + the TMA thread's expect_tx arrival) | chunk_done[4] | d1_full[2] |
+  //           d2_full[2] | d_free[2] (8 epilogue warps)
+  const uint32_t ready = smem_u32(bars), chunk_done = smem_u32(bars + 4);
+  const uint32_t d1_full = smem_u32(bars + 8), d2_full = smem_u32(bars + 10), d_free = smem_u32(bars + 12);
+  const uint32_t ring = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const mb_gated_mlp& d = *reinterpret_cast<const mb_gated_mlp*>(smem + GP_DESC_OFF);
+  {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(&d_param);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(smem + GP_DESC_OFF);
+    for (int i = tid; i < (int)(sizeof(mb_gated_mlp) / 4); i += GP_THREADS) dst[i] = src[i];
+  }
+  __syncthreads();
+  const int64_t n_rows = d.n_rows;
+  const int n_row_tiles = (int)((n_rows + 127) >> 7);
+  const int n_src = d.n_src, nch1 = 4 * n_src;
+  const int first_rt = (int)blockIdx.x, step_rt = (int)gridDim.x;
+  const int n_units = 2 * ((n_row_tiles - first_rt + step_rt - 1) / step_rt);  // the grid never exceeds the tile count
+  const int n_phases = 2 * n_units;
+  // phase p of the tensor pipe's sequence -> (layer, unit)
+  auto decode = [&](int p, bool& is_l2, int& k) {
+    if (p == n_phases - 1) { is_l2 = true; k = n_units - 1; }
+    else if (p == 0) { is_l2 = false; k = 0; }
+    else if (p & 1) { is_l2 = false; k = (p + 1) >> 1; }
+    else { is_l2 = true; k = (p >> 1) - 1; }
+  };
+
+  // ---- producer state (same gather as k_gemm_ps; both units of a row tile read the same rows)
+  const int pw = (warp - PS_PROD_WARP0) & 7;
+  const int par = pw >> 2, quarter = warp & 3;
+  const int lr = lane >> 3, lc = lane & 7;
+  const uint32_t patch0 = smem_u32(smem + PS_RING_BYTES + pw * (2 * 32 * 128));
+  const uint32_t dst_even = patch0 + lr * 128 + ((lc ^ lr) << 4), dst_odd = patch0 + lr * 128 + ((lc ^ (lr | 4)) << 4);
+  const float* a_ptr[8];
+  int32_t a_row[8];
+  int g_unit = 0, g_seg = 0, g_cnt = 0;
+  bool g_second = false;
+  auto resolve_rows = [&](int unit, int seg) {
+    const int64_t row0 = (int64_t)(first_rt + (unit >> 1) * step_rt) * 128;
+    const int32_t* idx = d.src[seg].idx;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int64_t r = row0 + quarter * 32 + lr + 4 * i;
+      r = r < n_rows ? r : n_rows - 1;  // rows past the end repeat the last row; their results are never written
+      a_row[i] = idx ? idx[r] : (int32_t)(r - row0);
+    }
+  };
+  auto gather_next = [&]() {
+    if (g_unit >= n_units) {
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
+    const uint32_t st = (uint32_t)(g_cnt & 1) * (32 * 128);
+    const uint32_t de = dst_even + st, dq = dst_odd + st;
+    if (!g_second) {
+      const mb_src& s = d.src[g_seg];
+      const float* base = s.ptr + s.col + lc * 4 + par * TC_BK;
+      const int64_t ld = s.ld;
+      const int64_t row0 = s.idx ? 0 : (int64_t)(first_rt + (g_unit >> 1) * step_rt) * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a_ptr[i] = base + (row0 + a_row[i]) * ld;
+      MB_CP16(de, 0, a_ptr[0], 0);    MB_CP16(dq, 512, a_ptr[1], 0);  MB_CP16(de, 1024, a_ptr[2], 0); MB_CP16(dq, 1536, a_ptr[3], 0);
+      MB_CP16(de, 2048, a_ptr[4], 0); MB_CP16(dq, 2560, a_ptr[5], 0); MB_CP16(de, 3072, a_ptr[6], 0); MB_CP16(dq, 3584, a_ptr[7], 0);
+    } else {
+      MB_CP16(de, 0, a_ptr[0], 256);    MB_CP16(dq, 512, a_ptr[1], 256);  MB_CP16(de, 1024, a_ptr[2], 256); MB_CP16(dq, 1536, a_ptr[3], 256);
+      MB_CP16(de, 2048, a_ptr[4], 256); MB_CP16(dq, 2560, a_ptr[5], 256); MB_CP16(de, 3072, a_ptr[6], 256); MB_CP16(dq, 3584, a_ptr[7], 256);
+      if (++g_seg == n_src) {
+        g_seg = 0;
+        ++g_unit;
+      }
+      if (g_unit < n_units) resolve_rows(g_unit, g_seg);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    ++g_cnt;
+    g_second = !g_second;
+  };
+
+  if (warp == PS_MMA_WARP) {
+    if (lane == 0) {
+      for (int b = 0; b < 4; ++b) { mbar_init(ready + 8 * b, 5); mbar_init(chunk_done + 8 * b, 1); }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(d1_full + 8 * b, 1); mbar_init(d2_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8);
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(tmem_slot)), "r"(PS_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else if (warp >= PS_PROD_WARP0 && warp < PS_EPI_WARP0) {
+    resolve_rows(0, 0);
+    gather_next();
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == PS_MMA_WARP) {
+    // ---------------------------------------------------------------- MMA warp (warp-uniform, one elected lane issues)
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
+    bool alive = true;
+    uint32_t g = 0;
+    for (int p = 0; p < n_phases; ++p) {
+      bool is_l2;
+      int k;
+      decode(p, is_l2, k);
+      const int acc = k & 1;
+      const uint32_t d_tmem = tmem_u + 128u * acc;
+      const int nch = is_l2 ? 4 : nch1;
+      const uint32_t full_bar = (is_l2 ? d2_full : d1_full) + 8 * acc;
+      for (int c = 0; c < nch; ++c, ++g) {
+        const uint32_t ab = g & 3;
+        if (c == 0 && is_l2) {
+          // Layer 2 overwrites the accumulator that holds z1: its first MMA may issue only when all four operand
+          // chunks have been read out of it and stored (each `ready` phase below implies that chunk's tcgen05.ld).
+          for (uint32_t b = 0; b < 4; ++b)
+            if (alive) alive = mbar_wait(ready + 8 * b, (g >> 2) & 1);
+        } else {
+          if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);
+        }
+        // layer 1 of unit k overwrites the accumulator unit k - 2 left: its epilogue must have taken it
+        if (c == 0 && !is_l2 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
+        alive = __all_sync(0xffffffffu, alive);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t wb = ring_u + ab * 2 * TC_TILE_BYTES;
+        const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
+        const uint32_t ta_hi = tmem_u + 256 + 64 * ab, ta_lo = ta_hi + 32;
+        if (elected) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t adv = (uint64_t)(2 * kk);
+            umma_tf32_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (c > 0 || kk > 0) ? 1u : 0u);
+            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
+            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                       :: "r"(chunk_done + 8 * ab) : "memory");
+          if (c == nch - 1)
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(full_bar) : "memory");
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == PS_TMA_WARP) {
+    // ---------------------------------------------------------------- TMA warp: W1 / W2 tiles (hi, lo), 4 chunks ahead
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
+    bool alive = true;
+    uint32_t w_g = 0;
+    for (int p = 0; p < n_phases && alive; ++p) {
+      bool is_l2;
+      int k;
+      decode(p, is_l2, k);
+      const int nch = is_l2 ? 4 : nch1;
+      const int wrow = 128 * (k & 1);  // first weight row of this unit's branch
+      const CUtensorMap* const m_hi = is_l2 ? &maps.w2[0] : &maps.w1[0];
+      const CUtensorMap* const m_lo = is_l2 ? &maps.w2[1] : &maps.w1[1];
+      for (int c = 0; c < nch && alive; ++c, ++w_g) {
+        const uint32_t slot = w_g & 3;
+        if (w_g >= 4) alive = mbar_wait(chunk_done + 8 * slot, ((w_g >> 2) - 1) & 1);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
+        const uint32_t bar = ready + 8 * slot;
+        if (elected) {
+          const uint32_t dst = ring_u + slot * 2 * TC_TILE_BYTES;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
+          tma_load_2d(dst, m_hi, bar, c * TC_BK, wrow);
+          tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, c * TC_BK, wrow);
+        }
+        __syncwarp();
+      }
+    }
+    if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
+      for (uint32_t i = w_g >= 4 ? w_g - 4 : 0; i < w_g; ++i) mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
+    }
+  } else if (warp >= PS_EPI_WARP0) {
+    // ---------------------------------------------------------------- epilogue warps: mid(k) then epi(k), unit by unit
+    // Warp (q, hf): rows 32 q.. of the tile (its TMEM lane quarter), columns 64 hf.. of the branch; thread = row.
+    const int e = warp - PS_EPI_WARP0, q = warp & 3, hf = e >> 2;
+    const uint32_t lane_q = tmem_base + ((uint32_t)(q * 32) << 16);
+    float* const xs = reinterpret_cast<float*>(smem + GP_XSUM_OFF);
+    const float* const b1 = d.b1;
+    const float* const b2 = d.b2;
+    float* const z1 = d.z1;
+    float* const z2 = d.z2;
+    float* const hout = d.h;
+    float* const out2 = d.out2;
+    const float* const res = d.res;
+    const float* const res_w = d.res_w;
+    bool alive = true;
+    for (int k = 0; k < n_units; ++k) {
+      const int acc = k & 1;  // = branch: 0 core, 1 gate
+      const int64_t row = (int64_t)(first_rt + (k >> 1) * step_rt) * 128 + q * 32 + lane;
+      const bool valid = row < n_rows;
+      const uint32_t upar = (uint32_t)((k >> 1) & 1);
+      const uint32_t d_lane = lane_q + 128u * acc + 64u * hf;
+      // ------------------------------------------------ mid(k): z1 -> SiLU -> hi / lo -> A operand of layer 2
+      if (alive) alive = mbar_wait(d1_full + 8 * acc, upar);
+      alive = __all_sync(0xffffffffu, alive);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t gl2 = (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k);  // first chunk of L2(k)
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * hf + cc;  // K chunk of layer 2 = columns 32 c.. of this branch's z1
+        float x[32];
+        {
+          uint32_t v[32];
+          MB_TMEM_LD32(d_lane + 32u * cc, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
+        }
+        if (b1) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float bv[8];
+            ld8(b1 + 128 * acc + 32 * c + 8 * jj, bv);  // same address in every lane: a broadcast load
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[8 * jj + i] += bv[i];
+          }
+        }
+        if (z1 && valid) {
+          float* zp = z1 + row * d.ld_z1 + 128 * acc + 32 * c;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = x[8 * jj + i];
+            st8(zp + 8 * jj, o);
+          }
+        }
+        const uint32_t gi = gl2 + (uint32_t)c, ab = gi & 3;
+        const uint32_t ta = lane_q + 256 + 64 * ab;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float s = silu_fast_f(x[16 * hh + i]);
+            hi[i] = __float_as_uint(s) & 0xFFFFE000u;
+            lo[i] = __float_as_uint(s - __uint_as_float(hi[i]));
+          }
+          if (hh == 0) {
+            if (alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);  // A buffer ab is free again
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          }
+          MB_TMEM_ST16(ta + 16 * hh, hi);
+          MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready + 8 * ab);
+      }
+      // ------------------------------------------------ epi(k): z2 -> RMSNorm -> activation -> h
+      if (alive) alive = mbar_wait(d2_full + 8 * acc, upar);
+      alive = __all_sync(0xffffffffu, alive);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float y[64];
+      {
+        uint32_t v0[32], v1[32];
+        MB_TMEM_LD32(d_lane, v0);
+        MB_TMEM_LD32(d_lane + 32u, v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { y[i] = __uint_as_float(v0[i]); y[32 + i] = __uint_as_float(v1[i]); }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the accumulator is in registers: the next unit may overwrite it
+      float ss = 0.f;
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        if (b2) {
+          float bv[8];
+          ld8(b2 + 128 * acc + 64 * hf + 8 * jj, bv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[8 * jj + i] += bv[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(y[8 * jj + i], y[8 * jj + i], ss);
+      }
+      if (z2 && valid) {
+        float* zp = z2 + row * d.ld_z2 + 128 * acc + 64 * hf;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = y[8 * jj + i];
+          st8(zp + 8 * jj, o);
+        }
+      }
+      // the other half of the row's sum of squares comes from the partner warp (same quarter, other column half)
+      xs[acc * 256 + hf * 128 + q * 32 + lane] = ss;
+      asm volatile("bar.sync %0, 64;" :: "r"(1 + q) : "memory");
+      ss += xs[acc * 256 + (hf ^ 1) * 128 + q * 32 + lane];
+      const float rinv = rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
+      // the core unit parks c = SiLU(.) in the output row; the gate unit (same thread, next unit) reads it back
+      float* const park = (hout ? hout + row * d.ld_h : out2 + row * d.ld_out2) + 64 * hf;
+      if (!alive || !valid) {
+        // nothing to write for rows past the end (or after an expired wait)
+      } else if (acc == 0) {
+        const float* const nw = d.norm_core + 64 * hf;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          float w[8], o[8];
+          ld8(nw + 8 * jj, w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = silu_fast_f(y[8 * jj + i] * rinv * w[i]);
+          st8(park + 8 * jj, o);
+        }
+      } else {
+        const float* const nw = d.norm_gate + 64 * hf;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          float w[8], cprev[8], o[8];
+          ld8(nw + 8 * jj, w);
+          ld8(park + 8 * jj, cprev);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = cprev[i] * sigmoid_fast_f(y[8 * jj + i] * rinv * w[i]);
+          if (hout) st8(park + 8 * jj, o);
+          if (out2) {
+            float r8[8];
+            ld8(res + row * d.ld_res + 64 * hf + 8 * jj, r8);
+            if (res_w) {
+              float rw[8];
+              ld8(res_w + 64 * hf + 8 * jj, rw);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = fmaf(rw[i], r8[i], o[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] += r8[i];
+            }
+            st8(out2 + row * d.ld_out2 + 64 * hf + 8 * jj, o);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- producers (layer-1 chunks only)
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    bool alive = true;
+    uint32_t g = 0;
+    int n = 0;
+    int act_mask = 0;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) act_mask |= (s < n_src && d.src[s].act) ? (1 << s) : 0;
+    for (int p = 0; p < n_phases; ++p) {
+      bool is_l2;
+      int k;
+      decode(p, is_l2, k);
+      if (is_l2) {
+        g += 4;
+        continue;
+      }
+      for (int c = par; c < nch1; c += 2, ++n) {
+        const uint32_t gi = g + c, ab = gi & 3;
+        gather_next();
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncwarp();
+        const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
+        const bool act = (act_mask >> (c >> 2)) & 1;
+        const uint32_t ta = lane_base + 256 + 64 * ab;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          float x[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t addr = patch + lane * 128 + (((4 * hh + j) ^ (lane & 7)) << 4);
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]),
+                         "=f"(x[4 * j + 2]), "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
+          }
+          if (act) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = silu_fast_f(x[i]);
+          }
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            hi[i] = __float_as_uint(x[i]) & 0xFFFFE000u;
+            lo[i] = __float_as_uint(x[i] - __uint_as_float(hi[i]));
+          }
+          if (hh == 0) {
+            if (gi >= 4 && alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          }
+          MB_TMEM_ST16(ta + 16 * hh, hi);
+          MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready + 8 * ab);
+      }
+      g += (uint32_t)nch1;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  }
+
+  // ------------------------------------------------------------------ common exit: release tensor memory
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == PS_MMA_WARP) {
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(PS_TMEM_COLS) : "memory");
+  }
+}

@@ -224,30 +224,17 @@ struct alignas(64) TcMaps { CUtensorMap m[4][2]; };  // per column block: W_hi, 
 
 __device__ int g_gemm_status = 0;  // bit 0: an mbarrier wait expired
 
-#ifdef MB_GEMM_TIMING  // diagnostic build only: per-phase clock64() totals of thread 0 (producer) and the control thread
-__device__ unsigned long long g_gemm_timing[32];
-#define MB_TSTART const long long t_kernel0 = clock64()
-#define MB_TDECL long long t_last = t_kernel0; long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define MB_T(slot) do { const long long _n = clock64(); tacc[slot] += _n - t_last; t_last = _n; } while (0)
-#define MB_TFLUSH(base, n) do { for (int _k = 0; _k < (n); ++_k) atomicAdd(&g_gemm_timing[(base) + _k], (unsigned long long)tacc[_k]); } while (0)
-#else
-#define MB_TSTART
-#define MB_TDECL
-#define MB_T(slot)
-#define MB_TFLUSH(base, n)
-#endif
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // Bounded wait.  The suspend-time hint lets the hardware park the thread until the phase completes (or the hint runs
 // out) instead of re-issuing the poll: waiting warps then leave the issue slots to the warps that convert and store.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = TC_WAIT_LIMIT) {
   uint32_t ok;
   // fast path: a phase that has already completed is seen by one non-blocking test
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   if (ok) return true;
-  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
     if (ok) return true;
@@ -315,7 +302,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 
 __global__ void __launch_bounds__(TC_THREADS, 2)
 k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps maps) {
-  MB_TSTART;
   const int jb = (int)(blockIdx.x % (unsigned)d.n_blocks);  // column block (fastest: the blocks of a row tile share A in L2)
   const int64_t row0 = (int64_t)(blockIdx.x / (unsigned)d.n_blocks) * 128;
   const mb_colblock& cb = d.blk[jb];
@@ -416,13 +402,10 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
     // ------------------------------------------------------------ control thread: TMA + MMA issue
     if (lane == 0) {
       bool alive = true;
-      MB_TDECL;
       for (int c = 0; c < n_chunks; ++c) {
         const int ab = c & 1;  // A buffer, W slot and completion barrier of this chunk
         if (alive) alive = mbar_wait(a_full + 8 * ab, (uint32_t)((c >> 1) & 1));
-        MB_T(0);
         if (alive) alive = mbar_wait(w_full + 8 * ab, (uint32_t)((c >> 1) & 1));
-        MB_T(1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t wb = ring + (uint32_t)ab * 2 * TC_TILE_BYTES;
         const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
@@ -436,14 +419,11 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                      :: "r"(mma_done + 8 * ab) : "memory");
-        MB_T(2);
         if (c + 2 < n_chunks) {  // this chunk's W slot is refilled as soon as its MMAs have retired
           if (alive) alive = mbar_wait(mma_done + 8 * ab, (uint32_t)((c >> 1) & 1));
           load_w(c + 2);
         }
-        MB_T(3);
       }
-      MB_TFLUSH(8, 4);
     }
     return;
   }
@@ -455,15 +435,12 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   for (int sgm = 0; sgm < 4; ++sgm) act_of_seg[sgm] = sgm < cb.n_src ? cb.src[sgm].act : 0;
 
   bool alive = true;
-  MB_TDECL;
-  MB_T(0);
   for (int c = 0; c < n_chunks; ++c) {
     const int ab = c & 1;
     // stage (c+2) % 3 was last read for chunk c-1, and the __syncwarp that closed that chunk orders those reads
     if (c + 2 < n_chunks) gather(c + 2); else asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 2;" ::: "memory");  // chunk c's copies of this lane have landed
     __syncwarp();                                          // ... and so have the other lanes'
-    MB_T(1);
     const uint32_t patch = patch0 + (uint32_t)(c % TC_A_STAGES) * (32 * 128);
     float x[32];
 #pragma unroll
@@ -472,7 +449,6 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
       asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]), "=f"(x[4 * j + 2]),
                    "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
     }
-    MB_T(2);
     uint32_t hi[32], lo[32];
     if (act_of_seg[c >> 2]) {  // branch once per chunk: the SiLU must not be evaluated (and discarded) on the plain path
 #pragma unroll
@@ -485,7 +461,6 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
       lo[q] = __float_as_uint(x[q] - h);
     }
     if (c >= 2 && alive) alive = mbar_wait(mma_done + 8 * ab, (uint32_t)(((c >> 1) - 1) & 1));  // A buffer ab is free again
-    MB_T(3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t ta = lane_base + 128 + 64 * ab;
     MB_TMEM_ST32(ta, hi);
@@ -494,12 +469,10 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncwarp();  // all lanes have read their patch rows: the stage may be overwritten two chunks from now
     if (lane == 0) mbar_arrive(a_full + 8 * ab);
-    MB_T(4);
   }
   // all MMAs retire in order: the last chunk's commit covers the whole accumulator
   if (alive) alive = mbar_wait(mma_done + 8 * ((n_chunks - 1) & 1), (uint32_t)(((n_chunks - 1) >> 1) & 1));
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  MB_T(5);
 
   // -------------------------------------------------------------- epilogue
   // (1) accumulator row -> staging (the W ring is idle: every TMA landed and every MMA retired)
@@ -518,7 +491,6 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
   }
-  MB_T(6);
   // (2) warp w finishes rows w, w+4, ...: lane l owns columns 4l..4l+3, every global access is a full 512-byte row
   const int col = lane * 4;
   const float* const gate = cb.gate;
@@ -588,23 +560,20 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
   auto pick_res = [&](auto g, auto a) { if (res) finish_rows(g, a, T{}); else finish_rows(g, a, F{}); };
   auto pick_act = [&](auto g) { if (out_act) pick_res(g, T{}); else pick_res(g, F{}); };
   if (gate) pick_act(T{}); else pick_act(F{});
-  MB_T(7);
-#ifdef MB_GEMM_TIMING
-  if (tid == 0) MB_TFLUSH(0, 8);
-#endif
 }
 
 #include "gemm_persistent.cuh"
+#include "gated_persistent.cuh"
 
 static int g_gemm_mode = 0;  // 0: persistent tcgen05 3xTF32, 1: fp32 SIMT, 2: one-tile-per-CTA tcgen05 3xTF32
 
-// TMA descriptor of a [128, k] float32 weight block (row stride ldw), box 128 rows x 32 columns, 128-byte swizzle.
-// Encoding depends only on (address, stride, k), so descriptors are cached per host thread.
+// TMA descriptor of a [rows, k] float32 weight block (row stride ldw), box 128 rows x 32 columns, 128-byte swizzle.
+// Encoding depends only on (address, stride, k, rows), so descriptors are cached per host thread.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out) {
+static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out, int rows = 128) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     void* fn = nullptr;
@@ -618,18 +587,18 @@ static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out) {
     MB_CUDA_CHECK(cudaFree(nullptr));
     bound = true;
   }
-  struct Key { const float* w; int64_t ld; int k; };
+  struct Key { const float* w; int64_t ld; int k; int rows; };
   struct Entry { Key key; CUtensorMap map; };
   constexpr int SLOTS = 1024;
   static thread_local Entry* cache = nullptr;
   if (!cache) cache = new Entry[SLOTS]();
-  const size_t hsh = ((reinterpret_cast<uintptr_t>(w) >> 4) * 0x9E3779B97F4A7C15ull + (uint64_t)k) >> 54;  // 10 bits
+  const size_t hsh = ((reinterpret_cast<uintptr_t>(w) >> 4) * 0x9E3779B97F4A7C15ull + (uint64_t)(k + rows)) >> 54;  // 10 bits
   Entry& e = cache[hsh % SLOTS];
-  if (e.key.w == w && e.key.ld == ldw && e.key.k == k) {
+  if (e.key.w == w && e.key.ld == ldw && e.key.k == k && e.key.rows == rows) {
     *out = e.map;
     return MB_OK;
   }
-  const cuuint64_t dims[2] = {(cuuint64_t)k, 128};
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ldw * sizeof(float)};
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128};
   const cuuint32_t estr[2] = {1, 1};
@@ -642,9 +611,105 @@ static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out) {
     set_cuda_error(cudaErrorInvalidValue, where);
     return MB_ERR_CUDA;
   }
-  e.key = Key{w, ldw, k};
+  e.key = Key{w, ldw, k, rows};
   e.map = *out;
   return MB_OK;
+}
+
+// Per-device set-up of the tensor-core kernels: the dynamic shared-memory attribute belongs to the (function, device)
+// pair and the persistent grids are sized by the device's SM count.  One slot per device ordinal; two host threads
+// that race on a device's first call write the same values.
+struct DeviceConfig { bool ready; int n_sm; };
+static DeviceConfig g_device_config[64];
+
+static int device_config(int* n_sm) {
+  int dev = 0;
+  MB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return MB_ERR_INVALID;
+  DeviceConfig& c = g_device_config[dev];
+  if (!c.ready) {
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
+    int n = 0;
+    MB_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    c.n_sm = n;
+    c.ready = true;
+  }
+  *n_sm = c.n_sm;
+  return MB_OK;
+}
+
+// ---- self-test of the bounded wait: a barrier nothing arrives at, a limit of a few polls
+__global__ void k_selftest_wait_expiry() {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // same wait, same give-up path as in the GEMM kernels (status bit 0), with 8 polls of at most 4 us instead of 2^20
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, 8);
+  __syncthreads();
+}
+
+// ---- issue rate of tcgen05.mma with resident operands (TS form: A in tensor memory, B in shared memory)
+template <int KIND>  // 0: kind::tf32 (K = 8 per instruction), 1: kind::f16 with bf16 operands (K = 16)
+__global__ void __launch_bounds__(128, 1) k_mma_rate(int iters) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t slot;
+  if ((smem_u32(smem) & 1023u) != 0) return;
+  for (int i = threadIdx.x; i < 32 * 1024 / 4; i += blockDim.x) reinterpret_cast<float*>(smem)[i] = 0.f;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" :: "r"(smem_u32(&slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tb = slot;
+  if (threadIdx.x < 32) {  // warp-uniform loop, one elected lane issues
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const uint32_t fmt = KIND == 0 ? 2u : 1u;  // operand format field: tf32 / bf16
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+    const uint64_t db = umma_desc(smem_u32(smem));
+    const uint32_t ta = tb + 256;
+    for (int i = 0; i < iters; ++i) {
+      if (elected) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          if (KIND == 0)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+                         :: "r"(tb), "r"(ta + 8 * kk), "l"(db + (uint64_t)(2 * kk)), "r"(idesc), "r"(1u) : "memory");
+          else
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                         :: "r"(tb), "r"(ta + 8 * kk), "l"(db + (uint64_t)(2 * kk)), "r"(idesc), "r"(1u) : "memory");
+        }
+      }
+      __syncwarp();
+    }
+    if (elected)
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                   :: "r"(smem_u32(&bar)) : "memory");
+    __syncwarp();
+    // every issued instruction has retired when the commit arrives; bounded like every other wait here
+    mbar_wait(smem_u32(&bar), 0, 1u << 22);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" :: "r"(tb) : "memory");
+  }
 }
 
 }  // namespace mb
@@ -654,16 +719,6 @@ extern "C" int mb_set_gemm_mode(int mode) {
   mb::g_gemm_mode = mode;
   return MB_OK;
 }
-
-#ifdef MB_GEMM_TIMING
-extern "C" int mb_gemm_read_timing(unsigned long long* host16) {
-  unsigned long long zero[32] = {0};
-  MB_CUDA_CHECK(cudaDeviceSynchronize());
-  MB_CUDA_CHECK(cudaMemcpyFromSymbol(host16, mb::g_gemm_timing, sizeof(zero)));
-  MB_CUDA_CHECK(cudaMemcpyToSymbol(mb::g_gemm_timing, zero, sizeof(zero)));
-  return MB_OK;
-}
-#endif
 
 extern "C" int mb_gemm_status(int* status, void* stream_) {
   if (!status) return MB_ERR_INVALID;
@@ -681,6 +736,48 @@ extern "C" int mb_gemm_status_async(int* host_status, void* stream_) {
   return MB_OK;
 }
 
+extern "C" int mb_gemm_status_clear(void* stream_) {
+  void* addr = nullptr;
+  MB_CUDA_CHECK(cudaGetSymbolAddress(&addr, mb::g_gemm_status));
+  MB_CUDA_CHECK(cudaMemsetAsync(addr, 0, sizeof(int), (cudaStream_t)stream_));
+  return MB_OK;
+}
+
+extern "C" int mb_selftest_wait_expiry(void* stream_) {
+  mb::k_selftest_wait_expiry<<<1, 32, 0, (cudaStream_t)stream_>>>();
+  MB_LAUNCH_CHECK("k_selftest_wait_expiry");
+  return MB_OK;
+}
+
+extern "C" int mb_bench_mma_rate(int kind, int iters, float* elapsed_ms, int* n_sms, void* stream_) {
+  if ((kind != 0 && kind != 1) || iters < 1 || iters > (1 << 24) || !elapsed_ms || !n_sms) return MB_ERR_INVALID;
+  int n_sm = 0;
+  int rc = mb::device_config(&n_sm);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream_;
+  const int smem = 33 * 1024;
+  cudaEvent_t e0, e1;
+  MB_CUDA_CHECK(cudaEventCreate(&e0));
+  MB_CUDA_CHECK(cudaEventCreate(&e1));
+  cudaError_t err = cudaEventRecord(e0, st);
+  if (err == cudaSuccess) {
+    if (kind == 0) mb::k_mma_rate<0><<<n_sm, 128, smem, st>>>(iters);
+    else mb::k_mma_rate<1><<<n_sm, 128, smem, st>>>(iters);
+    err = cudaGetLastError();
+  }
+  if (err == cudaSuccess) err = cudaEventRecord(e1, st);
+  if (err == cudaSuccess) err = cudaEventSynchronize(e1);
+  if (err == cudaSuccess) err = cudaEventElapsedTime(elapsed_ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (err != cudaSuccess) {
+    mb::set_cuda_error(err, "mb_bench_mma_rate");
+    return MB_ERR_CUDA;
+  }
+  *n_sms = n_sm;
+  return MB_OK;
+}
+
 extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
   int rc = gemm_validate(desc);
   if (rc) return rc;
@@ -691,16 +788,9 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
     dim3 grid((unsigned)gx, (unsigned)desc->n_blocks);
     mb::k_gemm<<<grid, mb::GEMM_THREADS, 0, (cudaStream_t)stream_>>>(*desc);
   } else {
-    static bool configured = false;  // per process; the attribute is per device function and context
-    static int n_sm = 0;
-    if (!configured) {
-      MB_CUDA_CHECK(cudaFuncSetAttribute(mb::k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, mb::TC_SMEM_BYTES));
-      MB_CUDA_CHECK(cudaFuncSetAttribute(mb::k_gemm_ps, cudaFuncAttributeMaxDynamicSharedMemorySize, mb::PS_SMEM_BYTES));
-      int dev = 0;
-      MB_CUDA_CHECK(cudaGetDevice(&dev));
-      MB_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-      configured = true;
-    }
+    int n_sm = 0;
+    rc = mb::device_config(&n_sm);
+    if (rc) return rc;
     mb::TcMaps maps;
     for (int j = 0; j < desc->n_blocks; ++j) {
       const mb_colblock& cb = desc->blk[j];
@@ -711,7 +801,8 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
       if (rc) return rc;
     }
     const long long n_tiles = gx * desc->n_blocks;
-    // the persistent kernel's epilogue uses 32-byte accesses; operands aligned to 16 bytes only take the tile kernel
+    // The persistent kernel's epilogue uses 32-byte accesses.  Operands aligned to 16 bytes only (a caller of the C
+    // ABI that passes views at odd column offsets; the Python host side never does) take the one-tile kernel.
     bool wide_ok = true;
     for (int j = 0; j < desc->n_blocks; ++j) {
       const mb_colblock& cb = desc->blk[j];
@@ -730,5 +821,74 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
     }
   }
   MB_LAUNCH_CHECK("k_gemm");
+  return MB_OK;
+}
+
+// The same result as the fused kernel from the separate kernels (GEMM modes 1 and 2, or operands that are only
+// 16-byte aligned): two mb_gemm launches and the row-wise gate kernel, with z1 / z2 as scratch.
+static int gated_mlp_composed(const mb_gated_mlp* g, void* stream_) {
+  if (!g->z1 || !g->z2 || g->ld_z2 != 256 || !g->W1 || !g->W2) return MB_ERR_INVALID;
+  if ((g->h && g->ld_h != 128) || (g->out2 && (g->ld_out2 != 128 || g->ld_res != 128))) return MB_ERR_INVALID;
+  mb_gemm_desc a = {}, b = {};
+  a.n_rows = b.n_rows = g->n_rows;
+  a.n_blocks = b.n_blocks = 2;
+  for (int j = 0; j < 2; ++j) {
+    mb_colblock& ca = a.blk[j];
+    ca.n_src = g->n_src;
+    for (int s = 0; s < g->n_src; ++s) ca.src[s] = g->src[s];
+    ca.W = g->W1 + (int64_t)128 * j * g->ldw1;
+    ca.W_hi = g->W1_hi ? g->W1_hi + (int64_t)128 * j * g->ldw1 : nullptr;
+    ca.W_lo = g->W1_lo ? g->W1_lo + (int64_t)128 * j * g->ldw1 : nullptr;
+    ca.ldw = g->ldw1;
+    ca.bias = g->b1 ? g->b1 + 128 * j : nullptr;
+    ca.out = g->z1; ca.ld_out = g->ld_z1; ca.col_out = 128 * j; ca.out_scale = 1.f; ca.mode = MB_OUT_STORE;
+    mb_colblock& cb = b.blk[j];
+    cb.n_src = 1;
+    cb.src[0].ptr = g->z1; cb.src[0].ld = g->ld_z1; cb.src[0].col = 128 * j; cb.src[0].act = 1;
+    cb.W = g->W2 + (int64_t)128 * j * g->ldw2;
+    cb.W_hi = g->W2_hi ? g->W2_hi + (int64_t)128 * j * g->ldw2 : nullptr;
+    cb.W_lo = g->W2_lo ? g->W2_lo + (int64_t)128 * j * g->ldw2 : nullptr;
+    cb.ldw = g->ldw2;
+    cb.bias = g->b2 ? g->b2 + 128 * j : nullptr;
+    cb.out = g->z2; cb.ld_out = g->ld_z2; cb.col_out = 128 * j; cb.out_scale = 1.f; cb.mode = MB_OUT_STORE;
+  }
+  int rc = mb_gemm(&a, stream_);
+  if (rc) return rc;
+  rc = mb_gemm(&b, stream_);
+  if (rc) return rc;
+  return mb_gate_fwd(g->n_rows, g->z2, g->norm_core, g->norm_gate, g->h, g->res, g->res_w, g->out2, stream_);
+}
+
+extern "C" int mb_gated_mlp_fwd(const mb_gated_mlp* g, void* stream_) {
+  if (!g || g->n_rows < 0 || g->n_src < 1 || g->n_src > 4) return MB_ERR_INVALID;
+  if (!g->norm_core || !g->norm_gate || (!g->h && !g->out2) || (g->out2 && !g->res)) return MB_ERR_INVALID;
+  if (g->ldw1 < 128 * g->n_src || (g->ldw1 & 3) || g->ldw2 < 128 || (g->ldw2 & 3)) return MB_ERR_INVALID;
+  for (int s = 0; s < g->n_src; ++s) {
+    const mb_src& sr = g->src[s];
+    if (!sr.ptr || !mb::aligned16(sr.ptr) || (sr.ld & 3) || (sr.col & 3)) return MB_ERR_INVALID;
+  }
+  if (g->n_rows == 0) return MB_OK;
+  if ((g->n_rows + 127) / 128 > 0x3fffffffLL) return MB_ERR_OVERFLOW;
+  auto ok32 = [](const void* p, int64_t ld) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0 && (ld & 7) == 0; };
+  const bool wide_ok = (!g->z1 || ok32(g->z1, g->ld_z1)) && (!g->z2 || ok32(g->z2, g->ld_z2)) &&
+                       (!g->h || ok32(g->h, g->ld_h)) && (!g->out2 || (ok32(g->out2, g->ld_out2) && ok32(g->res, g->ld_res))) &&
+                       (!g->b1 || ok32(g->b1, 0)) && (!g->b2 || ok32(g->b2, 0)) && ok32(g->norm_core, 0) &&
+                       ok32(g->norm_gate, 0) && (!g->res_w || ok32(g->res_w, 0));
+  if (mb::g_gemm_mode != 0 || !wide_ok) return gated_mlp_composed(g, stream_);
+  if (!g->W1_hi || !g->W1_lo || !g->W2_hi || !g->W2_lo) return MB_ERR_INVALID;
+  if (!mb::aligned16(g->W1_hi) || !mb::aligned16(g->W1_lo) || !mb::aligned16(g->W2_hi) || !mb::aligned16(g->W2_lo))
+    return MB_ERR_INVALID;
+  int n_sm = 0;
+  int rc = mb::device_config(&n_sm);
+  if (rc) return rc;
+  mb::GatedMaps maps;
+  if ((rc = mb::weight_map(g->W1_hi, g->ldw1, 128 * g->n_src, &maps.w1[0], 256))) return rc;
+  if ((rc = mb::weight_map(g->W1_lo, g->ldw1, 128 * g->n_src, &maps.w1[1], 256))) return rc;
+  if ((rc = mb::weight_map(g->W2_hi, g->ldw2, 128, &maps.w2[0], 256))) return rc;
+  if ((rc = mb::weight_map(g->W2_lo, g->ldw2, 128, &maps.w2[1], 256))) return rc;
+  const long long n_tiles = (g->n_rows + 127) / 128;
+  const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
+  mb::k_gated_fwd<<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
+  MB_LAUNCH_CHECK("k_gated_fwd");
   return MB_OK;
 }

@@ -54,7 +54,6 @@ static_assert(PS_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 
 __global__ void __launch_bounds__(PS_THREADS, 1)
 k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ TcMaps maps) {
-  MB_TSTART;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PS_BAR_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + PS_BAR_OFF + 128);
@@ -181,7 +180,6 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
     const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
     bool alive = true;
-    MB_TDECL;
     uint32_t nch_of = 0;  // chunks per tile of the (up to four) column blocks, a byte each: no descriptor read per tile
     for (int j = 0; j < n_blocks; ++j) nch_of |= (uint32_t)(d.blk[j].n_src * 4) << (8 * j);
     nch_of = __shfl_sync(0xffffffffu, nch_of, 0);
@@ -194,10 +192,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       for (int c = 0; c < nch; ++c, ++g) {
         const uint32_t ab = g & 3, slot = ab;  // A buffer and W slot of chunk g
         if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);  // A rows stored and W tiles landed
-        MB_T(0);
         if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
         alive = __all_sync(0xffffffffu, alive);
-        MB_T(2);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t wb = ring_u + slot * 2 * TC_TILE_BYTES;
         const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
@@ -217,12 +213,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
                          :: "r"(d_full + 8 * acc) : "memory");
         }
         __syncwarp();
-        MB_T(3);
       }
     }
-#ifdef MB_GEMM_TIMING
-    if (lane == 0) MB_TFLUSH(8, 4);
-#endif
   } else if (warp == PS_TMA_WARP) {
     // ---------------------------------------------------------------- TMA warp: W_hi / W_lo tiles, up to 4 chunks ahead
     // (warp-uniform loop, one elected lane issues: same reason as in the MMA warp)
@@ -265,7 +257,6 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     const int e = warp - PS_EPI_WARP0, quarter_e = warp & 3, half = e >> 2;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter_e * 32) << 16) + (uint32_t)(half * 64);
     bool alive = true;
-    MB_TDECL;
     int k = 0;
     for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
       const int acc = k & 1;
@@ -293,7 +284,6 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       }
       if (alive) alive = mbar_wait(d_full + 8 * acc, (uint32_t)((k >> 1) & 1));
       alive = __all_sync(0xffffffffu, alive);
-      MB_T(0);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       auto finish = [&](auto has_gate, auto has_act, auto has_res) {
 #pragma unroll 1
@@ -428,17 +418,11 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       if (mode != MB_OUT_STORE) finish_reduce();
       else if (gate) pick_act(T{});
       else pick_act(F{});
-      MB_T(2);
     }
-#ifdef MB_GEMM_TIMING
-    if (warp == PS_EPI_WARP0 && lane == 0) MB_TFLUSH(16, 3);
-#endif
   } else {
     // ---------------------------------------------------------------- producers: thread = row = TMEM lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool alive = true;
-    MB_TDECL;
-    MB_T(0);
     uint32_t g = 0;
     int n = 0;  // chunks this warp has converted
     for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb)) {
@@ -450,11 +434,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       for (int c = par; c < nch; c += 2, ++n) {
         const uint32_t gi = g + c, ab = gi & 3;
         gather_next();  // into the stage read one chunk ago; the __syncwarp that closed that chunk orders the reads
-        MB_T(5);
         asm volatile("cp.async.wait_group 1;" ::: "memory");  // this chunk's copies of this lane have landed
-        MB_T(6);
         __syncwarp();                                          // ... and so have the other lanes'
-        MB_T(1);
         const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
         const bool act = (act_mask >> (c >> 2)) & 1;  // branch once per chunk: no SiLU is evaluated on the plain path
         const uint32_t ta = lane_base + 256 + 64 * ab;
@@ -478,10 +459,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
             lo[q] = __float_as_uint(x[q] - __uint_as_float(hi[q]));
           }
           if (h == 0) {
-            MB_T(2);
             if (gi >= 4 && alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);  // A buffer ab is free again
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            MB_T(3);
           }
           MB_TMEM_ST16(ta + 16 * h, hi);
           MB_TMEM_ST16(ta + 32 + 16 * h, lo);
@@ -490,14 +469,10 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();  // all lanes have read their patch rows and written their A rows
         if (lane == 0) mbar_arrive(ready + 8 * ab);
-        MB_T(4);
       }
       g += (uint32_t)nch;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-#ifdef MB_GEMM_TIMING
-    if (warp == PS_PROD_WARP0 && lane == 0) MB_TFLUSH(0, 8);
-#endif
   }
 
   // ------------------------------------------------------------------ common exit: release tensor memory

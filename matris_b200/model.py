@@ -134,14 +134,10 @@ def row_graphs(g: BatchedGraph):
 
 
 # ------------------------------------------------------------------ gated MLP building block
-def gated_fwd(p, n_rows, srcs):
-    """z1 = X W1^T + b1 (core|gate, pre-activation), z2 = SiLU(z1) W2^T + b2 (pre-norm)."""
-    ref = srcs[0][0]
-    z1, z2 = ops.new(n_rows, 2 * D, ref), ops.new(n_rows, 2 * D, ref)
-    gemm(n_rows, [B(srcs, p.w1, w_row=D * j, bias=p.b1, bias_off=D * j, out=z1, out_col=D * j) for j in (0, 1)])
-    gemm(n_rows, [B([S(z1, None, D * j, 1)], p.w2, w_row=D * j, bias=p.b2, bias_off=D * j, out=z2, out_col=D * j)
-                  for j in (0, 1)])
-    return z1, z2
+def gated_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True):
+    """GatedMLP.forward (matris/model/functions.py:300-311) in one kernel: returns (z1, z2, h, out2) with
+    z1 = X W1^T + b1 (core|gate pre-activations) and z2 = SiLU(z1) W2^T + b2 (pre-norm) only when ``save``."""
+    return ops.gated_mlp_fwd(p, n_rows, srcs, want_h=want_h, res=res, res_w=res_w, save=save)
 
 
 def gated_bwd(p, n_rows, z1, z2, dh, dests):
@@ -165,18 +161,19 @@ def gated_bwd(p, n_rows, z1, z2, dh, dests):
 
 
 # ------------------------------------------------------------------ attention layer
-def _attn_forward(P, rg, node, edge):
+def _attn_forward(P, rg, node, edge, save=True):
+    """``save``: also return the internals the backward pass reads (z1, z2 of both gated MLPs are then written)."""
     R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
-    z1, z2 = gated_fwd(P.edge, R, [S(edge, rg.emap), S(node, rg.tgt), S(node, rg.src)])
+    srcs = [S(edge, rg.emap), S(node, rg.tgt), S(node, rg.src)]
     if rg.is_atom:
-        h, _ = ops.gate_fwd(z2, P.edge.nc, P.edge.ng)
+        z1, z2, h, _ = gated_fwd(P.edge, R, srcs, save=save)
         edge_out = ops.pair_mean_res(Ne, rg.u2d, rg.rev, h, edge, P.we)
     else:
-        h, edge_out = ops.gate_fwd(z2, P.edge.nc, P.edge.ng, res=edge, res_w=P.we)
+        z1, z2, h, edge_out = gated_fwd(P.edge, R, srcs, res=edge, res_w=P.we, save=save)
     logits = ops.linear(edge, P.wst)                      # [Ne,256]: source | target logits
     agg_t, agg_s, stats = ops.seg_attn_fwd(Nn, rg.tgt_ptr, rg.src_ptr, rg.src_perm, rg.emap, logits, h)
-    z1n, z2n = gated_fwd(P.node, Nn, [S(node), S(agg_t), S(agg_s)])
-    _, node_out = ops.gate_fwd(z2n, P.node.nc, P.node.ng, want_h=False, res=node, res_w=P.wn)
+    z1n, z2n, _, node_out = gated_fwd(P.node, Nn, [S(node), S(agg_t), S(agg_s)], want_h=False, res=node, res_w=P.wn,
+                                      save=save)
     return node_out, edge_out, (z1, z2, h, logits, agg_t, agg_s, stats, z1n, z2n)
 
 
@@ -186,10 +183,11 @@ class AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, node, edge, P, rg):
         node, edge = node.contiguous(), edge.contiguous()
-        node_out, edge_out, inter = _attn_forward(P, rg, node, edge)
+        keep = bool(rg.keep and any(ctx.needs_input_grad))
+        node_out, edge_out, inter = _attn_forward(P, rg, node, edge, save=keep)
         ctx.save_for_backward(node, edge)
         ctx.P, ctx.rg = P, rg
-        ctx.inter = inter if (rg.keep and any(ctx.needs_input_grad)) else None
+        ctx.inter = inter if keep else None
         return node_out, edge_out
 
     @staticmethod
@@ -230,14 +228,13 @@ class AttentionFn(torch.autograd.Function):
 
 
 # ------------------------------------------------------------------ refinement layer
-def _refine_forward(P, rg, node, edge, rbf, atom_feat):
+def _refine_forward(P, rg, node, edge, rbf, atom_feat, save=True):
     R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
     if rg.is_atom:
         srcs = [S(edge, rg.emap), S(node, rg.tgt), S(node, rg.src)]
     else:
         srcs = [S(edge), S(atom_feat, rg.ctr), S(node, rg.tgt), S(node, rg.src)]
-    z1, z2 = gated_fwd(P.edge, R, srcs)
-    h, _ = ops.gate_fwd(z2, P.edge.nc, P.edge.ng)
+    z1, z2, h, _ = gated_fwd(P.edge, R, srcs, save=save)
     env = ops.small_linear_fwd(rbf, P.wenv)               # [bonds,128]
     agg = ops.seg_smooth_sum_fwd(Nn, rg.tgt_ptr, rg.emap, None if rg.is_atom else rg.src, env, h)
     zn = ops.linear(agg, P.nffn.w1)
@@ -259,10 +256,11 @@ class RefineFn(torch.autograd.Function):
         node, edge, rbf = node.contiguous(), edge.contiguous(), rbf.contiguous()
         if atom_feat is not None:
             atom_feat = atom_feat.contiguous()
-        node_out, edge_out, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+        keep = bool(rg.keep and any(ctx.needs_input_grad))
+        node_out, edge_out, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat, save=keep)
         ctx.save_for_backward(node, edge, rbf, atom_feat)
         ctx.P, ctx.rg = P, rg
-        ctx.inter = inter if (rg.keep and any(ctx.needs_input_grad)) else None
+        ctx.inter = inter if keep else None
         return node_out, edge_out
 
     @staticmethod
@@ -584,12 +582,23 @@ class MatRIS(nn.Module):
             flag = getattr(self, "_gemm_flag", None)
             if flag is None:
                 flag = self._gemm_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
-            elif int(flag[0]) != 0:
-                raise MbError(f"a tensor-core GEMM wait expired in an earlier evaluation (status {int(flag[0])}); "
-                              "its results were invalid")
+            self.check_status()
             out = self._evaluate(g, task)
             ops.gemm_status_async(flag)
             return out
+
+    def check_status(self) -> None:
+        """Raise if a bounded wait of a tensor-core kernel expired in an evaluation whose status word has reached
+        the host (``forward`` enqueues the copy; it is valid once the stream has been synchronised, e.g. by reading
+        a result).  The word is cleared on raising, so that one expiry does not disable the model."""
+        flag = getattr(self, "_gemm_flag", None)
+        if flag is not None and int(flag[0]) != 0:
+            status = int(flag[0])
+            flag.zero_()
+            with torch.cuda.device(self.device):
+                ops.gemm_status_clear()
+            raise MbError(f"a tensor-core kernel's bounded wait expired (status {status}): the results of that "
+                          "evaluation are invalid")
 
     def _evaluate(self, g: BatchedGraph, task: str):
         cfg = self.config

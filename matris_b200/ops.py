@@ -117,8 +117,54 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
             float(b["scale"]))
     if _lib.profile is not None:
         _lib.profile_meta = dict(flops=sum(2.0 * n_rows * D * D * len(b["srcs"]) for b in blocks), rows=int(n_rows),
-                                 k=D * len(blocks[0]["srcs"]), n=D * len(blocks))
+                                 k=D * len(blocks[0]["srcs"]), n=D * len(blocks),
+                                 bytes=4.0 * n_rows * D * (len(blocks[0]["srcs"]) + len(blocks)))
     call("mb_gemm", C.byref(_lib.MbGemmDesc.from_buffer(buf)), _stream())
+
+
+_GATED_FMT = struct.Struct("<qii" + "QQqii" * 4 + "QQQqQ" + "QQQqQ" + "QQ" + "Qq" * 3 + "QQq" + "Qq")
+assert _GATED_FMT.size == C.sizeof(_lib.MbGatedMlp)
+
+
+def gated_mlp_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True):
+    """GatedMLP forward as one fused kernel (mb_gated_mlp_fwd).  ``p`` holds the packed weights (w1 [256,K], b1,
+    w2 [256,128], b2, nc, ng).  Returns (z1, z2, h, out2); z1 / z2 only when ``save`` (the backward pass reads
+    them), h only when ``want_h``, out2 = h + res_w * res only when ``res`` is given."""
+    ref = srcs[0][0]
+    n_rows = int(n_rows)
+    # the composed path of the non-default GEMM modes uses z1 / z2 as scratch
+    save = save or _gemm_mode != 0
+    z1 = new(n_rows, 2 * D, ref) if save else None
+    z2 = new(n_rows, 2 * D, ref) if save else None
+    h = new(n_rows, D, ref) if want_h else None
+    out2 = new(n_rows, D, ref) if res is not None else None
+    if n_rows == 0:
+        return z1, z2, h, out2
+    flat = []
+    for t, idx, col, act in srcs:
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+        flat += (t.data_ptr(), 0 if idx is None else idx.data_ptr(), t.stride(0), int(col), int(act))
+    for _ in range(4 - len(srcs)):
+        flat += _NO_SRC
+    w1, w2 = as_split(p.w1), as_split(p.w2)
+    assert w1.shape[0] == 2 * D and w1.shape[1] == D * len(srcs) and tuple(w2.shape) == (2 * D, D)
+
+    def pl(t):
+        return (0, 0) if t is None else (t.data_ptr(), t.stride(0))
+
+    buf = _GATED_FMT.pack(
+        n_rows, len(srcs), 0, *flat,
+        w1.w.data_ptr(), w1.hi.data_ptr(), w1.lo.data_ptr(), w1.w.stride(0), 0 if p.b1 is None else p.b1.data_ptr(),
+        w2.w.data_ptr(), w2.hi.data_ptr(), w2.lo.data_ptr(), w2.w.stride(0), 0 if p.b2 is None else p.b2.data_ptr(),
+        p.nc.data_ptr(), p.ng.data_ptr(), *pl(z1), *pl(z2), *pl(h),
+        0 if res is None else res.data_ptr(), 0 if res is None or res_w is None else res_w.data_ptr(),
+        0 if res is None else res.stride(0), *pl(out2))
+    if _lib.profile is not None:
+        cols = len(srcs) + (4 if z1 is not None else 0) + (h is not None) + 2 * (out2 is not None)
+        _lib.profile_meta = dict(flops=2.0 * n_rows * 2 * D * D * (len(srcs) + 1), rows=n_rows, k=D * len(srcs),
+                                 n=2 * D, fused=True, bytes=4.0 * n_rows * D * cols)
+    call("mb_gated_mlp_fwd", C.byref(_lib.MbGatedMlp.from_buffer_copy(buf)), _stream())
+    return z1, z2, h, out2
 
 
 def linear(x, W, bias=None, out_act=0, in_act=0, gate=None, res=None, res_w=None, scale=1.0, idx=None, out=None):
@@ -315,16 +361,40 @@ def angle_basis_bwd(line_graph, unit, factor, cutoff, dbasis):
 
 
 # ------------------------------------------------------------------ GEMM core selection / status
+_gemm_mode = 0
+
+
 def set_gemm_mode(mode: str) -> None:
-    """'tcgen05' (default): persistent tensor-core kernel, 3-term TF32 split; 'simt': exact fp32 FMA cross-check;
-    'tcgen05_tile': the one-tile-per-CTA tensor-core kernel (same arithmetic as the default)."""
-    _lib.check(_lib.load().mb_set_gemm_mode({"tcgen05": 0, "simt": 1, "tcgen05_tile": 2}[mode]), "mb_set_gemm_mode")
+    """'tcgen05' (default): persistent tensor-core kernels, 3-term TF32 split; 'simt': exact fp32 FMA cross-check;
+    'tcgen05_tile': the one-tile-per-CTA tensor-core kernel (same arithmetic as the default).  A test knob."""
+    global _gemm_mode
+    _gemm_mode = {"tcgen05": 0, "simt": 1, "tcgen05_tile": 2}[mode]
+    _lib.check(_lib.load().mb_set_gemm_mode(_gemm_mode), "mb_set_gemm_mode")
 
 
 def gemm_status_async(pinned_int32: torch.Tensor) -> None:
     """Enqueue a copy of the tensor-core kernels' status word into a pinned int32 tensor (no synchronisation)."""
     assert pinned_int32.dtype == torch.int32 and pinned_int32.is_pinned()
     call("mb_gemm_status_async", pinned_int32.data_ptr(), _stream())
+
+
+def gemm_status_clear() -> None:
+    """Zero the status word in stream order."""
+    call("mb_gemm_status_clear", _stream())
+
+
+def selftest_wait_expiry() -> None:
+    """Launch the one-CTA self-test whose bounded wait runs out (sets bit 0 of the status word)."""
+    call("mb_selftest_wait_expiry", _stream())
+
+
+def mma_rate(kind: str = "tf32", iters: int = 20000):
+    """Timed tcgen05.mma issue rate with resident operands: (TFLOP/s, elapsed ms)."""
+    ms, sms = C.c_float(0), C.c_int(0)
+    k = {"tf32": 0, "bf16": 1}[kind]
+    _lib.check(_lib.load().mb_bench_mma_rate(k, int(iters), C.byref(ms), C.byref(sms), _stream()), "mb_bench_mma_rate")
+    flops = 2.0 * 128 * 128 * (8 if k == 0 else 16) * 4 * iters * sms.value
+    return flops / (ms.value * 1e-3) / 1e12, ms.value
 
 
 def gemm_status() -> int:

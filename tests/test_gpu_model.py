@@ -207,3 +207,31 @@ def test_recompute_equals_kept_activations():
         res[keep] = (torch.cat(list(out["f"])).cpu(), torch.stack(out["s"]).cpu())
     report("keep vs recompute F", res[True][0], res[False][0], 2e-6)
     report("keep vs recompute S", res[True][1] / GPA, res[False][1] / GPA, 2e-7)
+
+
+def test_forward_raises_once_after_an_expired_wait_and_recovers():
+    """An expired bounded wait surfaces as one exception (at the next forward, or at check_status once the stream
+    has been synchronised) and the model then works again."""
+    from matris_b200 import MatRIS, ops
+    from matris_b200._lib import MbError
+    ck = random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=6)
+    model = MatRIS.from_dict(ck).to("cuda")
+    cr = [workloads.demo_pu4si6()]
+    first = model.predict(cr, "ef")
+    e0 = first["e"].cpu()
+    model.check_status()                 # nothing expired
+    ops.selftest_wait_expiry()           # a wait runs out on this device
+    out = model.predict(cr, "ef")        # this call's status copy carries the bit
+    torch.cuda.synchronize()
+    with pytest.raises(MbError, match="bounded wait expired"):
+        model.check_status()
+    again = model.predict(cr, "ef")      # the word was cleared on raising: no second exception
+    report("energy after recovery", again["e"].cpu(), e0, 1e-6)
+    torch.cuda.synchronize()
+    model.check_status()
+    ops.selftest_wait_expiry()
+    model.predict(cr, "e")
+    with pytest.raises(MbError):         # ... or the next forward raises
+        torch.cuda.synchronize()
+        model.predict(cr, "e")
+    model.predict(cr, "e")

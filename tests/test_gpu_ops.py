@@ -144,6 +144,120 @@ def test_tensor_core_gemm_matches_fp32_simt(ops):
     report("tcgen05 vs float64", outs["tcgen05"][0], want, 1e-5)
 
 
+# ---------------------------------------------------------------- fused gated MLP
+def _gated_weights(k, seed):
+    from types import SimpleNamespace
+    w1, b1 = rnd(256, k, seed=seed, scale=k ** -0.5), rnd(256, seed=seed + 1, scale=0.1)
+    w2, b2 = rnd(256, 128, seed=seed + 2, scale=128 ** -0.5), rnd(256, seed=seed + 3, scale=0.1)
+    nc, ng = 1 + 0.1 * rnd(128, seed=seed + 4), 1 + 0.1 * rnd(128, seed=seed + 5)
+    host = SimpleNamespace(w1=w1, b1=b1, w2=w2, b2=b2, nc=nc, ng=ng)
+    device = SimpleNamespace(**{k_: dev(v) for k_, v in vars(host).items()})
+    return host, device
+
+
+def _gated_ref(hp, x):
+    """GatedMLP.forward (matris/model/functions.py:300-311) in float64 on the concatenated input x."""
+    x = x.double()
+    z1 = F.linear(x, hp.w1.double(), hp.b1.double())
+    a = F.silu(z1)
+    z2 = torch.cat([F.linear(a[:, :128], hp.w2[:128].double(), hp.b2[:128].double()),
+                    F.linear(a[:, 128:], hp.w2[128:].double(), hp.b2[128:].double())], 1)
+    return z1, z2, _gate_ref(z2, hp.nc.double(), hp.ng.double())
+
+
+@pytest.mark.parametrize("n_rows", [1, 127, 128, 129, 1000, 148 * 128 + 77, 148 * 128 * 2 + 5])
+def test_gated_mlp_fwd_row_counts(ops, n_rows):
+    """One to many tiles per CTA, ragged last tiles, K = 384, all outputs requested, against float64."""
+    hp, dp = _gated_weights(384, seed=31)
+    x = rnd(n_rows, 384, seed=32)
+    res, rw = rnd(n_rows, 128, seed=33), rnd(128, seed=34)
+    dx = dev(x)
+    z1, z2, h, out2 = ops.gated_mlp_fwd(dp, n_rows, [ops.S(dx, None, 128 * s) for s in range(3)], res=dev(res),
+                                        res_w=dev(rw))
+    assert ops.gemm_status() == 0
+    r1, r2, rh = _gated_ref(hp, x)
+    report(f"gated_mlp_fwd z1 R={n_rows}", z1, r1, 1e-5)
+    report(f"gated_mlp_fwd z2 R={n_rows}", z2, r2, 1e-5)
+    report(f"gated_mlp_fwd h R={n_rows}", h, rh, 1e-5)
+    report(f"gated_mlp_fwd out2 R={n_rows}", out2, rh + rw.double() * res.double(), 1e-5)
+
+
+@pytest.mark.parametrize("k", [128, 256, 384, 512])
+def test_gated_mlp_fwd_gathered_sources_and_output_subsets(ops, k):
+    """Gathered and direct K segments (one of them through SiLU on load), and every combination of optional outputs:
+    without z1 / z2 (the no-save path), h only, out2 only."""
+    R, n1 = 3000 + 19, 211
+    hp, dp = _gated_weights(k, seed=41)
+    edge, node = rnd(R, 128, seed=42), rnd(n1, 128, seed=43)
+    g = torch.Generator().manual_seed(k)
+    idx = [torch.randint(0, n1, (R,), generator=g) for _ in range(3)]
+    de, dn = dev(edge), dev(node)
+    parts, srcs = [F.silu(edge)], [ops.S(de, None, 0, 1)]
+    for s in range(k // 128 - 1):
+        parts.append(node[idx[s]])
+        srcs.append(ops.S(dn, dev(idx[s], torch.int32)))
+    x = torch.cat(parts, 1)
+    res, rw = rnd(R, 128, seed=44), rnd(128, seed=45)
+    r1, r2, rh = _gated_ref(hp, x)
+    z1, z2, h, out2 = ops.gated_mlp_fwd(dp, R, srcs, save=False)
+    assert z1 is None and z2 is None and out2 is None
+    report(f"gated_mlp_fwd K={k} h (no save)", h, rh, 1e-5)
+    z1, z2, h, out2 = ops.gated_mlp_fwd(dp, R, srcs, want_h=False, res=dev(res), res_w=None, save=True)
+    assert h is None
+    report(f"gated_mlp_fwd K={k} out2 only (unit residual weight)", out2, rh + res.double(), 1e-5)
+    report(f"gated_mlp_fwd K={k} z1", z1, r1, 1e-5)
+    report(f"gated_mlp_fwd K={k} z2", z2, r2, 1e-5)
+    assert ops.gemm_status() == 0
+
+
+def test_gated_mlp_fwd_fused_equals_composed(ops):
+    """The fused kernel against the same result composed from the separate kernels on the exact-fp32 SIMT core."""
+    R, n1 = 9000 + 3, 500
+    hp, dp = _gated_weights(512, seed=51)
+    edge, node = rnd(R, 128, seed=52) * 2, rnd(n1, 128, seed=53) * 2
+    g = torch.Generator().manual_seed(9)
+    idx = [dev(torch.randint(0, n1, (R,), generator=g), torch.int32) for _ in range(3)]
+    de, dn = dev(edge), dev(node)
+    srcs = [ops.S(de)] + [ops.S(dn, i) for i in idx]
+    res, rw = dev(rnd(R, 128, seed=54)), dev(rnd(128, seed=55))
+    outs = {}
+    for mode in ("simt", "tcgen05_tile", "tcgen05"):
+        ops.set_gemm_mode(mode)
+        outs[mode] = [t.cpu() for t in ops.gated_mlp_fwd(dp, R, srcs, res=res, res_w=rw)]
+        assert ops.gemm_status() == 0
+    ops.set_gemm_mode("tcgen05")
+    for name, a, b, c in zip(("z1", "z2", "h", "out2"), outs["tcgen05"], outs["simt"], outs["tcgen05_tile"]):
+        report(f"gated_mlp_fwd fused vs simt-composed {name}", a, b, 1e-5)
+        report(f"gated_mlp_fwd fused vs tile-composed {name}", a, c, 1e-5)
+
+
+def test_bounded_wait_expiry_sets_status_and_clears(ops):
+    """The failure path of the tensor-core kernels: a wait that runs out raises the status word, nothing hangs, and
+    the next kernel runs normally.  The wait is made to run out by a self-test kernel that waits (a few polls) on a
+    barrier nothing arrives at."""
+    assert ops.gemm_status() == 0
+    ops.selftest_wait_expiry()
+    flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    ops.gemm_status_async(flag)
+    torch.cuda.synchronize()
+    assert int(flag[0]) == 1
+    ops.gemm_status_clear()
+    x, W = rnd(300, 128, seed=1), rnd(128, 128, seed=2)
+    y = ops.linear(dev(x), dev(W))
+    report("gemm after an expired wait", y, F.linear(x.double(), W.double()), 2e-5)
+    assert ops.gemm_status() == 0
+    ops.selftest_wait_expiry()
+    assert ops.gemm_status() == 1 and ops.gemm_status() == 0  # the synchronous read clears the word
+
+
+def test_timed_mma_rate_is_plausible(ops):
+    tf32, ms = ops.mma_rate("tf32", 4000)
+    bf16, _ = ops.mma_rate("bf16", 4000)
+    print(f"tcgen05.mma issue rate: tf32 {tf32:.0f} TFLOP/s, bf16 {bf16:.0f} TFLOP/s ({ms:.2f} ms)")
+    assert 300 < tf32 < 1400 and 1.7 < bf16 / tf32 < 2.3
+    assert ops.gemm_status() == 0
+
+
 # ---------------------------------------------------------------- row-wise
 def _gate_ref(z, wc, wg):
     c = F.rms_norm(z[:, :128], (128,), wc, torch.finfo(torch.float32).eps)
