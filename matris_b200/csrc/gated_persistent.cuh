@@ -37,21 +37,36 @@ constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): 
 static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word");
 
+#ifdef MB_GATED_TRACE
+__device__ volatile int* g_trace = nullptr;
+#define TR(slot, val) do { if (g_trace) { g_trace[1024 + threadIdx.x] = (val); if ((threadIdx.x & 31) == 0) g_trace[(threadIdx.x >> 5) * 32 + (slot)] = (val); __threadfence_system(); } } while (0)
+#else
+#define TR(slot, val)
+#endif
+
 __device__ __forceinline__ float sigmoid_fast_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 __global__ void __launch_bounds__(GP_THREADS, 1)
 k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant__ GatedMaps maps) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GP_BAR_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 128);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 192);
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
     return;
   }
   // barriers: ready[4] (4 storing warps + the TMA thread's expect_tx arrival) | chunk_done[4] | d1_full[2] |
-  //           d2_full[2] | d_free[2] (8 epilogue warps)
+  //           d2_full[2] | d_free[2] (8 epilogue warps) | l2_free[4]
+  // A parity wait can tell apart only the current and the preceding phase of a barrier, so every waiter must see
+  // every phase of the barriers it waits on.  chunk_done[b] completes once per chunk; the TMA warp waits on each of
+  // those.  The producers skip the layer-2 chunks and the epilogue warps skip the layer-1 chunks, so
+  //   * the epilogue warps wait for "A buffer b may take a layer-2 chunk" on l2_free[b], which completes exactly once
+  //     per unit (committed with the last four chunks of the phase that precedes the layer-2 phase);
+  //   * the producers wait for the previous layer-1 phase to be complete (d1_full) before the first chunk of a phase
+  //     that follows a layer-2 phase: chunk_done[b] is then at most one phase away from the one they wait for.
   const uint32_t ready = smem_u32(bars), chunk_done = smem_u32(bars + 4);
   const uint32_t d1_full = smem_u32(bars + 8), d2_full = smem_u32(bars + 10), d_free = smem_u32(bars + 12);
+  const uint32_t l2_free = smem_u32(bars + 14);
   const uint32_t ring = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const mb_gated_mlp& d = *reinterpret_cast<const mb_gated_mlp*>(smem + GP_DESC_OFF);
@@ -127,7 +142,9 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
 
   if (warp == PS_MMA_WARP) {
     if (lane == 0) {
-      for (int b = 0; b < 4; ++b) { mbar_init(ready + 8 * b, 5); mbar_init(chunk_done + 8 * b, 1); }
+      for (int b = 0; b < 4; ++b) {
+        mbar_init(ready + 8 * b, 5); mbar_init(chunk_done + 8 * b, 1); mbar_init(l2_free + 8 * b, 1);
+      }
       for (int b = 0; b < 2; ++b) {
         mbar_init(d1_full + 8 * b, 1); mbar_init(d2_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8);
       }
@@ -146,6 +163,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  TR(0, 1 + (int)tmem_base);
 
   if (warp == PS_MMA_WARP) {
     // ---------------------------------------------------------------- MMA warp (warp-uniform, one elected lane issues)
@@ -163,6 +181,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       const uint32_t d_tmem = tmem_u + 128u * acc;
       const int nch = is_l2 ? 4 : nch1;
       const uint32_t full_bar = (is_l2 ? d2_full : d1_full) + 8 * acc;
+      // the phase after this one is a layer-2 phase: its operand chunks go into the A buffers of the last four chunks
+      const bool frees_l2 = is_l2 ? (k == n_units - 2) : (k >= 1);
       for (int c = 0; c < nch; ++c, ++g) {
         const uint32_t ab = g & 3;
         if (c == 0 && is_l2) {
@@ -176,6 +196,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         // layer 1 of unit k overwrites the accumulator unit k - 2 left: its epilogue must have taken it
         if (c == 0 && !is_l2 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
         alive = __all_sync(0xffffffffu, alive);
+        TR(1, 1000 + (int)g + (alive ? 0 : 100000));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t wb = ring_u + ab * 2 * TC_TILE_BYTES;
         const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
@@ -190,11 +211,15 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           }
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                        :: "r"(chunk_done + 8 * ab) : "memory");
+          if (frees_l2 && c >= nch - 4)
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(l2_free + 8 * ab) : "memory");
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(full_bar) : "memory");
         }
         __syncwarp();
+        TR(2, 2000 + (int)g);
       }
     }
   } else if (warp == PS_TMA_WARP) {
@@ -225,6 +250,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, c * TC_BK, wrow);
         }
         __syncwarp();
+        TR(1, 1000 + (int)w_g);
       }
     }
     if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
@@ -254,6 +280,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       // ------------------------------------------------ mid(k): z1 -> SiLU -> hi / lo -> A operand of layer 2
       if (alive) alive = mbar_wait(d1_full + 8 * acc, upar);
       alive = __all_sync(0xffffffffu, alive);
+      TR(1, 100 + k + (alive ? 0 : 100000));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t gl2 = (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k);  // first chunk of L2(k)
 #pragma unroll 1
@@ -267,6 +294,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
         }
+        TR(2, 200 + 10 * k + cc);
         if (b1) {
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
@@ -286,6 +314,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
             st8(zp + 8 * jj, o);
           }
         }
+        __syncwarp();
+        TR(3, 300 + 10 * k + cc);
         const uint32_t gi = gl2 + (uint32_t)c, ab = gi & 3;
         const uint32_t ta = lane_q + 256 + 64 * ab;
 #pragma unroll
@@ -298,20 +328,25 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
             lo[i] = __float_as_uint(s - __uint_as_float(hi[i]));
           }
           if (hh == 0) {
-            if (alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);  // A buffer ab is free again
+            if (alive) alive = mbar_wait(l2_free + 8 * ab, (uint32_t)(k & 1));  // A buffer ab may take this chunk
+            __syncwarp();
+            TR(4, 400 + 10 * k + cc + (alive ? 0 : 100000));
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           }
           MB_TMEM_ST16(ta + 16 * hh, hi);
           MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        TR(5, 500 + 10 * k + cc);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(ready + 8 * ab);
+        TR(6, 600 + 10 * k + cc);
       }
       // ------------------------------------------------ epi(k): z2 -> RMSNorm -> activation -> h
       if (alive) alive = mbar_wait(d2_full + 8 * acc, upar);
       alive = __all_sync(0xffffffffu, alive);
+      TR(7, 700 + k + (alive ? 0 : 100000));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float y[64];
       {
@@ -325,6 +360,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the accumulator is in registers: the next unit may overwrite it
+      TR(8, 800 + k);
       float ss = 0.f;
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
@@ -348,8 +384,11 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         }
       }
       // the other half of the row's sum of squares comes from the partner warp (same quarter, other column half)
+      __syncwarp();
+      TR(9, 900 + k);
       xs[acc * 256 + hf * 128 + q * 32 + lane] = ss;
       asm volatile("bar.sync %0, 64;" :: "r"(1 + q) : "memory");
+      TR(10, 1000 + k);
       ss += xs[acc * 256 + (hf ^ 1) * 128 + q * 32 + lane];
       const float rinv = rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
       // the core unit parks c = SiLU(.) in the output row; the gate unit (same thread, next unit) reads it back
@@ -392,6 +431,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           }
         }
       }
+      __syncwarp();
+      TR(11, 1100 + k);
     }
   } else {
     // ---------------------------------------------------------------- producers (layer-1 chunks only)
@@ -410,11 +451,16 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         g += 4;
         continue;
       }
+      if (k >= 2) {  // this phase follows a layer-2 phase (see the note on the barriers)
+        if (alive) alive = mbar_wait(d1_full + 8 * ((k - 1) & 1), (uint32_t)(((k - 1) >> 1) & 1));
+        alive = __all_sync(0xffffffffu, alive);
+      }
       for (int c = par; c < nch1; c += 2, ++n) {
         const uint32_t gi = g + c, ab = gi & 3;
         gather_next();
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncwarp();
+        TR(1, 1000 + (int)gi);
         const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
         const bool act = (act_mask >> (c >> 2)) & 1;
         const uint32_t ta = lane_base + 256 + 64 * ab;
@@ -448,6 +494,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(ready + 8 * ab);
+        TR(2, 2000 + (int)gi);
       }
       g += (uint32_t)nch1;
     }
@@ -455,8 +502,10 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   }
 
   // ------------------------------------------------------------------ common exit: release tensor memory
+  TR(30, 8888);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  TR(31, 9999);
   if (warp == PS_MMA_WARP) {
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
