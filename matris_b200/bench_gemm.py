@@ -1,6 +1,11 @@
-"""Kernel micro-benchmark: one `mb_gemm` launch shape, timed with CUDA events.
+"""Kernel micro-benchmark: one `mb_gemm` or `mb_gated_mlp_fwd` launch shape, timed with CUDA events.
 
     python -m matris_b200.bench_gemm K N [act] [gate] [rows] [mode] [scatter]
+    python -m matris_b200.bench_gemm gated K [rows] [save] [res] [gather]
+
+gated: the fused gated-MLP forward (K -> 256 -> 2 x 128 -> 128); save: also write z1 / z2 (default 1); res: also
+write out2 = h + res_w * res (default 1); gather: 1 = K segments 1.. are gathered from a table of rows/6 rows through
+random indices (default 0: all segments read row r).
 
 K: reduction width (a multiple of 128: K/128 concatenated sources), N: output width (a multiple of 128: N/128 column
 blocks), act: SiLU on load, gate: SiLU' gate in the epilogue, rows: default 151,552 (8 tiles per SM on 148 SMs),
@@ -14,7 +19,52 @@ import torch
 from matris_b200 import ops
 
 
+def gated(argv):
+    from types import SimpleNamespace
+    K = int(argv[0])
+    rows = int(argv[1]) if len(argv) > 1 else 148 * 128 * 8
+    save = bool(int(argv[2])) if len(argv) > 2 else True
+    with_res = bool(int(argv[3])) if len(argv) > 3 else True
+    gather = bool(int(argv[4])) if len(argv) > 4 else False
+    torch.manual_seed(0)
+    dev = "cuda"
+    p = SimpleNamespace(w1=ops.SplitWeight(torch.randn(256, K, device=dev) * K ** -0.5), b1=torch.randn(256, device=dev) * 0.1,
+                        w2=ops.SplitWeight(torch.randn(256, 128, device=dev) * 128 ** -0.5),
+                        b2=torch.randn(256, device=dev) * 0.1, nc=torch.ones(128, device=dev), ng=torch.ones(128, device=dev))
+    x = torch.randn(rows, 128, device=dev)
+    srcs = [ops.S(x)]
+    if gather:
+        table = torch.randn(rows // 6 + 1, 128, device=dev)
+        for s_ in range(K // 128 - 1):
+            idx = torch.randint(0, table.shape[0], (rows,), device=dev, dtype=torch.int32)
+            srcs.append(ops.S(table, idx))
+    else:
+        more = torch.randn(rows, K - 128, device=dev) if K > 128 else None
+        srcs += [ops.S(more, None, 128 * s_) for s_ in range(K // 128 - 1)]
+    res = torch.randn(rows, 128, device=dev) if with_res else None
+    rw = torch.randn(128, device=dev) if with_res else None
+
+    def launch():
+        return ops.gated_mlp_fwd(p, rows, srcs, res=res, res_w=rw, save=save)
+
+    for _ in range(3):
+        launch()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    launch()
+    e1.record()
+    torch.cuda.synchronize()
+    assert ops.gemm_status() == 0
+    ms = e0.elapsed_time(e1)
+    flops = 2.0 * rows * 256 * (K + 128)
+    gbytes = 4.0 * rows * (K + 128 * (1 + 4 * save + 2 * with_res)) / 1e9
+    print(f"gated rows={rows} K={K} save={int(save)} res={int(with_res)} gather={int(gather)}: {ms:.3f} ms, "
+          f"{flops / ms / 1e9:.1f} TFLOP/s fp32-equivalent, {gbytes / ms * 1e3:.0f} GB/s of algorithmic traffic")
+
+
 def main(argv):
+    if argv[0] == "gated":
+        return gated(argv[1:])
     K, N = int(argv[0]), int(argv[1])
     act = int(argv[2]) if len(argv) > 2 else 0
     gate = int(argv[3]) if len(argv) > 3 else 0

@@ -23,26 +23,21 @@
 // A buffer g & 3 and W ring slot g & 3, exactly as in k_gemm_ps, and every phase has a multiple of four chunks.
 //
 // Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64 b (hi | lo).
-// Shared memory: W ring 4 x 32 KB | producer patches 64 KB | sums of squares 2 KB | barriers | descriptor copy.
+// Shared memory: W ring 4 x 32 KB | producer patches 64 KB | sums of squares 2 KB | per-channel constants 3.5 KB |
+// barriers | descriptor copy.
 // Every mbarrier wait is bounded; on expiry the status word is set, the role stops waiting and runs to the common exit.
 
 struct alignas(64) GatedMaps { CUtensorMap w1[2]; CUtensorMap w2[2]; };  // hi, lo of W1 [256, K] and W2 [256, 128]
 
 constexpr int GP_THREADS = PS_THREADS;
 constexpr int GP_XSUM_OFF = PS_RING_BYTES + PS_PATCH_BYTES;
-constexpr int GP_BAR_OFF = GP_XSUM_OFF + 2 * 2 * 128 * 4;
+constexpr int GP_CONST_OFF = GP_XSUM_OFF + 2 * 2 * 128 * 4;  // b1[256] b2[256] norm_core[128] norm_gate[128] res_w[128]
+constexpr int GP_BAR_OFF = GP_CONST_OFF + 896 * 4;
 constexpr int GP_DESC_OFF = GP_BAR_OFF + 256;
 constexpr int GP_SMEM_BYTES = GP_DESC_OFF + (int)((sizeof(mb_gated_mlp) + 15) / 16 * 16);
 constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): float32 machine epsilon
 static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word");
-
-#ifdef MB_GATED_TRACE
-__device__ volatile int* g_trace = nullptr;
-#define TR(slot, val) do { if (g_trace) { g_trace[1024 + threadIdx.x] = (val); if ((threadIdx.x & 31) == 0) g_trace[(threadIdx.x >> 5) * 32 + (slot)] = (val); __threadfence_system(); } } while (0)
-#else
-#define TR(slot, val)
-#endif
 
 __device__ __forceinline__ float sigmoid_fast_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
@@ -76,6 +71,18 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     for (int i = tid; i < (int)(sizeof(mb_gated_mlp) / 4); i += GP_THREADS) dst[i] = src[i];
   }
   __syncthreads();
+  // per-channel constants -> shared memory (missing biases read as 0, a missing residual weight as 1): the epilogue
+  // warps fetch them per column group, and from global memory each fetch would be a dependent round trip
+  float* const cst = reinterpret_cast<float*>(smem + GP_CONST_OFF);
+  for (int i = tid; i < 896; i += GP_THREADS) {
+    float v;
+    if (i < 256) v = d.b1 ? d.b1[i] : 0.f;
+    else if (i < 512) v = d.b2 ? d.b2[i - 256] : 0.f;
+    else if (i < 640) v = d.norm_core[i - 512];
+    else if (i < 768) v = d.norm_gate[i - 640];
+    else v = d.res_w ? d.res_w[i - 768] : 1.f;
+    cst[i] = v;
+  }
   const int64_t n_rows = d.n_rows;
   const int n_row_tiles = (int)((n_rows + 127) >> 7);
   const int n_src = d.n_src, nch1 = 4 * n_src;
@@ -163,7 +170,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  TR(0, 1 + (int)tmem_base);
 
   if (warp == PS_MMA_WARP) {
     // ---------------------------------------------------------------- MMA warp (warp-uniform, one elected lane issues)
@@ -196,7 +202,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         // layer 1 of unit k overwrites the accumulator unit k - 2 left: its epilogue must have taken it
         if (c == 0 && !is_l2 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
         alive = __all_sync(0xffffffffu, alive);
-        TR(1, 1000 + (int)g + (alive ? 0 : 100000));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t wb = ring_u + ab * 2 * TC_TILE_BYTES;
         const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
@@ -219,7 +224,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
                          :: "r"(full_bar) : "memory");
         }
         __syncwarp();
-        TR(2, 2000 + (int)g);
       }
     }
   } else if (warp == PS_TMA_WARP) {
@@ -250,7 +254,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, c * TC_BK, wrow);
         }
         __syncwarp();
-        TR(1, 1000 + (int)w_g);
       }
     }
     if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
@@ -262,14 +265,13 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     const int e = warp - PS_EPI_WARP0, q = warp & 3, hf = e >> 2;
     const uint32_t lane_q = tmem_base + ((uint32_t)(q * 32) << 16);
     float* const xs = reinterpret_cast<float*>(smem + GP_XSUM_OFF);
-    const float* const b1 = d.b1;
-    const float* const b2 = d.b2;
+    const float4* const b1s = reinterpret_cast<const float4*>(cst);
+    const float4* const b2s = reinterpret_cast<const float4*>(cst + 256);
     float* const z1 = d.z1;
     float* const z2 = d.z2;
     float* const hout = d.h;
     float* const out2 = d.out2;
     const float* const res = d.res;
-    const float* const res_w = d.res_w;
     bool alive = true;
     for (int k = 0; k < n_units; ++k) {
       const int acc = k & 1;  // = branch: 0 core, 1 gate
@@ -280,7 +282,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       // ------------------------------------------------ mid(k): z1 -> SiLU -> hi / lo -> A operand of layer 2
       if (alive) alive = mbar_wait(d1_full + 8 * acc, upar);
       alive = __all_sync(0xffffffffu, alive);
-      TR(1, 100 + k + (alive ? 0 : 100000));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t gl2 = (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k);  // first chunk of L2(k)
 #pragma unroll 1
@@ -294,15 +295,10 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
         }
-        TR(2, 200 + 10 * k + cc);
-        if (b1) {
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float bv[8];
-            ld8(b1 + 128 * acc + 32 * c + 8 * jj, bv);  // same address in every lane: a broadcast load
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[8 * jj + i] += bv[i];
-          }
+        for (int jj = 0; jj < 8; ++jj) {  // same address in every lane: a broadcast read
+          const float4 bv = b1s[32 * acc + 8 * c + jj];
+          x[4 * jj] += bv.x; x[4 * jj + 1] += bv.y; x[4 * jj + 2] += bv.z; x[4 * jj + 3] += bv.w;
         }
         if (z1 && valid) {
           float* zp = z1 + row * d.ld_z1 + 128 * acc + 32 * c;
@@ -315,7 +311,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           }
         }
         __syncwarp();
-        TR(3, 300 + 10 * k + cc);
         const uint32_t gi = gl2 + (uint32_t)c, ab = gi & 3;
         const uint32_t ta = lane_q + 256 + 64 * ab;
 #pragma unroll
@@ -330,23 +325,19 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           if (hh == 0) {
             if (alive) alive = mbar_wait(l2_free + 8 * ab, (uint32_t)(k & 1));  // A buffer ab may take this chunk
             __syncwarp();
-            TR(4, 400 + 10 * k + cc + (alive ? 0 : 100000));
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           }
           MB_TMEM_ST16(ta + 16 * hh, hi);
           MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        TR(5, 500 + 10 * k + cc);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(ready + 8 * ab);
-        TR(6, 600 + 10 * k + cc);
       }
       // ------------------------------------------------ epi(k): z2 -> RMSNorm -> activation -> h
       if (alive) alive = mbar_wait(d2_full + 8 * acc, upar);
       alive = __all_sync(0xffffffffu, alive);
-      TR(7, 700 + k + (alive ? 0 : 100000));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float y[64];
       {
@@ -360,18 +351,13 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the accumulator is in registers: the next unit may overwrite it
-      TR(8, 800 + k);
       float ss = 0.f;
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) {
-        if (b2) {
-          float bv[8];
-          ld8(b2 + 128 * acc + 64 * hf + 8 * jj, bv);
+      for (int jj = 0; jj < 16; ++jj) {
+        const float4 bv = b2s[32 * acc + 16 * hf + jj];
+        y[4 * jj] += bv.x; y[4 * jj + 1] += bv.y; y[4 * jj + 2] += bv.z; y[4 * jj + 3] += bv.w;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) y[8 * jj + i] += bv[i];
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(y[8 * jj + i], y[8 * jj + i], ss);
+        for (int i = 0; i < 4; ++i) ss = fmaf(y[4 * jj + i], y[4 * jj + i], ss);
       }
       if (z2 && valid) {
         float* zp = z2 + row * d.ld_z2 + 128 * acc + 64 * hf;
@@ -385,54 +371,60 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       }
       // the other half of the row's sum of squares comes from the partner warp (same quarter, other column half)
       __syncwarp();
-      TR(9, 900 + k);
       xs[acc * 256 + hf * 128 + q * 32 + lane] = ss;
       asm volatile("bar.sync %0, 64;" :: "r"(1 + q) : "memory");
-      TR(10, 1000 + k);
       ss += xs[acc * 256 + (hf ^ 1) * 128 + q * 32 + lane];
       const float rinv = rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
       // the core unit parks c = SiLU(.) in the output row; the gate unit (same thread, next unit) reads it back
       float* const park = (hout ? hout + row * d.ld_h : out2 + row * d.ld_out2) + 64 * hf;
+      const float4* const nws = reinterpret_cast<const float4*>(cst + 512 + 128 * acc + 64 * hf);
       if (!alive || !valid) {
         // nothing to write for rows past the end (or after an expired wait)
       } else if (acc == 0) {
-        const float* const nw = d.norm_core + 64 * hf;
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
-          float w[8], o[8];
-          ld8(nw + 8 * jj, w);
+          const float4 wa = nws[2 * jj], wb = nws[2 * jj + 1];
+          const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+          float o[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = silu_fast_f(y[8 * jj + i] * rinv * w[i]);
           st8(park + 8 * jj, o);
         }
       } else {
-        const float* const nw = d.norm_gate + 64 * hf;
+        // 16 columns per round: the parked values and the residual row are requested together, so a round costs one
+        // memory latency (both were touched by this SM a moment ago and sit in L2)
+        const float* const rrow = out2 ? res + row * d.ld_res + 64 * hf : nullptr;
+        float* const orow = out2 ? out2 + row * d.ld_out2 + 64 * hf : nullptr;
+        const float4* const rws = reinterpret_cast<const float4*>(cst + 768 + 64 * hf);
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          float w[8], cprev[8], o[8];
-          ld8(nw + 8 * jj, w);
-          ld8(park + 8 * jj, cprev);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = cprev[i] * sigmoid_fast_f(y[8 * jj + i] * rinv * w[i]);
-          if (hout) st8(park + 8 * jj, o);
+        for (int b = 0; b < 4; ++b) {
+          float cp[2][8], rr[2][8];
+          ld8(park + 16 * b, cp[0]);
+          ld8(park + 16 * b + 8, cp[1]);
           if (out2) {
-            float r8[8];
-            ld8(res + row * d.ld_res + 64 * hf + 8 * jj, r8);
-            if (res_w) {
-              float rw[8];
-              ld8(res_w + 64 * hf + 8 * jj, rw);
+            ld8(rrow + 16 * b, rr[0]);
+            ld8(rrow + 16 * b + 8, rr[1]);
+          }
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = fmaf(rw[i], r8[i], o[i]);
-            } else {
+          for (int t = 0; t < 2; ++t) {
+            const int jj = 2 * b + t;
+            const float4 wa = nws[2 * jj], wb = nws[2 * jj + 1];
+            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            float o[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] += r8[i];
+            for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fast_f(y[8 * jj + i] * rinv * w[i]);
+            if (hout) st8(park + 8 * jj, o);
+            if (out2) {
+              const float4 ra = rws[2 * jj], rb = rws[2 * jj + 1];
+              const float rw[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = fmaf(rw[i], rr[t][i], o[i]);
+              st8(orow + 8 * jj, o);
             }
-            st8(out2 + row * d.ld_out2 + 64 * hf + 8 * jj, o);
           }
         }
       }
       __syncwarp();
-      TR(11, 1100 + k);
     }
   } else {
     // ---------------------------------------------------------------- producers (layer-1 chunks only)
@@ -460,7 +452,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         gather_next();
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncwarp();
-        TR(1, 1000 + (int)gi);
         const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
         const bool act = (act_mask >> (c >> 2)) & 1;
         const uint32_t ta = lane_base + 256 + 64 * ab;
@@ -494,7 +485,6 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(ready + 8 * ab);
-        TR(2, 2000 + (int)gi);
       }
       g += (uint32_t)nch1;
     }
@@ -502,10 +492,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   }
 
   // ------------------------------------------------------------------ common exit: release tensor memory
-  TR(30, 8888);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  TR(31, 9999);
   if (warp == PS_MMA_WARP) {
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

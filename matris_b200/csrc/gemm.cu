@@ -714,14 +714,6 @@ __global__ void __launch_bounds__(128, 1) k_mma_rate(int iters) {
 
 }  // namespace mb
 
-#ifdef MB_GATED_TRACE
-extern "C" int mb_debug_set_trace(void* p) {
-  int* q = (int*)p;
-  MB_CUDA_CHECK(cudaMemcpyToSymbol(mb::g_trace, &q, sizeof(q)));
-  return MB_OK;
-}
-#endif
-
 extern "C" int mb_set_gemm_mode(int mode) {
   if (mode < 0 || mode > 2) return MB_ERR_INVALID;
   mb::g_gemm_mode = mode;
