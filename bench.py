@@ -1,18 +1,22 @@
 #!/usr/bin/env python
-"""Throughput of the E/F/S evaluation path: atoms*evals/s on a batch of random crystals.
+"""Throughput of the E/F/S/M evaluation path: atoms*evals/s.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload random256|perov512|cu32|fe16k|lipscl] [--md-steps N]
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+                    [--workload perov512|random256|random64|cu32|fe16k|lipscl] [--scaling weak|strong]
+                    [--md-steps N] [--no-cpu-baseline] [--keep auto|on|off]
 
-Workload (default): 256 random periodic crystals, 8-64 atoms each, seed 1 (+ rank), task
-"efs", MatRIS with 10 interaction blocks and seeded random-init weights.  One step =
-graph build + forward + backward for the whole batch.  N > 1: one process per GPU
-(torchrun), every rank evaluates its own batch (weak scaling, no data-path collective),
-energies are gathered to rank 0.
+Default workload: the high-throughput screen of random ABX3 perovskite cells (2x2x2 supercells, 40 atoms, seed 4),
+task "efsm", 512 cells per GPU, MatRIS with 10 interaction blocks and seeded random-init weights.  One step = graph
+build + forward + backward for the whole batch + the gather of energies, forces, stresses and magnetic moments.
+N > 1 (one process per GPU under torchrun): the list of 512 N cells is sharded over the ranks by predicted cost
+(matris_b200.parallel), every rank evaluates its share, and the results are gathered to rank 0 with one NCCL gather
+per step; no other collective is on the path.  `--scaling strong` keeps the total fixed (256 random crystals by
+default there) and splits it over the ranks instead.  Single large structures (cu32, fe16k, lipscl) run on one GPU.
 
-`value` is timed with inputs resident in HBM (positions, lattices); `e2e` goes through the
-public API (`MatRIS.predict` on host structures) with the host->device copies and the
-device->host read of E/F/S inside the timed region.  `--impl reference` times the CPU
-oracle (the restatement of the reference's PyTorch path) on a bounded sample instead.
+`value` is timed with the inputs resident in HBM (positions, lattices); `e2e` goes through the public API
+(`MatRIS.predict_sharded` on host structures) with the host->device copies of the inputs and the device->host read
+of E / F / S / M inside the timed region.  `--impl reference` times the CPU oracle (the restatement of the
+reference's PyTorch path, pinned to it by golden vectors) on a bounded sample of the same workload instead.
 """
 from __future__ import annotations
 
@@ -32,17 +36,22 @@ if ROOT not in sys.path:
 
 NUM_LAYERS = 10
 GEMM_CALLS = ("mb_gemm", "mb_gated_mlp_fwd")  # the tensor-core entry points
-METRIC = "atoms*evals/s (efs, fp32-tol)"
+PER_GPU = {"perov512": 512, "random256": 256, "random64": 64}
 
 
-def make_workload(name: str, rank: int):
+def metric_name(task: str) -> str:
+    return f"atoms*evals/s ({task}, fp32-tol)"
+
+
+def make_workload(name: str, world: int, scaling: str):
+    """(structures of the whole job, task, description).  Batched workloads grow with the number of ranks under weak
+    scaling (the generators are sequential in their seed, so N ranks evaluate the first N x per-GPU structures)."""
     from matris_b200 import workloads as w
-    if name == "random256":
-        return w.random_crystals(256, seed=1 + rank), "efs", "256 random crystals (8-64 atoms), seed 1+rank"
-    if name == "random64":  # small case for profiler captures (activations still exceed the L2)
-        return w.random_crystals(64, seed=1 + rank), "efs", "64 random crystals (8-64 atoms), seed 1+rank"
+    n = PER_GPU.get(name, 1) * (world if scaling == "weak" else 1)
     if name == "perov512":
-        return w.perovskites(512, seed=4 + rank), "efsm", "512 ABX3 2x2x2 perovskite cells (40 atoms)"
+        return w.perovskites(n, seed=4), "efsm", f"{n} ABX3 2x2x2 perovskite cells (40 atoms), seed 4"
+    if name in ("random256", "random64"):
+        return w.random_crystals(n, seed=1), "efs", f"{n} random crystals (8-64 atoms), seed 1"
     if name == "cu32":
         return [w.cu_fcc()], "efsm", "Cu FCC 2x2x2, 32 atoms"
     if name == "fe16k":
@@ -52,10 +61,22 @@ def make_workload(name: str, rank: int):
     raise SystemExit(f"unknown workload {name}")
 
 
-def flops_per_eval(g, layers):
+def cpu_workload(name: str, crystals):
+    """What the CPU arm evaluates.  The two single large structures would cost the host cores tens of minutes per
+    evaluation, so a down-sized replica from the same generator stands in for them (the rate is per atom, and the
+    cost per atom is set by the local density, which the replica keeps)."""
+    from matris_b200 import workloads as w
+    if name == "lipscl":
+        return [w.lipscl(n_atoms=256)], "256-atom replica of the Li6PS5Cl cell (same density and generator)"
+    if name == "fe16k":
+        return [w.fe_bcc(reps=(4, 4, 4))], "4x4x4 (128-atom) replica of the BCC Fe supercell"
+    return crystals, None
+
+
+def flops_per_eval(atoms, edges, triplets, layers):
     """Algorithmic GEMM FLOPs of one forward + backward evaluation (no recompute counted):
-    2 (fwd+bwd) * 2 (MAC) * L * (360448 T + 327680 Ed + 163840 Eu + 163840 N)."""
-    return 4.0 * layers * (360448.0 * g.n_triplets + 327680.0 * g.n_edges + 163840.0 * g.n_bonds + 163840.0 * g.n_atoms)
+    2 (fwd+bwd) * 2 (MAC) * L * (360448 T + 327680 Ed + 163840 Eu + 163840 N), Eu = Ed / 2."""
+    return 4.0 * layers * (360448.0 * triplets + 327680.0 * edges + 163840.0 * edges / 2 + 163840.0 * atoms)
 
 
 class ClockSampler:
@@ -149,9 +170,37 @@ class ClockSampler:
                 "samples": len(self.sm), "source": self.source}
 
 
-def cpu_oracle_rate(crystals, task, budget_s=20.0, max_structs=16, threads=None):
-    """atoms*evals/s of the CPU oracle on the first structures of the workload, evaluated as one batch
-    (graph construction included); repeated until about ``budget_s`` seconds of CPU work are spent."""
+def cpu_oracle_eval(ck, sample, task):
+    """One evaluation of the CPU oracle on ``sample`` as one batch, graph construction included: (seconds, graph s)."""
+    from oracle import pipeline
+    cfg = ck["config"]
+    t0 = time.perf_counter()
+    graphs = [pipeline.graph_from_arrays(c.numbers, c.cart, c.lattice, float(cfg["pairwise_cutoff"]),
+                                         float(cfg["three_body_cutoff"])) for c in sample]
+    t1 = time.perf_counter()
+    pipeline.evaluate(ck, sample, task, graphs=graphs)
+    return time.perf_counter() - t0, t1 - t0
+
+
+def cpu_sample(crystals, max_structs=32, max_cost=1.8e5):
+    """The bounded sample the CPU arm evaluates: the first structures of the workload, up to ``max_structs`` of them
+    and up to ``max_cost`` of predicted work (about the number of triplet plus edge rows: 32 random crystals, 8 of
+    the much denser perovskite cells), so that one evaluation takes the host cores some ten seconds.  The rate is
+    per atom, and the cost per atom of a structure does not depend on the size of the batch it is evaluated in."""
+    from matris_b200.parallel import predicted_cost
+    sample, atoms, cost = [], 0, 0.0
+    for c in crystals[:max_structs]:
+        w = predicted_cost(c.numbers, c.lattice)
+        if sample and cost + w > max_cost:
+            break
+        sample.append(c)
+        atoms += len(c.numbers)
+        cost += w
+    return sample, atoms
+
+
+def cpu_oracle_rate(crystals, task, budget_s=20.0, threads=None, max_structs=32, max_cost=1.8e5, max_reps=8):
+    """atoms*evals/s of the CPU oracle on a bounded sample; repeated until about ``budget_s`` seconds are spent."""
     import torch
 
     from matris_b200.weights import random_checkpoint
@@ -159,44 +208,54 @@ def cpu_oracle_rate(crystals, task, budget_s=20.0, max_structs=16, threads=None)
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
     ck = random_checkpoint(dict(num_layers=NUM_LAYERS, reference_energy="mpa"), seed=0)
-    cfg = ck["config"]
-    sample = crystals[:max_structs]
-    atoms = sum(len(c.numbers) for c in sample)
+    sample, atoms = cpu_sample(crystals, max_structs, max_cost)
     pipeline.evaluate(ck, sample[:1], task)  # warm-up
-    t_total = t_graph = 0.0
-    reps = 0
-    while t_total < budget_s and reps < 8:
-        t0 = time.perf_counter()
-        graphs = [pipeline.graph_from_arrays(c.numbers, c.cart, c.lattice, float(cfg["pairwise_cutoff"]),
-                                             float(cfg["three_body_cutoff"])) for c in sample]
-        t1 = time.perf_counter()
-        pipeline.evaluate(ck, sample, task, graphs=graphs)
-        t2 = time.perf_counter()
-        t_graph += t1 - t0
-        t_total += t2 - t0
-        reps += 1
-    return atoms * reps / t_total, dict(structures=len(sample), atoms=atoms, reps=reps, seconds=t_total,
-                                        graph_seconds=t_graph, threads=threads)
+    times, t_graph = [], 0.0
+    while sum(times) < budget_s and len(times) < max_reps:
+        t, tg = cpu_oracle_eval(ck, sample, task)
+        times.append(t)
+        t_graph += tg
+    return atoms * len(times) / sum(times), dict(structures=len(sample), atoms=atoms, reps=len(times),
+                                                 seconds=sum(times), graph_seconds=t_graph, threads=threads,
+                                                 rate_min=atoms / max(times), rate_median=atoms / float(np.median(times)),
+                                                 rate_max=atoms / min(times))
 
 
 def run_reference(args, rank, world):
-    """The reference arm: the CPU restatement of the reference's PyTorch path on the host cores."""
+    """The reference arm: the CPU restatement of the reference's PyTorch path on all host cores; every step
+    evaluates the same bounded sample of the workload (one batch, graph construction included)."""
     if rank != 0:
         return
-    crystals, task, desc = make_workload(args.workload, 0)
-    rates, info = [], None
+    import torch
+
+    from matris_b200.weights import random_checkpoint
+    from oracle import pipeline
+    crystals, task, desc = make_workload(args.workload, world, args.scaling)
+    crystals, replica = cpu_workload(args.workload, crystals)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    ck = random_checkpoint(dict(num_layers=NUM_LAYERS, reference_energy="mpa"), seed=0)
+    sample, atoms = cpu_sample(crystals)
+    pipeline.evaluate(ck, sample[:1], task)
+    times, t_graph = [], 0.0
     for _ in range(args.warmup + args.steps):
-        r, info = cpu_oracle_rate(crystals, task, budget_s=1.0, max_structs=16)  # one batch evaluation per step
-        rates.append(r)
-    rate = float(np.mean(rates[args.warmup:]))
-    sample = (f"first {info['structures']} structures ({info['atoms']} atoms) of the workload per step as one "
-              f"batch, graph construction included ({info['graph_seconds']:.2f}s of {info['seconds']:.2f}s)")
-    line = {"impl": "reference", "metric": METRIC, "value": rate, "unit": "atoms*evals/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * info["seconds"] / info["reps"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "task": task, "num_layers": NUM_LAYERS, "weights": "random-init seed 0"},
-            "cpu_baseline": {"value": rate, "unit": "atoms*evals/s", "cores": info["threads"], "kind": "port",
-                             "sample": sample},
+        t, tg = cpu_oracle_eval(ck, sample, task)
+        times.append(t)
+        t_graph += tg
+    timed = times[args.warmup:]
+    rate = atoms * len(timed) / sum(timed)
+    what = (f"first {len(sample)} structures ({atoms} atoms) of the workload per step as one batch, graph "
+            f"construction included ({t_graph:.2f}s of {sum(times):.2f}s)")
+    if replica:
+        what = f"{replica}, one evaluation per step, graph construction included"
+    line = {"impl": "reference", "metric": metric_name(task), "value": rate, "unit": "atoms*evals/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(timed) / len(timed),
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": desc, "task": task, "num_layers": NUM_LAYERS, "weights": "random-init seed 0",
+                       "sample": what},
+            "per_step_rate": {"min": atoms / max(timed), "median": atoms / float(np.median(timed)),
+                              "max": atoms / min(timed)},
+            "cpu_baseline": {"value": rate, "unit": "atoms*evals/s", "cores": threads, "kind": "port", "sample": what},
             "e2e": {"value": rate, "unit": "atoms*evals/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -207,13 +266,16 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="random256")
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--md-steps", type=int, default=None,
                     help="with --workload lipscl: Langevin MD steps to time (default 200; 0 skips the MD leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--keep", default="auto", choices=["auto", "on", "off"],
                     help="keep sub-block internals for the backward pass (auto: when they fit in memory)")
     args = ap.parse_args()
+    if args.workload is None:
+        args.workload = "perov512" if args.scaling == "weak" else "random256"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -224,7 +286,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from matris_b200 import MatRIS, _lib
+    from matris_b200 import MatRIS, _lib, ops, parallel
     from matris_b200.graph import HostBatch, build_on_device, upload
     from matris_b200.weights import random_checkpoint
 
@@ -233,62 +295,89 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-    crystals, task, desc = make_workload(args.workload, rank)
+    crystals, task, desc = make_workload(args.workload, world, args.scaling)
     ck = random_checkpoint(dict(num_layers=NUM_LAYERS, reference_energy="mpa"), seed=0)
     model = MatRIS.from_dict(ck).to(device)
     model.keep_activations = {"auto": None, "on": True, "off": False}[args.keep]
     cut, lcut = model.config["pairwise_cutoff"], model.config["three_body_cutoff"]
-    n_atoms = sum(len(c.numbers) for c in crystals)
+    # the same assignment predict_sharded makes: every rank computes it from the whole list
+    costs = [parallel.predicted_cost(c.numbers, c.lattice, cut, lcut) for c in crystals]
+    shards = parallel.shard_by_cost(costs, world)
+    mine = [crystals[i] for i in shards[rank]]
+    n_atoms = sum(len(c.numbers) for c in mine)
+    atoms_job = sum(len(c.numbers) for c in crystals)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def gather_energy(e):
-        if world > 1:
-            parts = [torch.empty_like(e) for _ in range(world)] if rank == 0 else None
-            dist.gather(e, parts, dst=0)
+    widths = []
+    for sh in shards:
+        b, n = len(sh), sum(len(crystals[i].numbers) for i in sh)
+        widths.append(2 * b + (9 * b if "s" in task else 0) + (3 * n if "f" in task else 0) + (n if "m" in task else 0))
+    width = max(widths)
 
-    # ---- device-resident arm: positions/lattices already in HBM; a step = graph build + forward + backward
-    hb = HostBatch([c.numbers for c in crystals], [c.cart for c in crystals], [c.lattice for c in crystals], cut)
+    def gather_results(out):
+        """The result gather of the sharded path: one flat float32 buffer per rank, one NCCL gather."""
+        parts = [out["e"], out["ref_energy"]]
+        if "s" in task:
+            parts.append(torch.stack(list(out["s"])).reshape(-1))
+        if "f" in task:
+            parts.append(torch.cat(list(out["f"])).reshape(-1))
+        if "m" in task:
+            parts.append(torch.cat(list(out["m"])).reshape(-1))
+        flat = torch.cat([p.reshape(-1).float() for p in parts])
+        if world > 1:
+            buf = torch.zeros(width, dtype=torch.float32, device=device)
+            buf[:flat.numel()] = flat
+            dest = [torch.empty_like(buf) for _ in range(world)] if rank == 0 else None
+            dist.gather(buf, dest, dst=0)
+        return flat
+
+    # ---- device-resident arm: positions/lattices already in HBM; a step = graph build + forward + backward + gather
+    hb = HostBatch([c.numbers for c in mine], [c.cart for c in mine], [c.lattice for c in mine], cut)
     g = upload(hb, cut, lcut, device)
 
     def step_resident(gather=True):
         build_on_device(g)
         out = model(g, task=task)
         if gather:
-            gather_energy(out["e"])
+            gather_results(out)
         return out
 
     for _ in range(args.warmup):
         step_resident()
     barrier()
     launches0 = _lib.launch_count
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0, ev1, evg = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     with ClockSampler(local_rank) as clocks:
         ev0.record()
         for _ in range(args.steps):
-            out = step_resident()
+            out = step_resident(gather=False)
+            evg.record()
+            gather_results(out)
         ev1.record()
         barrier()
+    t_gather = evg.elapsed_time(ev1)  # the last step's gather (includes waiting for the slowest rank)
     launches = _lib.launch_count - launches0
-    t_res = torch.tensor([ev0.elapsed_time(ev1) * 1e-3], device=device)
-    atoms_total = torch.tensor([float(n_atoms)], device=device)
+    my_ms = ev0.elapsed_time(ev1) / args.steps
+    t_res = torch.tensor([my_ms * args.steps * 1e-3], device=device)
     if world > 1:
         dist.all_reduce(t_res, op=dist.ReduceOp.MAX)
-        dist.all_reduce(atoms_total, op=dist.ReduceOp.SUM)
-    t_res, atoms_total = float(t_res), float(atoms_total)
+    t_res = float(t_res)
+    model.check_status()
 
     # ---- end-to-end arm: the public API on host structures, H2D of inputs and D2H of results inside the timing
     def step_e2e():
-        o = model.predict(crystals, task)
-        res = [o["e"].cpu(), torch.cat(list(o["f"])).cpu()]
+        o = model.predict_sharded(crystals, task)
+        if o is None:
+            return None
+        res = [o["e"].cpu(), o["ref_energy"].cpu(), torch.cat(list(o["f"])).cpu()]
         if "s" in o:
-            res.append(torch.stack(o["s"]).cpu())
+            res.append(torch.stack(list(o["s"])).cpu())
         if "m" in o:
-            res.append(torch.cat(o["m"]).cpu())
-        gather_energy(o["e"])
+            res.append(torch.cat(list(o["m"])).cpu())
         return res
 
     step_e2e()
@@ -300,15 +389,34 @@ def main():
         ev1.record()
         barrier()
     t_e2e = torch.tensor([ev0.elapsed_time(ev1) * 1e-3], device=device)
+    h2d = torch.tensor([float(hb.h2d_bytes)], device=device)
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
-    t_e2e = float(t_e2e)
-    d2h = sum(r.numel() * r.element_size() for r in res)
+        dist.all_reduce(h2d, op=dist.ReduceOp.SUM)
+    t_e2e, h2d = float(t_e2e), int(h2d)
+    d2h = sum(r.numel() * r.element_size() for r in res) if res is not None else 0
+    model.check_status()
+
+    # ---- per-rank table (what limits the scaling can be read from it)
+    mine_row = torch.tensor([my_ms, float(n_atoms), float(g.n_edges), float(g.n_triplets), t_gather, float(len(mine))],
+                            device=device)
+    rows = [torch.empty_like(mine_row) for _ in range(world)] if (world > 1 and rank == 0) else None
+    if world > 1:
+        dist.gather(mine_row, rows, dst=0)
+    else:
+        rows = [mine_row]
+    rank_table = None
+    if rank == 0:
+        rank_table = [{"rank": r, "ms_per_step": round(float(x[0]), 3), "atoms": int(x[1]), "directed_edges": int(x[2]),
+                       "triplets": int(x[3]), "last_gather_ms": round(float(x[4]), 3), "structures": int(x[5])}
+                      for r, x in enumerate(rows)]
 
     # ---- one instrumented step: per-kernel device time (CUDA events on the launching stream)
     roofline, roofline_graph, kernel_table, gemm_shapes = None, None, None, None
     if rank == 0:
         torch.cuda.synchronize()
+        with ClockSampler(local_rank) as clocks_peak:
+            tf32_peak, peak_ms = ops.mma_rate("tf32", 400000)  # >= 50 ms of resident-operand tcgen05.mma issue
         _lib.profile = []
         step_resident(gather=False)  # rank 0 only: no collective in here
         torch.cuda.synchronize()
@@ -344,31 +452,38 @@ def main():
         src = "measured" if peaks else "fallback"
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
         n_gemm = sum(per[k][0] for k in GEMM_CALLS if k in per)
-        # DRAM traffic per launch: ncu measured 0.906 x (A read + output write) on a captured K=384 N=256 launch of
-        # 151,552 rows (profiles/k_gemm_ps.md); scaled here to the average launch of the step by its rows x (K + N).
-        roofline = {"kernel": "k_gemm_ps + k_gated_fwd (mb_gemm, mb_gated_mlp_fwd)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.906 * gemm_bytes / n_gemm,
-                    "traffic_note": "bytes per average launch, scaled from one ncu capture by rows x (K + N)",
+        # DRAM traffic per launch: an ncu capture of a 151,552-row K=384 N=256 launch measured 0.906 x (A rows read +
+        # output rows written); scaled here to the average launch of the step by its algorithmic bytes.
+        pk = clocks_peak.summary()
+        roofline = {"kernel": "k_gemm_ps + k_gated_fwd (mb_gemm, mb_gated_mlp_fwd)", "bound": "tensor", "achieved": ach,
+                    "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.906 * gemm_bytes / n_gemm,
+                    "traffic_note": "bytes per average launch, scaled from one ncu capture by the algorithmic bytes",
                     "peak_source": src + " bf16 sustained",
                     "launches": n_gemm, "avg_launch_ms": gemm_ms / n_gemm,
-                    "flops_per_step": gemm_flops, "tf32_issued_tflops": 3.0 * ach, "tf32_peak_measured_tflops": 1151.0,
-                    "frac_of_tf32_peak": 3.0 * ach / 1151.0,
-                    "note": "tcgen05 kind::tf32 with a 3-term operand split: 3 tensor FLOPs are issued per "
-                            "algorithmic FLOP; 1151 TFLOP/s = measured raw tcgen05.mma tf32 rate (64 cycles per "
-                            "M128 N128 K8 MMA x 148 SMs x 1.9 GHz)"}
+                    "flops_per_step": gemm_flops, "tf32_issued_tflops": 3.0 * ach,
+                    "tf32_peak_timed_tflops": tf32_peak, "tf32_peak_timed_ms": peak_ms,
+                    "tf32_peak_timed_sm_mhz": pk["sm_mhz"], "frac_of_tf32_peak": 3.0 * ach / tf32_peak,
+                    "note": "tcgen05 kind::tf32 with a 3-term operand split: 3 tensor FLOPs are issued per algorithmic "
+                            "FLOP; tf32_peak_timed = CUDA-event-timed tcgen05.mma issue loop on resident operands in "
+                            "this run (mb_bench_mma_rate), with the SM clock sampled during it"}
         gms = sum(per[k][1] for k in per if k.startswith("mb_graph"))
         gbytes = 26.0 * g.n_edges + 20.0 * g.n_triplets + 16.0 * g.n_atoms
-        roofline_graph = {"kernels": "mb_graph_* (3 phases)", "bound": "hbm", "achieved": gbytes / (gms * 1e-3) / 1e9,
+        roofline_graph = {"kernels": "mb_graph_*", "bound": "hbm", "achieved": gbytes / (gms * 1e-3) / 1e9,
                           "peak": peak_gb, "unit": "GB/s", "frac": gbytes / (gms * 1e-3) / 1e9 / peak_gb,
                           "traffic": None, "algorithmic_bytes": gbytes, "ms": gms, "peak_source": src}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        rate, info = cpu_oracle_rate(crystals, task, budget_s=20.0, max_structs=16)
+        cpu_crystals, replica = cpu_workload(args.workload, crystals)
+        rate, info = cpu_oracle_rate(cpu_crystals, task, budget_s=20.0)
         cpu_baseline = {"value": rate, "unit": "atoms*evals/s", "cores": info["threads"], "kind": "port",
-                        "sample": f"first {info['structures']} structures ({info['atoms']} atoms) of the workload as "
-                                  f"one batch, {info['reps']} repetitions, {info['seconds']:.1f}s of CPU work"}
-        rate1, info1 = cpu_oracle_rate(crystals, task, budget_s=8.0, max_structs=4, threads=1)
+                        "sample": (replica + ", " if replica else "") +
+                                  f"first {info['structures']} structures ({info['atoms']} atoms) of the workload as "
+                                  f"one batch, {info['reps']} repetitions, {info['seconds']:.1f}s of CPU work",
+                        "per_repetition": {"min": info["rate_min"], "median": info["rate_median"],
+                                           "max": info["rate_max"]}}
+        rate1, info1 = cpu_oracle_rate(cpu_crystals, task, budget_s=8.0, threads=1, max_structs=4, max_cost=2.5e4,
+                                       max_reps=3)
         cpu_baseline["one_thread"] = {"value": rate1, "cores": 1,
                                       "sample": f"first {info1['structures']} structures ({info1['atoms']} atoms), "
                                                 f"{info1['reps']} repetitions, {info1['seconds']:.1f}s of CPU work"}
@@ -381,38 +496,43 @@ def main():
         from matris_b200.applications import MolecularDynamics
 
         dyn = MolecularDynamics(crystals[0], model=model, ensemble="nvt", thermostat="langevin", temperature=600,
-                                starting_temperature=600, timestep=1.0, friction=0.01, task="efsm", device="cuda",
+                                starting_temperature=600, timestep=1.0, friction=0.01, task="efsm", device=device,
                                 seed=2)
         dyn.run(3)
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        dyn.run(md_steps)
-        torch.cuda.synchronize()
-        t_md = time.perf_counter() - t0
+        with ClockSampler(local_rank) as clocks_md:
+            t0 = time.perf_counter()
+            dyn.run(md_steps)
+            torch.cuda.synchronize()
+            t_md = time.perf_counter() - t0
         md = {"metric": "md_steps_per_s", "value": md_steps / t_md, "steps": md_steps, "ms_per_step": 1e3 * t_md / md_steps,
               "atoms": n_atoms, "setup": "Langevin (BAOAB) NVT 600 K, dt 1 fs, friction 0.01/fs, efsm every step, "
                                          "integrator state and graph rebuild on the device (MolecularDynamics device_resident=True)",
-              "temperature_K_end": float(dyn.atoms.get_temperature())}
+              "temperature_K_end": float(dyn.atoms.get_temperature()), "clocks": clocks_md.summary()}
 
     if rank == 0:
-        value = atoms_total * args.steps / t_res
-        line = {"metric": METRIC, "value": value, "unit": "atoms*evals/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        value = atoms_job * args.steps / t_res
+        job_flops = sum(flops_per_eval(r["atoms"], r["directed_edges"], r["triplets"], NUM_LAYERS) for r in rank_table)
+        line = {"metric": metric_name(task), "value": value, "unit": "atoms*evals/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps,
+                "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
                 "config": {"workload": desc, "task": task, "num_layers": NUM_LAYERS, "weights": "random-init seed 0",
-                           "atoms_per_rank": n_atoms, "directed_edges": g.n_edges, "triplets": g.n_triplets,
+                           "atoms": atoms_job, "structures": len(crystals),
                            "l2": "per-step working set (>1 GB of activations) exceeds the 126 MB L2",
-                           "parallelism": f"structures sharded, {world} rank(s), result gather only"},
+                           "parallelism": f"structures sharded by predicted cost over {world} rank(s); one gather of "
+                                          "E, F, S, M per step, no other collective"},
+                "ranks": rank_table,
                 "clocks": clocks.summary(), "clocks_e2e": clocks_e2e.summary(),
-                "e2e": {"value": atoms_total * args.steps / t_e2e, "unit": "atoms*evals/s",
-                        "h2d_bytes_per_step": hb.h2d_bytes, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": 1e3 * t_e2e / args.steps},
-                "gpu_launches": launches, "gpu_launches_note": "C-ABI kernel-launching calls in the timed region "
-                                                               "(each issues one or more kernels)",
-                "achieved_tflops_algorithmic": flops_per_eval(g, NUM_LAYERS) * world * args.steps / t_res / 1e12,
+                "e2e": {"value": atoms_job * args.steps / t_e2e, "unit": "atoms*evals/s",
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": 1e3 * t_e2e / args.steps,
+                        "api": "MatRIS.predict_sharded(structures, task) + .cpu() of E, F, S, M on rank 0"},
+                "gpu_launches": launches, "gpu_launches_note": "C-ABI kernel-launching calls of rank 0 in the timed "
+                                                               "region (each issues one or more kernels)",
+                "achieved_tflops_algorithmic": job_flops * args.steps / t_res / 1e12,
                 "roofline": roofline, "roofline_graph_build": roofline_graph, "kernels": kernel_table,
-                "gemm_shapes": gemm_shapes if rank == 0 else None,
-                "cpu_baseline": cpu_baseline}
+                "gemm_shapes": gemm_shapes, "cpu_baseline": cpu_baseline}
         if md is not None:
             line["md"] = md
         print(json.dumps(line), flush=True)

@@ -686,3 +686,10 @@ class MatRIS(nn.Module):
     def predict(self, structures, task: str = "efsm"):
         """Evaluate a list of structures (any accepted structure type) as one batch."""
         return self.forward(self.graph_converter.batch(structures), task=task)
+
+    def predict_sharded(self, structures, task: str = "efsm", group=None, dst: int = 0):
+        """``predict`` over all ranks of a ``torch.distributed`` group (one process per GPU, every rank passes the
+        same list): structures are assigned to ranks by predicted cost, evaluated locally, and E / F / S / M are
+        gathered to rank ``dst`` (see matris_b200.parallel.evaluate).  Returns the full result there, None elsewhere."""
+        from .parallel import evaluate
+        return evaluate(self, structures, task, group=group, dst=dst)
