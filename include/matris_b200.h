@@ -265,12 +265,17 @@ int mb_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* tgt, const int32_t
                                const int32_t* emap, const float* env, const float* dagg, float* dh,
                                int32_t accumulate, void* stream);
 /* gradient w.r.t. env.  Atom graph (src_ptr == NULL): denv[u] = sum over the two directed rows e of
- * bond u of dagg[tgt[e]]*h[e]  (u2d / rev give the rows).  Line graph: denv[n] = sum_{r in tgt segment n}
- * dagg[n]*h[r]*env[src[r]] + sum_{r in src segment n} dagg[tgt[r]]*h[r]*env[tgt[r]]. */
+ * bond u of (dagg[tgt[e]] + drow[e])*h[e]  (u2d / rev give the rows; drow, optional, is a gradient that reached
+ * the smoothed rows h*s directly: use_smoothed_for_delta_edge, matris/model/interaction_block.py:262-266).
+ * Line graph (drow must be NULL): denv[n] = sum_{r in tgt segment n} dagg[n]*h[r]*env[src[r]]
+ * + sum_{r in src segment n} dagg[tgt[r]]*h[r]*env[tgt[r]]. */
 int mb_seg_smooth_sum_bwd_env(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* src_ptr,
                               const int32_t* src_perm, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
                               const int32_t* u2d, const int32_t* rev, const float* env, const float* h,
-                              const float* dagg, float* denv, void* stream);
+                              const float* dagg, const float* drow, float* denv, void* stream);
+/* y[r] = x[r] * s[idx ? idx[r] : r] channel-wise: the smoothed rows h * envelope of the refinement layer
+ * (matris/model/interaction_block.py:253) where they are needed as a tensor, and their adjoint w.r.t. x. */
+int mb_mul_rows_gather(int64_t n_rows, const float* x, const float* s, const int32_t* idx, float* y, void* stream);
 
 /* directed -> bond mean with residual (aggregate(..., average=True) over directed2undirected,
  * matris/model/interaction_block.py:123, 270-273): out[u] = 0.5*(y[u2d[u]] + y[rev[u2d[u]]]) + res_w*res[u] */

@@ -89,7 +89,8 @@ _SIGNATURES = {
     "mb_seg_attn_bwd": [_i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp],
     "mb_seg_smooth_sum_fwd": [_i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp],
     "mb_seg_smooth_sum_bwd_rows": [_i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp],
-    "mb_seg_smooth_sum_bwd_env": [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "mb_seg_smooth_sum_bwd_env": [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "mb_mul_rows_gather": [_i64, _vp, _vp, _vp, _vp, _vp],
     "mb_pair_mean_res": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_scale_rows": [_i64, _vp, _vp, _vp, _i32, _vp],
     "mb_small_linear_fwd": [_i64, _i32, _vp, _vp, _vp, _vp],

@@ -223,12 +223,24 @@ __global__ void k_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* __restr
 
 __global__ void k_smooth_env_bwd_atom(int n_bonds, const int32_t* __restrict__ u2d, const int32_t* __restrict__ rev,
                                       const int32_t* __restrict__ tgt, const float* __restrict__ h,
-                                      const float* __restrict__ dagg, float* __restrict__ denv) {
+                                      const float* __restrict__ dagg, const float* __restrict__ drow,
+                                      float* __restrict__ denv) {
   MB_ROW_PROLOGUE(n_bonds)
   const int64_t e1 = u2d[row], e2 = rev[e1];
-  const float4 a = mul4(ld4(dagg + (int64_t)tgt[e1] * 128 + c), ld4(h + e1 * 128 + c));
-  const float4 b = mul4(ld4(dagg + (int64_t)tgt[e2] * 128 + c), ld4(h + e2 * 128 + c));
-  st4(denv + row * 128 + c, add4(a, b));
+  float4 g1 = ld4(dagg + (int64_t)tgt[e1] * 128 + c), g2 = ld4(dagg + (int64_t)tgt[e2] * 128 + c);
+  if (drow) {  // gradient that reached the smoothed rows directly (edge FFN fed with h * s)
+    g1 = add4(g1, ld4(drow + e1 * 128 + c));
+    g2 = add4(g2, ld4(drow + e2 * 128 + c));
+  }
+  st4(denv + row * 128 + c, add4(mul4(g1, ld4(h + e1 * 128 + c)), mul4(g2, ld4(h + e2 * 128 + c))));
+}
+
+// y[r] = x[r] * s[idx[r]]  (rows scaled channel-wise by a gathered row)
+__global__ void k_mul_rows_gather(int64_t n_rows, const float* __restrict__ x, const float* __restrict__ s,
+                                  const int32_t* __restrict__ idx, float* __restrict__ y) {
+  MB_ROW_PROLOGUE(n_rows)
+  const int64_t sr = idx ? idx[row] : row;
+  st4(y + row * 128 + c, mul4(ld4(x + row * 128 + c), ld4(s + sr * 128 + c)));
 }
 
 __global__ void k_smooth_env_bwd_line(int n_nodes, const int32_t* __restrict__ tgt_ptr,
@@ -477,18 +489,28 @@ extern "C" int mb_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* tgt, co
 extern "C" int mb_seg_smooth_sum_bwd_env(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* src_ptr,
                                          const int32_t* src_perm, const int32_t* tgt, const int32_t* src,
                                          int32_t idx_stride, const int32_t* u2d, const int32_t* rev, const float* env,
-                                         const float* h, const float* dagg, float* denv, void* stream) {
+                                         const float* h, const float* dagg, const float* drow, float* denv,
+                                         void* stream) {
   MB_REQUIRE(n_nodes >= 0 && tgt && h && dagg && denv && idx_stride > 0);
   if (n_nodes == 0) return MB_OK;
   if (!src_ptr) {
     MB_REQUIRE(u2d && rev && idx_stride == 1);
-    k_smooth_env_bwd_atom<<<row_grid(n_nodes), RW_THREADS, 0, STREAM>>>(n_nodes, u2d, rev, tgt, h, dagg, denv);
+    k_smooth_env_bwd_atom<<<row_grid(n_nodes), RW_THREADS, 0, STREAM>>>(n_nodes, u2d, rev, tgt, h, dagg, drow, denv);
   } else {
-    MB_REQUIRE(tgt_ptr && src_perm && src && env);
+    MB_REQUIRE(tgt_ptr && src_perm && src && env && !drow);
     k_smooth_env_bwd_line<<<row_grid(n_nodes), RW_THREADS, 0, STREAM>>>(n_nodes, tgt_ptr, src_ptr, src_perm, tgt, src,
                                                                        idx_stride, env, h, dagg, denv);
   }
   MB_LAUNCH_CHECK("k_smooth_env_bwd");
+  return MB_OK;
+}
+
+extern "C" int mb_mul_rows_gather(int64_t n_rows, const float* x, const float* s, const int32_t* idx, float* y,
+                                  void* stream) {
+  MB_REQUIRE(n_rows >= 0 && x && s && y);
+  if (n_rows == 0) return MB_OK;
+  k_mul_rows_gather<<<row_grid(n_rows), RW_THREADS, 0, STREAM>>>(n_rows, x, s, idx, y);
+  MB_LAUNCH_CHECK("k_mul_rows_gather");
   return MB_OK;
 }
 

@@ -55,10 +55,13 @@ def _pack_gated(get, prefix, dev):
         k=w1.shape[1])
 
 
-def _pack_ffn(get, prefix):
+def _pack_ffn(get, prefix, bias):
+    """node_FFN / edge_FFN (matris/model/interaction_block.py:197-210): two linear layers, biases only with use_bias."""
     w1, w2 = get(prefix + "layers.0.weight"), get(prefix + "layers.3.weight")
     SW = ops.SplitWeight
-    return SimpleNamespace(w1=SW(w1), w2=SW(w2), w1t=SW(w1.t()), w2t=SW(w2.t()))
+    b1 = get(prefix + "layers.0.bias").contiguous() if bias else None
+    b2 = get(prefix + "layers.3.bias").contiguous() if bias else None
+    return SimpleNamespace(w1=SW(w1), w2=SW(w2), w1t=SW(w1.t()), w2t=SW(w2.t()), b1=b1, b2=b2)
 
 
 def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
@@ -97,7 +100,9 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
             setattr(L, "attn_" + gname, A)
             p = f"interaction_block.{i}.refine_block_{gname}_graph."
             R = SimpleNamespace(edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
-                                nffn=_pack_ffn(get, p + "node_FFN."), effn=_pack_ffn(get, p + "edge_FFN."),
+                                nffn=_pack_ffn(get, p + "node_FFN.", bool(cfg["use_bias"])),
+                                effn=_pack_ffn(get, p + "edge_FFN.", bool(cfg["use_bias"])),
+                                smoothed_edge=bool(cfg["use_smoothed_for_delta_edge"]) and gname == "atom",
                                 wenv=get(p + "learnable_envelope.weight").contiguous(),
                                 wn=get(p + "node_res_weight").reshape(-1).contiguous(),
                                 we=get(p + "edge_res_weight").reshape(-1).contiguous())
@@ -237,14 +242,17 @@ def _refine_forward(P, rg, node, edge, rbf, atom_feat, save=True):
     z1, z2, h, _ = gated_fwd(P.edge, R, srcs, save=save)
     env = ops.small_linear_fwd(rbf, P.wenv)               # [bonds,128]
     agg = ops.seg_smooth_sum_fwd(Nn, rg.tgt_ptr, rg.emap, None if rg.is_atom else rg.src, env, h)
-    zn = ops.linear(agg, P.nffn.w1)
-    node_out = ops.linear(zn, P.nffn.w2, in_act=1, res=node, res_w=P.wn)
-    ze = ops.linear(h, P.effn.w1)
+    zn = ops.linear(agg, P.nffn.w1, bias=P.nffn.b1)
+    node_out = ops.linear(zn, P.nffn.w2, bias=P.nffn.b2, in_act=1, res=node, res_w=P.wn)
+    # the edge update reads the unsmoothed rows unless use_smoothed_for_delta_edge (atom graph only,
+    # interaction_block.py:262-266): then it reads h * s, s = the envelope row of the edge's bond
+    ffn_in = ops.mul_rows_gather(h, env, rg.emap) if P.smoothed_edge else h
+    ze = ops.linear(ffn_in, P.effn.w1, bias=P.effn.b1)
     if rg.is_atom:
-        y = ops.linear(ze, P.effn.w2, in_act=1)
+        y = ops.linear(ze, P.effn.w2, bias=P.effn.b2, in_act=1)
         edge_out = ops.pair_mean_res(Ne, rg.u2d, rg.rev, y, edge, P.we)
     else:
-        edge_out = ops.linear(ze, P.effn.w2, in_act=1, res=edge, res_w=P.we)
+        edge_out = ops.linear(ze, P.effn.w2, bias=P.effn.b2, in_act=1, res=edge, res_w=P.we)
     return node_out, edge_out, (z1, z2, h, env, zn, ze)
 
 
@@ -287,11 +295,16 @@ class RefineFn(torch.autograd.Function):
             dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze)
         dh = ops.linear(dze, P.effn.w1t)
         del ze, dze
+        drow = None
+        if P.smoothed_edge:  # dh so far is the gradient of the smoothed rows h * s
+            drow, dh = dh, ops.mul_rows_gather(dh, env, rg.emap)
         # smoothed aggregation
         src = None if rg.is_atom else rg.src
         ops.seg_smooth_sum_bwd_rows(rg.tgt, src, rg.emap, env, dagg, dh, accumulate=True)
         denv = ops.seg_smooth_sum_bwd_env(env.shape[0], rg.tgt_ptr, None if rg.is_atom else rg.src_ptr, rg.src_perm,
-                                          rg.tgt, src if src is not None else rg.src, rg.u2d, rg.rev, env, h, dagg)
+                                          rg.tgt, src if src is not None else rg.src, rg.u2d, rg.rev, env, h, dagg,
+                                          drow=drow)
+        del drow
         d_rbf = ops.small_linear_bwd(denv, P.wenv)
         del env, denv, dagg, h
         # gated MLP
@@ -455,8 +468,6 @@ class MatRIS(nn.Module):
         self.config = {k: v for k, v in locals().items() if k not in ("self", "__class__", "seed")}
         cfg = full_config(self.config)
         check_supported(cfg)
-        if use_smoothed_for_delta_edge:
-            raise NotImplementedError("use_smoothed_for_delta_edge=True is not implemented")
         self.is_intensive = is_intensive
         self.graph_converter = GraphConverter(atom_graph_cutoff=pairwise_cutoff, line_graph_cutoff=three_body_cutoff)
         for key, value in random_state_dict(cfg, seed=seed).items():

@@ -224,11 +224,18 @@ def seg_smooth_sum_bwd_rows(tgt, src, emap, env, dagg, dh, accumulate=True):
          int(accumulate), _stream())
 
 
-def seg_smooth_sum_bwd_env(n_nodes, tgt_ptr, src_ptr, src_perm, tgt, src, u2d, rev, env, h, dagg):
+def seg_smooth_sum_bwd_env(n_nodes, tgt_ptr, src_ptr, src_perm, tgt, src, u2d, rev, env, h, dagg, drow=None):
     denv = new(n_nodes, D, h)
     call("mb_seg_smooth_sum_bwd_env", n_nodes, ptr(tgt_ptr), ptr(src_ptr), ptr(src_perm), ptr(tgt), ptr(src), 1,
-         ptr(u2d), ptr(rev), ptr(env), ptr(h), ptr(dagg), ptr(denv), _stream())
+         ptr(u2d), ptr(rev), ptr(env), ptr(h), ptr(dagg), ptr(drow), ptr(denv), _stream())
     return denv
+
+
+def mul_rows_gather(x, s, idx=None):
+    """y[r] = x[r] * s[idx[r]] channel-wise."""
+    y = torch.empty_like(x)
+    call("mb_mul_rows_gather", x.shape[0], ptr(x), ptr(s), ptr(idx), ptr(y), _stream())
+    return y
 
 
 def pair_mean_res(n_bonds, u2d, rev, y, res=None, res_w=None):

@@ -60,8 +60,6 @@ def check_supported(cfg: dict) -> None:
         raise NotImplementedError("matris_b200 implements the conservative force/stress head only")
     if float(cfg["dropout"]) != 0.0:
         raise NotImplementedError("dropout is a training-only option")
-    if cfg["use_bias"]:
-        raise NotImplementedError("use_bias=True (biases in the FFN layers) is not implemented")
 
 
 def schema(config: dict | None = None) -> "OrderedDict[str, tuple]":
@@ -108,10 +106,11 @@ def schema(config: dict | None = None) -> "OrderedDict[str, tuple]":
             s[p + "node_res_weight"] = (1, D)
             s[p + "edge_res_weight"] = (1, D)
             gated(p + "edge_nonlinear_update.", 3 * D if g == "atom" else 4 * D)
-            s[p + "node_FFN.layers.0.weight"] = (D, D)
-            s[p + "node_FFN.layers.3.weight"] = (D, D)
-            s[p + "edge_FFN.layers.0.weight"] = (D, D)
-            s[p + "edge_FFN.layers.3.weight"] = (D, D)
+            for ffn in ("node_FFN", "edge_FFN"):  # biases only with use_bias (interaction_block.py:197-210)
+                for j in (0, 3):
+                    s[f"{p}{ffn}.layers.{j}.weight"] = (D, D)
+                    if cfg["use_bias"]:
+                        s[f"{p}{ffn}.layers.{j}.bias"] = (D,)
             s[p + "learnable_envelope.weight"] = (D, R)
     s["readout_norm.weight"] = (D,)
     for j, (o, k) in zip((0, 3, 6), ((D, D), (D, D), (1, D))):

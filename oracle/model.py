@@ -158,7 +158,7 @@ def attention_layer(p, node, edge, g, d2u=None):
     return node_new + p("node_res_weight") * node, edge_new + p("edge_res_weight") * edge
 
 
-def refinement_layer(p, node, edge, smooth, g, d2u=None, atom_feat=None, smoothed_delta_edge=False):
+def refinement_layer(p, node, edge, smooth, g, d2u=None, atom_feat=None, smoothed_delta_edge=False, ffn_bias=False):
     src, tgt = g["source_index"], g["target_index"]
     atom_graph = d2u is not None
     if atom_graph:
@@ -171,8 +171,8 @@ def refinement_layer(p, node, edge, smooth, g, d2u=None, atom_feat=None, smoothe
         x = torch.cat([edge, atom_feat[g["atom_list"]], node[tgt], node[src]], dim=1)
     h = gated_mlp(p.sub("edge_nonlinear_update"), x)
     hs = h * s
-    node_delta = mlp2(p.sub("node_FFN"), segment_sum(hs, tgt, len(node)), False)
-    edge_delta = mlp2(p.sub("edge_FFN"), hs if (atom_graph and smoothed_delta_edge) else h, False)
+    node_delta = mlp2(p.sub("node_FFN"), segment_sum(hs, tgt, len(node)), ffn_bias)
+    edge_delta = mlp2(p.sub("edge_FFN"), hs if (atom_graph and smoothed_delta_edge) else h, ffn_bias)
     if atom_graph:
         edge_delta = pair_mean(edge_delta, d2u)
     return node_delta + p("node_res_weight") * node, edge_delta + p("edge_res_weight") * edge
@@ -276,6 +276,7 @@ def forward(sd, cfg, graphs, task="ef", dtype=torch.float32):
         trip = F.silu(F.linear(F.linear(basis, pe("angle_embedding.weight")), pe("swish_layer.linear.weight")))
     # interaction blocks (interaction_block.py:372-446)
     sde = cfg.get("use_smoothed_for_delta_edge", False)
+    fb = bool(cfg.get("use_bias", False))  # biases of node_FFN / edge_FFN (interaction_block.py:197-210)
     for i in range(cfg.get("num_layers", 6)):
         pb = P.sub(f"interaction_block.{i}")
         e_att, t_att = edge, trip
@@ -285,9 +286,9 @@ def forward(sd, cfg, graphs, task="ef", dtype=torch.float32):
         e_upd, t_upd = edge, trip
         if trip is not None:
             e_upd, t_upd = refinement_layer(pb.sub("refine_block_line_graph"), e_att, t_att, rbf3, lgd,
-                                            atom_feat=n_att)
+                                            atom_feat=n_att, ffn_bias=fb)
         node, edge = refinement_layer(pb.sub("refine_block_atom_graph"), n_att, e_upd, rbf2, bg["atom_graph"],
-                                      d2u, smoothed_delta_edge=sde)
+                                      d2u, smoothed_delta_edge=sde, ffn_bias=fb)
         trip = t_upd
     # readout
     node = F.rms_norm(node, (node.shape[1],), P("readout_norm.weight"), None)

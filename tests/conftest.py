@@ -25,7 +25,12 @@ def load_golden(name):
 
 
 GOLDEN_CASES = ["cu32_L10", "cu32_L2_jit", "cu32_ideal_L1", "random2_L2", "pu4si6_L2", "cu1_L1", "perov_L3",
-                "fe432_L2", "lipscl256_L2", "random8_L2", "democif_L2"]
+                "fe432_L2", "lipscl256_L2", "random8_L2", "democif_L2", "random2_L2_bias_smoothed"]
+
+
+def golden_config(meta):
+    """Constructor arguments of a golden case: layers, reference energy and any non-default options."""
+    return dict(num_layers=meta["num_layers"], reference_energy=meta["reference_energy"], **meta.get("config", {}))
 
 # tolerances of the evaluation path (energy eV/atom, force eV/A, stress eV/A^3, magmom mu_B)
 TOL = dict(e=1e-5, f=1e-4, s=1e-5, m=1e-4)

@@ -31,7 +31,7 @@ from oracle.neighbors import neighbor_list  # noqa: E402
 from oracle.refshim import import_reference  # noqa: E402
 
 CASES = {
-    # name: (crystal factory, num_layers, task, weight jitter)
+    # name: (crystal factory, num_layers, task, weight jitter[, extra constructor arguments])
     "cu32_L10": (lambda: workloads.cu_fcc(), 10, "efsm", 0.0),
     "cu32_L2_jit": (lambda: workloads.cu_fcc(), 2, "efsm", 0.1),
     "cu32_ideal_L1": (lambda: workloads.cu_fcc(sigma=0.0), 1, "efsm", 0.1),  # exact 180-degree triplets
@@ -47,6 +47,9 @@ CASES = {
     "random8_L2": (lambda: workloads.random_crystals(8, seed=1), 2, "efs", 0.1),
     # the structure file the reference ships (example/cif_file/demo.cif; a copy sits beside this script)
     "democif_L2": (lambda: demo_cif(), 2, "efsm", 0.1),
+    # non-default options: biases in the FFN layers, smoothed rows into the atom graph's edge update
+    "random2_L2_bias_smoothed": (lambda: workloads.random_crystals(2, seed=11), 2, "efsm", 0.1,
+                                 dict(use_bias=True, use_smoothed_for_delta_edge=True)),
 }
 
 
@@ -83,8 +86,8 @@ def reference_graph(ns, crystal, cutoff=6.0, line_cutoff=4.0):
     return rg, (c, n, im, d)
 
 
-def run_reference(ns, graphs, layers, task, jitter, double):
-    cfg = dict(num_layers=layers, reference_energy="mpa")
+def run_reference(ns, graphs, layers, task, jitter, double, extra=None):
+    cfg = dict(num_layers=layers, reference_energy="mpa", **(extra or {}))
     model = ns.MatRIS(**cfg)
     model.load_state_dict(random_state_dict(cfg, seed=0, jitter=jitter))
     model.eval()
@@ -121,7 +124,9 @@ def main():
     with open(os.path.join(HERE, "schema.json"), "w") as f:
         json.dump({"num_layers": 2, "reference_energy": "mpa",
                    "keys": [[k, list(v.shape)] for k, v in ref_model.state_dict().items()]}, f, indent=0)
-    for name, (factory, layers, task, jitter) in CASES.items():
+    for name, case in CASES.items():
+        factory, layers, task, jitter = case[:4]
+        extra = case[4] if len(case) > 4 else {}
         if only and name not in only:
             continue
         crystals = factory()
@@ -136,14 +141,14 @@ def main():
                            f"nl_image{b}": im.astype(np.int8), f"nl_distance{b}": d,
                            f"d2u{b}": rg.directed2undirected.numpy(), f"u2d{b}": rg.undirected2directed.numpy(),
                            f"line_graph{b}": rg.line_graph.numpy().reshape(-1, 5).astype(np.int32)})
-        r32 = run_reference(ns, graphs, layers, task, jitter, False)
-        r64 = run_reference(ns, graphs, layers, task, jitter, True)
+        r32 = run_reference(ns, graphs, layers, task, jitter, False, extra)
+        r64 = run_reference(ns, graphs, layers, task, jitter, True, extra)
         for k, v in r32.items():
             arrays["ref32_" + k] = v
         for k, v in r64.items():
             arrays["ref64_" + k] = v
         arrays["meta"] = np.array(json.dumps(dict(n_structures=len(crystals), num_layers=layers, task=task,
-                                                  jitter=jitter, seed=0, reference_energy="mpa")))
+                                                  jitter=jitter, seed=0, reference_energy="mpa", config=extra)))
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
         print(name, {k: float(np.abs(r32[k] - r64[k]).max()) for k in r32},
               "Fmax", float(np.abs(r32.get("f", np.zeros(1))).max()))

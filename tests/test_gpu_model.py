@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN_CASES, GPA, TOL, load_golden
+from conftest import GOLDEN_CASES, GPA, TOL, golden_config, load_golden
 from functools import partial
 
 from gpu_util import dev, report
@@ -117,8 +117,7 @@ def test_end_to_end_matches_reference(case, keep):
     """Whole evaluations against the reference's own float32 results; the gates are ABSOLUTE.  Both memory
     policies run every case (the reference itself recomputes above 60,000 triplets; fe432_L2 is above that)."""
     meta, crystals, z = load_golden(case)
-    ck = random_checkpoint(dict(num_layers=meta["num_layers"], reference_energy=meta["reference_energy"]),
-                           seed=meta["seed"], jitter=meta["jitter"])
+    ck = random_checkpoint(golden_config(meta), seed=meta["seed"], jitter=meta["jitter"])
     res, out, _ = _evaluate(ck, crystals, meta["task"], keep=keep)
     tag = f"e2e[{case},{'keep' if keep else 'recompute'}]"
     report(f"{tag} E (eV/atom)", res["e"], z["ref32_e"], TOL["e"])

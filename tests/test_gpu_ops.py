@@ -361,6 +361,16 @@ def test_seg_smooth_sum_fwd_bwd(ops, line):
                                       d_tgt, d_src, None if line else dev(u2d, i32), None if line else dev(rev, i32),
                                       dev(env), dev(h), dev(dagg))
     report(f"seg_smooth_sum_bwd_env line={line}", denv, dE, 2e-5)
+    if not line:
+        # smoothed rows h * s as a tensor (the edge update of use_smoothed_for_delta_edge) and its adjoints
+        hs = ops.mul_rows_gather(dev(h), dev(env), d_emap)
+        report("mul_rows_gather", hs, (H * s).detach(), 1e-6)
+        drow = rnd(R, 128, seed=9)
+        both = (ref * dagg.double()).sum() + (H * s * drow.double()).sum()
+        dE2, _ = torch.autograd.grad(both, [E, H])
+        denv2 = ops.seg_smooth_sum_bwd_env(env.shape[0], dev(tptr, i32), None, dev(perm, i32), d_tgt, d_src,
+                                           dev(u2d, i32), dev(rev, i32), dev(env), dev(h), dev(dagg), drow=dev(drow))
+        report("seg_smooth_sum_bwd_env with a per-row gradient", denv2, dE2, 2e-5)
 
 
 def test_pair_mean_scale_small_linear_norms(ops):

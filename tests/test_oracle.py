@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN, GOLDEN_CASES, GPA, TOL, load_golden
+from conftest import GOLDEN, GOLDEN_CASES, GPA, TOL, golden_config, load_golden
 from matris_b200.weights import random_checkpoint, schema
 from oracle import graph as og
 from oracle import pipeline
@@ -53,8 +53,7 @@ def test_graph_restatement_order_independent_semantics():
 @pytest.mark.parametrize("case", GOLDEN_CASES)
 def test_model_restatement_matches_reference(case):
     meta, crystals, z = load_golden(case)
-    ckpt = random_checkpoint(dict(num_layers=meta["num_layers"], reference_energy=meta["reference_energy"]),
-                             seed=meta["seed"], jitter=meta["jitter"])
+    ckpt = random_checkpoint(golden_config(meta), seed=meta["seed"], jitter=meta["jitter"])
     torch.set_num_threads(min(8, os.cpu_count() or 1))
     res = pipeline.evaluate(ckpt, crystals, meta["task"])
     # same code path as the reference up to summation order: far inside the gates
