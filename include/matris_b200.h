@@ -31,6 +31,7 @@ extern "C" {
 #define MB_ERR_UNPAIRED 4  /* a directed edge has no reverse edge (bond exactly on the cutoff) */
 #define MB_ERR_ISOLATED 5  /* an atom has no neighbour inside the cutoff */
 #define MB_ERR_TOO_LARGE 6 /* problem exceeds the fixed capacity of an allocation-free entry point */
+#define MB_ERR_CAPACITY 7  /* a caller-supplied capacity buffer is too small; the needed sizes are in counts[] */
 
 int mb_version(void);
 const char* mb_status_string(int status);
@@ -51,16 +52,20 @@ const char* mb_last_cuda_error(void);
  * directed edge; triplets are grouped by target bond.  This is exactly what the
  * reference's Graph produces when fed a neighbour list in that order.
  *
- * Three phases, because the caller allocates the outputs:
- *   mb_graph_count_edges     -> n_edges (host)
- *   mb_graph_build_edges     -> n_bonds, n_triplets (host)
- *   mb_graph_build_triplets
- * Each phase synchronises the stream once to return its counts.
+ * One asynchronous call: mb_graph_build queues ONE cooperative kernel and returns; it never synchronises.  The
+ * caller supplies capacity buffers (cap_edges directed edges, cap_triplets triplets) and a device status block
+ * `counts`; after the stream has reached the call it holds
+ *   counts[0] directed edges, [1] bonds, [2] triplets (the sizes actually needed, also when a capacity was too
+ *   small), [3] isolated atoms, [4] image index outside +-127, [5] unpaired edges, [6] edge capacity too small,
+ *   [7] triplet capacity too small, [8] triplets counted by source bond (must equal [2]).
+ * Copy the 16 ints to the host together with whatever else the caller reads back and pass them to mb_graph_status,
+ * which maps them to a status code; on MB_ERR_CAPACITY enlarge the buffers to counts[0] / counts[2] and call again
+ * (in a molecular-dynamics loop the previous step's counts plus a margin make that rare).
  */
 typedef struct mb_graph {
   /* sizes and parameters (host) */
   int32_t n_atoms, n_struct, n_cells;
-  int32_t n_edges, n_bonds, n_triplets;        /* written by the phases */
+  int32_t cap_edges, cap_triplets, pad;        /* capacities of the edge / triplet buffers below */
   double cutoff, line_cutoff, tol;             /* tol < d <= cutoff ; line graph: target d <= lc, source d < lc */
   /* inputs (device) */
   const double* cart;         /* [n_atoms,3] Cartesian, not wrapped */
@@ -75,36 +80,35 @@ typedef struct mb_graph {
   int32_t* cell_atoms;        /* [n_atoms] */
   int32_t* atom_cell;         /* [n_atoms,4] */
   int32_t* atom_wrap;         /* [n_atoms,4] */
-  int32_t* scan_tmp;          /* [mb_graph_scan_tmp_len(max(n_atoms, n_edges))] */
-  int32_t* status;            /* [8] device status words */
-  uint64_t* key_unsorted;     /* [n_edges]   (phase 2) */
-  double* dist_unsorted;      /* [n_edges]   (phase 2) */
-  uint64_t* key;              /* [n_edges]   (phase 2, 3) */
-  int32_t* atom_counts;       /* [n_atoms,2] src/tgt-eligible out-edge counts (phase 2, 3) */
-  int32_t* edge_rank;         /* [n_edges,2] (phase 2, 3) */
-  int32_t* bond_counts;       /* [n_bonds+1,2]... see graph.cu (phase 2, 3): length 2*(n_edges/2+1) suffices */
-  uint8_t* edge_flag;         /* [n_edges] bit0: may be a triplet target, bit1: may be a triplet source */
-  /* outputs phase 1 (device) */
+  int32_t* scan_tmp;          /* [mb_graph_scan_tmp_len(max(n_atoms, n_cells, cap_edges))] */
+  int32_t* counts;            /* [16] device status block, see above */
+  uint64_t* key_unsorted;     /* [cap_edges] */
+  double* dist_unsorted;      /* [cap_edges] */
+  uint64_t* key;              /* [cap_edges] */
+  int32_t* atom_counts;       /* [n_atoms,2] source- / target-eligible out-edge counts */
+  int32_t* edge_rank;         /* [2*cap_edges+2] */
+  int32_t* bond_counts;       /* [cap_edges+4] */
+  uint8_t* edge_flag;         /* [cap_edges] bit0: may be a triplet target, bit1: may be a triplet source */
+  /* outputs (device) */
   int32_t* edge_ptr;          /* [n_atoms+1] CSR of directed edges by centre atom */
-  /* outputs phase 2 (device), caller-allocated with n_edges known */
-  int32_t* center;            /* [n_edges] */
-  int32_t* neighbor;          /* [n_edges] */
-  int32_t* image;             /* [n_edges,3] */
-  double* dist;               /* [n_edges] float64 bond lengths used for the membership tests */
-  int32_t* rev;               /* [n_edges] index of the reverse directed edge */
-  int32_t* d2u;               /* [n_edges] directed -> bond */
-  int32_t* u2d;               /* [n_edges/2] bond -> its first directed edge */
-  int32_t* trip_ptr;          /* [n_edges/2+1] CSR of triplets by target bond */
-  int32_t* trip_src_ptr;      /* [n_edges/2+1] CSR of triplets by source bond */
-  /* outputs phase 3 (device), caller-allocated with n_triplets known */
-  int32_t* line_graph;        /* [n_triplets,5] rows (centre atom, target bond, target DE, source bond, source DE) */
-  int32_t* trip_src_perm;     /* [n_triplets] triplet ids grouped by source bond (see trip_src_ptr) */
+  int32_t* center;            /* [cap_edges] */
+  int32_t* neighbor;          /* [cap_edges] */
+  int32_t* image;             /* [cap_edges,3] */
+  double* dist;               /* [cap_edges] float64 bond lengths used for the membership tests */
+  int32_t* rev;               /* [cap_edges] index of the reverse directed edge */
+  int32_t* d2u;               /* [cap_edges] directed -> bond */
+  int32_t* u2d;               /* [cap_edges/2] bond -> its first directed edge */
+  int32_t* trip_ptr;          /* [cap_edges/2+1] CSR of triplets by target bond */
+  int32_t* trip_src_ptr;      /* [cap_edges/2+1] CSR of triplets by source bond */
+  int32_t* line_graph;        /* [cap_triplets,5] rows (centre atom, target bond, target DE, source bond, source DE) */
+  int32_t* trip_src_perm;     /* [cap_triplets] triplet ids grouped by source bond (see trip_src_ptr) */
 } mb_graph;
 
 size_t mb_graph_scan_tmp_len(int64_t n);
-int mb_graph_count_edges(mb_graph* g, void* stream);
-int mb_graph_build_edges(mb_graph* g, void* stream);
-int mb_graph_build_triplets(mb_graph* g, void* stream);
+int mb_graph_build(const mb_graph* g, void* stream);
+/* status code of a build from the host copy of counts[16]: MB_OK, MB_ERR_ISOLATED, MB_ERR_OVERFLOW (image index or
+ * a count beyond int32), MB_ERR_CAPACITY, MB_ERR_UNPAIRED */
+int mb_graph_status(const int32_t* counts_host);
 
 /* ------------------------------------------------------------------ dense row GEMM
  * out[r, 128*j + n] = epilogue( sum_k A_j[r, k] * W_j[n, k] )        j = 0..n_blocks-1

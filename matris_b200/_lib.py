@@ -12,6 +12,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libmatris_b200.so")
 
 MB_OK = 0
+MB_ERR_CAPACITY = 7
 OUT_STORE, OUT_ADD, OUT_ATOMIC = 0, 1, 2
 
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
@@ -28,11 +29,11 @@ class IsolatedAtomError(ValueError):
 class MbGraph(C.Structure):
     _fields_ = [
         ("n_atoms", _i32), ("n_struct", _i32), ("n_cells", _i32),
-        ("n_edges", _i32), ("n_bonds", _i32), ("n_triplets", _i32),
+        ("cap_edges", _i32), ("cap_triplets", _i32), ("pad", _i32),
         ("cutoff", C.c_double), ("line_cutoff", C.c_double), ("tol", C.c_double),
         ("cart", _vp), ("lattice", _vp), ("inv_lattice", _vp), ("atom_struct", _vp), ("grid", _vp),
         ("cell_ptr", _vp), ("cell_fill", _vp), ("cell_atoms", _vp), ("atom_cell", _vp), ("atom_wrap", _vp),
-        ("scan_tmp", _vp), ("status", _vp), ("key_unsorted", _vp), ("dist_unsorted", _vp), ("key", _vp),
+        ("scan_tmp", _vp), ("counts", _vp), ("key_unsorted", _vp), ("dist_unsorted", _vp), ("key", _vp),
         ("atom_counts", _vp), ("edge_rank", _vp), ("bond_counts", _vp), ("edge_flag", _vp),
         ("edge_ptr", _vp),
         ("center", _vp), ("neighbor", _vp), ("image", _vp), ("dist", _vp), ("rev", _vp), ("d2u", _vp),
@@ -72,9 +73,8 @@ class MbGatedMlp(C.Structure):
 
 # name -> argtypes (every function returns int status unless listed in _OTHER)
 _SIGNATURES = {
-    "mb_graph_count_edges": [C.POINTER(MbGraph), _vp],
-    "mb_graph_build_edges": [C.POINTER(MbGraph), _vp],
-    "mb_graph_build_triplets": [C.POINTER(MbGraph), _vp],
+    "mb_graph_build": [C.POINTER(MbGraph), _vp],
+    "mb_graph_status": [C.POINTER(C.c_int32)],
     "mb_gemm": [C.POINTER(MbGemmDesc), _vp],
     "mb_set_gemm_mode": [C.c_int],
     "mb_gemm_status": [C.POINTER(C.c_int), _vp],

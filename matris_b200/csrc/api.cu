@@ -22,6 +22,7 @@ extern "C" const char* mb_status_string(int status) {
     case MB_ERR_UNPAIRED: return "directed edge without a reverse edge";
     case MB_ERR_ISOLATED: return "isolated atom: no neighbour inside the cutoff";
     case MB_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this allocation-free entry point";
+    case MB_ERR_CAPACITY: return "capacity buffer too small";
     default: return "unknown status";
   }
 }

@@ -1,28 +1,39 @@
-// Periodic radius graph, bond graph and line graph (angle triplets) on the GPU.
+// Periodic radius graph, bond graph and line graph (angle triplets) on the GPU: ONE cooperative kernel per batch.
 //
-// Integer / indexing work, HBM-bound.  The inclusion tests run in float64 with
-// explicit round-to-nearest intrinsics (no FMA contraction) in a fixed operation
-// order, so membership is decided by exactly the same numbers as a NumPy
-// evaluation of the same formula.
+// Integer / indexing work, HBM-bound.  The inclusion tests run in float64 with explicit round-to-nearest
+// intrinsics (no FMA contraction) in a fixed operation order, so membership is decided by exactly the same numbers
+// as a NumPy evaluation of the same formula.
 //
-// Pipeline (see include/matris_b200.h for what each phase returns):
-//   bin atoms into cells -> per-atom neighbour count (warp per atom, ballot
-//   compaction) -> scan -> fill -> per-atom rank sort by (neighbour, image) ->
-//   reverse-edge search (binary search inside the neighbour's own segment) ->
-//   bond numbering (scan of "first of its pair" flags) -> per-bond triplet counts
-//   -> scan -> triplet fill grouped by target bond + permutation grouped by
-//   source bond.
+// The whole pipeline is a single persistent kernel (cudaLaunchCooperativeKernel, as many CTAs as are co-resident)
+// whose phases are separated by grid-wide barriers, so a build is one launch and no host synchronisation: every
+// count stays on the device (counts[]), the outputs go into caller-supplied capacity buffers, and a capacity that
+// turns out too small is reported in counts[] (the caller enlarges the buffer and calls again).
+//
+//   bin atoms into cells -> per-atom neighbour count (one CTA per cell: the home cell's atoms and each neighbouring
+//   cell's atoms are staged in shared memory, ballot compaction) -> scan -> fill -> per-atom rank sort by
+//   (neighbour, image) -> reverse-edge
+//   search (binary search inside the neighbour's own segment) -> bond numbering (scan of "first of its pair" flags)
+//   -> per-bond triplet counts -> scans -> triplet fill grouped by target bond + permutation grouped by source bond.
+#include <cooperative_groups.h>
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace mb {
 
-// ---------------------------------------------------------------- exclusive scan
-constexpr int SCAN_THREADS = 256;
+constexpr int GB_THREADS = 256;
 constexpr int SCAN_ITEMS = 8;  // per thread
-constexpr int SCAN_CHUNK = SCAN_THREADS * SCAN_ITEMS;
+constexpr int SCAN_CHUNK = GB_THREADS * SCAN_ITEMS;
 
+// counts[] layout (device, int32[16]); also the status block the caller reads back
+enum {
+  CT_EDGES = 0, CT_BONDS = 1, CT_TRIPLETS = 2, CT_ISOLATED = 3, CT_IMAGE_OVERFLOW = 4, CT_UNPAIRED = 5,
+  CT_EDGE_CAPACITY = 6, CT_TRIPLET_CAPACITY = 7, CT_TRIPLETS_BY_SOURCE = 8
+};
+
+// ---------------------------------------------------------------- block / grid exclusive scan
 __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
-  __shared__ int warp_sums[SCAN_THREADS / 32];
+  __shared__ int warp_sums[GB_THREADS / 32];
   __shared__ int block_total;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   int x = v;
@@ -34,14 +45,14 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
   if (lane == 31) warp_sums[w] = x;
   __syncthreads();
   if (w == 0) {
-    int s = lane < SCAN_THREADS / 32 ? warp_sums[lane] : 0;
+    int s = lane < GB_THREADS / 32 ? warp_sums[lane] : 0;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       int y = __shfl_up_sync(0xffffffffu, s, o);
       if (lane >= o) s += y;
     }
-    if (lane < SCAN_THREADS / 32) warp_sums[lane] = s;  // inclusive over warps
-    if (lane == SCAN_THREADS / 32 - 1) block_total = s;
+    if (lane < GB_THREADS / 32) warp_sums[lane] = s;  // inclusive over warps
+    if (lane == GB_THREADS / 32 - 1) block_total = s;
   }
   __syncthreads();
   int prefix = (w > 0 ? warp_sums[w - 1] : 0) + x - v;
@@ -50,114 +61,63 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
   return prefix;
 }
 
-__global__ void k_scan_reduce(const int32_t* __restrict__ in, int64_t n, int32_t* __restrict__ block_sums) {
-  int64_t base = (int64_t)blockIdx.x * SCAN_CHUNK;
-  int s = 0;
+// Exclusive scan of in[0..n) into out[0..n], out[n] = total; in may alias out; n is the same in every thread.
+// Three steps separated by grid barriers: per-chunk sums, scan of the chunk sums by one block, apply.
+__device__ void grid_scan(cg::grid_group& grid, const int32_t* in, int32_t* out, int64_t n, int32_t* tmp) {
+  const int n_chunks = (int)((n + SCAN_CHUNK - 1) / SCAN_CHUNK);
+  for (int ch = blockIdx.x; ch < n_chunks; ch += gridDim.x) {
+    const int64_t base = (int64_t)ch * SCAN_CHUNK + (int64_t)threadIdx.x * SCAN_ITEMS;
+    int s = 0;
 #pragma unroll
-  for (int k = 0; k < SCAN_ITEMS; ++k) {
-    int64_t i = base + (int64_t)threadIdx.x * SCAN_ITEMS + k;
-    if (i < n) s += in[i];
-  }
-  int total;
-  block_exclusive_scan(s, &total);
-  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
-}
-
-// single block: exclusive scan of the block sums in place, sequentially over chunks
-__global__ void k_scan_block_sums(int32_t* __restrict__ block_sums, int n_blocks) {
-  __shared__ int carry;
-  if (threadIdx.x == 0) carry = 0;
-  __syncthreads();
-  for (int base = 0; base < n_blocks; base += SCAN_THREADS) {
-    int i = base + threadIdx.x;
-    int v = i < n_blocks ? block_sums[i] : 0;
+    for (int k = 0; k < SCAN_ITEMS; ++k)
+      if (base + k < n) s += in[base + k];
     int total;
-    int p = block_exclusive_scan(v, &total);
-    if (i < n_blocks) block_sums[i] = carry + p;
+    block_exclusive_scan(s, &total);
+    if (threadIdx.x == 0) tmp[ch] = total;
+  }
+  grid.sync();
+  if (blockIdx.x == 0) {
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
     __syncthreads();
-    if (threadIdx.x == 0) carry += total;
-    __syncthreads();
+    for (int base = 0; base < n_chunks; base += GB_THREADS) {
+      const int i = base + threadIdx.x;
+      const int v = i < n_chunks ? tmp[i] : 0;
+      int total;
+      const int p = block_exclusive_scan(v, &total);
+      if (i < n_chunks) tmp[i] = carry + p;
+      __syncthreads();
+      if (threadIdx.x == 0) carry += total;
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      tmp[n_chunks] = carry;
+      if (n_chunks == 0) out[0] = 0;
+    }
   }
-  if (threadIdx.x == 0) block_sums[n_blocks] = carry;
-}
-
-__global__ void k_scan_apply(const int32_t* in, int64_t n, const int32_t* __restrict__ block_sums, int32_t* out,
-                             int n_blocks) {
-  int64_t base = (int64_t)blockIdx.x * SCAN_CHUNK;
-  int v[SCAN_ITEMS];
-  int s = 0;
+  grid.sync();
+  for (int ch = blockIdx.x; ch < n_chunks; ch += gridDim.x) {
+    const int64_t base = (int64_t)ch * SCAN_CHUNK + (int64_t)threadIdx.x * SCAN_ITEMS;
+    int v[SCAN_ITEMS];
+    int s = 0;
 #pragma unroll
-  for (int k = 0; k < SCAN_ITEMS; ++k) {
-    int64_t i = base + (int64_t)threadIdx.x * SCAN_ITEMS + k;
-    v[k] = i < n ? in[i] : 0;
-    s += v[k];
-  }
-  int total;
-  int p = block_exclusive_scan(s, &total) + block_sums[blockIdx.x];
+    for (int k = 0; k < SCAN_ITEMS; ++k) {
+      v[k] = base + k < n ? in[base + k] : 0;
+      s += v[k];
+    }
+    int total;
+    int p = block_exclusive_scan(s, &total) + tmp[ch];
 #pragma unroll
-  for (int k = 0; k < SCAN_ITEMS; ++k) {
-    int64_t i = base + (int64_t)threadIdx.x * SCAN_ITEMS + k;
-    if (i < n) out[i] = p;
-    p += v[k];
+    for (int k = 0; k < SCAN_ITEMS; ++k) {
+      if (base + k < n) out[base + k] = p;
+      p += v[k];
+    }
+    if (ch == n_chunks - 1 && threadIdx.x == 0) out[n] = tmp[n_chunks];
   }
-  if (blockIdx.x == n_blocks - 1 && threadIdx.x == 0) out[n] = block_sums[n_blocks];
+  grid.sync();
 }
 
-int scan_exclusive(const int32_t* in, int32_t* out, int64_t n, int32_t* tmp, cudaStream_t s) {
-  if (n <= 0) {
-    MB_CUDA_CHECK(cudaMemsetAsync(out, 0, sizeof(int32_t), s));
-    return MB_OK;
-  }
-  int n_blocks = cdiv(n, SCAN_CHUNK);
-  k_scan_reduce<<<n_blocks, SCAN_THREADS, 0, s>>>(in, n, tmp);
-  k_scan_block_sums<<<1, SCAN_THREADS, 0, s>>>(tmp, n_blocks);
-  k_scan_apply<<<n_blocks, SCAN_THREADS, 0, s>>>(in, n, tmp, out, n_blocks);
-  MB_LAUNCH_CHECK("scan_exclusive");
-  return MB_OK;
-}
-
-// ---------------------------------------------------------------- status words
-enum { ST_ISOLATED = 0, ST_IMAGE_OVERFLOW = 1, ST_UNPAIRED = 2 };
-
-// ---------------------------------------------------------------- binning
-__global__ void k_bin_count(int n_atoms, const double* __restrict__ cart, const double* __restrict__ inv_lattice,
-                            const int32_t* __restrict__ atom_struct, const int32_t* __restrict__ grid,
-                            int32_t* __restrict__ atom_cell, int32_t* __restrict__ atom_wrap,
-                            int32_t* __restrict__ cell_count) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_atoms) return;
-  int b = atom_struct[i];
-  const double* inv = inv_lattice + 9 * b;
-  const int32_t* g = grid + 8 * b;
-  double x = cart[3 * i], y = cart[3 * i + 1], z = cart[3 * i + 2];
-  int c[3], w[3];
-#pragma unroll
-  for (int k = 0; k < 3; ++k) {
-    double f = x * inv[k] + y * inv[3 + k] + z * inv[6 + k];
-    double fl = floor(f);
-    double fw = f - fl;
-    if (fw >= 1.0) { fw = 0.0; fl += 1.0; }
-    w[k] = (int)fl;
-    int ck = (int)(fw * (double)g[k]);
-    c[k] = ck < g[k] - 1 ? ck : g[k] - 1;
-    if (c[k] < 0) c[k] = 0;
-  }
-  int cell = g[6] + (c[0] * g[1] + c[1]) * g[2] + c[2];
-  reinterpret_cast<int4*>(atom_cell)[i] = make_int4(c[0], c[1], c[2], cell);
-  reinterpret_cast<int4*>(atom_wrap)[i] = make_int4(w[0], w[1], w[2], 0);
-  atomicAdd(&cell_count[cell], 1);
-}
-
-__global__ void k_bin_fill(int n_atoms, const int32_t* __restrict__ atom_cell, const int32_t* __restrict__ cell_ptr,
-                           int32_t* __restrict__ cell_fill, int32_t* __restrict__ cell_atoms) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_atoms) return;
-  int cell = atom_cell[4 * i + 3];
-  int pos = cell_ptr[cell] + atomicAdd(&cell_fill[cell], 1);
-  cell_atoms[pos] = i;
-}
-
-// ---------------------------------------------------------------- neighbour search
+// ---------------------------------------------------------------- helpers
 __device__ __forceinline__ int floor_div(int a, int b) {
   int q = a / b;
   return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q;
@@ -168,250 +128,371 @@ __device__ __forceinline__ uint64_t pack_key(int j, int n0, int n1, int n2) {
          ((uint64_t)(uint32_t)(n1 + 128) << 8) | (uint64_t)(uint32_t)(n2 + 128);
 }
 
+// Neighbour search, one CTA per cell of the cell list.  The atoms of the home cell (in chunks of HOME_MAX) and, for
+// every neighbouring cell inside the search range, that cell's atoms (in chunks of CAND_MAX) are staged in shared
+// memory once per CTA; warp w then takes home atoms w, w + 8, ... and its lanes test 32 staged candidates per
+// round.  FILL = false counts (edge_ptr[i] = number of neighbours of atom i), FILL = true writes packed keys and
+// distances from edge_ptr[i] on.  Both passes walk the candidates in the same order.
+constexpr int HOME_MAX = 64, CAND_MAX = 128;
+
+struct NeighborStage {
+  int home_id[HOME_MAX];
+  int4 home_wrap[HOME_MAX];
+  double home_x[HOME_MAX], home_y[HOME_MAX], home_z[HOME_MAX];
+  int home_count[HOME_MAX];
+  int cand_id[CAND_MAX];
+  int4 cand_wrap[CAND_MAX];
+  double cand_x[CAND_MAX], cand_y[CAND_MAX], cand_z[CAND_MAX];
+};
+
 template <bool FILL>
-__global__ void k_neighbors(int n_atoms, double cutoff, double tol, const double* __restrict__ cart,
-                            const double* __restrict__ lattice, const int32_t* __restrict__ atom_struct,
-                            const int32_t* __restrict__ grid, const int32_t* __restrict__ atom_cell,
-                            const int32_t* __restrict__ atom_wrap, const int32_t* __restrict__ cell_ptr,
-                            const int32_t* __restrict__ cell_atoms, int32_t* __restrict__ edge_ptr,
-                            uint64_t* __restrict__ key_out, double* __restrict__ dist_out,
-                            int32_t* __restrict__ status) {
-  const int lane = threadIdx.x & 31;
-  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (i >= n_atoms) return;
-  const int b = atom_struct[i];
-  const int32_t* g = grid + 8 * b;
-  const int g0 = g[0], g1 = g[1], g2 = g[2], s0 = g[3], s1 = g[4], s2 = g[5], base = g[6];
-  double L[9];
+__device__ void neighbors_of_cells(const mb_graph& g, NeighborStage& st) {
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const double cutoff = g.cutoff, tol = g.tol;
+  for (int cell = blockIdx.x; cell < g.n_cells; cell += gridDim.x) {
+    const int hp0 = g.cell_ptr[cell], hp1 = g.cell_ptr[cell + 1];  // home atoms (block-uniform)
+    if (hp1 == hp0) continue;
+    const int first = g.cell_atoms[hp0];
+    const int b = g.atom_struct[first];
+    const int32_t* gr = g.grid + 8 * b;
+    const int g0 = gr[0], g1 = gr[1], g2 = gr[2], s0 = gr[3], s1 = gr[4], s2 = gr[5], base = gr[6];
+    const int4 ci = reinterpret_cast<const int4*>(g.atom_cell)[first];  // cell coordinates: the same for all home atoms
+    double L[9];
 #pragma unroll
-  for (int k = 0; k < 9; ++k) L[k] = lattice[9 * b + k];
-  const double xi = cart[3 * i], yi = cart[3 * i + 1], zi = cart[3 * i + 2];
-  const int4 ci = reinterpret_cast<const int4*>(atom_cell)[i];
-  const int4 wi = reinterpret_cast<const int4*>(atom_wrap)[i];
-  const int out_base = FILL ? edge_ptr[i] : 0;
-  int count = 0;
-  for (int d0 = -s0; d0 <= s0; ++d0) {
-    int c0 = ci.x + d0, h0 = floor_div(c0, g0);
-    c0 -= h0 * g0;
-    for (int d1 = -s1; d1 <= s1; ++d1) {
-      int c1 = ci.y + d1, h1 = floor_div(c1, g1);
-      c1 -= h1 * g1;
-      for (int d2 = -s2; d2 <= s2; ++d2) {
-        int c2 = ci.z + d2, h2 = floor_div(c2, g2);
-        c2 -= h2 * g2;
-        const int cell = base + (c0 * g1 + c1) * g2 + c2;
-        const int p0 = cell_ptr[cell], p1 = cell_ptr[cell + 1];
-        for (int pb = p0; pb < p1; pb += 32) {
-          const int p = pb + lane;
-          bool ok = false;
-          int j = 0, n0 = 0, n1 = 0, n2 = 0;
-          double d = 0.0;
-          if (p < p1) {
-            j = cell_atoms[p];
-            const int4 wj = reinterpret_cast<const int4*>(atom_wrap)[j];
-            n0 = h0 - wj.x + wi.x;
-            n1 = h1 - wj.y + wi.y;
-            n2 = h2 - wj.z + wi.z;
-            const double f0 = (double)n0, f1 = (double)n1, f2 = (double)n2;
-            // s = (n0*L0 + n1*L1) + n2*L2 ; dx = (x_j + s) - x_i ; no FMA contraction
-            const double sx = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[0]), __dmul_rn(f1, L[3])), __dmul_rn(f2, L[6]));
-            const double sy = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[1]), __dmul_rn(f1, L[4])), __dmul_rn(f2, L[7]));
-            const double sz = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[2]), __dmul_rn(f1, L[5])), __dmul_rn(f2, L[8]));
-            const double dx = __dsub_rn(__dadd_rn(cart[3 * j], sx), xi);
-            const double dy = __dsub_rn(__dadd_rn(cart[3 * j + 1], sy), yi);
-            const double dz = __dsub_rn(__dadd_rn(cart[3 * j + 2], sz), zi);
-            const double q = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
-            d = __dsqrt_rn(q);
-            ok = (d > tol) && (d <= cutoff);
+    for (int k = 0; k < 9; ++k) L[k] = g.lattice[9 * b + k];
+    for (int hb = hp0; hb < hp1; hb += HOME_MAX) {
+      const int n_home = hp1 - hb < HOME_MAX ? hp1 - hb : HOME_MAX;
+      __syncthreads();  // the previous chunk's readers are done with the home arrays
+      for (int t = threadIdx.x; t < n_home; t += blockDim.x) {
+        const int i = g.cell_atoms[hb + t];
+        st.home_id[t] = i;
+        st.home_wrap[t] = reinterpret_cast<const int4*>(g.atom_wrap)[i];
+        st.home_x[t] = g.cart[3 * i];
+        st.home_y[t] = g.cart[3 * i + 1];
+        st.home_z[t] = g.cart[3 * i + 2];
+        st.home_count[t] = 0;
+      }
+      bool bad_image = false;
+      for (int d0 = -s0; d0 <= s0; ++d0) {
+        int c0 = ci.x + d0;
+        const int h0 = floor_div(c0, g0);
+        c0 -= h0 * g0;
+        for (int d1 = -s1; d1 <= s1; ++d1) {
+          int c1 = ci.y + d1;
+          const int h1 = floor_div(c1, g1);
+          c1 -= h1 * g1;
+          for (int d2 = -s2; d2 <= s2; ++d2) {
+            int c2 = ci.z + d2;
+            const int h2 = floor_div(c2, g2);
+            c2 -= h2 * g2;
+            const int nc = base + (c0 * g1 + c1) * g2 + c2;
+            const int p0 = g.cell_ptr[nc], p1 = g.cell_ptr[nc + 1];
+            for (int pb = p0; pb < p1; pb += CAND_MAX) {
+              const int n_cand = p1 - pb < CAND_MAX ? p1 - pb : CAND_MAX;
+              __syncthreads();  // the previous round's readers are done with the candidate arrays
+              for (int t = threadIdx.x; t < n_cand; t += blockDim.x) {
+                const int j = g.cell_atoms[pb + t];
+                st.cand_id[t] = j;
+                st.cand_wrap[t] = reinterpret_cast<const int4*>(g.atom_wrap)[j];
+                st.cand_x[t] = g.cart[3 * j];
+                st.cand_y[t] = g.cart[3 * j + 1];
+                st.cand_z[t] = g.cart[3 * j + 2];
+              }
+              __syncthreads();
+              for (int ha = wib; ha < n_home; ha += GB_THREADS / 32) {
+                const int i = st.home_id[ha];
+                const int4 wi = st.home_wrap[ha];
+                const double xi = st.home_x[ha], yi = st.home_y[ha], zi = st.home_z[ha];
+                const int out_base = FILL ? g.edge_ptr[i] : 0;
+                int count = st.home_count[ha];
+                for (int cb = 0; cb < n_cand; cb += 32) {
+                  const int t = cb + lane;
+                  bool ok = false;
+                  int j = 0, n0 = 0, n1 = 0, n2 = 0;
+                  double d = 0.0;
+                  if (t < n_cand) {
+                    j = st.cand_id[t];
+                    const int4 wj = st.cand_wrap[t];
+                    n0 = h0 - wj.x + wi.x;
+                    n1 = h1 - wj.y + wi.y;
+                    n2 = h2 - wj.z + wi.z;
+                    const double f0 = (double)n0, f1 = (double)n1, f2 = (double)n2;
+                    // s = (n0*L0 + n1*L1) + n2*L2 ; dx = (x_j + s) - x_i ; no FMA contraction
+                    const double sx = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[0]), __dmul_rn(f1, L[3])), __dmul_rn(f2, L[6]));
+                    const double sy = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[1]), __dmul_rn(f1, L[4])), __dmul_rn(f2, L[7]));
+                    const double sz = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[2]), __dmul_rn(f1, L[5])), __dmul_rn(f2, L[8]));
+                    const double dx = __dsub_rn(__dadd_rn(st.cand_x[t], sx), xi);
+                    const double dy = __dsub_rn(__dadd_rn(st.cand_y[t], sy), yi);
+                    const double dz = __dsub_rn(__dadd_rn(st.cand_z[t], sz), zi);
+                    const double q = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+                    d = __dsqrt_rn(q);
+                    ok = (d > tol) && (d <= cutoff);
+                  }
+                  const unsigned mask = __ballot_sync(0xffffffffu, ok);
+                  if (ok) {
+                    if (n0 < -127 || n0 > 127 || n1 < -127 || n1 > 127 || n2 < -127 || n2 > 127) bad_image = true;
+                    if (FILL) {
+                      const int pos = out_base + count + __popc(mask & ((1u << lane) - 1u));
+                      if (pos < g.cap_edges) {
+                        g.key_unsorted[pos] = pack_key(j, n0, n1, n2);
+                        g.dist_unsorted[pos] = d;
+                      }
+                    }
+                  }
+                  count += __popc(mask);
+                }
+                __syncwarp();
+                if (lane == 0) st.home_count[ha] = count;  // a home atom belongs to one warp: no race
+                __syncwarp();
+              }
+            }
           }
-          const unsigned mask = __ballot_sync(0xffffffffu, ok);
-          if (FILL && ok) {
-            const int pos = out_base + count + __popc(mask & ((1u << lane) - 1u));
-            key_out[pos] = pack_key(j, n0, n1, n2);
-            dist_out[pos] = d;
-            if (n0 < -127 || n0 > 127 || n1 < -127 || n1 > 127 || n2 < -127 || n2 > 127)
-              atomicOr(&status[ST_IMAGE_OVERFLOW], 1);
-          }
-          count += __popc(mask);
+        }
+      }
+      __syncthreads();
+      if (!FILL) {
+        // the image range is checked in the counting pass: nothing is packed or paired when it fails
+        if (bad_image) atomicOr(&g.counts[CT_IMAGE_OVERFLOW], 1);
+        for (int t = threadIdx.x; t < n_home; t += blockDim.x) {
+          g.edge_ptr[st.home_id[t]] = st.home_count[t];
+          if (st.home_count[t] == 0) atomicAdd(&g.counts[CT_ISOLATED], 1);
         }
       }
     }
   }
-  if (!FILL && lane == 0) {
-    edge_ptr[i] = count;
-    if (count == 0) atomicAdd(&status[ST_ISOLATED], 1);
-  }
 }
 
-// rank sort of each atom's out-edges by key (neighbour, image); warp per atom
-__global__ void k_sort_edges(int n_atoms, const int32_t* __restrict__ edge_ptr,
-                             const uint64_t* __restrict__ key_in, const double* __restrict__ dist_in,
-                             uint64_t* __restrict__ key, double* __restrict__ dist, int32_t* __restrict__ center,
-                             int32_t* __restrict__ neighbor, int32_t* __restrict__ image) {
+// ---------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(GB_THREADS, 2) k_graph_build(const mb_graph g) {
+  cg::grid_group grid = cg::this_grid();
+  __shared__ NeighborStage stage;
   const int lane = threadIdx.x & 31;
-  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (i >= n_atoms) return;
-  const int e0 = edge_ptr[i], n = edge_ptr[i + 1] - e0;
-  for (int a = lane; a < n; a += 32) {
-    const uint64_t k = key_in[e0 + a];
-    int rank = 0;
-    for (int m = 0; m < n; ++m) rank += key_in[e0 + m] < k ? 1 : 0;
-    const int e = e0 + rank;
-    key[e] = k;
-    dist[e] = dist_in[e0 + a];
-    center[e] = i;
-    neighbor[e] = (int)(k >> 24);
-    image[3 * e + 0] = (int)((k >> 16) & 0xff) - 128;
-    image[3 * e + 1] = (int)((k >> 8) & 0xff) - 128;
-    image[3 * e + 2] = (int)(k & 0xff) - 128;
-  }
-}
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  const int warp_g = (int)(tid >> 5), n_warps = (int)(nth >> 5);
+  const int n_atoms = g.n_atoms, n_cells = g.n_cells;
+  int32_t* const counts = g.counts;
 
-// reverse edge of e = (i, j, n): the edge (j, i, -n), found by binary search in j's segment
-__global__ void k_pair_edges(int n_edges, const int32_t* __restrict__ edge_ptr, const uint64_t* __restrict__ key,
-                             const int32_t* __restrict__ center, int32_t* __restrict__ rev,
-                             int32_t* __restrict__ first_flag, int32_t* __restrict__ status) {
-  int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= n_edges) return;
-  const uint64_t k = key[e];
-  const int i = center[e], j = (int)(k >> 24);
-  const int n0 = (int)((k >> 16) & 0xff) - 128, n1 = (int)((k >> 8) & 0xff) - 128, n2 = (int)(k & 0xff) - 128;
-  const uint64_t want = pack_key(i, -n0, -n1, -n2);
-  int lo = edge_ptr[j], hi = edge_ptr[j + 1];
-  while (lo < hi) {
-    int mid = (lo + hi) >> 1;
-    if (key[mid] < want) lo = mid + 1; else hi = mid;
-  }
-  int r = -1;
-  if (lo < edge_ptr[j + 1] && key[lo] == want) r = lo;
-  if (r < 0) atomicAdd(&status[ST_UNPAIRED], 1);
-  rev[e] = r;
-  first_flag[e] = (r < 0 || r > e) ? 1 : 0;
-}
+  // ---- clear the cell counters and the status block
+  for (int64_t i = tid; i <= n_cells; i += nth) g.cell_ptr[i] = 0;
+  for (int64_t i = tid; i < n_cells; i += nth) g.cell_fill[i] = 0;
+  if (tid < 16) counts[tid] = 0;
+  grid.sync();
 
-__global__ void k_number_bonds(int n_edges, const int32_t* __restrict__ rev, const int32_t* __restrict__ first_rank,
-                               int32_t* __restrict__ d2u, int32_t* __restrict__ u2d) {
-  int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= n_edges) return;
-  const int r = rev[e];
-  const int f = (r >= 0 && r < e) ? r : e;
-  const int u = first_rank[f];
-  d2u[e] = u;
-  if (f == e) u2d[u] = e;
-}
-
-// bit0: the bond of e may be a triplet target (first directed edge's length <= lc)
-// bit1: e may be the source ("other") edge of a triplet (its own length < lc)
-__global__ void k_edge_flags(int n_edges, double lc, const double* __restrict__ dist, const int32_t* __restrict__ rev,
-                             uint8_t* __restrict__ flag) {
-  int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= n_edges) return;
-  const int r = rev[e];
-  const int f = (r >= 0 && r < e) ? r : e;
-  flag[e] = (uint8_t)((dist[f] <= lc ? 1 : 0) | (dist[e] < lc ? 2 : 0));
-}
-
-// per atom: exclusive ranks of source-/target-eligible edges inside the atom's segment
-__global__ void k_edge_ranks(int n_atoms, const int32_t* __restrict__ edge_ptr, const uint8_t* __restrict__ flag,
-                             int32_t* __restrict__ edge_rank, int32_t* __restrict__ atom_counts) {
-  const int lane = threadIdx.x & 31;
-  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (i >= n_atoms) return;
-  const int e0 = edge_ptr[i], e1 = edge_ptr[i + 1];
-  int ns = 0, nt = 0;
-  for (int eb = e0; eb < e1; eb += 32) {
-    const int e = eb + lane;
-    const int f = e < e1 ? flag[e] : 0;
-    const unsigned ms = __ballot_sync(0xffffffffu, f & 2), mt = __ballot_sync(0xffffffffu, f & 1);
-    const unsigned lt = (1u << lane) - 1u;
-    if (e < e1) {
-      edge_rank[2 * e] = ns + __popc(ms & lt);
-      edge_rank[2 * e + 1] = nt + __popc(mt & lt);
-    }
-    ns += __popc(ms);
-    nt += __popc(mt);
-  }
-  if (lane == 0) {
-    atom_counts[2 * i] = ns;
-    atom_counts[2 * i + 1] = nt;
-  }
-}
-
-__global__ void k_bond_counts(int n_bonds, const int32_t* __restrict__ u2d, const int32_t* __restrict__ rev,
-                              const int32_t* __restrict__ center, const uint8_t* __restrict__ flag,
-                              const int32_t* __restrict__ atom_counts, int32_t* __restrict__ tgt_count,
-                              int32_t* __restrict__ src_count) {
-  int u = blockIdx.x * blockDim.x + threadIdx.x;
-  if (u >= n_bonds) return;
-  const int a0 = u2d[u], a1 = rev[a0];
-  int tc = 0, sc = 0;
-  const int a[2] = {a0, a1};
+  // ---- bin the atoms
+  for (int64_t i = tid; i < n_atoms; i += nth) {
+    const int b = g.atom_struct[i];
+    const double* inv = g.inv_lattice + 9 * b;
+    const int32_t* gr = g.grid + 8 * b;
+    const double x = g.cart[3 * i], y = g.cart[3 * i + 1], z = g.cart[3 * i + 2];
+    int c[3], w[3];
 #pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    if (a[s] < 0) continue;
-    const int f = flag[a[s]], c = center[a[s]];
-    if (f & 1) tc += atom_counts[2 * c] - ((f >> 1) & 1);
-    if (f & 2) sc += atom_counts[2 * c + 1] - (f & 1);
+    for (int k = 0; k < 3; ++k) {
+      const double f = x * inv[k] + y * inv[3 + k] + z * inv[6 + k];
+      double fl = floor(f);
+      double fw = f - fl;
+      if (fw >= 1.0) { fw = 0.0; fl += 1.0; }
+      w[k] = (int)fl;
+      const int ck = (int)(fw * (double)gr[k]);
+      c[k] = ck < gr[k] - 1 ? ck : gr[k] - 1;
+      if (c[k] < 0) c[k] = 0;
+    }
+    const int cell = gr[6] + (c[0] * gr[1] + c[1]) * gr[2] + c[2];
+    reinterpret_cast<int4*>(g.atom_cell)[i] = make_int4(c[0], c[1], c[2], cell);
+    reinterpret_cast<int4*>(g.atom_wrap)[i] = make_int4(w[0], w[1], w[2], 0);
+    atomicAdd(&g.cell_ptr[cell], 1);
   }
-  tgt_count[u] = tc;
-  src_count[u] = sc;
-}
+  grid.sync();
+  grid_scan(grid, g.cell_ptr, g.cell_ptr, n_cells, g.scan_tmp);
+  for (int64_t i = tid; i < n_atoms; i += nth) {
+    const int cell = g.atom_cell[4 * i + 3];
+    g.cell_atoms[g.cell_ptr[cell] + atomicAdd(&g.cell_fill[cell], 1)] = (int)i;
+  }
+  grid.sync();
 
-// warp per bond: rows with this bond as target (contiguous), and the ids of the
-// rows that have this bond as source
-__global__ void k_fill_triplets(int n_bonds, const int32_t* __restrict__ edge_ptr, const int32_t* __restrict__ u2d,
-                                const int32_t* __restrict__ rev, const int32_t* __restrict__ center,
-                                const int32_t* __restrict__ d2u, const uint8_t* __restrict__ flag,
-                                const int32_t* __restrict__ edge_rank, const int32_t* __restrict__ atom_counts,
-                                const int32_t* __restrict__ trip_ptr, const int32_t* __restrict__ trip_src_ptr,
-                                int32_t* __restrict__ line_graph, int32_t* __restrict__ src_perm) {
-  const int lane = threadIdx.x & 31;
-  const int u = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (u >= n_bonds) return;
+  // ---- directed edges: count, scan, fill
+  neighbors_of_cells<false>(g, stage);
+  grid.sync();
+  grid_scan(grid, g.edge_ptr, g.edge_ptr, n_atoms, g.scan_tmp);
+  const int ne = g.edge_ptr[n_atoms];
+  if (tid == 0) counts[CT_EDGES] = ne;
+  if (ne > g.cap_edges) {  // the same value in every thread: the whole grid leaves here
+    if (tid == 0) counts[CT_EDGE_CAPACITY] = 1;
+    return;
+  }
+  if (counts[CT_IMAGE_OVERFLOW] || counts[CT_ISOLATED] || ne <= 0 || (ne & 1)) {
+    if (tid == 0 && (ne & 1)) counts[CT_UNPAIRED] = 1;
+    return;
+  }
+  neighbors_of_cells<true>(g, stage);
+  grid.sync();
+
+  // ---- rank sort of each atom's out-edges by key (neighbour, image); warp per atom
+  for (int i = warp_g; i < n_atoms; i += n_warps) {
+    const int e0 = g.edge_ptr[i], n = g.edge_ptr[i + 1] - e0;
+    for (int a = lane; a < n; a += 32) {
+      const uint64_t k = g.key_unsorted[e0 + a];
+      int rank = 0;
+      for (int m = 0; m < n; ++m) rank += g.key_unsorted[e0 + m] < k ? 1 : 0;
+      const int e = e0 + rank;
+      g.key[e] = k;
+      g.dist[e] = g.dist_unsorted[e0 + a];
+      g.center[e] = i;
+      g.neighbor[e] = (int)(k >> 24);
+      g.image[3 * e + 0] = (int)((k >> 16) & 0xff) - 128;
+      g.image[3 * e + 1] = (int)((k >> 8) & 0xff) - 128;
+      g.image[3 * e + 2] = (int)(k & 0xff) - 128;
+    }
+  }
+  grid.sync();
+
+  // ---- reverse edge of e = (i, j, n): the edge (j, i, -n), found by binary search in j's segment
+  // edge_rank doubles as scratch here: [0, ne) first-of-pair flags, [ne, 2 ne + 1) their scan
+  int32_t* const first_flag = g.edge_rank;
+  int32_t* const first_rank = g.edge_rank + ne;
+  for (int64_t e = tid; e < ne; e += nth) {
+    const uint64_t k = g.key[e];
+    const int i = g.center[e], j = (int)(k >> 24);
+    const int n0 = (int)((k >> 16) & 0xff) - 128, n1 = (int)((k >> 8) & 0xff) - 128, n2 = (int)(k & 0xff) - 128;
+    const uint64_t want = pack_key(i, -n0, -n1, -n2);
+    int lo = g.edge_ptr[j], hi = g.edge_ptr[j + 1];
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (g.key[mid] < want) lo = mid + 1; else hi = mid;
+    }
+    int r = -1;
+    if (lo < g.edge_ptr[j + 1] && g.key[lo] == want) r = lo;
+    if (r < 0) atomicAdd(&counts[CT_UNPAIRED], 1);
+    g.rev[e] = r;
+    first_flag[e] = (r < 0 || r > e) ? 1 : 0;
+  }
+  grid.sync();
+  grid_scan(grid, first_flag, first_rank, ne, g.scan_tmp);
+  const int nb = first_rank[ne];
+  if (tid == 0) counts[CT_BONDS] = nb;
+  if (counts[CT_UNPAIRED] || nb * 2 != ne) {
+    if (tid == 0) counts[CT_UNPAIRED] = counts[CT_UNPAIRED] ? counts[CT_UNPAIRED] : 1;
+    return;
+  }
+
+  // ---- bond numbering and triplet eligibility of every directed edge
+  // flag bit0: the bond of e may be a triplet target (first directed edge's length <= lc)
+  //      bit1: e may be the source ("other") edge of a triplet (its own length < lc)
+  for (int64_t e = tid; e < ne; e += nth) {
+    const int r = g.rev[e];
+    const int f = (r >= 0 && r < e) ? r : (int)e;
+    const int u = first_rank[f];
+    g.d2u[e] = u;
+    if (f == e) g.u2d[u] = (int)e;
+    g.edge_flag[e] = (uint8_t)((g.dist[f] <= g.line_cutoff ? 1 : 0) | (g.dist[e] < g.line_cutoff ? 2 : 0));
+  }
+  grid.sync();  // first_rank is dead from here on: edge_rank takes its final meaning
+
+  // ---- per atom: exclusive ranks of source- / target-eligible edges inside the atom's segment
+  for (int i = warp_g; i < n_atoms; i += n_warps) {
+    const int e0 = g.edge_ptr[i], e1 = g.edge_ptr[i + 1];
+    int ns = 0, nt = 0;
+    for (int eb = e0; eb < e1; eb += 32) {
+      const int e = eb + lane;
+      const int f = e < e1 ? g.edge_flag[e] : 0;
+      const unsigned ms = __ballot_sync(0xffffffffu, f & 2), mt = __ballot_sync(0xffffffffu, f & 1);
+      const unsigned lt = (1u << lane) - 1u;
+      if (e < e1) {
+        g.edge_rank[2 * e] = ns + __popc(ms & lt);
+        g.edge_rank[2 * e + 1] = nt + __popc(mt & lt);
+      }
+      ns += __popc(ms);
+      nt += __popc(mt);
+    }
+    if (lane == 0) {
+      g.atom_counts[2 * i] = ns;
+      g.atom_counts[2 * i + 1] = nt;
+    }
+  }
+  grid.sync();
+
+  // ---- triplets per bond, as target and as source
+  int32_t* const tgt_count = g.bond_counts;
+  int32_t* const src_count = g.bond_counts + (nb + 1);
+  for (int64_t u = tid; u < nb; u += nth) {
+    const int a0 = g.u2d[u], a1 = g.rev[a0];
+    int tc = 0, sc = 0;
+    const int a[2] = {a0, a1};
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      if (a[s] < 0) continue;
+      const int f = g.edge_flag[a[s]], c = g.center[a[s]];
+      if (f & 1) tc += g.atom_counts[2 * c] - ((f >> 1) & 1);
+      if (f & 2) sc += g.atom_counts[2 * c + 1] - (f & 1);
+    }
+    tgt_count[u] = tc;
+    src_count[u] = sc;
+  }
+  grid.sync();
+  grid_scan(grid, tgt_count, g.trip_ptr, nb, g.scan_tmp);
+  grid_scan(grid, src_count, g.trip_src_ptr, nb, g.scan_tmp);
+  const int ntr = g.trip_ptr[nb];
+  if (tid == 0) {
+    counts[CT_TRIPLETS] = ntr;
+    counts[CT_TRIPLETS_BY_SOURCE] = g.trip_src_ptr[nb];
+  }
+  if (ntr > g.cap_triplets) {
+    if (tid == 0) counts[CT_TRIPLET_CAPACITY] = 1;
+    return;
+  }
+  if (ntr <= 0) return;
+
+  // ---- warp per bond: rows with this bond as target (contiguous), and the ids of the rows that have it as source
   const unsigned lt = (1u << lane) - 1u;
-  const int a0 = u2d[u], a1 = rev[a0];
-  int t_out = trip_ptr[u], s_out = trip_src_ptr[u];
-  for (int s = 0; s < 2; ++s) {
-    const int a = s == 0 ? a0 : a1;
-    if (a < 0) continue;
-    const int fa = flag[a], c = center[a];
-    const int e0 = edge_ptr[c], e1 = edge_ptr[c + 1];
-    if (fa & 1) {  // target rows (c, u, a, bond(b), b) for b != a with length < lc
-      for (int eb = e0; eb < e1; eb += 32) {
-        const int b = eb + lane;
-        const bool ok = b < e1 && b != a && (flag[b] & 2);
-        const unsigned m = __ballot_sync(0xffffffffu, ok);
-        if (ok) {
-          int32_t* row = line_graph + 5 * (size_t)(t_out + __popc(m & lt));
-          row[0] = c; row[1] = u; row[2] = a; row[3] = d2u[b]; row[4] = b;
+  for (int u = warp_g; u < nb; u += n_warps) {
+    const int a0 = g.u2d[u], a1 = g.rev[a0];
+    int t_out = g.trip_ptr[u], s_out = g.trip_src_ptr[u];
+    for (int s = 0; s < 2; ++s) {
+      const int a = s == 0 ? a0 : a1;
+      if (a < 0) continue;
+      const int fa = g.edge_flag[a], c = g.center[a];
+      const int e0 = g.edge_ptr[c], e1 = g.edge_ptr[c + 1];
+      if (fa & 1) {  // target rows (c, u, a, bond(b), b) for b != a with length < lc
+        for (int eb = e0; eb < e1; eb += 32) {
+          const int b = eb + lane;
+          const bool ok = b < e1 && b != a && (g.edge_flag[b] & 2);
+          const unsigned m = __ballot_sync(0xffffffffu, ok);
+          if (ok) {
+            int32_t* row = g.line_graph + 5 * (size_t)(t_out + __popc(m & lt));
+            row[0] = c; row[1] = u; row[2] = a; row[3] = g.d2u[b]; row[4] = b;
+          }
+          t_out += __popc(m);
         }
-        t_out += __popc(m);
       }
-    }
-    if (fa & 2) {  // rows whose source edge is a: targets t != a at the same centre
-      const int rank_a = edge_rank[2 * a];
-      for (int eb = e0; eb < e1; eb += 32) {
-        const int t = eb + lane;
-        const bool ok = t < e1 && t != a && (flag[t] & 1);
-        const unsigned m = __ballot_sync(0xffffffffu, ok);
-        if (ok) {
-          const int ut = d2u[t], tf = u2d[ut];
-          int side_off = 0;
-          if (t != tf) side_off = atom_counts[2 * center[tf]] - ((flag[tf] >> 1) & 1);
-          const int row = trip_ptr[ut] + side_off + rank_a - ((t < a && (flag[t] & 2)) ? 1 : 0);
-          src_perm[s_out + __popc(m & lt)] = row;
+      if (fa & 2) {  // rows whose source edge is a: targets t != a at the same centre
+        const int rank_a = g.edge_rank[2 * a];
+        for (int eb = e0; eb < e1; eb += 32) {
+          const int t = eb + lane;
+          const bool ok = t < e1 && t != a && (g.edge_flag[t] & 1);
+          const unsigned m = __ballot_sync(0xffffffffu, ok);
+          if (ok) {
+            const int ut = g.d2u[t], tf = g.u2d[ut];
+            int side_off = 0;
+            if (t != tf) side_off = g.atom_counts[2 * g.center[tf]] - ((g.edge_flag[tf] >> 1) & 1);
+            const int row = g.trip_ptr[ut] + side_off + rank_a - ((t < a && (g.edge_flag[t] & 2)) ? 1 : 0);
+            g.trip_src_perm[s_out + __popc(m & lt)] = row;
+          }
+          s_out += __popc(m);
         }
-        s_out += __popc(m);
       }
     }
   }
 }
 
 static int check_graph(const mb_graph* g) {
-  if (!g || g->n_atoms <= 0 || g->n_struct <= 0 || g->n_cells <= 0) return MB_ERR_INVALID;
-  if (!g->cart || !g->lattice || !g->inv_lattice || !g->atom_struct || !g->grid) return MB_ERR_INVALID;
+  if (!g || g->n_atoms <= 0 || g->n_struct <= 0 || g->n_cells <= 0 || g->cap_edges < 2 || g->cap_triplets < 0)
+    return MB_ERR_INVALID;
+  if (!g->cart || !g->lattice || !g->inv_lattice || !g->atom_struct || !g->grid || !g->counts) return MB_ERR_INVALID;
   if (!g->cell_ptr || !g->cell_fill || !g->cell_atoms || !g->atom_cell || !g->atom_wrap || !g->scan_tmp ||
-      !g->status || !g->edge_ptr)
+      !g->edge_ptr || !g->key_unsorted || !g->dist_unsorted || !g->key || !g->atom_counts || !g->edge_rank ||
+      !g->bond_counts || !g->edge_flag)
+    return MB_ERR_INVALID;
+  if (!g->center || !g->neighbor || !g->image || !g->dist || !g->rev || !g->d2u || !g->u2d || !g->trip_ptr ||
+      !g->trip_src_ptr || (g->cap_triplets > 0 && (!g->line_graph || !g->trip_src_perm)))
     return MB_ERR_INVALID;
   return MB_OK;
 }
@@ -422,100 +503,35 @@ using namespace mb;
 
 extern "C" size_t mb_graph_scan_tmp_len(int64_t n) { return (size_t)(n / SCAN_CHUNK + 4); }
 
-extern "C" int mb_graph_count_edges(mb_graph* g, void* stream_) {
-  cudaStream_t s = (cudaStream_t)stream_;
+extern "C" int mb_graph_build(const mb_graph* g, void* stream_) {
   int rc = check_graph(g);
   if (rc) return rc;
-  const int n = g->n_atoms, tb = 128;
-  MB_CUDA_CHECK(cudaMemsetAsync(g->cell_ptr, 0, sizeof(int32_t) * (size_t)(g->n_cells + 1), s));
-  MB_CUDA_CHECK(cudaMemsetAsync(g->cell_fill, 0, sizeof(int32_t) * (size_t)g->n_cells, s));
-  MB_CUDA_CHECK(cudaMemsetAsync(g->status, 0, sizeof(int32_t) * 8, s));
-  k_bin_count<<<cdiv(n, tb), tb, 0, s>>>(n, g->cart, g->inv_lattice, g->atom_struct, g->grid, g->atom_cell,
-                                         g->atom_wrap, g->cell_ptr);
-  MB_LAUNCH_CHECK("k_bin_count");
-  rc = scan_exclusive(g->cell_ptr, g->cell_ptr, g->n_cells, g->scan_tmp, s);
-  if (rc) return rc;
-  k_bin_fill<<<cdiv(n, tb), tb, 0, s>>>(n, g->atom_cell, g->cell_ptr, g->cell_fill, g->cell_atoms);
-  k_neighbors<false><<<cdiv((long long)n * 32, tb), tb, 0, s>>>(
-      n, g->cutoff, g->tol, g->cart, g->lattice, g->atom_struct, g->grid, g->atom_cell, g->atom_wrap, g->cell_ptr,
-      g->cell_atoms, g->edge_ptr, nullptr, nullptr, g->status);
-  MB_LAUNCH_CHECK("k_neighbors<count>");
-  rc = scan_exclusive(g->edge_ptr, g->edge_ptr, n, g->scan_tmp, s);
-  if (rc) return rc;
-  int32_t total = 0, st[8];
-  MB_CUDA_CHECK(cudaMemcpyAsync(&total, g->edge_ptr + n, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-  MB_CUDA_CHECK(cudaMemcpyAsync(st, g->status, sizeof(st), cudaMemcpyDeviceToHost, s));
-  MB_CUDA_CHECK(cudaStreamSynchronize(s));
-  if (total < 0) return MB_ERR_OVERFLOW;
-  g->n_edges = total;
-  if (st[ST_ISOLATED]) return MB_ERR_ISOLATED;
+  // as many CTAs as the device keeps resident at once (a cooperative launch requires it); per device
+  static int grid_of_device[64];
+  int dev = 0;
+  MB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return MB_ERR_INVALID;
+  if (grid_of_device[dev] == 0) {
+    int n_sm = 0, per_sm = 0;
+    MB_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    MB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_graph_build, GB_THREADS, 0));
+    if (per_sm < 1) return MB_ERR_CUDA;
+    grid_of_device[dev] = n_sm * (per_sm < 4 ? per_sm : 4);
+  }
+  mb_graph arg = *g;
+  void* params[] = {&arg};
+  MB_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)k_graph_build, dim3(grid_of_device[dev]), dim3(GB_THREADS),
+                                            params, 0, (cudaStream_t)stream_));
   return MB_OK;
 }
 
-extern "C" int mb_graph_build_edges(mb_graph* g, void* stream_) {
-  cudaStream_t s = (cudaStream_t)stream_;
-  int rc = check_graph(g);
-  if (rc) return rc;
-  const int n = g->n_atoms, ne = g->n_edges, tb = 128;
-  if (ne <= 0 || (ne & 1)) return ne <= 0 ? MB_ERR_INVALID : MB_ERR_UNPAIRED;
-  if (!g->key_unsorted || !g->dist_unsorted || !g->key || !g->atom_counts || !g->edge_rank || !g->bond_counts ||
-      !g->edge_flag || !g->center || !g->neighbor || !g->image || !g->dist || !g->rev || !g->d2u || !g->u2d ||
-      !g->trip_ptr || !g->trip_src_ptr)
-    return MB_ERR_INVALID;
-  k_neighbors<true><<<cdiv((long long)n * 32, tb), tb, 0, s>>>(
-      n, g->cutoff, g->tol, g->cart, g->lattice, g->atom_struct, g->grid, g->atom_cell, g->atom_wrap, g->cell_ptr,
-      g->cell_atoms, g->edge_ptr, g->key_unsorted, g->dist_unsorted, g->status);
-  MB_LAUNCH_CHECK("k_neighbors<fill>");
-  k_sort_edges<<<cdiv((long long)n * 32, tb), tb, 0, s>>>(n, g->edge_ptr, g->key_unsorted, g->dist_unsorted, g->key,
-                                                         g->dist, g->center, g->neighbor, g->image);
-  // edge_rank doubles as scratch here: [0, ne) first-of-pair flags, [ne, 2ne+1) their scan
-  int32_t* first_flag = g->edge_rank;
-  int32_t* first_rank = g->edge_rank + ne;
-  k_pair_edges<<<cdiv(ne, tb), tb, 0, s>>>(ne, g->edge_ptr, g->key, g->center, g->rev, first_flag, g->status);
-  MB_LAUNCH_CHECK("k_pair_edges");
-  rc = scan_exclusive(first_flag, first_rank, ne, g->scan_tmp, s);
-  if (rc) return rc;
-  int32_t nb = 0, st[8];
-  MB_CUDA_CHECK(cudaMemcpyAsync(&nb, first_rank + ne, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-  MB_CUDA_CHECK(cudaMemcpyAsync(st, g->status, sizeof(st), cudaMemcpyDeviceToHost, s));
-  MB_CUDA_CHECK(cudaStreamSynchronize(s));
-  if (st[ST_IMAGE_OVERFLOW]) return MB_ERR_OVERFLOW;
-  if (st[ST_UNPAIRED] || nb * 2 != ne) return MB_ERR_UNPAIRED;
-  g->n_bonds = nb;
-  k_number_bonds<<<cdiv(ne, tb), tb, 0, s>>>(ne, g->rev, first_rank, g->d2u, g->u2d);
-  k_edge_flags<<<cdiv(ne, tb), tb, 0, s>>>(ne, g->line_cutoff, g->dist, g->rev, g->edge_flag);
-  MB_LAUNCH_CHECK("k_edge_flags");
-  // first_rank is dead from here on: edge_rank takes its final meaning
-  k_edge_ranks<<<cdiv((long long)n * 32, tb), tb, 0, s>>>(n, g->edge_ptr, g->edge_flag, g->edge_rank, g->atom_counts);
-  int32_t* tgt_count = g->bond_counts;
-  int32_t* src_count = g->bond_counts + (nb + 1);
-  k_bond_counts<<<cdiv(nb, tb), tb, 0, s>>>(nb, g->u2d, g->rev, g->center, g->edge_flag, g->atom_counts, tgt_count,
-                                            src_count);
-  MB_LAUNCH_CHECK("k_bond_counts");
-  rc = scan_exclusive(tgt_count, g->trip_ptr, nb, g->scan_tmp, s);
-  if (rc) return rc;
-  rc = scan_exclusive(src_count, g->trip_src_ptr, nb, g->scan_tmp, s);
-  if (rc) return rc;
-  int32_t nt = 0, nt2 = 0;
-  MB_CUDA_CHECK(cudaMemcpyAsync(&nt, g->trip_ptr + nb, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-  MB_CUDA_CHECK(cudaMemcpyAsync(&nt2, g->trip_src_ptr + nb, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-  MB_CUDA_CHECK(cudaStreamSynchronize(s));
-  if (nt < 0) return MB_ERR_OVERFLOW;
-  if (nt != nt2) return MB_ERR_INVALID;
-  g->n_triplets = nt;
-  return MB_OK;
-}
-
-extern "C" int mb_graph_build_triplets(mb_graph* g, void* stream_) {
-  cudaStream_t s = (cudaStream_t)stream_;
-  int rc = check_graph(g);
-  if (rc) return rc;
-  if (g->n_triplets == 0) return MB_OK;
-  if (!g->line_graph || !g->trip_src_perm || g->n_bonds <= 0) return MB_ERR_INVALID;
-  const int tb = 128;
-  k_fill_triplets<<<cdiv((long long)g->n_bonds * 32, tb), tb, 0, s>>>(
-      g->n_bonds, g->edge_ptr, g->u2d, g->rev, g->center, g->d2u, g->edge_flag, g->edge_rank, g->atom_counts,
-      g->trip_ptr, g->trip_src_ptr, g->line_graph, g->trip_src_perm);
-  MB_LAUNCH_CHECK("k_fill_triplets");
+extern "C" int mb_graph_status(const int32_t* counts_host) {
+  if (!counts_host) return MB_ERR_INVALID;
+  if (counts_host[CT_IMAGE_OVERFLOW]) return MB_ERR_OVERFLOW;
+  if (counts_host[CT_ISOLATED]) return MB_ERR_ISOLATED;
+  if (counts_host[CT_EDGES] < 0 || counts_host[CT_TRIPLETS] < 0) return MB_ERR_OVERFLOW;
+  if (counts_host[CT_EDGE_CAPACITY] || counts_host[CT_TRIPLET_CAPACITY]) return MB_ERR_CAPACITY;
+  if (counts_host[CT_UNPAIRED]) return MB_ERR_UNPAIRED;
+  if (counts_host[CT_TRIPLETS] != counts_host[CT_TRIPLETS_BY_SOURCE]) return MB_ERR_INVALID;
   return MB_OK;
 }

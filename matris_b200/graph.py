@@ -173,59 +173,96 @@ def upload(hb: HostBatch, cutoff, line_cutoff, device) -> BatchedGraph:
     return g
 
 
+def _capacity_estimate(g: BatchedGraph) -> tuple[int, int]:
+    """First guess of the edge / triplet capacities from the number density of every structure (neighbours inside a
+    sphere; triplets = ordered pairs of short bonds per atom), with a margin.  A guess that turns out too small costs
+    one more launch with the exact sizes."""
+    n = np.asarray(g.atoms_per_graph, dtype=np.float64)
+    lat = g.lattice64_host
+    vol = np.abs(np.einsum("bi,bi->b", lat[:, 0], np.cross(lat[:, 1], lat[:, 2])))
+    rho = n / vol
+    nbr = 4.0 / 3.0 * np.pi * g.cutoff ** 3 * rho
+    short = 4.0 / 3.0 * np.pi * g.line_cutoff ** 3 * rho
+    edges = float((n * nbr).sum())
+    trips = float((n * short * np.maximum(short - 1.0, 0.0)).sum())
+    return int(1.25 * edges) + 1024, int(1.5 * trips) + 4096
+
+
+class _GraphBuffers:
+    """Capacity buffers of one batch: outputs and scratch of mb_graph_build, kept across rebuilds of the same batch
+    (an MD or relaxation loop rebuilds the graph of the same atoms every step)."""
+
+    def __init__(self, g: BatchedGraph, cap_e: int, cap_t: int, device):
+        lib = _lib.load()
+        cap_e += cap_e & 1
+        n_atoms, n_cells = g.n_atoms, g.n_cells
+        self.cap_e, self.cap_t = cap_e, cap_t
+        i64 = lambda n: torch.empty(max(int(n), 1), dtype=torch.int64, device=device)  # noqa: E731
+        self.scratch = dict(
+            cell_ptr=_i32(n_cells + 1, device), cell_fill=_i32(n_cells, device), cell_atoms=_i32(n_atoms, device),
+            atom_cell=_i32(4 * n_atoms, device), atom_wrap=_i32(4 * n_atoms, device),
+            scan_tmp=_i32(lib.mb_graph_scan_tmp_len(max(n_atoms, n_cells, cap_e)), device),
+            key_unsorted=i64(cap_e), dist_unsorted=torch.empty(cap_e, dtype=torch.float64, device=device),
+            key=i64(cap_e), atom_counts=_i32(2 * n_atoms, device), edge_rank=_i32(2 * cap_e + 2, device),
+            bond_counts=_i32(cap_e + 4, device), edge_flag=torch.empty(cap_e, dtype=torch.uint8, device=device))
+        self.out = dict(
+            edge_ptr=_i32(n_atoms + 1, device), center=_i32(cap_e, device), neighbor=_i32(cap_e, device),
+            image=_i32(3 * cap_e, device), dist=torch.empty(cap_e, dtype=torch.float64, device=device),
+            rev=_i32(cap_e, device), d2u=_i32(cap_e, device), u2d=_i32(cap_e // 2, device),
+            trip_ptr=_i32(cap_e // 2 + 1, device), trip_src_ptr=_i32(cap_e // 2 + 1, device),
+            line_graph=_i32(5 * cap_t, device), trip_src_perm=_i32(cap_t, device))
+        self.counts = torch.zeros(16, dtype=torch.int32, device=device)
+        self.counts_host = torch.zeros(16, dtype=torch.int32).pin_memory()
+
+
 def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None) -> BatchedGraph:
-    """Run the three graph phases on the device-resident inputs of ``g`` (positions, lattices, cell grid)
-    and attach the outputs.  Can be called again after ``g.cart64`` changed on the device."""
+    """Build the graph of the device-resident inputs of ``g`` (positions, lattices, cell grid) and attach the outputs.
+    Can be called again after ``g.cart64`` changed on the device: the capacity buffers of the previous build are
+    reused.  One asynchronous launch (mb_graph_build) and one copy of the 16-int status block to the host, which is
+    the only synchronisation: the sizes of the model's tensors depend on the counts in it."""
     lib = _lib.load()
     device = g.cart64.device
     n_atoms, n_struct, n_cells = g.n_atoms, g.n_struct, g.n_cells
     with torch.cuda.device(device):
         st = torch.cuda.current_stream().cuda_stream if stream is None else stream
-        m = _lib.MbGraph()
-        m.n_atoms, m.n_struct, m.n_cells = n_atoms, n_struct, n_cells
-        m.cutoff, m.line_cutoff, m.tol = g.cutoff, g.line_cutoff, float(tol)
-        m.cart, m.lattice, m.inv_lattice = g.cart64.data_ptr(), g.lattice64.data_ptr(), g.inv_lattice64.data_ptr()
-        m.atom_struct, m.grid = g.atom_struct.data_ptr(), g.grid.data_ptr()
-        scr = dict(cell_ptr=_i32(n_cells + 1, device), cell_fill=_i32(n_cells, device), cell_atoms=_i32(n_atoms, device),
-                   atom_cell=_i32(4 * n_atoms, device), atom_wrap=_i32(4 * n_atoms, device), status=_i32(8, device),
-                   scan_tmp=_i32(lib.mb_graph_scan_tmp_len(max(n_atoms, n_cells)), device))
-        g.edge_ptr = _i32(n_atoms + 1, device)
-        for k, v in scr.items():
-            setattr(m, k, v.data_ptr())
-        m.edge_ptr = g.edge_ptr.data_ptr()
-        _lib.call("mb_graph_count_edges", C.byref(m), st)
-        ne = int(m.n_edges)
-        if ne <= 0 or ne % 2:
-            raise _lib.MbError(f"graph build produced {ne} directed edges")
-        scr2 = dict(scan_tmp=_i32(lib.mb_graph_scan_tmp_len(ne), device),
-                    key_unsorted=torch.empty(ne, dtype=torch.int64, device=device),
-                    dist_unsorted=torch.empty(ne, dtype=torch.float64, device=device),
-                    key=torch.empty(ne, dtype=torch.int64, device=device),
-                    atom_counts=_i32(2 * n_atoms, device), edge_rank=_i32(2 * ne + 2, device),
-                    bond_counts=_i32(ne + 4, device), edge_flag=torch.empty(ne, dtype=torch.uint8, device=device))
-        for k, v in scr2.items():
-            setattr(m, k, v.data_ptr())
-        g.center, g.neighbor, g.image = _i32(ne, device), _i32(ne, device), _i32(3 * ne, device).view(ne, 3)
-        g.dist64 = torch.empty(ne, dtype=torch.float64, device=device)
-        g.rev, g.d2u, g.u2d = _i32(ne, device), _i32(ne, device), _i32(ne // 2, device)
-        g.trip_ptr, g.trip_src_ptr = _i32(ne // 2 + 1, device), _i32(ne // 2 + 1, device)
-        for k in ("center", "neighbor", "image", "rev", "d2u", "u2d", "trip_ptr", "trip_src_ptr"):
-            setattr(m, k, getattr(g, k).data_ptr())
-        m.dist = g.dist64.data_ptr()
-        _lib.call("mb_graph_build_edges", C.byref(m), st)
-        g.n_edges, g.n_bonds, nt = ne, int(m.n_bonds), int(m.n_triplets)
-        g.n_triplets = nt
-        g.line_graph = _i32(5 * nt, device).view(-1, 5)[:nt]
-        g.trip_src_perm = _i32(nt, device)[:nt]
-        if nt:
-            m.line_graph, m.trip_src_perm = g.line_graph.data_ptr(), g.trip_src_perm.data_ptr()
-            _lib.call("mb_graph_build_triplets", C.byref(m), st)
-            # column-major copy: each of (centre atom, target bond, target DE, source bond, source DE) contiguous
-            g.lg_cols = g.line_graph.t().contiguous()
-        else:
-            g.lg_cols = torch.empty(5, 0, dtype=torch.int32, device=device)
-        # the scratch tensors were used on this stream only, so the caching allocator may reuse them in order
-        del scr, scr2
+        buf = getattr(g, "_buffers", None)
+        if buf is None:
+            buf = g._buffers = _GraphBuffers(g, *_capacity_estimate(g), device)
+        for attempt in range(4):
+            m = _lib.MbGraph()
+            m.n_atoms, m.n_struct, m.n_cells = n_atoms, n_struct, n_cells
+            m.cap_edges, m.cap_triplets = buf.cap_e, buf.cap_t
+            m.cutoff, m.line_cutoff, m.tol = g.cutoff, g.line_cutoff, float(tol)
+            m.cart, m.lattice, m.inv_lattice = g.cart64.data_ptr(), g.lattice64.data_ptr(), g.inv_lattice64.data_ptr()
+            m.atom_struct, m.grid = g.atom_struct.data_ptr(), g.grid.data_ptr()
+            for k, v in buf.scratch.items():
+                setattr(m, k, v.data_ptr())
+            for k, v in buf.out.items():
+                setattr(m, k, v.data_ptr())
+            m.counts = buf.counts.data_ptr()
+            _lib.call("mb_graph_build", C.byref(m), st)
+            buf.counts_host.copy_(buf.counts, non_blocking=True)
+            torch.cuda.current_stream().synchronize() if stream is None else torch.cuda.synchronize()
+            counts = buf.counts_host.numpy()
+            status = lib.mb_graph_status(counts.ctypes.data_as(C.POINTER(C.c_int32)))
+            if status != _lib.MB_ERR_CAPACITY:
+                break
+            # enlarge to what this build needed (plus a margin for the steps to come) and run it again
+            cap_e = max(buf.cap_e, int(1.1 * counts[0]) + 64)
+            cap_t = int(1.1 * counts[2]) + 64 if counts[7] else max(buf.cap_t, int(1.5 * buf.cap_t * cap_e / buf.cap_e))
+            buf = g._buffers = _GraphBuffers(g, cap_e, cap_t, device)
+        _lib.check(status, "mb_graph_build")
+        ne, nb, nt = int(counts[0]), int(counts[1]), int(counts[2])
+        g.n_edges, g.n_bonds, g.n_triplets = ne, nb, nt
+        o = buf.out
+        g.edge_ptr = o["edge_ptr"]
+        g.center, g.neighbor, g.image = o["center"][:ne], o["neighbor"][:ne], o["image"][:3 * ne].view(ne, 3)
+        g.dist64, g.rev, g.d2u, g.u2d = o["dist"][:ne], o["rev"][:ne], o["d2u"][:ne], o["u2d"][:nb]
+        g.trip_ptr, g.trip_src_ptr = o["trip_ptr"][:nb + 1], o["trip_src_ptr"][:nb + 1]
+        g.line_graph = o["line_graph"][:5 * nt].view(nt, 5)
+        g.trip_src_perm = o["trip_src_perm"][:nt]
+        # column-major copy: each of (centre atom, target bond, target DE, source bond, source DE) contiguous
+        g.lg_cols = g.line_graph.t().contiguous() if nt else torch.empty(5, 0, dtype=torch.int32, device=device)
     g._row_graphs = g._slices = None
     return g
 

@@ -120,3 +120,36 @@ def test_converter_single_structure_reference_layout():
     assert rg.atom_frac_coord.dtype == torch.float32 and rg.lattice.shape == (3, 3)
     assert np.array_equal(rg.line_graph.cpu().numpy(), o["line_graph"])
     assert rg.to("cuda").atom_graph.is_cuda
+
+
+def test_capacity_too_small_is_reported_and_retried():
+    """Undersized edge / triplet buffers: the builder reports the sizes it needed in the device status block, the host
+    enlarges the buffers and runs it again; the result is the same graph.  Rebuilding after the positions changed on
+    the device reuses the buffers."""
+    from matris_b200 import graph as G
+    crystals = workloads.random_crystals(6, seed=2)
+    ref = check_batch(crystals)
+    hb = G.HostBatch([c.numbers for c in crystals], [c.cart for c in crystals], [c.lattice for c in crystals], 6.0)
+    g = G.upload(hb, 6.0, 4.0, torch.device("cuda"))
+    g._buffers = G._GraphBuffers(g, 64, 8, g.cart64.device)  # far too small on purpose
+    G.build_on_device(g)
+    assert (g.n_edges, g.n_bonds, g.n_triplets) == (ref.n_edges, ref.n_bonds, ref.n_triplets)
+    assert g._buffers.cap_e >= g.n_edges and g._buffers.cap_t >= g.n_triplets
+    for k in ("center", "neighbor", "image", "rev", "d2u", "u2d", "line_graph", "trip_src_perm", "trip_ptr"):
+        assert torch.equal(getattr(g, k), getattr(ref, k)), k
+    buffers = g._buffers
+    g.cart64 += 0.01
+    G.build_on_device(g)
+    assert g._buffers is buffers and g.n_edges > 0
+
+
+def test_periodic_image_beyond_the_packed_range_is_an_error_before_anything_is_paired():
+    """An atom that has drifted more than 127 cell lengths away from its neighbours (unwrapped coordinates in a long
+    run): the image index does not fit the packed key.  The counting pass reports it and the build stops there."""
+    from matris_b200._lib import MbError
+    from matris_b200.graph import build_batched_graph
+    cr = workloads.cu_fcc(reps=(1, 1, 1), sigma=0.0)
+    cart = cr.cart.copy()
+    cart[0] += 200 * cr.lattice[0]
+    with pytest.raises(MbError, match="out of range"):
+        build_batched_graph([cr.numbers], [cart], [cr.lattice])
