@@ -103,6 +103,8 @@ class MatRISCalculator(_AseCalculator):
             stress=None if stress is None else stress * self.stress_unit,
             magmoms=get("m"),
         )
+        # the copies above synchronised the stream: a bounded wait that expired in this evaluation is known now
+        self.model.check_status()
 
     # convenience for ASE-free use
     def get_property_dict(self, atoms) -> dict:
@@ -338,7 +340,7 @@ def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, 
     norms) come back to the host for the FIRE decisions, and the full state only when the observer logs."""
     import torch
 
-    from .graph import build_on_device
+    from .graph import build_on_device, set_positions_on_device
 
     calc = atoms.calc
     model, task = calc.model, calc.task
@@ -356,8 +358,7 @@ def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, 
     it, out = 0, None
     for it in range(steps):
         if it > 0:
-            g.cart64.copy_(x)
-            g.cart32.copy_(x)
+            set_positions_on_device(g, x)
             build_on_device(g)
         out = model(g, task=task)
         f = out["f"][0].to(torch.float64)
@@ -386,8 +387,7 @@ def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, 
             step = step * (max_step / norm)
         x = x + step
     # the loop ended on the step limit: evaluate the final positions so that the stored results match them
-    g.cart64.copy_(x)
-    g.cart32.copy_(x)
+    set_positions_on_device(g, x)
     build_on_device(g)
     push_state(model(g, task=task))
     return steps
@@ -543,7 +543,7 @@ class MolecularDynamics:
         only."""
         import torch
 
-        from .graph import build_on_device
+        from .graph import build_on_device, set_positions_on_device
 
         a, calc = self.atoms, self.atoms.calc
         model, task = calc.model, calc.task
@@ -571,8 +571,7 @@ class MolecularDynamics:
                 x = x + 0.5 * dt * p / m
             else:
                 x = x + dt * p / m
-            g.cart64.copy_(x)
-            g.cart32.copy_(x)
+            set_positions_on_device(g, x)
             build_on_device(g)
             out = model(g, task=task)
             f = out["f"][0].to(torch.float64)

@@ -9,8 +9,8 @@
 // count stays on the device (counts[]), the outputs go into caller-supplied capacity buffers, and a capacity that
 // turns out too small is reported in counts[] (the caller enlarges the buffer and calls again).
 //
-//   bin atoms into cells -> per-atom neighbour count (one CTA per cell: the home cell's atoms and each neighbouring
-//   cell's atoms are staged in shared memory, ballot compaction) -> scan -> fill -> per-atom rank sort by
+//   bin atoms into cells -> per-atom neighbour count (warp per atom in cell order; the atoms of each visited cell
+//   pass through a shared-memory stage, ballot compaction) -> scan -> fill -> per-atom rank sort by
 //   (neighbour, image) -> reverse-edge
 //   search (binary search inside the neighbour's own segment) -> bond numbering (scan of "first of its pair" flags)
 //   -> per-bond triplet counts -> scans -> triplet fill grouped by target bond + permutation grouped by source bond.
@@ -21,7 +21,7 @@ namespace cg = cooperative_groups;
 
 namespace mb {
 
-constexpr int GB_THREADS = 256;
+constexpr int GB_THREADS = 1024;  // one CTA per SM: a grid-wide barrier costs less the fewer CTAs take part
 constexpr int SCAN_ITEMS = 8;  // per thread
 constexpr int SCAN_CHUNK = GB_THREADS * SCAN_ITEMS;
 
@@ -62,57 +62,71 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
 }
 
 // Exclusive scan of in[0..n) into out[0..n], out[n] = total; in may alias out; n is the same in every thread.
-// Three steps separated by grid barriers: per-chunk sums, scan of the chunk sums by one block, apply.
-__device__ void grid_scan(cg::grid_group& grid, const int32_t* in, int32_t* out, int64_t n, int32_t* tmp) {
+// Two steps separated by a grid barrier: per-chunk sums, then every block adds up the sums of the chunks in front of
+// its own (a few thousand values at most) and applies them.  A second array can ride along (in2 / out2, same n).
+__device__ void grid_scan(cg::grid_group& grid, const int32_t* in, int32_t* out, int64_t n, int32_t* tmp,
+                          const int32_t* in2 = nullptr, int32_t* out2 = nullptr) {
   const int n_chunks = (int)((n + SCAN_CHUNK - 1) / SCAN_CHUNK);
+  int32_t* const tmp2 = tmp + n_chunks;
   for (int ch = blockIdx.x; ch < n_chunks; ch += gridDim.x) {
     const int64_t base = (int64_t)ch * SCAN_CHUNK + (int64_t)threadIdx.x * SCAN_ITEMS;
-    int s = 0;
+    int s = 0, s2 = 0;
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; ++k)
-      if (base + k < n) s += in[base + k];
+      if (base + k < n) {
+        s += in[base + k];
+        if (in2) s2 += in2[base + k];
+      }
     int total;
     block_exclusive_scan(s, &total);
     if (threadIdx.x == 0) tmp[ch] = total;
+    if (in2) {
+      block_exclusive_scan(s2, &total);
+      if (threadIdx.x == 0) tmp2[ch] = total;
+    }
   }
-  grid.sync();
-  if (blockIdx.x == 0) {
-    __shared__ int carry;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
-    for (int base = 0; base < n_chunks; base += GB_THREADS) {
-      const int i = base + threadIdx.x;
-      const int v = i < n_chunks ? tmp[i] : 0;
-      int total;
-      const int p = block_exclusive_scan(v, &total);
-      if (i < n_chunks) tmp[i] = carry + p;
-      __syncthreads();
-      if (threadIdx.x == 0) carry += total;
-      __syncthreads();
-    }
-    if (threadIdx.x == 0) {
-      tmp[n_chunks] = carry;
-      if (n_chunks == 0) out[0] = 0;
-    }
+  if (n_chunks == 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+    out[0] = 0;
+    if (out2) out2[0] = 0;
   }
   grid.sync();
   for (int ch = blockIdx.x; ch < n_chunks; ch += gridDim.x) {
+    // sum of the chunk totals in front of this chunk
+    int part = 0, part2 = 0;
+    for (int i = threadIdx.x; i < ch; i += GB_THREADS) {
+      part += tmp[i];
+      if (in2) part2 += tmp2[i];
+    }
+    int offset, offset2 = 0, dummy;
+    block_exclusive_scan(part, &offset);
+    if (in2) block_exclusive_scan(part2, &offset2);
     const int64_t base = (int64_t)ch * SCAN_CHUNK + (int64_t)threadIdx.x * SCAN_ITEMS;
-    int v[SCAN_ITEMS];
-    int s = 0;
+    int v[SCAN_ITEMS], v2[SCAN_ITEMS];
+    int s = 0, s2 = 0;
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; ++k) {
       v[k] = base + k < n ? in[base + k] : 0;
+      v2[k] = (in2 && base + k < n) ? in2[base + k] : 0;
       s += v[k];
+      s2 += v2[k];
     }
-    int total;
-    int p = block_exclusive_scan(s, &total) + tmp[ch];
+    int total, total2 = 0;
+    int p = block_exclusive_scan(s, &total) + offset;
+    int p2 = in2 ? block_exclusive_scan(s2, &total2) + offset2 : 0;
+    (void)dummy;
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; ++k) {
-      if (base + k < n) out[base + k] = p;
+      if (base + k < n) {
+        out[base + k] = p;
+        if (in2) out2[base + k] = p2;
+      }
       p += v[k];
+      p2 += v2[k];
     }
-    if (ch == n_chunks - 1 && threadIdx.x == 0) out[n] = tmp[n_chunks];
+    if (ch == n_chunks - 1 && threadIdx.x == 0) {
+      out[n] = offset + total;
+      if (in2) out2[n] = offset2 + total2;
+    }
   }
   grid.sync();
 }
@@ -128,145 +142,115 @@ __device__ __forceinline__ uint64_t pack_key(int j, int n0, int n1, int n2) {
          ((uint64_t)(uint32_t)(n1 + 128) << 8) | (uint64_t)(uint32_t)(n2 + 128);
 }
 
-// Neighbour search, one CTA per cell of the cell list.  The atoms of the home cell (in chunks of HOME_MAX) and, for
-// every neighbouring cell inside the search range, that cell's atoms (in chunks of CAND_MAX) are staged in shared
-// memory once per CTA; warp w then takes home atoms w, w + 8, ... and its lanes test 32 staged candidates per
-// round.  FILL = false counts (edge_ptr[i] = number of neighbours of atom i), FILL = true writes packed keys and
-// distances from edge_ptr[i] on.  Both passes walk the candidates in the same order.
-constexpr int HOME_MAX = 64, CAND_MAX = 128;
-
-struct NeighborStage {
-  int home_id[HOME_MAX];
-  int4 home_wrap[HOME_MAX];
-  double home_x[HOME_MAX], home_y[HOME_MAX], home_z[HOME_MAX];
-  int home_count[HOME_MAX];
-  int cand_id[CAND_MAX];
-  int4 cand_wrap[CAND_MAX];
-  double cand_x[CAND_MAX], cand_y[CAND_MAX], cand_z[CAND_MAX];
+// Neighbour search of one atom by one warp.  The atoms of a visited cell pass through a per-warp shared-memory
+// stage, 32 at a time (index, wrap count and position: one coalesced fetch per round, then every lane tests one
+// staged candidate); atoms are taken in cell order, so the warps of a CTA work on neighbouring atoms and their
+// fetches hit the same lines.  FILL = false counts (edge_ptr[i] = number of neighbours of atom i), FILL = true
+// writes packed keys and distances from edge_ptr[i] on.  Both passes walk the candidates in the same order.
+struct CellStage {
+  int j[32];
+  int4 wrap[32];
+  double x[32], y[32], z[32];
 };
 
 template <bool FILL>
-__device__ void neighbors_of_cells(const mb_graph& g, NeighborStage& st) {
-  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const double cutoff = g.cutoff, tol = g.tol;
-  for (int cell = blockIdx.x; cell < g.n_cells; cell += gridDim.x) {
-    const int hp0 = g.cell_ptr[cell], hp1 = g.cell_ptr[cell + 1];  // home atoms (block-uniform)
-    if (hp1 == hp0) continue;
-    const int first = g.cell_atoms[hp0];
-    const int b = g.atom_struct[first];
-    const int32_t* gr = g.grid + 8 * b;
-    const int g0 = gr[0], g1 = gr[1], g2 = gr[2], s0 = gr[3], s1 = gr[4], s2 = gr[5], base = gr[6];
-    const int4 ci = reinterpret_cast<const int4*>(g.atom_cell)[first];  // cell coordinates: the same for all home atoms
-    double L[9];
+__device__ __forceinline__ void neighbors_of_atom(const mb_graph& g, int i, int lane, CellStage& st) {
+  const int b = g.atom_struct[i];
+  const int32_t* gr = g.grid + 8 * b;
+  const int g0 = gr[0], g1 = gr[1], g2 = gr[2], s0 = gr[3], s1 = gr[4], s2 = gr[5], base = gr[6];
+  double L[9];
 #pragma unroll
-    for (int k = 0; k < 9; ++k) L[k] = g.lattice[9 * b + k];
-    for (int hb = hp0; hb < hp1; hb += HOME_MAX) {
-      const int n_home = hp1 - hb < HOME_MAX ? hp1 - hb : HOME_MAX;
-      __syncthreads();  // the previous chunk's readers are done with the home arrays
-      for (int t = threadIdx.x; t < n_home; t += blockDim.x) {
-        const int i = g.cell_atoms[hb + t];
-        st.home_id[t] = i;
-        st.home_wrap[t] = reinterpret_cast<const int4*>(g.atom_wrap)[i];
-        st.home_x[t] = g.cart[3 * i];
-        st.home_y[t] = g.cart[3 * i + 1];
-        st.home_z[t] = g.cart[3 * i + 2];
-        st.home_count[t] = 0;
-      }
-      bool bad_image = false;
-      for (int d0 = -s0; d0 <= s0; ++d0) {
-        int c0 = ci.x + d0;
-        const int h0 = floor_div(c0, g0);
-        c0 -= h0 * g0;
-        for (int d1 = -s1; d1 <= s1; ++d1) {
-          int c1 = ci.y + d1;
-          const int h1 = floor_div(c1, g1);
-          c1 -= h1 * g1;
-          for (int d2 = -s2; d2 <= s2; ++d2) {
-            int c2 = ci.z + d2;
-            const int h2 = floor_div(c2, g2);
-            c2 -= h2 * g2;
-            const int nc = base + (c0 * g1 + c1) * g2 + c2;
-            const int p0 = g.cell_ptr[nc], p1 = g.cell_ptr[nc + 1];
-            for (int pb = p0; pb < p1; pb += CAND_MAX) {
-              const int n_cand = p1 - pb < CAND_MAX ? p1 - pb : CAND_MAX;
-              __syncthreads();  // the previous round's readers are done with the candidate arrays
-              for (int t = threadIdx.x; t < n_cand; t += blockDim.x) {
-                const int j = g.cell_atoms[pb + t];
-                st.cand_id[t] = j;
-                st.cand_wrap[t] = reinterpret_cast<const int4*>(g.atom_wrap)[j];
-                st.cand_x[t] = g.cart[3 * j];
-                st.cand_y[t] = g.cart[3 * j + 1];
-                st.cand_z[t] = g.cart[3 * j + 2];
-              }
-              __syncthreads();
-              for (int ha = wib; ha < n_home; ha += GB_THREADS / 32) {
-                const int i = st.home_id[ha];
-                const int4 wi = st.home_wrap[ha];
-                const double xi = st.home_x[ha], yi = st.home_y[ha], zi = st.home_z[ha];
-                const int out_base = FILL ? g.edge_ptr[i] : 0;
-                int count = st.home_count[ha];
-                for (int cb = 0; cb < n_cand; cb += 32) {
-                  const int t = cb + lane;
-                  bool ok = false;
-                  int j = 0, n0 = 0, n1 = 0, n2 = 0;
-                  double d = 0.0;
-                  if (t < n_cand) {
-                    j = st.cand_id[t];
-                    const int4 wj = st.cand_wrap[t];
-                    n0 = h0 - wj.x + wi.x;
-                    n1 = h1 - wj.y + wi.y;
-                    n2 = h2 - wj.z + wi.z;
-                    const double f0 = (double)n0, f1 = (double)n1, f2 = (double)n2;
-                    // s = (n0*L0 + n1*L1) + n2*L2 ; dx = (x_j + s) - x_i ; no FMA contraction
-                    const double sx = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[0]), __dmul_rn(f1, L[3])), __dmul_rn(f2, L[6]));
-                    const double sy = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[1]), __dmul_rn(f1, L[4])), __dmul_rn(f2, L[7]));
-                    const double sz = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[2]), __dmul_rn(f1, L[5])), __dmul_rn(f2, L[8]));
-                    const double dx = __dsub_rn(__dadd_rn(st.cand_x[t], sx), xi);
-                    const double dy = __dsub_rn(__dadd_rn(st.cand_y[t], sy), yi);
-                    const double dz = __dsub_rn(__dadd_rn(st.cand_z[t], sz), zi);
-                    const double q = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
-                    d = __dsqrt_rn(q);
-                    ok = (d > tol) && (d <= cutoff);
-                  }
-                  const unsigned mask = __ballot_sync(0xffffffffu, ok);
-                  if (ok) {
-                    if (n0 < -127 || n0 > 127 || n1 < -127 || n1 > 127 || n2 < -127 || n2 > 127) bad_image = true;
-                    if (FILL) {
-                      const int pos = out_base + count + __popc(mask & ((1u << lane) - 1u));
-                      if (pos < g.cap_edges) {
-                        g.key_unsorted[pos] = pack_key(j, n0, n1, n2);
-                        g.dist_unsorted[pos] = d;
-                      }
-                    }
-                  }
-                  count += __popc(mask);
-                }
-                __syncwarp();
-                if (lane == 0) st.home_count[ha] = count;  // a home atom belongs to one warp: no race
-                __syncwarp();
+  for (int k = 0; k < 9; ++k) L[k] = g.lattice[9 * b + k];
+  const double xi = g.cart[3 * i], yi = g.cart[3 * i + 1], zi = g.cart[3 * i + 2];
+  const int4 ci = reinterpret_cast<const int4*>(g.atom_cell)[i];
+  const int4 wi = reinterpret_cast<const int4*>(g.atom_wrap)[i];
+  const int out_base = FILL ? g.edge_ptr[i] : 0;
+  const double cutoff = g.cutoff, tol = g.tol;
+  int count = 0;
+  bool bad_image = false;
+  for (int d0 = -s0; d0 <= s0; ++d0) {
+    int c0 = ci.x + d0;
+    const int h0 = floor_div(c0, g0);
+    c0 -= h0 * g0;
+    for (int d1 = -s1; d1 <= s1; ++d1) {
+      int c1 = ci.y + d1;
+      const int h1 = floor_div(c1, g1);
+      c1 -= h1 * g1;
+      for (int d2 = -s2; d2 <= s2; ++d2) {
+        int c2 = ci.z + d2;
+        const int h2 = floor_div(c2, g2);
+        c2 -= h2 * g2;
+        const int cell = base + (c0 * g1 + c1) * g2 + c2;
+        const int p0 = g.cell_ptr[cell], p1 = g.cell_ptr[cell + 1];
+        // a structure with one cell per axis names the same atoms at every offset: they stay staged
+        const bool restage = !(g0 == 1 && g1 == 1 && g2 == 1 && p1 - p0 <= 32 && (d0 != -s0 || d1 != -s1 || d2 != -s2));
+        for (int pb = p0; pb < p1; pb += 32) {
+          const int p = pb + lane;
+          if (restage) {
+            __syncwarp();
+            if (p < p1) {
+              const int jj = g.cell_atoms[p];
+              st.j[lane] = jj;
+              st.wrap[lane] = reinterpret_cast<const int4*>(g.atom_wrap)[jj];
+              st.x[lane] = g.cart[3 * jj];
+              st.y[lane] = g.cart[3 * jj + 1];
+              st.z[lane] = g.cart[3 * jj + 2];
+            }
+            __syncwarp();
+          }
+          bool ok = false;
+          int j = 0, n0 = 0, n1 = 0, n2 = 0;
+          double d = 0.0;
+          if (p < p1) {
+            j = st.j[lane];
+            const int4 wj = st.wrap[lane];
+            n0 = h0 - wj.x + wi.x;
+            n1 = h1 - wj.y + wi.y;
+            n2 = h2 - wj.z + wi.z;
+            const double f0 = (double)n0, f1 = (double)n1, f2 = (double)n2;
+            // s = (n0*L0 + n1*L1) + n2*L2 ; dx = (x_j + s) - x_i ; no FMA contraction
+            const double sx = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[0]), __dmul_rn(f1, L[3])), __dmul_rn(f2, L[6]));
+            const double sy = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[1]), __dmul_rn(f1, L[4])), __dmul_rn(f2, L[7]));
+            const double sz = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[2]), __dmul_rn(f1, L[5])), __dmul_rn(f2, L[8]));
+            const double dx = __dsub_rn(__dadd_rn(st.x[lane], sx), xi);
+            const double dy = __dsub_rn(__dadd_rn(st.y[lane], sy), yi);
+            const double dz = __dsub_rn(__dadd_rn(st.z[lane], sz), zi);
+            const double q = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+            d = __dsqrt_rn(q);
+            ok = (d > tol) && (d <= cutoff);
+          }
+          const unsigned mask = __ballot_sync(0xffffffffu, ok);
+          if (ok) {
+            if (n0 < -127 || n0 > 127 || n1 < -127 || n1 > 127 || n2 < -127 || n2 > 127) bad_image = true;
+            if (FILL) {
+              const int pos = out_base + count + __popc(mask & ((1u << lane) - 1u));
+              if (pos < g.cap_edges) {
+                g.key_unsorted[pos] = pack_key(j, n0, n1, n2);
+                g.dist_unsorted[pos] = d;
               }
             }
           }
+          count += __popc(mask);
         }
       }
-      __syncthreads();
-      if (!FILL) {
-        // the image range is checked in the counting pass: nothing is packed or paired when it fails
-        if (bad_image) atomicOr(&g.counts[CT_IMAGE_OVERFLOW], 1);
-        for (int t = threadIdx.x; t < n_home; t += blockDim.x) {
-          g.edge_ptr[st.home_id[t]] = st.home_count[t];
-          if (st.home_count[t] == 0) atomicAdd(&g.counts[CT_ISOLATED], 1);
-        }
-      }
+    }
+  }
+  __syncwarp();
+  if (!FILL) {
+    // the image range is checked in the counting pass: nothing is packed or paired when it fails
+    if (__any_sync(0xffffffffu, bad_image) && lane == 0) atomicOr(&g.counts[CT_IMAGE_OVERFLOW], 1);
+    if (lane == 0) {
+      g.edge_ptr[i] = count;
+      if (count == 0) atomicAdd(&g.counts[CT_ISOLATED], 1);
     }
   }
 }
 
 // ---------------------------------------------------------------- the kernel
-__global__ void __launch_bounds__(GB_THREADS, 2) k_graph_build(const mb_graph g) {
+__global__ void __launch_bounds__(GB_THREADS, 1) k_graph_build(const mb_graph g) {
   cg::grid_group grid = cg::this_grid();
-  __shared__ NeighborStage stage;
-  const int lane = threadIdx.x & 31;
+  __shared__ CellStage stage[GB_THREADS / 32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
   const int warp_g = (int)(tid >> 5), n_warps = (int)(nth >> 5);
   const int n_atoms = g.n_atoms, n_cells = g.n_cells;
@@ -310,7 +294,7 @@ __global__ void __launch_bounds__(GB_THREADS, 2) k_graph_build(const mb_graph g)
   grid.sync();
 
   // ---- directed edges: count, scan, fill
-  neighbors_of_cells<false>(g, stage);
+  for (int ii = warp_g; ii < n_atoms; ii += n_warps) neighbors_of_atom<false>(g, g.cell_atoms[ii], lane, stage[wib]);
   grid.sync();
   grid_scan(grid, g.edge_ptr, g.edge_ptr, n_atoms, g.scan_tmp);
   const int ne = g.edge_ptr[n_atoms];
@@ -323,7 +307,7 @@ __global__ void __launch_bounds__(GB_THREADS, 2) k_graph_build(const mb_graph g)
     if (tid == 0 && (ne & 1)) counts[CT_UNPAIRED] = 1;
     return;
   }
-  neighbors_of_cells<true>(g, stage);
+  for (int ii = warp_g; ii < n_atoms; ii += n_warps) neighbors_of_atom<true>(g, g.cell_atoms[ii], lane, stage[wib]);
   grid.sync();
 
   // ---- rank sort of each atom's out-edges by key (neighbour, image); warp per atom
@@ -428,8 +412,7 @@ __global__ void __launch_bounds__(GB_THREADS, 2) k_graph_build(const mb_graph g)
     src_count[u] = sc;
   }
   grid.sync();
-  grid_scan(grid, tgt_count, g.trip_ptr, nb, g.scan_tmp);
-  grid_scan(grid, src_count, g.trip_src_ptr, nb, g.scan_tmp);
+  grid_scan(grid, tgt_count, g.trip_ptr, nb, g.scan_tmp, src_count, g.trip_src_ptr);
   const int ntr = g.trip_ptr[nb];
   if (tid == 0) {
     counts[CT_TRIPLETS] = ntr;
@@ -501,7 +484,7 @@ static int check_graph(const mb_graph* g) {
 
 using namespace mb;
 
-extern "C" size_t mb_graph_scan_tmp_len(int64_t n) { return (size_t)(n / SCAN_CHUNK + 4); }
+extern "C" size_t mb_graph_scan_tmp_len(int64_t n) { return (size_t)(2 * (n / SCAN_CHUNK + 4)); }
 
 extern "C" int mb_graph_build(const mb_graph* g, void* stream_) {
   int rc = check_graph(g);
@@ -516,7 +499,7 @@ extern "C" int mb_graph_build(const mb_graph* g, void* stream_) {
     MB_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     MB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_graph_build, GB_THREADS, 0));
     if (per_sm < 1) return MB_ERR_CUDA;
-    grid_of_device[dev] = n_sm * (per_sm < 4 ? per_sm : 4);
+    grid_of_device[dev] = n_sm;  // one CTA per SM (per_sm >= 1 was checked above)
   }
   mb_graph arg = *g;
   void* params[] = {&arg};

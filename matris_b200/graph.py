@@ -211,8 +211,8 @@ class _GraphBuffers:
             rev=_i32(cap_e, device), d2u=_i32(cap_e, device), u2d=_i32(cap_e // 2, device),
             trip_ptr=_i32(cap_e // 2 + 1, device), trip_src_ptr=_i32(cap_e // 2 + 1, device),
             line_graph=_i32(5 * cap_t, device), trip_src_perm=_i32(cap_t, device))
-        self.counts = torch.zeros(16, dtype=torch.int32, device=device)
-        self.counts_host = torch.zeros(16, dtype=torch.int32).pin_memory()
+        self.counts = torch.zeros(64, dtype=torch.int32, device=device)  # 16 used; the rest is spare
+        self.counts_host = torch.zeros(64, dtype=torch.int32).pin_memory()
 
 
 def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None) -> BatchedGraph:
@@ -265,6 +265,16 @@ def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None) -> BatchedG
         g.lg_cols = g.line_graph.t().contiguous() if nt else torch.empty(5, 0, dtype=torch.int32, device=device)
     g._row_graphs = g._slices = None
     return g
+
+
+def set_positions_on_device(g: BatchedGraph, cart64: torch.Tensor) -> None:
+    """New Cartesian positions (float64, on the device) for the atoms of ``g``.  The float32 positions the model
+    reads are derived exactly as for a fresh batch and as in the reference: fractional coordinates rounded to
+    float32, times the float32 lattice (matris/graph/converter.py:82-83, matris/model/processgraph.py:87)."""
+    g.cart64.copy_(cart64)
+    struct = g.atom_struct.long()
+    frac32 = torch.einsum("ni,nij->nj", g.cart64, g.inv_lattice64[struct]).to(torch.float32)
+    g.cart32.copy_(torch.einsum("ni,nij->nj", frac32, g.lattice32[struct]))
 
 
 def build_batched_graph(numbers: Sequence[np.ndarray], carts: Sequence[np.ndarray], lattices: Sequence[np.ndarray],

@@ -7,6 +7,7 @@ from conftest import GPA, load_golden
 from gpu_util import report
 from matris_b200 import workloads
 from matris_b200.weights import random_checkpoint
+from matris_b200.workloads import Crystal
 
 pytestmark = pytest.mark.gpu
 
@@ -78,6 +79,47 @@ def test_device_resident_nve_follows_the_host_loop():
         runs.append((md.atoms.get_positions(), md.atoms.get_momenta()))
     report("device-resident NVE positions vs host loop", torch.tensor(runs[1][0]), torch.tensor(runs[0][0]), 1e-6)
     report("device-resident NVE momenta vs host loop", torch.tensor(runs[1][1]), torch.tensor(runs[0][1]), 1e-5)
+
+
+def test_device_resident_evaluation_equals_predict_at_the_same_positions():
+    """The loops that keep their state on the GPU derive the model's float32 positions from the float64 ones on the
+    device; the results stored at the end must be those of a fresh evaluation of the final positions."""
+    from matris_b200 import MatRIS
+    from matris_b200.applications import MolecularDynamics
+    model = MatRIS.from_dict(random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)).to("cuda")
+    cr = workloads.random_crystals(3, seed=14)[1]  # triclinic: the fractional / Cartesian round trip is not trivial
+    md = MolecularDynamics(_atoms(cr), model=model, ensemble="nve", timestep=1.0, starting_temperature=500,
+                           task="efsm", device="cuda", seed=3, device_resident=True)
+    md.run(4)
+    stored = dict(md.atoms.calc.results)
+    fresh = model.predict([Crystal(cr.numbers, md.atoms.get_positions(), cr.lattice)], "efsm")
+    n = len(cr.numbers)
+    report("device loop vs predict: energy (eV/atom)", np.array([stored["energy"] / n]), fresh["e"].cpu(), 1e-6)
+    report("device loop vs predict: forces", stored["forces"], fresh["f"][0].cpu(), 2e-6)
+    report("device loop vs predict: stress (eV/A^3)", stored["stress"], fresh["s"][0].cpu() / GPA, 1e-7)
+    report("device loop vs predict: magmoms", stored["magmoms"], fresh["m"][0].cpu(), 2e-6)
+
+
+def test_langevin_thermostat_holds_the_target_temperature():
+    """Statistical check of the device-resident BAOAB loop: the mean kinetic temperature over 3,000 steps of the
+    32-atom Cu cell at 600 K.  Samples are taken 75 steps apart (several velocity correlation times at a friction
+    of 0.05 / fs); one sample of 32 atoms scatters by sqrt(2 / (3 N)) = 14 %, the mean of 40 by 14 K: the bound is
+    3 sigma."""
+    from matris_b200 import MatRIS
+    from matris_b200.applications import MolecularDynamics
+    model = MatRIS.from_dict(random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=0)).to("cuda")
+    md = MolecularDynamics(_atoms(workloads.cu_fcc()), model=model, ensemble="nvt", thermostat="langevin",
+                           temperature=600, starting_temperature=600, timestep=1.0, friction=0.05, task="ef",
+                           device="cuda", seed=11)
+    md.run(300)  # equilibration
+    temps = []
+    for _ in range(40):
+        md.run(75)
+        temps.append(md.atoms.get_temperature())
+    mean, sigma = float(np.mean(temps)), 600.0 * np.sqrt(2.0 / (3 * 32)) / np.sqrt(len(temps))
+    print(f"Langevin: mean kinetic temperature {mean:.1f} K over {md.steps_done} steps (sigma of the mean {sigma:.1f} K)")
+    assert abs(mean - 600.0) < 3 * sigma + 5.0, (mean, sigma)
+    assert np.isfinite(md.atoms.get_potential_energy())
 
 
 def test_md_writes_an_extxyz_trajectory(tmp_path):

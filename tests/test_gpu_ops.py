@@ -366,8 +366,11 @@ def test_seg_smooth_sum_fwd_bwd(ops, line):
         hs = ops.mul_rows_gather(dev(h), dev(env), d_emap)
         report("mul_rows_gather", hs, (H * s).detach(), 1e-6)
         drow = rnd(R, 128, seed=9)
-        both = (ref * dagg.double()).sum() + (H * s * drow.double()).sum()
-        dE2, _ = torch.autograd.grad(both, [E, H])
+        E2, H2 = env.double().requires_grad_(True), h.double().requires_grad_(True)
+        hs2 = H2 * E2[emap]
+        both = (torch.zeros(Nn, 128, dtype=torch.float64).index_add_(0, tgt, hs2) * dagg.double()).sum() \
+            + (hs2 * drow.double()).sum()
+        dE2, _ = torch.autograd.grad(both, [E2, H2])
         denv2 = ops.seg_smooth_sum_bwd_env(env.shape[0], dev(tptr, i32), None, dev(perm, i32), d_tgt, d_src,
                                            dev(u2d, i32), dev(rev, i32), dev(env), dev(h), dev(dagg), drow=dev(drow))
         report("seg_smooth_sum_bwd_env with a per-row gradient", denv2, dE2, 2e-5)
