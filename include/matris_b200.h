@@ -141,9 +141,11 @@ typedef struct mb_colblock {
   int32_t out_act;             /* 0 none, 1 SiLU */
   mb_src src[4];
   const float* W;              /* [128, K] row-major: weight rows of this column block */
-  const float* W_hi;           /* tf32(W), same layout (tensor-core mode; NULL allowed in SIMT mode) */
+  const float* W_hi;           /* tf32(W), same layout (3xTF32 modes 2, 3; NULL allowed otherwise) */
   const float* W_lo;           /* W - tf32(W), same layout */
-  int64_t ldw;                 /* row stride of W, W_hi, W_lo in floats (>= K) */
+  const uint16_t* W_hi16;      /* bf16(W), same layout in 16-bit elements (3xBF16, mode 0; NULL allowed otherwise) */
+  const uint16_t* W_lo16;      /* bf16(W - bf16(W)) */
+  int64_t ldw;                 /* row stride of W and of every split, in elements (>= K; a multiple of 8 in mode 0) */
   const float* bias;           /* [128] or NULL */
   const float* gate;           /* optional pre-activation z: multiply by d/dz SiLU(z) */
   int64_t ld_gate; int32_t col_gate; int32_t pad0;
@@ -162,9 +164,13 @@ typedef struct mb_gemm_desc {
 } mb_gemm_desc;
 
 int mb_gemm(const mb_gemm_desc* desc, void* stream);
-/* Contraction core used by mb_gemm and mb_gated_mlp_fwd: 0 = tcgen05 tensor cores, kind::tf32 with a 3-term hi/lo
- * operand split accumulated in fp32 TMEM, persistent kernels with one CTA per SM (default); 1 = fp32 SIMT FMA
- * (bit-faithful fp32, the cross-check); 2 = the same tensor-core arithmetic as 0 in a one-tile-per-CTA kernel.
+/* Contraction core used by mb_gemm and mb_gated_mlp_fwd.  Every tensor-core core splits both operands into hi + lo
+ * and accumulates lo*hi + hi*lo + hi*hi in fp32 tensor memory:
+ *   0 (default) persistent kernels, one CTA per SM, 3xBF16: hi = bf16(x), lo = bf16(x - hi), kind::f16 MMAs at twice
+ *               the tf32 rate; an operand pair carries 16 mantissa bits;
+ *   3           the same kernels with 3xTF32: hi = x cut to tf32, lo = x - hi, kind::tf32 MMAs; 22 mantissa bits;
+ *   2           3xTF32 in a one-tile-per-CTA kernel;
+ *   1           fp32 SIMT FMA (bit-faithful fp32, the cross-check).
  * A test knob: it is process-wide and not meant to be switched while other host threads launch.
  * MB_OUT_ADD is performed as one memory-side fp32 addition per element in mode 0 (read-add-write in modes 1, 2):
  * identical results as long as no other kernel writes the output rows concurrently. */
@@ -211,11 +217,15 @@ typedef struct mb_gated_mlp {
   const float* W1;             /* [256, K] row-major (SIMT mode) */
   const float* W1_hi;          /* tf32(W1) */
   const float* W1_lo;          /* W1 - tf32(W1) */
+  const uint16_t* W1_hi16;     /* bf16(W1) */
+  const uint16_t* W1_lo16;     /* bf16(W1 - bf16(W1)) */
   int64_t ldw1;                /* row stride of W1* in floats (>= K) */
   const float* b1;             /* [256] or NULL */
   const float* W2;             /* [256, 128] */
   const float* W2_hi;
   const float* W2_lo;
+  const uint16_t* W2_hi16;
+  const uint16_t* W2_lo16;
   int64_t ldw2;                /* row stride of W2* in floats (>= 128) */
   const float* b2;             /* [256] or NULL */
   const float* norm_core;      /* [128] RMSNorm weights */

@@ -49,7 +49,7 @@ class MbSrc(C.Structure):
 class MbColBlock(C.Structure):
     _fields_ = [
         ("n_src", _i32), ("out_act", _i32), ("src", MbSrc * 4),
-        ("W", _vp), ("W_hi", _vp), ("W_lo", _vp), ("ldw", _i64), ("bias", _vp),
+        ("W", _vp), ("W_hi", _vp), ("W_lo", _vp), ("W_hi16", _vp), ("W_lo16", _vp), ("ldw", _i64), ("bias", _vp),
         ("gate", _vp), ("ld_gate", _i64), ("col_gate", _i32), ("pad0", _i32),
         ("res", _vp), ("res_w", _vp), ("ld_res", _i64), ("col_res", _i32), ("mode", _i32),
         ("out", _vp), ("out_idx", _vp), ("ld_out", _i64), ("col_out", _i32), ("out_scale", _f32),
@@ -63,8 +63,8 @@ class MbGemmDesc(C.Structure):
 class MbGatedMlp(C.Structure):
     _fields_ = [
         ("n_rows", _i64), ("n_src", _i32), ("pad", _i32), ("src", MbSrc * 4),
-        ("W1", _vp), ("W1_hi", _vp), ("W1_lo", _vp), ("ldw1", _i64), ("b1", _vp),
-        ("W2", _vp), ("W2_hi", _vp), ("W2_lo", _vp), ("ldw2", _i64), ("b2", _vp),
+        ("W1", _vp), ("W1_hi", _vp), ("W1_lo", _vp), ("W1_hi16", _vp), ("W1_lo16", _vp), ("ldw1", _i64), ("b1", _vp),
+        ("W2", _vp), ("W2_hi", _vp), ("W2_lo", _vp), ("W2_hi16", _vp), ("W2_lo16", _vp), ("ldw2", _i64), ("b2", _vp),
         ("norm_core", _vp), ("norm_gate", _vp),
         ("z1", _vp), ("ld_z1", _i64), ("z2", _vp), ("ld_z2", _i64), ("h", _vp), ("ld_h", _i64),
         ("res", _vp), ("res_w", _vp), ("ld_res", _i64), ("out2", _vp), ("ld_out2", _i64),

@@ -8,10 +8,11 @@
 // + gridDim.x, ... and runs the core unit and then the gate unit of each.  A unit is two chained contractions on the
 // same tensor-memory accumulator (unit k uses accumulator k & 1):
 //
-//   L1(k)   12 or 16 K chunks of X against rows 128 j.. of W1  ->  D (128 x 128 fp32)
+//   L1(k)   12 or 16 K chunks (of 32 floats) of X against rows 128 j.. of W1  ->  D (128 x 128 fp32)
 //   mid(k)  the eight epilogue warps read D back (tcgen05.ld, thread = row), add b1, optionally write z1, apply SiLU,
-//           split into tf32 hi / lo and store the result as the A operand of layer 2 into the four A buffers
-//           (tcgen05.st): z1 never travels through shared or global memory on its way to layer 2
+//           split into hi / lo (bf16 or tf32, see gemm_persistent.cuh) and store the result as the A operand of
+//           layer 2 into four A buffers (tcgen05.st): z1 never travels through shared or global memory on its way
+//           to layer 2
 //   L2(k)   4 K chunks against rows 128 j.. of W2, written over D (every column of D has been read by then)
 //   epi(k)  D -> registers, + b2, optional z2 store, RMSNorm (the two warps that share a row exchange their partial
 //           sums of squares through shared memory), then  core unit: c = SiLU(.) is parked in the output row;
@@ -20,9 +21,9 @@
 // The tensor pipe executes L1(0) L1(1) L2(0) L1(2) L2(1) ... L1(n-1) L2(n-2) L2(n-1): while it works on L1(k+1) the
 // epilogue warps drain unit k-1 and prepare unit k's layer-2 operand, so neither hand-off idles the tensor cores for
 // longer than one tcgen05.st + mbarrier round trip.  All roles walk that one chunk sequence (counter g): chunk g uses
-// A buffer g & 3 and W ring slot g & 3, exactly as in k_gemm_ps, and every phase has a multiple of four chunks.
+// A buffer g % NB and W-slot use g / CPW, exactly as in k_gemm_ps, and every phase has a multiple of four chunks.
 //
-// Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64 b (hi | lo).
+// Tensor memory (512 columns): accumulators at 0 and 128, A buffers from 256 on (hi | lo each).
 // Shared memory: W ring 4 x 32 KB | producer patches 64 KB | sums of squares 2 KB | per-channel constants 3.5 KB |
 // barriers | descriptor copy.
 // Every mbarrier wait is bounded; on expiry the status word is set, the role stops waiting and runs to the common exit.
@@ -33,7 +34,7 @@ constexpr int GP_THREADS = PS_THREADS;
 constexpr int GP_XSUM_OFF = PS_RING_BYTES + PS_PATCH_BYTES;
 constexpr int GP_CONST_OFF = GP_XSUM_OFF + 2 * 2 * 128 * 4;  // b1[256] b2[256] norm_core[128] norm_gate[128] res_w[128]
 constexpr int GP_BAR_OFF = GP_CONST_OFF + 896 * 4;
-constexpr int GP_DESC_OFF = GP_BAR_OFF + 256;
+constexpr int GP_DESC_OFF = GP_BAR_OFF + 320;
 constexpr int GP_SMEM_BYTES = GP_DESC_OFF + (int)((sizeof(mb_gated_mlp) + 15) / 16 * 16);
 constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): float32 machine epsilon
 static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
@@ -41,27 +42,31 @@ static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word"
 
 __device__ __forceinline__ float sigmoid_fast_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
+template <bool BF>
 __global__ void __launch_bounds__(GP_THREADS, 1)
 k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant__ GatedMaps maps) {
+  using Fmt = PsFormat<BF>;
+  constexpr uint32_t NB = Fmt::N_ABUF, CPW = Fmt::CH_PER_W;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GP_BAR_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 192);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 300);
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
     return;
   }
-  // barriers: ready[4] (4 storing warps + the TMA thread's expect_tx arrival) | chunk_done[4] | d1_full[2] |
-  //           d2_full[2] | d_free[2] (8 epilogue warps) | l2_free[4]
+  // barriers: a_ready[8] (A chunk stored: 4 warps) | a_done[8] (its MMAs retired) | w_ready[4] (W slot landed) |
+  //           w_done[4] (slot free) | d1_full[2] | d2_full[2] | d_free[2] (8 epilogue warps) | l2_free[4]
   // A parity wait can tell apart only the current and the preceding phase of a barrier, so every waiter must see
-  // every phase of the barriers it waits on.  chunk_done[b] completes once per chunk; the TMA warp waits on each of
-  // those.  The producers skip the layer-2 chunks and the epilogue warps skip the layer-1 chunks, so
-  //   * the epilogue warps wait for "A buffer b may take a layer-2 chunk" on l2_free[b], which completes exactly once
-  //     per unit (committed with the last four chunks of the phase that precedes the layer-2 phase);
+  // every phase of the barriers it waits on.  The MMA warp sees every chunk and the TMA warp every W-slot use.  The
+  // producers skip the layer-2 chunks and the epilogue warps skip the layer-1 chunks, so
+  //   * the epilogue warps wait for "the A buffer of layer-2 chunk c may be written" on l2_free[c], which completes
+  //     exactly once per unit: it is committed with the chunk, NB chunks earlier, that used the same buffer;
   //   * the producers wait for the previous layer-1 phase to be complete (d1_full) before the first chunk of a phase
-  //     that follows a layer-2 phase: chunk_done[b] is then at most one phase away from the one they wait for.
-  const uint32_t ready = smem_u32(bars), chunk_done = smem_u32(bars + 4);
-  const uint32_t d1_full = smem_u32(bars + 8), d2_full = smem_u32(bars + 10), d_free = smem_u32(bars + 12);
-  const uint32_t l2_free = smem_u32(bars + 14);
+  //     that follows a layer-2 phase: a_done[b] is then at most one phase away from the one they wait for.
+  const uint32_t a_ready = smem_u32(bars), a_done = smem_u32(bars + 8);
+  const uint32_t w_ready = smem_u32(bars + 16), w_done = smem_u32(bars + 20);
+  const uint32_t d1_full = smem_u32(bars + 24), d2_full = smem_u32(bars + 26), d_free = smem_u32(bars + 28);
+  const uint32_t l2_free = smem_u32(bars + 30);
   const uint32_t ring = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const mb_gated_mlp& d = *reinterpret_cast<const mb_gated_mlp*>(smem + GP_DESC_OFF);
@@ -149,8 +154,9 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
 
   if (warp == PS_MMA_WARP) {
     if (lane == 0) {
+      for (int b = 0; b < 8; ++b) { mbar_init(a_ready + 8 * b, 4); mbar_init(a_done + 8 * b, 1); }
       for (int b = 0; b < 4; ++b) {
-        mbar_init(ready + 8 * b, 5); mbar_init(chunk_done + 8 * b, 1); mbar_init(l2_free + 8 * b, 1);
+        mbar_init(w_ready + 8 * b, 1); mbar_init(w_done + 8 * b, 1); mbar_init(l2_free + 8 * b, 1);
       }
       for (int b = 0; b < 2; ++b) {
         mbar_init(d1_full + 8 * b, 1); mbar_init(d2_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8);
@@ -179,6 +185,14 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
     bool alive = true;
     uint32_t g = 0;
+    // Hand-over of the A buffers to the layer-2 writers (the epilogue warps): chunk t of layer-2 phase k_l2 may be
+    // written once the chunk NB before it has retired, which is signalled on l2_free[t], one completion per unit.  The
+    // writers of unit k must have seen completion k before completion k + 1 can happen (a parity wait cannot tell
+    // two phases apart), so the signal is never given before the same chunk of the preceding layer-2 phase, which
+    // needs their operand: sig_first = max(first chunk of the phase - NB, first chunk of the preceding layer-2 phase).
+    auto l2_start = [&](int k) { return (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k); };
+    int k_l2 = 0;
+    uint32_t sig_first = l2_start(0) - NB;  // n_units >= 2 and nch1 >= 4: never negative
     for (int p = 0; p < n_phases; ++p) {
       bool is_l2;
       int k;
@@ -187,43 +201,45 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       const uint32_t d_tmem = tmem_u + 128u * acc;
       const int nch = is_l2 ? 4 : nch1;
       const uint32_t full_bar = (is_l2 ? d2_full : d1_full) + 8 * acc;
-      // the phase after this one is a layer-2 phase: its operand chunks go into the A buffers of the last four chunks
-      const bool frees_l2 = is_l2 ? (k == n_units - 2) : (k >= 1);
       for (int c = 0; c < nch; ++c, ++g) {
-        const uint32_t ab = g & 3;
+        const uint32_t ab = g % NB, wu = g / CPW, slot = wu & 3;
         if (c == 0 && is_l2) {
           // Layer 2 overwrites the accumulator that holds z1: its first MMA may issue only when all four operand
-          // chunks have been read out of it and stored (each `ready` phase below implies that chunk's tcgen05.ld).
+          // chunks have been read out of it and stored (each a_ready phase below implies that chunk's tcgen05.ld).
           for (uint32_t b = 0; b < 4; ++b)
-            if (alive) alive = mbar_wait(ready + 8 * b, (g >> 2) & 1);
+            if (alive) alive = mbar_wait(a_ready + 8 * ((g + b) % NB), ((g + b) / NB) & 1);
         } else {
-          if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);
+          if (alive) alive = mbar_wait(a_ready + 8 * ab, (g / NB) & 1);
         }
+        if (g % CPW == 0 && alive) alive = mbar_wait(w_ready + 8 * slot, (wu >> 2) & 1);
         // layer 1 of unit k overwrites the accumulator unit k - 2 left: its epilogue must have taken it
         if (c == 0 && !is_l2 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
         alive = __all_sync(0xffffffffu, alive);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t wb = ring_u + ab * 2 * TC_TILE_BYTES;
-        const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
-        const uint32_t ta_hi = tmem_u + 256 + 64 * ab, ta_lo = ta_hi + 32;
+        const uint32_t wb = ring_u + slot * 2 * TC_TILE_BYTES;
+        const uint32_t ta = tmem_u + 256 + Fmt::A_COLS * ab;
+        // < 4: this chunk's retirement frees layer-2 chunk t_l2 of unit k_l2
+        const uint32_t t_l2 = k_l2 < n_units ? g - sig_first : 4u;
         if (elected) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t adv = (uint64_t)(2 * kk);
-            umma_tf32_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (c > 0 || kk > 0) ? 1u : 0u);
-            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
-            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
-          }
+          issue_chunk_mmas<BF>(d_tmem, ta, wb, g % CPW, c == 0);
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                       :: "r"(chunk_done + 8 * ab) : "memory");
-          if (frees_l2 && c >= nch - 4)
+                       :: "r"(a_done + 8 * ab) : "memory");
+          if (g % CPW == CPW - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                         :: "r"(l2_free + 8 * ab) : "memory");
+                         :: "r"(w_done + 8 * slot) : "memory");
+          if (t_l2 < 4u)
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(l2_free + 8 * t_l2) : "memory");
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(full_bar) : "memory");
         }
         __syncwarp();
+        if (t_l2 == 3u) {
+          ++k_l2;
+          const uint32_t by_buffer = l2_start(k_l2) - NB, by_order = l2_start(k_l2 - 1);
+          sig_first = by_buffer > by_order ? by_buffer : by_order;
+        }
       }
     }
   } else if (warp == PS_TMA_WARP) {
@@ -232,32 +248,32 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
     const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
     bool alive = true;
-    uint32_t w_g = 0;
+    uint32_t wu = 0;  // W-slot uses issued so far
     for (int p = 0; p < n_phases && alive; ++p) {
       bool is_l2;
       int k;
       decode(p, is_l2, k);
-      const int nch = is_l2 ? 4 : nch1;
+      const int n_w = (is_l2 ? 4 : nch1) / (int)CPW;
       const int wrow = 128 * (k & 1);  // first weight row of this unit's branch
       const CUtensorMap* const m_hi = is_l2 ? &maps.w2[0] : &maps.w1[0];
       const CUtensorMap* const m_lo = is_l2 ? &maps.w2[1] : &maps.w1[1];
-      for (int c = 0; c < nch && alive; ++c, ++w_g) {
-        const uint32_t slot = w_g & 3;
-        if (w_g >= 4) alive = mbar_wait(chunk_done + 8 * slot, ((w_g >> 2) - 1) & 1);
+      for (int wi = 0; wi < n_w && alive; ++wi, ++wu) {
+        const uint32_t slot = wu & 3;
+        if (wu >= 4) alive = mbar_wait(w_done + 8 * slot, ((wu >> 2) - 1) & 1);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) break;
-        const uint32_t bar = ready + 8 * slot;
+        const uint32_t bar = w_ready + 8 * slot;
         if (elected) {
           const uint32_t dst = ring_u + slot * 2 * TC_TILE_BYTES;
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
-          tma_load_2d(dst, m_hi, bar, c * TC_BK, wrow);
-          tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, c * TC_BK, wrow);
+          tma_load_2d(dst, m_hi, bar, wi * Fmt::W_BOX_K, wrow);
+          tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, wi * Fmt::W_BOX_K, wrow);
         }
         __syncwarp();
       }
     }
     if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
-      for (uint32_t i = w_g >= 4 ? w_g - 4 : 0; i < w_g; ++i) mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
+      for (uint32_t i = wu >= 4 ? wu - 4 : 0; i < wu; ++i) mbar_wait(w_ready + 8 * (i & 3), (i >> 2) & 1);
     }
   } else if (warp >= PS_EPI_WARP0) {
     // ---------------------------------------------------------------- epilogue warps: mid(k) then epi(k), unit by unit
@@ -311,29 +327,39 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           }
         }
         __syncwarp();
-        const uint32_t gi = gl2 + (uint32_t)c, ab = gi & 3;
-        const uint32_t ta = lane_q + 256 + 64 * ab;
+        const uint32_t gi = gl2 + (uint32_t)c, ab = gi % NB;
+        const uint32_t ta = lane_q + 256 + Fmt::A_COLS * ab;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          uint32_t hi[16], lo[16];
+          float sx[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float s = silu_fast_f(x[16 * hh + i]);
-            hi[i] = __float_as_uint(s) & 0xFFFFE000u;
-            lo[i] = __float_as_uint(s - __uint_as_float(hi[i]));
+          for (int i = 0; i < 16; ++i) sx[i] = silu_fast_f(x[16 * hh + i]);
+          if (BF) {
+            uint32_t hi[8], lo[8];
+            split_bf16(sx, hi, lo);
+            if (hh == 0) {
+              if (alive) alive = mbar_wait(l2_free + 8 * c, (uint32_t)(k & 1));  // the A buffer may take this chunk
+              __syncwarp();
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            MB_TMEM_ST8(ta + 8 * hh, hi);
+            MB_TMEM_ST8(ta + 16 + 8 * hh, lo);
+          } else {
+            uint32_t hi[16], lo[16];
+            split_tf32(sx, hi, lo);
+            if (hh == 0) {
+              if (alive) alive = mbar_wait(l2_free + 8 * c, (uint32_t)(k & 1));  // the A buffer may take this chunk
+              __syncwarp();
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            MB_TMEM_ST16(ta + 16 * hh, hi);
+            MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
           }
-          if (hh == 0) {
-            if (alive) alive = mbar_wait(l2_free + 8 * ab, (uint32_t)(k & 1));  // A buffer ab may take this chunk
-            __syncwarp();
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          }
-          MB_TMEM_ST16(ta + 16 * hh, hi);
-          MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(ready + 8 * ab);
+        if (lane == 0) mbar_arrive(a_ready + 8 * ab);
       }
       // ------------------------------------------------ epi(k): z2 -> RMSNorm -> activation -> h
       if (alive) alive = mbar_wait(d2_full + 8 * acc, upar);
@@ -448,43 +474,21 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         alive = __all_sync(0xffffffffu, alive);
       }
       for (int c = par; c < nch1; c += 2, ++n) {
-        const uint32_t gi = g + c, ab = gi & 3;
+        const uint32_t gi = g + c, ab = gi % NB;
         gather_next();
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncwarp();
         const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
         const bool act = (act_mask >> (c >> 2)) & 1;
-        const uint32_t ta = lane_base + 256 + 64 * ab;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          float x[16];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t addr = patch + lane * 128 + (((4 * hh + j) ^ (lane & 7)) << 4);
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]),
-                         "=f"(x[4 * j + 2]), "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
-          }
-          if (act) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) x[i] = silu_fast_f(x[i]);
-          }
-          uint32_t hi[16], lo[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            hi[i] = __float_as_uint(x[i]) & 0xFFFFE000u;
-            lo[i] = __float_as_uint(x[i] - __uint_as_float(hi[i]));
-          }
-          if (hh == 0) {
-            if (gi >= 4 && alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          }
-          MB_TMEM_ST16(ta + 16 * hh, hi);
-          MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
-        }
+        const uint32_t ta = lane_base + 256 + Fmt::A_COLS * ab;
+        convert_chunk<BF>(patch, lane, act, ta, [&]() {
+          if (gi >= NB && alive) alive = mbar_wait(a_done + 8 * ab, ((gi / NB) - 1) & 1);  // A buffer ab is free again
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        });
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(ready + 8 * ab);
+        if (lane == 0) mbar_arrive(a_ready + 8 * ab);
       }
       g += (uint32_t)nch1;
     }

@@ -565,7 +565,8 @@ k_gemm_tc(const __grid_constant__ mb_gemm_desc d, const __grid_constant__ TcMaps
 #include "gemm_persistent.cuh"
 #include "gated_persistent.cuh"
 
-static int g_gemm_mode = 0;  // 0: persistent tcgen05 3xTF32, 1: fp32 SIMT, 2: one-tile-per-CTA tcgen05 3xTF32
+// 0: persistent tcgen05 3xBF16 (default), 1: fp32 SIMT, 2: one-tile-per-CTA tcgen05 3xTF32, 3: persistent tcgen05 3xTF32
+static int g_gemm_mode = 0;
 
 // TMA descriptor of a [rows, k] float32 weight block (row stride ldw), box 128 rows x 32 columns, 128-byte swizzle.
 // Encoding depends only on (address, stride, k, rows), so descriptors are cached per host thread.
@@ -573,7 +574,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out, int rows = 128) {
+static int weight_map(const void* w, int64_t ldw, int k, CUtensorMap* out, int rows = 128, bool bf16 = false) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     void* fn = nullptr;
@@ -587,22 +588,25 @@ static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out, int 
     MB_CUDA_CHECK(cudaFree(nullptr));
     bound = true;
   }
-  struct Key { const float* w; int64_t ld; int k; int rows; };
+  struct Key { const void* w; int64_t ld; int k; int rows; int bf16; };
   struct Entry { Key key; CUtensorMap map; };
   constexpr int SLOTS = 1024;
   static thread_local Entry* cache = nullptr;
   if (!cache) cache = new Entry[SLOTS]();
   const size_t hsh = ((reinterpret_cast<uintptr_t>(w) >> 4) * 0x9E3779B97F4A7C15ull + (uint64_t)(k + rows)) >> 54;  // 10 bits
   Entry& e = cache[hsh % SLOTS];
-  if (e.key.w == w && e.key.ld == ldw && e.key.k == k && e.key.rows == rows) {
+  if (e.key.w == w && e.key.ld == ldw && e.key.k == k && e.key.rows == rows && e.key.bf16 == (int)bf16) {
     *out = e.map;
     return MB_OK;
   }
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ldw * sizeof(float)};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, 128};
+  // float32 tiles: 128 rows x 32 values; bfloat16 tiles: 128 rows x 64 values (both 128 bytes per row).  The format
+  // is part of the cache key: an allocator may hand the address of a freed weight of one format to one of the other.
+  const cuuint64_t strides[1] = {(cuuint64_t)ldw * (bf16 ? 2 : 4)};
+  const cuuint32_t box[2] = {(cuuint32_t)(bf16 ? 64 : TC_BK), 128};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(w), dims, strides, box, estr,
+  CUresult r = encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                      const_cast<void*>(w), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -611,7 +615,7 @@ static int weight_map(const float* w, int64_t ldw, int k, CUtensorMap* out, int 
     set_cuda_error(cudaErrorInvalidValue, where);
     return MB_ERR_CUDA;
   }
-  e.key = Key{w, ldw, k, rows};
+  e.key = Key{w, ldw, k, rows, (int)bf16};
   e.map = *out;
   return MB_OK;
 }
@@ -629,8 +633,10 @@ static int device_config(int* n_sm) {
   DeviceConfig& c = g_device_config[dev];
   if (!c.ready) {
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
-    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
-    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
     int n = 0;
     MB_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     c.n_sm = n;
@@ -715,7 +721,7 @@ __global__ void __launch_bounds__(128, 1) k_mma_rate(int iters) {
 }  // namespace mb
 
 extern "C" int mb_set_gemm_mode(int mode) {
-  if (mode < 0 || mode > 2) return MB_ERR_INVALID;
+  if (mode < 0 || mode > 3) return MB_ERR_INVALID;
   mb::g_gemm_mode = mode;
   return MB_OK;
 }
@@ -791,17 +797,7 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
     int n_sm = 0;
     rc = mb::device_config(&n_sm);
     if (rc) return rc;
-    mb::TcMaps maps;
-    for (int j = 0; j < desc->n_blocks; ++j) {
-      const mb_colblock& cb = desc->blk[j];
-      if (!cb.W_hi || !cb.W_lo) return MB_ERR_INVALID;
-      rc = mb::weight_map(cb.W_hi, cb.ldw, 128 * cb.n_src, &maps.m[j][0]);
-      if (rc) return rc;
-      rc = mb::weight_map(cb.W_lo, cb.ldw, 128 * cb.n_src, &maps.m[j][1]);
-      if (rc) return rc;
-    }
-    const long long n_tiles = gx * desc->n_blocks;
-    // The persistent kernel's epilogue uses 32-byte accesses.  Operands aligned to 16 bytes only (a caller of the C
+    // The persistent kernels' epilogue uses 32-byte accesses.  Operands aligned to 16 bytes only (a caller of the C
     // ABI that passes views at odd column offsets; the Python host side never does) take the one-tile kernel.
     bool wide_ok = true;
     for (int j = 0; j < desc->n_blocks; ++j) {
@@ -813,9 +809,24 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
                 (!cb.res || ok32(cb.res, cb.ld_res, cb.col_res)) && (!cb.bias || ok32(cb.bias, 0, 0)) &&
                 (!cb.res_w || ok32(cb.res_w, 0, 0));
     }
-    if (mb::g_gemm_mode == 0 && wide_ok) {
+    const bool persistent = (mb::g_gemm_mode == 0 || mb::g_gemm_mode == 3) && wide_ok;
+    const bool bf16 = persistent && mb::g_gemm_mode == 0;
+    mb::TcMaps maps;
+    for (int j = 0; j < desc->n_blocks; ++j) {
+      const mb_colblock& cb = desc->blk[j];
+      const void* hi = bf16 ? (const void*)cb.W_hi16 : (const void*)cb.W_hi;
+      const void* lo = bf16 ? (const void*)cb.W_lo16 : (const void*)cb.W_lo;
+      if (!hi || !lo || !mb::aligned16(hi) || !mb::aligned16(lo) || (bf16 && (cb.ldw & 7))) return MB_ERR_INVALID;
+      rc = mb::weight_map(hi, cb.ldw, 128 * cb.n_src, &maps.m[j][0], 128, bf16);
+      if (rc) return rc;
+      rc = mb::weight_map(lo, cb.ldw, 128 * cb.n_src, &maps.m[j][1], 128, bf16);
+      if (rc) return rc;
+    }
+    const long long n_tiles = gx * desc->n_blocks;
+    if (persistent) {
       const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
-      mb::k_gemm_ps<<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
+      if (bf16) mb::k_gemm_ps<true><<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
+      else mb::k_gemm_ps<false><<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
     } else {
       mb::k_gemm_tc<<<(unsigned)n_tiles, mb::TC_THREADS, mb::TC_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
     }
@@ -839,6 +850,8 @@ static int gated_mlp_composed(const mb_gated_mlp* g, void* stream_) {
     ca.W = g->W1 + (int64_t)128 * j * g->ldw1;
     ca.W_hi = g->W1_hi ? g->W1_hi + (int64_t)128 * j * g->ldw1 : nullptr;
     ca.W_lo = g->W1_lo ? g->W1_lo + (int64_t)128 * j * g->ldw1 : nullptr;
+    ca.W_hi16 = g->W1_hi16 ? g->W1_hi16 + (int64_t)128 * j * g->ldw1 : nullptr;
+    ca.W_lo16 = g->W1_lo16 ? g->W1_lo16 + (int64_t)128 * j * g->ldw1 : nullptr;
     ca.ldw = g->ldw1;
     ca.bias = g->b1 ? g->b1 + 128 * j : nullptr;
     ca.out = g->z1; ca.ld_out = g->ld_z1; ca.col_out = 128 * j; ca.out_scale = 1.f; ca.mode = MB_OUT_STORE;
@@ -848,6 +861,8 @@ static int gated_mlp_composed(const mb_gated_mlp* g, void* stream_) {
     cb.W = g->W2 + (int64_t)128 * j * g->ldw2;
     cb.W_hi = g->W2_hi ? g->W2_hi + (int64_t)128 * j * g->ldw2 : nullptr;
     cb.W_lo = g->W2_lo ? g->W2_lo + (int64_t)128 * j * g->ldw2 : nullptr;
+    cb.W_hi16 = g->W2_hi16 ? g->W2_hi16 + (int64_t)128 * j * g->ldw2 : nullptr;
+    cb.W_lo16 = g->W2_lo16 ? g->W2_lo16 + (int64_t)128 * j * g->ldw2 : nullptr;
     cb.ldw = g->ldw2;
     cb.bias = g->b2 ? g->b2 + 128 * j : nullptr;
     cb.out = g->z2; cb.ld_out = g->ld_z2; cb.col_out = 128 * j; cb.out_scale = 1.f; cb.mode = MB_OUT_STORE;
@@ -874,21 +889,27 @@ extern "C" int mb_gated_mlp_fwd(const mb_gated_mlp* g, void* stream_) {
                        (!g->h || ok32(g->h, g->ld_h)) && (!g->out2 || (ok32(g->out2, g->ld_out2) && ok32(g->res, g->ld_res))) &&
                        (!g->b1 || ok32(g->b1, 0)) && (!g->b2 || ok32(g->b2, 0)) && ok32(g->norm_core, 0) &&
                        ok32(g->norm_gate, 0) && (!g->res_w || ok32(g->res_w, 0));
-  if (mb::g_gemm_mode != 0 || !wide_ok) return gated_mlp_composed(g, stream_);
-  if (!g->W1_hi || !g->W1_lo || !g->W2_hi || !g->W2_lo) return MB_ERR_INVALID;
-  if (!mb::aligned16(g->W1_hi) || !mb::aligned16(g->W1_lo) || !mb::aligned16(g->W2_hi) || !mb::aligned16(g->W2_lo))
-    return MB_ERR_INVALID;
+  if ((mb::g_gemm_mode != 0 && mb::g_gemm_mode != 3) || !wide_ok) return gated_mlp_composed(g, stream_);
+  const bool bf16 = mb::g_gemm_mode == 0;
+  const void* w1h = bf16 ? (const void*)g->W1_hi16 : (const void*)g->W1_hi;
+  const void* w1l = bf16 ? (const void*)g->W1_lo16 : (const void*)g->W1_lo;
+  const void* w2h = bf16 ? (const void*)g->W2_hi16 : (const void*)g->W2_hi;
+  const void* w2l = bf16 ? (const void*)g->W2_lo16 : (const void*)g->W2_lo;
+  if (!w1h || !w1l || !w2h || !w2l) return MB_ERR_INVALID;
+  if (!mb::aligned16(w1h) || !mb::aligned16(w1l) || !mb::aligned16(w2h) || !mb::aligned16(w2l)) return MB_ERR_INVALID;
+  if (bf16 && ((g->ldw1 & 7) || (g->ldw2 & 7))) return MB_ERR_INVALID;
   int n_sm = 0;
   int rc = mb::device_config(&n_sm);
   if (rc) return rc;
   mb::GatedMaps maps;
-  if ((rc = mb::weight_map(g->W1_hi, g->ldw1, 128 * g->n_src, &maps.w1[0], 256))) return rc;
-  if ((rc = mb::weight_map(g->W1_lo, g->ldw1, 128 * g->n_src, &maps.w1[1], 256))) return rc;
-  if ((rc = mb::weight_map(g->W2_hi, g->ldw2, 128, &maps.w2[0], 256))) return rc;
-  if ((rc = mb::weight_map(g->W2_lo, g->ldw2, 128, &maps.w2[1], 256))) return rc;
+  if ((rc = mb::weight_map(w1h, g->ldw1, 128 * g->n_src, &maps.w1[0], 256, bf16))) return rc;
+  if ((rc = mb::weight_map(w1l, g->ldw1, 128 * g->n_src, &maps.w1[1], 256, bf16))) return rc;
+  if ((rc = mb::weight_map(w2h, g->ldw2, 128, &maps.w2[0], 256, bf16))) return rc;
+  if ((rc = mb::weight_map(w2l, g->ldw2, 128, &maps.w2[1], 256, bf16))) return rc;
   const long long n_tiles = (g->n_rows + 127) / 128;
   const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
-  mb::k_gated_fwd<<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
+  if (bf16) mb::k_gated_fwd<true><<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
+  else mb::k_gated_fwd<false><<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
   MB_LAUNCH_CHECK("k_gated_fwd");
   return MB_OK;
 }

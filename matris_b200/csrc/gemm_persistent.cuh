@@ -1,29 +1,38 @@
 // Persistent tcgen05 GEMM (included by gemm.cu inside namespace mb, after the tcgen05 / TMA / mbarrier helpers).
 //
-// Same contract and arithmetic as k_gemm_tc (gathered, K-concatenated A operand; 3xTF32 with fp32 accumulation in
+// Same contract as k_gemm_tc (gathered, K-concatenated A operand; split-operand products with fp32 accumulation in
 // tensor memory; bias / SiLU' gate / SiLU / residual / scale epilogue with store, accumulate or atomic scatter), but
 // one CTA per SM walks over many 128x128 output tiles, so that the three stages of a tile run concurrently on
-// DIFFERENT tiles instead of one after the other:
+// DIFFERENT tiles instead of one after the other.
+//
+// Two operand formats (template parameter BF):
+//   BF = true   3xBF16: x = hi + lo with hi = bf16(x), lo = bf16(x - hi); kind::f16 MMAs (K = 16) at twice the
+//               tf32 rate; an operand pair carries 16 mantissa bits, which end to end stays within a small multiple
+//               of the float32 rounding noise of the same evaluation (measured on the golden cases).  Weights
+//               arrive as bf16 tiles of 64 K values (one 32 KB ring slot = hi + lo tile serves TWO 32-float A
+//               chunks); an A chunk takes 32 tensor-memory columns (two values per column), so there are 8 A buffers.
+//   BF = false  3xTF32: hi = x cut to 10 mantissa bits, lo = x - hi (exact), kind::tf32 MMAs (K = 8); 22 mantissa
+//               bits per operand pair.  A ring slot serves one chunk, an A chunk takes 64 columns, 4 A buffers.
+// Roles:
 //
 //   warp 0      MMA.  The whole warp walks the chunk sequence with warp-uniform addresses and descriptors; one elected
-//               lane issues the 12 tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi, A from tensor memory) into one
-//               of TWO accumulators; tcgen05.commit signals "chunk retired" (A buffer and W slot free) and, after a
+//               lane issues the tcgen05.mma of every chunk (lo*hi + hi*lo + hi*hi per K step, A from tensor memory)
+//               into one of TWO accumulators; tcgen05.commit signals "A buffer free", "W slot free" and, after a
 //               tile's last chunk, "accumulator full".
-//   warp 1      TMA.  Same structure; the elected lane streams W_hi / W_lo tiles into a 4-slot ring, up to four chunks
-//               ahead and across tile boundaries; a column block with K = 128 is loaded once and stays (its four
-//               chunks = the ring).
+//   warp 1      TMA.  Same structure; the elected lane streams W_hi / W_lo tiles into a 4-slot ring, up to four slots
+//               ahead and across tile boundaries; a column block with K = 128 is loaded once and stays.
 //   warps 2-9   producers.  A warp owns rows 32 (warp & 3).. of the tile (= its TMEM lane quarter); the first four
 //               take the even 32-float K chunks, the other four the odd ones.  A chunk is gathered with cp.async
 //               (coalesced 128-byte row reads through the optional index, two stages per warp) into a swizzled
 //               shared-memory patch, read back one row per thread, passed through the optional SiLU, split into tf32
-//               hi / lo and written with tcgen05.st into one of FOUR A buffers in tensor memory.
+//               hi / lo and written with tcgen05.st into one of the A buffers in tensor memory.
 //   warps 10-17 epilogue.  Epilogue warp e takes rows 32 (warp & 3).., columns 64 (e >> 2).. of the finished
 //               accumulator into registers (tcgen05.ld, thread = row), releases the accumulator, and finishes its
 //               rows there with 256-bit global loads / stores (a full 32-byte sector per thread) while the tensor
 //               cores already work on the next tile.  Scatter / accumulate modes go through a 4 KB patch per warp
 //               instead, so that their memory-side reductions leave as 128-byte row segments.
 //
-// Tensor memory (512 columns): accumulators at 0 and 128, A buffers at 256 + 64b (hi | lo).
+// Tensor memory (512 columns): accumulators at 0 and 128, A buffers from 256 on (hi | lo each).
 // Shared memory: W ring 4 x 32 KB | producer patches 64 KB | epilogue patches 32 KB | barriers | descriptor copy.
 // Every mbarrier wait is bounded; on expiry a status word is set, the role stops waiting and runs to the common exit,
 // where tensor memory is released.
@@ -36,6 +45,112 @@ __device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
 __device__ __forceinline__ void st8(float* p, const float (&v)[8]) {
   asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                :: "l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+
+#define MB_TMEM_ST8(taddr, v)                                                                                    \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"                   \
+               :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),      \
+                  "r"(v[7]) : "memory")
+
+// two floats -> one 32-bit word of two bf16 (round to nearest even): `first` in the low half (the lower K index)
+__device__ __forceinline__ uint32_t pack_bf16x2(float first, float second) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(second), "f"(first));
+  return r;
+}
+
+// hi / lo split of 16 consecutive K values into 8 + 8 packed words (BF16) ...
+__device__ __forceinline__ void split_bf16(const float (&x)[16], uint32_t (&hi)[8], uint32_t (&lo)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    hi[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
+    const float r0 = x[2 * i] - __uint_as_float(hi[i] << 16);
+    const float r1 = x[2 * i + 1] - __uint_as_float(hi[i] & 0xFFFF0000u);
+    lo[i] = pack_bf16x2(r0, r1);
+  }
+}
+// ... or into 16 + 16 words (TF32): hi = x cut to tf32's 10 mantissa bits, lo = the exact remainder
+__device__ __forceinline__ void split_tf32(const float (&x)[16], uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    hi[q] = __float_as_uint(x[q]) & 0xFFFFE000u;
+    lo[q] = __float_as_uint(x[q] - __uint_as_float(hi[q]));
+  }
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]^T, M = 128, N = 128, K = 16 (bf16 operands, fp32 accumulation)
+constexpr uint32_t TC_IDESC_BF16 = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               :: "r"(tmem_d), "r"(tmem_a), "l"(db), "r"(TC_IDESC_BF16), "r"(accumulate) : "memory");
+}
+
+// per-format constants of the persistent kernels
+template <bool BF> struct PsFormat {
+  static constexpr uint32_t A_COLS = BF ? 32 : 64;   // tensor-memory columns of one A chunk (hi | lo)
+  static constexpr uint32_t N_ABUF = BF ? 8 : 4;     // A buffers (256 columns in all)
+  static constexpr uint32_t CH_PER_W = BF ? 2 : 1;   // A chunks served by one W ring slot
+  static constexpr int W_BOX_K = BF ? 64 : 32;       // K values per W tile
+};
+
+// One chunk's MMAs: A buffer at tmem column `ta`, W slot at shared address `wb`, `half` = which 32-K half of a bf16
+// W tile this chunk reads (always 0 for tf32); `fresh` = this is the first chunk of the accumulation.
+template <bool BF>
+__device__ __forceinline__ void issue_chunk_mmas(uint32_t d_tmem, uint32_t ta, uint32_t wb, uint32_t half, bool fresh) {
+  const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
+  if (BF) {
+    const uint32_t ta_hi = ta, ta_lo = ta + 16;
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {  // K steps of 16: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
+      const uint64_t adv = (uint64_t)(2 * (2 * half + kk));
+      umma_bf16_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (!fresh || kk > 0) ? 1u : 0u);
+      umma_bf16_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
+      umma_bf16_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
+    }
+  } else {
+    const uint32_t ta_hi = ta, ta_lo = ta + 32;
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
+      const uint64_t adv = (uint64_t)(2 * kk);
+      umma_tf32_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (!fresh || kk > 0) ? 1u : 0u);
+      umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
+      umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
+    }
+  }
+}
+
+// One producer chunk: 32 floats of this thread's row from the swizzled patch -> optional SiLU -> hi / lo -> A buffer.
+// `wait_free` is called once, right before the first tcgen05.st (the conversion of the first half overlaps the wait).
+template <bool BF, typename WaitFree>
+__device__ __forceinline__ void convert_chunk(uint32_t patch, int lane, bool act, uint32_t ta, WaitFree wait_free) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {  // two halves of 16 floats keep the live registers of the split low
+    float x[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t addr = patch + lane * 128 + (((4 * h + j) ^ (lane & 7)) << 4);
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]),
+                   "=f"(x[4 * j + 2]), "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
+    }
+    if (act) {
+#pragma unroll
+      for (int q = 0; q < 16; ++q) x[q] = silu_fast_f(x[q]);
+    }
+    if (BF) {
+      uint32_t hi[8], lo[8];
+      split_bf16(x, hi, lo);
+      if (h == 0) wait_free();
+      MB_TMEM_ST8(ta + 8 * h, hi);
+      MB_TMEM_ST8(ta + 16 + 8 * h, lo);
+    } else {
+      uint32_t hi[16], lo[16];
+      split_tf32(x, hi, lo);
+      if (h == 0) wait_free();
+      MB_TMEM_ST16(ta + 16 * h, hi);
+      MB_TMEM_ST16(ta + 32 + 16 * h, lo);
+    }
+  }
 }
 
 constexpr int PS_THREADS = 576;          // 18 warps
@@ -52,20 +167,26 @@ constexpr int PS_SMEM_BYTES = PS_DESC_OFF + (int)((sizeof(mb_gemm_desc) + 15) / 
 constexpr uint32_t PS_TMEM_COLS = 512;
 static_assert(PS_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 
+template <bool BF>
 __global__ void __launch_bounds__(PS_THREADS, 1)
 k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ TcMaps maps) {
+  using Fmt = PsFormat<BF>;
+  constexpr uint32_t NB = Fmt::N_ABUF, CPW = Fmt::CH_PER_W;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PS_BAR_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + PS_BAR_OFF + 128);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + PS_BAR_OFF + 240);
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
     return;
   }
-  // barriers: ready[4] (chunk g & 3: 4 producer warps + the TMA thread's expect_tx arrival) | chunk_done[4] |
-  //           d_full[2] | d_free[2] (8 epilogue warps).  One wait per chunk for the MMA thread: every shared-memory
-  //           operation of that thread queues behind the data traffic of the other 17 warps.
-  const uint32_t ready = smem_u32(bars), chunk_done = smem_u32(bars + 4);
-  const uint32_t d_full = smem_u32(bars + 11), d_free = smem_u32(bars + 13);
+  // barriers: a_ready[8] (A chunk stored: 4 producer warps) | a_done[8] (its MMAs retired: the A buffer is free) |
+  //           w_ready[4] (W slot landed: the TMA thread's expect_tx arrival + bytes) | w_done[4] (slot free) |
+  //           d_full[2] | d_free[2] (8 epilogue warps).  Chunk g uses A buffer g % NB; W-slot use u = g / CPW uses
+  //           ring slot u % w_period.  Every waiter sees every phase of the barriers it waits on (a parity wait can
+  //           tell apart only two consecutive phases).
+  const uint32_t a_ready = smem_u32(bars), a_done = smem_u32(bars + 8);
+  const uint32_t w_ready = smem_u32(bars + 16), w_done = smem_u32(bars + 20);
+  const uint32_t d_full = smem_u32(bars + 24), d_free = smem_u32(bars + 26);
   const uint32_t ring = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // The descriptor is indexed dynamically (column block, K segment) all through the kernel.  From kernel-parameter
@@ -85,8 +206,9 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   const int first_rt = (int)(blockIdx.x / (unsigned)n_blocks), first_jb = (int)(blockIdx.x % (unsigned)n_blocks);
   const int step_rt = (int)(gridDim.x / (unsigned)n_blocks), step_jb = (int)(gridDim.x % (unsigned)n_blocks);
   // When every tile of this CTA belongs to the same column block and that block has a single 128-wide K segment,
-  // its four W chunks fill the four ring slots once and stay there for the whole kernel.
+  // its W tiles fill w_period ring slots once and stay there for the whole kernel.
   const bool w_resident = step_jb == 0 && d.blk[first_jb].n_src == 1;
+  const uint32_t w_period = w_resident ? 4u / CPW : 4u;
   auto next_tile = [&](int& rt, int& jb) {
     jb += step_jb;
     rt += step_rt;
@@ -152,7 +274,8 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
 
   if (warp == PS_MMA_WARP) {
     if (lane == 0) {
-      for (int b = 0; b < 4; ++b) { mbar_init(ready + 8 * b, 5); mbar_init(chunk_done + 8 * b, 1); }
+      for (int b = 0; b < 8; ++b) { mbar_init(a_ready + 8 * b, 4); mbar_init(a_done + 8 * b, 1); }
+      for (int b = 0; b < 4; ++b) { mbar_init(w_ready + 8 * b, 1); mbar_init(w_done + 8 * b, 1); }
       for (int b = 0; b < 2; ++b) { mbar_init(d_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8); }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -190,24 +313,21 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       const uint32_t d_tmem = tmem_u + 128u * acc;
       const int nch = (int)((nch_of >> (8 * jb)) & 0xffu);
       for (int c = 0; c < nch; ++c, ++g) {
-        const uint32_t ab = g & 3, slot = ab;  // A buffer and W slot of chunk g
-        if (alive) alive = mbar_wait(ready + 8 * ab, (g >> 2) & 1);  // A rows stored and W tiles landed
+        const uint32_t ab = g % NB, wu = g / CPW, slot = wu % w_period;  // A buffer, W-slot use and ring slot of chunk g
+        if (alive) alive = mbar_wait(a_ready + 8 * ab, (g / NB) & 1);  // A rows stored
+        if (g % CPW == 0 && alive) alive = mbar_wait(w_ready + 8 * slot, (wu / w_period) & 1);  // W tiles landed
         if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
         alive = __all_sync(0xffffffffu, alive);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t wb = ring_u + slot * 2 * TC_TILE_BYTES;
-        const uint64_t dbh = umma_desc(wb), dbl = umma_desc(wb + TC_TILE_BYTES);
-        const uint32_t ta_hi = tmem_u + 256 + 64 * ab, ta_lo = ta_hi + 32;
+        const uint32_t ta = tmem_u + 256 + Fmt::A_COLS * ab;
         if (elected) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {  // K steps of 8: 8 TMEM columns of A, 32 bytes (>> 4 = 2) of the W rows
-            const uint64_t adv = (uint64_t)(2 * kk);
-            umma_tf32_ts(d_tmem, ta_lo + 8 * kk, dbh + adv, (c > 0 || kk > 0) ? 1u : 0u);
-            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbl + adv, 1u);
-            umma_tf32_ts(d_tmem, ta_hi + 8 * kk, dbh + adv, 1u);
-          }
+          issue_chunk_mmas<BF>(d_tmem, ta, wb, g % CPW, c == 0);
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                       :: "r"(chunk_done + 8 * ab) : "memory");
+                       :: "r"(a_done + 8 * ab) : "memory");
+          if (g % CPW == CPW - 1)
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(w_done + 8 * slot) : "memory");
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(d_full + 8 * acc) : "memory");
@@ -222,31 +342,32 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
     const uint32_t ring_u = __shfl_sync(0xffffffffu, ring, 0);
     bool alive = true;
-    uint32_t w_g = 0;
+    uint32_t wu = 0;  // W-slot uses issued so far
     for (int rt = first_rt, jb = first_jb; rt < n_row_tiles && alive; next_tile(rt, jb)) {
-      const int nch = __shfl_sync(0xffffffffu, d.blk[jb].n_src * 4, 0);
-      for (int c = 0; c < nch && alive; ++c, ++w_g) {
-        const uint32_t slot = w_g & 3;
-        // slot and barrier were last used by chunk w_g - 4
-        if (w_g >= 4) alive = mbar_wait(chunk_done + 8 * slot, ((w_g >> 2) - 1) & 1);
+      const int n_w = __shfl_sync(0xffffffffu, d.blk[jb].n_src * 4 / (int)CPW, 0);
+      for (int wi = 0; wi < n_w && alive; ++wi, ++wu) {
+        const uint32_t slot = wu % w_period;
+        // slot and barrier were last used w_period uses ago
+        if (wu >= w_period) alive = mbar_wait(w_done + 8 * slot, ((wu / w_period) - 1) & 1);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) break;
-        const uint32_t bar = ready + 8 * slot;
+        const uint32_t bar = w_ready + 8 * slot;
         if (elected) {
-          if (w_resident && w_g >= 4) {  // the chunk is in its slot already: only this thread's arrival is due
+          if (w_resident && wu >= w_period) {  // the tiles are in their slot already: only this thread's arrival is due
             mbar_arrive(bar);
           } else {
             const uint32_t dst = ring_u + slot * 2 * TC_TILE_BYTES;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
-            tma_load_2d(dst, &maps.m[jb][0], bar, c * TC_BK, 0);
-            tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, c * TC_BK, 0);
+            tma_load_2d(dst, &maps.m[jb][0], bar, wi * Fmt::W_BOX_K, 0);
+            tma_load_2d(dst + TC_TILE_BYTES, &maps.m[jb][1], bar, wi * Fmt::W_BOX_K, 0);
           }
         }
         __syncwarp();
       }
     }
     if (!alive) {  // failure path only: no TMA write may still be in flight when the CTA's shared memory is released
-      for (uint32_t i = w_g >= 4 ? w_g - 4 : 0; i < w_g; ++i) mbar_wait(ready + 8 * (i & 3), (i >> 2) & 1);
+      for (uint32_t i = wu >= w_period ? wu - w_period : 0; i < wu; ++i)
+        mbar_wait(w_ready + 8 * (i % w_period), (i / w_period) & 1);
     }
   } else if (warp >= PS_EPI_WARP0) {
     // ---------------------------------------------------------------- epilogue warps
@@ -432,43 +553,21 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
 #pragma unroll
       for (int s = 0; s < 4; ++s) act_mask |= (s < cb.n_src && cb.src[s].act) ? (1 << s) : 0;
       for (int c = par; c < nch; c += 2, ++n) {
-        const uint32_t gi = g + c, ab = gi & 3;
+        const uint32_t gi = g + c, ab = gi % NB;
         gather_next();  // into the stage read one chunk ago; the __syncwarp that closed that chunk orders the reads
         asm volatile("cp.async.wait_group 1;" ::: "memory");  // this chunk's copies of this lane have landed
         __syncwarp();                                          // ... and so have the other lanes'
         const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
         const bool act = (act_mask >> (c >> 2)) & 1;  // branch once per chunk: no SiLU is evaluated on the plain path
-        const uint32_t ta = lane_base + 256 + 64 * ab;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {  // two halves of 16 floats keep the live registers of the split low
-          float x[16];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t addr = patch + lane * 128 + (((4 * h + j) ^ (lane & 7)) << 4);
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[4 * j]), "=f"(x[4 * j + 1]),
-                         "=f"(x[4 * j + 2]), "=f"(x[4 * j + 3]) : "r"(addr) : "memory");
-          }
-          if (act) {
-#pragma unroll
-            for (int q = 0; q < 16; ++q) x[q] = silu_fast_f(x[q]);
-          }
-          uint32_t hi[16], lo[16];
-#pragma unroll
-          for (int q = 0; q < 16; ++q) {  // hi = x cut to tf32's 10 mantissa bits, lo = the exact remainder
-            hi[q] = __float_as_uint(x[q]) & 0xFFFFE000u;
-            lo[q] = __float_as_uint(x[q] - __uint_as_float(hi[q]));
-          }
-          if (h == 0) {
-            if (gi >= 4 && alive) alive = mbar_wait(chunk_done + 8 * ab, ((gi >> 2) - 1) & 1);  // A buffer ab is free again
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          }
-          MB_TMEM_ST16(ta + 16 * h, hi);
-          MB_TMEM_ST16(ta + 32 + 16 * h, lo);
-        }
+        const uint32_t ta = lane_base + 256 + Fmt::A_COLS * ab;
+        convert_chunk<BF>(patch, lane, act, ta, [&]() {
+          if (gi >= NB && alive) alive = mbar_wait(a_done + 8 * ab, ((gi / NB) - 1) & 1);  // A buffer ab is free again
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        });
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();  // all lanes have read their patch rows and written their A rows
-        if (lane == 0) mbar_arrive(ready + 8 * ab);
+        if (lane == 0) mbar_arrive(a_ready + 8 * ab);
       }
       g += (uint32_t)nch;
     }

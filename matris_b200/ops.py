@@ -33,16 +33,20 @@ def new(rows, cols, like, zero=False):
 
 # ------------------------------------------------------------------ GEMM descriptors
 class SplitWeight:
-    """A weight matrix [n_out, K] with its tensor-core operand split: ``hi`` = tf32-rounded values,
-    ``lo`` = w - hi (both float32, same layout).  ``w`` itself feeds the exact-fp32 SIMT core."""
+    """A weight matrix [n_out, K] with its tensor-core operand splits, all in the layout of ``w``:
+    ``hi16`` = bf16(w), ``lo16`` = bf16(w - hi16) for the 3xBF16 core (the default);
+    ``hi`` = tf32-rounded values, ``lo`` = w - hi (float32) for the 3xTF32 cores.
+    ``w`` itself feeds the exact-fp32 SIMT core."""
 
-    __slots__ = ("w", "hi", "lo", "shape")
+    __slots__ = ("w", "hi", "lo", "hi16", "lo16", "shape")
 
     def __init__(self, w: torch.Tensor):
         w = w.detach().contiguous()
         bits = w.view(torch.int32)
         hi = ((bits + 0x1000) & ~0x1FFF).view(torch.float32)  # round to nearest (ties away) at 10 mantissa bits
         self.w, self.hi, self.lo, self.shape = w, hi.contiguous(), (w - hi).contiguous(), w.shape
+        self.hi16 = w.to(torch.bfloat16).contiguous()          # round to nearest even
+        self.lo16 = (w - self.hi16.float()).to(torch.bfloat16).contiguous()
 
     def t(self) -> "SplitWeight":
         return SplitWeight(self.w.t())
@@ -79,7 +83,7 @@ def B(srcs, W, w_row=0, bias=None, bias_off=0, gate=None, gate_col=0, out_act=0,
 # Byte layout of mb_colblock / mb_gemm_desc (little endian, every member naturally aligned; checked against the
 # ctypes mirror at import).  The descriptor is packed with one struct call per column block: filling the ctypes
 # mirror field by field costs more host time than a small launch takes on the device.
-_BLK_FMT = struct.Struct("<ii" + "QQqii" * 4 + "QQQqQ" + "Qqii" + "QQqii" + "QQqif")
+_BLK_FMT = struct.Struct("<ii" + "QQqii" * 4 + "QQQQQqQ" + "Qqii" + "QQqii" + "QQqif")
 _HDR_FMT = struct.Struct("<qii")
 _BLK_OFF, _BLK_SIZE, _DESC_SIZE = _lib.MbGemmDesc.blk.offset, C.sizeof(_lib.MbColBlock), C.sizeof(_lib.MbGemmDesc)
 assert _BLK_FMT.size == _BLK_SIZE and _HDR_FMT.size == _BLK_OFF and _DESC_SIZE == _BLK_OFF + 4 * _BLK_SIZE
@@ -104,10 +108,12 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
         ldw = W.stride(0)
         assert W.dim() == 2 and W.stride(1) == 1 and W.shape[1] >= D * len(srcs)
         w_off = 4 * ldw * int(b["w_row"])
+        w_off16 = w_off // 2
         bias, gate, res, res_w, out, out_idx = b["bias"], b["gate"], b["res"], b["res_w"], b["out"], b["out_idx"]
         _BLK_FMT.pack_into(
             buf, _BLK_OFF + j * _BLK_SIZE, len(srcs), int(b["out_act"]), *flat,
-            W.data_ptr() + w_off, sw.hi.data_ptr() + w_off, sw.lo.data_ptr() + w_off, ldw,
+            W.data_ptr() + w_off, sw.hi.data_ptr() + w_off, sw.lo.data_ptr() + w_off,
+            sw.hi16.data_ptr() + w_off16, sw.lo16.data_ptr() + w_off16, ldw,
             0 if bias is None else bias.data_ptr() + 4 * int(b["bias_off"]),
             0 if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0),
             0 if gate is None else int(b["gate_col"]), 0,
@@ -122,7 +128,7 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
     call("mb_gemm", C.byref(_lib.MbGemmDesc.from_buffer(buf)), _stream())
 
 
-_GATED_FMT = struct.Struct("<qii" + "QQqii" * 4 + "QQQqQ" + "QQQqQ" + "QQ" + "Qq" * 3 + "QQq" + "Qq")
+_GATED_FMT = struct.Struct("<qii" + "QQqii" * 4 + "QQQQQqQ" + "QQQQQqQ" + "QQ" + "Qq" * 3 + "QQq" + "Qq")
 assert _GATED_FMT.size == C.sizeof(_lib.MbGatedMlp)
 
 
@@ -133,7 +139,7 @@ def gated_mlp_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True)
     ref = srcs[0][0]
     n_rows = int(n_rows)
     # the composed path of the non-default GEMM modes uses z1 / z2 as scratch
-    save = save or _gemm_mode != 0
+    save = save or _gemm_mode in (1, 2)
     z1 = new(n_rows, 2 * D, ref) if save else None
     z2 = new(n_rows, 2 * D, ref) if save else None
     h = new(n_rows, D, ref) if want_h else None
@@ -154,8 +160,10 @@ def gated_mlp_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True)
 
     buf = _GATED_FMT.pack(
         n_rows, len(srcs), 0, *flat,
-        w1.w.data_ptr(), w1.hi.data_ptr(), w1.lo.data_ptr(), w1.w.stride(0), 0 if p.b1 is None else p.b1.data_ptr(),
-        w2.w.data_ptr(), w2.hi.data_ptr(), w2.lo.data_ptr(), w2.w.stride(0), 0 if p.b2 is None else p.b2.data_ptr(),
+        w1.w.data_ptr(), w1.hi.data_ptr(), w1.lo.data_ptr(), w1.hi16.data_ptr(), w1.lo16.data_ptr(), w1.w.stride(0),
+        0 if p.b1 is None else p.b1.data_ptr(),
+        w2.w.data_ptr(), w2.hi.data_ptr(), w2.lo.data_ptr(), w2.hi16.data_ptr(), w2.lo16.data_ptr(), w2.w.stride(0),
+        0 if p.b2 is None else p.b2.data_ptr(),
         p.nc.data_ptr(), p.ng.data_ptr(), *pl(z1), *pl(z2), *pl(h),
         0 if res is None else res.data_ptr(), 0 if res is None or res_w is None else res_w.data_ptr(),
         0 if res is None else res.stride(0), *pl(out2))
@@ -372,10 +380,11 @@ _gemm_mode = 0
 
 
 def set_gemm_mode(mode: str) -> None:
-    """'tcgen05' (default): persistent tensor-core kernels, 3-term TF32 split; 'simt': exact fp32 FMA cross-check;
-    'tcgen05_tile': the one-tile-per-CTA tensor-core kernel (same arithmetic as the default).  A test knob."""
+    """'tcgen05' (default): persistent tensor-core kernels, 3-term BF16 operand split; 'tcgen05_tf32': the same kernels
+    with a 3-term TF32 split; 'tcgen05_tile': a one-tile-per-CTA tensor-core kernel (3-term TF32); 'simt': exact fp32
+    FMA cross-check.  A test knob."""
     global _gemm_mode
-    _gemm_mode = {"tcgen05": 0, "simt": 1, "tcgen05_tile": 2}[mode]
+    _gemm_mode = {"tcgen05": 0, "simt": 1, "tcgen05_tile": 2, "tcgen05_tf32": 3}[mode]
     _lib.check(_lib.load().mb_set_gemm_mode(_gemm_mode), "mb_set_gemm_mode")
 
 

@@ -115,6 +115,7 @@ def test_gemm_descriptor_packing_matches_ctypes_mirror(monkeypatch):
     class FakeSplit:
         def __init__(self, w):
             self.w, self.hi, self.lo, self.shape = w, w.clone(), w.clone(), w.shape
+            self.hi16, self.lo16 = w.to(torch.bfloat16), w.to(torch.bfloat16)
 
     monkeypatch.setattr(ops, "as_split", lambda w: w if isinstance(w, FakeSplit) else FakeSplit(w))
     x, idx, W = torch.randn(300, 256), torch.arange(300, dtype=torch.int32), FakeSplit(torch.randn(256, 384))
@@ -132,6 +133,7 @@ def test_gemm_descriptor_packing_matches_ctypes_mirror(monkeypatch):
         assert (cb.src[1].idx, cb.src[1].col, cb.src[1].act) == (idx.data_ptr(), 128, 0) and not cb.src[3].ptr
         off = 4 * 384 * 128 * j
         assert (cb.W, cb.W_hi, cb.W_lo, cb.ldw) == (W.w.data_ptr() + off, W.hi.data_ptr() + off, W.lo.data_ptr() + off, 384)
+        assert (cb.W_hi16, cb.W_lo16) == (W.hi16.data_ptr() + off // 2, W.lo16.data_ptr() + off // 2)
         assert cb.bias == bias.data_ptr() + 512 * j
         assert (cb.gate, cb.ld_gate, cb.col_gate) == (g.data_ptr(), 256, 128 * j)
         assert (cb.res, cb.res_w, cb.ld_res, cb.col_res) == (r.data_ptr(), rw.data_ptr(), 256, 128 * j)
