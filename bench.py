@@ -269,7 +269,8 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--md-steps", type=int, default=None,
-                    help="with --workload lipscl: Langevin MD steps to time (default 200; 0 skips the MD leg)")
+                    help="Langevin MD steps to time on the 4,096-atom cell at N = 1 (default 200 with --workload lipscl, "
+                         "else 20; 0 skips the MD leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--keep", default="auto", choices=["auto", "on", "off"],
                     help="keep sub-block internals for the backward pass (auto: when they fit in memory)")
@@ -488,14 +489,17 @@ def main():
                                       "sample": f"first {info1['structures']} structures ({info1['atoms']} atoms), "
                                                 f"{info1['reps']} repetitions, {info1['seconds']:.1f}s of CPU work"}
 
-    # ---- MD leg (4,096-atom cell only): the public MolecularDynamics driver, Langevin NVT at 600 K, dt = 1 fs,
-    # friction 0.01 / fs, Maxwell-Boltzmann start, one efsm evaluation per step (graph rebuilt every step on the device)
+    # ---- MD leg (the metric's second figure: MD steps/s on the 4,096-atom Li6PS5Cl cell): the public MolecularDynamics
+    # driver, Langevin NVT at 600 K, dt = 1 fs, friction 0.01 / fs, Maxwell-Boltzmann start, one efsm evaluation per
+    # step (graph rebuilt every step on the device).  Runs at N = 1 after the evaluation arms: 200 steps when the
+    # cell is the workload, 20 otherwise (--md-steps overrides; 0 skips).
     md = None
-    md_steps = args.md_steps if args.md_steps is not None else (200 if args.workload == "lipscl" else 0)
-    if rank == 0 and world == 1 and args.workload == "lipscl" and md_steps > 0:
+    md_steps = args.md_steps if args.md_steps is not None else (200 if args.workload == "lipscl" else 20)
+    if rank == 0 and world == 1 and md_steps > 0:
         from matris_b200.applications import MolecularDynamics
 
-        dyn = MolecularDynamics(crystals[0], model=model, ensemble="nvt", thermostat="langevin", temperature=600,
+        md_cell = crystals[0] if args.workload == "lipscl" else make_workload("lipscl", 1, "weak")[0][0]
+        dyn = MolecularDynamics(md_cell, model=model, ensemble="nvt", thermostat="langevin", temperature=600,
                                 starting_temperature=600, timestep=1.0, friction=0.01, task="efsm", device=device,
                                 seed=2)
         dyn.run(3)
@@ -506,7 +510,8 @@ def main():
             torch.cuda.synchronize()
             t_md = time.perf_counter() - t0
         md = {"metric": "md_steps_per_s", "value": md_steps / t_md, "steps": md_steps, "ms_per_step": 1e3 * t_md / md_steps,
-              "atoms": n_atoms, "setup": "Langevin (BAOAB) NVT 600 K, dt 1 fs, friction 0.01/fs, efsm every step, "
+              "atoms": len(md_cell.numbers), "workload": "amorphous Li6PS5Cl, 4096 atoms",
+              "setup": "Langevin (BAOAB) NVT 600 K, dt 1 fs, friction 0.01/fs, efsm every step, "
                                          "integrator state and graph rebuild on the device (MolecularDynamics device_resident=True)",
               "temperature_K_end": float(dyn.atoms.get_temperature()), "clocks": clocks_md.summary()}
 

@@ -57,15 +57,31 @@ const char* mb_last_cuda_error(void);
  * `counts`; after the stream has reached the call it holds
  *   counts[0] directed edges, [1] bonds, [2] triplets (the sizes actually needed, also when a capacity was too
  *   small), [3] isolated atoms, [4] image index outside +-127, [5] unpaired edges, [6] edge capacity too small,
- *   [7] triplet capacity too small, [8] triplets counted by source bond (must equal [2]).
+ *   [7] triplet capacity too small, [8] triplets counted by source bond (must equal [2]), [9] candidate list
+ *   unusable (Verlet-skin reuse, below).
  * Copy the 16 ints to the host together with whatever else the caller reads back and pass them to mb_graph_status,
  * which maps them to a status code; on MB_ERR_CAPACITY enlarge the buffers to counts[0] / counts[2] and call again
  * (in a molecular-dynamics loop the previous step's counts plus a margin make that rare).
+ *
+ * Neighbour-list reuse with a Verlet skin (the reference rebuilds from scratch at every step,
+ * matris/applications/base.py:96-97; the graphs here are identical to a rebuild, only cheaper to get):
+ *   1. a CANDIDATE build: the same call with cutoff + skin, flags = MB_GRAPH_EDGES_ONLY (it stops after the sorted
+ *      directed-edge list; the pairing / line-graph scratch and outputs may be NULL) and its own status block;
+ *      with run_if set it runs only when *run_if != 0, so it can be queued at every step;
+ *   2. every step: mb_graph_skin_check sets a flag when an atom is half the skin or more away from where it was at
+ *      the last candidate build; the candidate build is queued with run_if = flag; mb_graph_skin_commit then
+ *      records the positions (and clears the flag) if it ran; the step's graph is a build with cand_ptr / cand_nbr /
+ *      cand_img = edge_ptr / neighbor / image of the candidate build and cand_counts = its status block: the cell
+ *      search is replaced by a distance test of the candidates (same expression, same order: bit-identical edges).
+ *      If the candidate build did not succeed, counts[9] is set and nothing else is written (status
+ *      MB_ERR_CAPACITY: enlarge the candidate buffers, set the flag, repeat).
+ *   Nothing in this sequence synchronises with the host; lattices must not change between candidate builds.
  */
+#define MB_GRAPH_EDGES_ONLY 1
 typedef struct mb_graph {
   /* sizes and parameters (host) */
   int32_t n_atoms, n_struct, n_cells;
-  int32_t cap_edges, cap_triplets, pad;        /* capacities of the edge / triplet buffers below */
+  int32_t cap_edges, cap_triplets, flags;      /* capacities of the edge / triplet buffers below; MB_GRAPH_* bits */
   double cutoff, line_cutoff, tol;             /* tol < d <= cutoff ; line graph: target d <= lc, source d < lc */
   /* inputs (device) */
   const double* cart;         /* [n_atoms,3] Cartesian, not wrapped */
@@ -102,6 +118,12 @@ typedef struct mb_graph {
   int32_t* trip_src_ptr;      /* [cap_edges/2+1] CSR of triplets by source bond */
   int32_t* line_graph;        /* [cap_triplets,5] rows (centre atom, target bond, target DE, source bond, source DE) */
   int32_t* trip_src_perm;     /* [cap_triplets] triplet ids grouped by source bond (see trip_src_ptr) */
+  /* Verlet-skin reuse (device; all NULL for a plain build) */
+  const int32_t* run_if;      /* [1] when non-NULL and zero at launch time the call does nothing */
+  const int32_t* cand_ptr;    /* [n_atoms+1] candidate CSR by centre atom ... */
+  const int32_t* cand_nbr;    /* [candidates] ... neighbour atom ... */
+  const int32_t* cand_img;    /* [candidates,3] ... and image; sorted by (neighbour, image) within an atom */
+  const int32_t* cand_counts; /* [16] status block of the build that produced the candidates */
 } mb_graph;
 
 size_t mb_graph_scan_tmp_len(int64_t n);
@@ -109,6 +131,11 @@ int mb_graph_build(const mb_graph* g, void* stream);
 /* status code of a build from the host copy of counts[16]: MB_OK, MB_ERR_ISOLATED, MB_ERR_OVERFLOW (image index or
  * a count beyond int32), MB_ERR_CAPACITY, MB_ERR_UNPAIRED */
 int mb_graph_status(const int32_t* counts_host);
+/* flag[0] |= 1 if any atom is >= half_skin away from cart_ref (flag is int32[2]; flag[1] counts candidate rebuilds) */
+int mb_graph_skin_check(int32_t n_atoms, const double* cart, const double* cart_ref, double half_skin, int32_t* flag,
+                        void* stream);
+/* if flag[0]: cart_ref = cart, flag[0] = 0, flag[1] += 1.  Queue it after the conditional candidate build. */
+int mb_graph_skin_commit(int32_t n_atoms, const double* cart, double* cart_ref, int32_t* flag, void* stream);
 
 /* ------------------------------------------------------------------ dense row GEMM
  * out[r, 128*j + n] = epilogue( sum_k A_j[r, k] * W_j[n, k] )        j = 0..n_blocks-1

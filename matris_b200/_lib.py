@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libmatris_b200.so")
 
 MB_OK = 0
 MB_ERR_CAPACITY = 7
+MB_GRAPH_EDGES_ONLY = 1
 OUT_STORE, OUT_ADD, OUT_ATOMIC = 0, 1, 2
 
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
@@ -29,7 +30,7 @@ class IsolatedAtomError(ValueError):
 class MbGraph(C.Structure):
     _fields_ = [
         ("n_atoms", _i32), ("n_struct", _i32), ("n_cells", _i32),
-        ("cap_edges", _i32), ("cap_triplets", _i32), ("pad", _i32),
+        ("cap_edges", _i32), ("cap_triplets", _i32), ("flags", _i32),
         ("cutoff", C.c_double), ("line_cutoff", C.c_double), ("tol", C.c_double),
         ("cart", _vp), ("lattice", _vp), ("inv_lattice", _vp), ("atom_struct", _vp), ("grid", _vp),
         ("cell_ptr", _vp), ("cell_fill", _vp), ("cell_atoms", _vp), ("atom_cell", _vp), ("atom_wrap", _vp),
@@ -39,6 +40,7 @@ class MbGraph(C.Structure):
         ("center", _vp), ("neighbor", _vp), ("image", _vp), ("dist", _vp), ("rev", _vp), ("d2u", _vp),
         ("u2d", _vp), ("trip_ptr", _vp), ("trip_src_ptr", _vp),
         ("line_graph", _vp), ("trip_src_perm", _vp),
+        ("run_if", _vp), ("cand_ptr", _vp), ("cand_nbr", _vp), ("cand_img", _vp), ("cand_counts", _vp),
     ]
 
 
@@ -75,6 +77,8 @@ class MbGatedMlp(C.Structure):
 _SIGNATURES = {
     "mb_graph_build": [C.POINTER(MbGraph), _vp],
     "mb_graph_status": [C.POINTER(C.c_int32)],
+    "mb_graph_skin_check": [_i32, _vp, _vp, C.c_double, _vp, _vp],
+    "mb_graph_skin_commit": [_i32, _vp, _vp, _vp, _vp],
     "mb_gemm": [C.POINTER(MbGemmDesc), _vp],
     "mb_set_gemm_mode": [C.c_int],
     "mb_gemm_status": [C.POINTER(C.c_int), _vp],

@@ -16,6 +16,7 @@ Unit conventions of ``results`` (base.py:115-122): ``energy`` total eV,
 """
 from __future__ import annotations
 
+import functools
 import pickle
 
 import numpy as np
@@ -248,7 +249,7 @@ class StructOptimizer:
         obs = TrajectoryObserver(atoms)
         relax_fn = fire_relax
         if kwargs.get("device_resident", True) and isinstance(atoms, SimpleAtoms) and bool(np.all(atoms.get_pbc())):
-            relax_fn = fire_relax_device
+            relax_fn = functools.partial(fire_relax_device, skin=float(kwargs.get("skin", 0.0)))
         relax_fn(atoms, fmax=fmax, steps=steps, observer=obs, interval=loginterval, verbose=verbose)
         obs()
         if save_path is not None:
@@ -333,11 +334,13 @@ def fire_relax(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, f_inc=1
 
 
 def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, f_inc=1.1, f_dec=0.5, alpha0=0.1,
-                      f_alpha=0.99, max_step=0.2, observer=None, interval=1, verbose=False):
+                      f_alpha=0.99, max_step=0.2, observer=None, interval=1, verbose=False, skin=0.0):
     """``fire_relax`` with positions, velocities and forces kept on the GPU (an extension; the reference's loop,
     relax.py:116-123, goes through ASE on the host).  Per step the positions of the device-resident batch are updated
     in place, the graph is rebuilt on the device and the model evaluated; three scalars (max force, F.v and the
-    norms) come back to the host for the FIRE decisions, and the full state only when the observer logs."""
+    norms) come back to the host for the FIRE decisions, and the full state only when the observer logs.
+    ``skin`` > 0 (Angstrom) reuses the neighbour search between steps (graph.build_on_device); the graphs, and so
+    the trajectory, are the same as with a rebuild at every step."""
     import torch
 
     from .graph import build_on_device, set_positions_on_device
@@ -359,7 +362,7 @@ def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, 
     for it in range(steps):
         if it > 0:
             set_positions_on_device(g, x)
-            build_on_device(g)
+            build_on_device(g, skin=skin)
         out = model(g, task=task)
         f = out["f"][0].to(torch.float64)
         stats = torch.stack([(f * f).sum(dim=1).max().sqrt(), (f * v).sum(), f.norm(), v.norm()]).tolist()
@@ -388,7 +391,7 @@ def fire_relax_device(atoms, fmax=0.05, steps=500, dt=0.1, dt_max=1.0, n_min=5, 
         x = x + step
     # the loop ended on the step limit: evaluate the final positions so that the stored results match them
     set_positions_on_device(g, x)
-    build_on_device(g)
+    build_on_device(g, skin=skin)
     push_state(model(g, task=task))
     return steps
 
@@ -405,9 +408,9 @@ class MolecularDynamics:
                  trajectory=None, logfile: str | None = None, loginterval: int = 1,
                  crystal_feas_logfile: str | None = None, append_trajectory: bool = False, task: str = "efs",
                  device: str | None = "cuda", friction: float = 0.01, seed: int = 0,
-                 device_resident: bool = True) -> None:
+                 device_resident: bool = True, skin: float = 0.0) -> None:
         self.ensemble, self.thermostat = ensemble, thermostat
-        self.device_resident, self.seed = bool(device_resident), int(seed)
+        self.device_resident, self.seed, self.skin = bool(device_resident), int(seed), float(skin)
         self.temperature, self.timestep, self.friction = temperature, timestep, friction
         self.trajectory, self.logfile, self.loginterval = trajectory, logfile, loginterval
         self.crystal_feas_logfile = crystal_feas_logfile
@@ -540,7 +543,10 @@ class MolecularDynamics:
         memory; each step updates the batch's positions in place, rebuilds the graph there and evaluates the
         model; nothing is copied to the host until the run ends.  The thermostat noise comes from a torch CUDA
         generator seeded with ``seed + steps_done``, so a trajectory differs from the host loop's in its noise
-        only."""
+        only.  ``skin`` > 0 (constructor argument, Angstrom) reuses the neighbour search between steps: the
+        reference rebuilds its neighbour list at every step (base.py:96-97); here a candidate list with the cut-off
+        enlarged by the skin is rebuilt only when an atom has moved by half the skin, and every step's graph is
+        identical to the one a full rebuild gives."""
         import torch
 
         from .graph import build_on_device, set_positions_on_device
@@ -572,7 +578,7 @@ class MolecularDynamics:
             else:
                 x = x + dt * p / m
             set_positions_on_device(g, x)
-            build_on_device(g)
+            build_on_device(g, skin=self.skin)
             out = model(g, task=task)
             f = out["f"][0].to(torch.float64)
             p = p + 0.5 * dt * f

@@ -28,7 +28,7 @@ constexpr int SCAN_CHUNK = GB_THREADS * SCAN_ITEMS;
 // counts[] layout (device, int32[16]); also the status block the caller reads back
 enum {
   CT_EDGES = 0, CT_BONDS = 1, CT_TRIPLETS = 2, CT_ISOLATED = 3, CT_IMAGE_OVERFLOW = 4, CT_UNPAIRED = 5,
-  CT_EDGE_CAPACITY = 6, CT_TRIPLET_CAPACITY = 7, CT_TRIPLETS_BY_SOURCE = 8
+  CT_EDGE_CAPACITY = 6, CT_TRIPLET_CAPACITY = 7, CT_TRIPLETS_BY_SOURCE = 8, CT_CANDIDATES_UNUSABLE = 9
 };
 
 // ---------------------------------------------------------------- block / grid exclusive scan
@@ -246,6 +246,56 @@ __device__ __forceinline__ void neighbors_of_atom(const mb_graph& g, int i, int 
   }
 }
 
+// Neighbour search of one atom among its candidates (Verlet-skin reuse): the candidate list is the sorted directed-edge
+// list of an earlier build with the cut-off enlarged by the skin, so it names every pair that can be inside the
+// cut-off while no atom has moved by half the skin; the distance is recomputed with the same expression as above
+// (same atom, same image, same operation order), so the surviving edges and their lengths are the fresh build's.
+template <bool FILL>
+__device__ __forceinline__ void neighbors_from_candidates(const mb_graph& g, int i, int lane) {
+  const int b = g.atom_struct[i];
+  double L[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) L[k] = g.lattice[9 * b + k];
+  const double xi = g.cart[3 * i], yi = g.cart[3 * i + 1], zi = g.cart[3 * i + 2];
+  const int out_base = FILL ? g.edge_ptr[i] : 0;
+  const double cutoff = g.cutoff, tol = g.tol;
+  const int c0 = g.cand_ptr[i], c1 = g.cand_ptr[i + 1];
+  int count = 0;
+  for (int cb = c0; cb < c1; cb += 32) {
+    const int c = cb + lane;
+    bool ok = false;
+    int j = 0, n0 = 0, n1 = 0, n2 = 0;
+    double d = 0.0;
+    if (c < c1) {
+      j = g.cand_nbr[c];
+      n0 = g.cand_img[3 * c], n1 = g.cand_img[3 * c + 1], n2 = g.cand_img[3 * c + 2];
+      const double f0 = (double)n0, f1 = (double)n1, f2 = (double)n2;
+      const double sx = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[0]), __dmul_rn(f1, L[3])), __dmul_rn(f2, L[6]));
+      const double sy = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[1]), __dmul_rn(f1, L[4])), __dmul_rn(f2, L[7]));
+      const double sz = __dadd_rn(__dadd_rn(__dmul_rn(f0, L[2]), __dmul_rn(f1, L[5])), __dmul_rn(f2, L[8]));
+      const double dx = __dsub_rn(__dadd_rn(g.cart[3 * j], sx), xi);
+      const double dy = __dsub_rn(__dadd_rn(g.cart[3 * j + 1], sy), yi);
+      const double dz = __dsub_rn(__dadd_rn(g.cart[3 * j + 2], sz), zi);
+      const double q = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+      d = __dsqrt_rn(q);
+      ok = (d > tol) && (d <= cutoff);
+    }
+    const unsigned mask = __ballot_sync(0xffffffffu, ok);
+    if (FILL && ok) {
+      const int pos = out_base + count + __popc(mask & ((1u << lane) - 1u));
+      if (pos < g.cap_edges) {
+        g.key_unsorted[pos] = pack_key(j, n0, n1, n2);
+        g.dist_unsorted[pos] = d;
+      }
+    }
+    count += __popc(mask);
+  }
+  if (!FILL && lane == 0) {
+    g.edge_ptr[i] = count;
+    if (count == 0) atomicAdd(&g.counts[CT_ISOLATED], 1);
+  }
+}
+
 // ---------------------------------------------------------------- the kernel
 __global__ void __launch_bounds__(GB_THREADS, 1) k_graph_build(const mb_graph g) {
   cg::grid_group grid = cg::this_grid();
@@ -255,13 +305,33 @@ __global__ void __launch_bounds__(GB_THREADS, 1) k_graph_build(const mb_graph g)
   const int warp_g = (int)(tid >> 5), n_warps = (int)(nth >> 5);
   const int n_atoms = g.n_atoms, n_cells = g.n_cells;
   int32_t* const counts = g.counts;
+  // A conditional build (the candidate list of a Verlet-skin loop is rebuilt only when an atom has moved too far):
+  // every thread reads the same word, so the whole grid stays or leaves, before any barrier and any write.
+  if (g.run_if && *g.run_if == 0) return;
+  const bool from_candidates = g.cand_ptr != nullptr;
+  if (from_candidates) {
+    // the candidate list is usable only if the build that made it ran to its end
+    const int32_t* cc = g.cand_counts;
+    const bool usable = cc[CT_EDGES] > 0 && !cc[CT_EDGE_CAPACITY] && !cc[CT_IMAGE_OVERFLOW] && !cc[CT_ISOLATED] &&
+                        !(cc[CT_EDGES] & 1);
+    if (!usable) {
+      if (tid < 16) counts[tid] = tid == CT_CANDIDATES_UNUSABLE ? 1 : 0;
+      return;
+    }
+  }
 
   // ---- clear the cell counters and the status block
-  for (int64_t i = tid; i <= n_cells; i += nth) g.cell_ptr[i] = 0;
-  for (int64_t i = tid; i < n_cells; i += nth) g.cell_fill[i] = 0;
+  if (!from_candidates) {
+    for (int64_t i = tid; i <= n_cells; i += nth) g.cell_ptr[i] = 0;
+    for (int64_t i = tid; i < n_cells; i += nth) g.cell_fill[i] = 0;
+  }
   if (tid < 16) counts[tid] = 0;
   grid.sync();
 
+  if (from_candidates) {
+    for (int i = warp_g; i < n_atoms; i += n_warps) neighbors_from_candidates<false>(g, i, lane);
+    grid.sync();
+  } else {
   // ---- bin the atoms
   for (int64_t i = tid; i < n_atoms; i += nth) {
     const int b = g.atom_struct[i];
@@ -296,6 +366,7 @@ __global__ void __launch_bounds__(GB_THREADS, 1) k_graph_build(const mb_graph g)
   // ---- directed edges: count, scan, fill
   for (int ii = warp_g; ii < n_atoms; ii += n_warps) neighbors_of_atom<false>(g, g.cell_atoms[ii], lane, stage[wib]);
   grid.sync();
+  }
   grid_scan(grid, g.edge_ptr, g.edge_ptr, n_atoms, g.scan_tmp);
   const int ne = g.edge_ptr[n_atoms];
   if (tid == 0) counts[CT_EDGES] = ne;
@@ -307,7 +378,11 @@ __global__ void __launch_bounds__(GB_THREADS, 1) k_graph_build(const mb_graph g)
     if (tid == 0 && (ne & 1)) counts[CT_UNPAIRED] = 1;
     return;
   }
-  for (int ii = warp_g; ii < n_atoms; ii += n_warps) neighbors_of_atom<true>(g, g.cell_atoms[ii], lane, stage[wib]);
+  if (from_candidates) {
+    for (int i = warp_g; i < n_atoms; i += n_warps) neighbors_from_candidates<true>(g, i, lane);
+  } else {
+    for (int ii = warp_g; ii < n_atoms; ii += n_warps) neighbors_of_atom<true>(g, g.cell_atoms[ii], lane, stage[wib]);
+  }
   grid.sync();
 
   // ---- rank sort of each atom's out-edges by key (neighbour, image); warp per atom
@@ -328,6 +403,7 @@ __global__ void __launch_bounds__(GB_THREADS, 1) k_graph_build(const mb_graph g)
     }
   }
   grid.sync();
+  if (g.flags & MB_GRAPH_EDGES_ONLY) return;  // a candidate build: the sorted directed-edge list is all that is read
 
   // ---- reverse edge of e = (i, j, n): the edge (j, i, -n), found by binary search in j's segment
   // edge_rank doubles as scratch here: [0, ne) first-of-pair flags, [ne, 2 ne + 1) their scan
@@ -470,12 +546,16 @@ static int check_graph(const mb_graph* g) {
   if (!g || g->n_atoms <= 0 || g->n_struct <= 0 || g->n_cells <= 0 || g->cap_edges < 2 || g->cap_triplets < 0)
     return MB_ERR_INVALID;
   if (!g->cart || !g->lattice || !g->inv_lattice || !g->atom_struct || !g->grid || !g->counts) return MB_ERR_INVALID;
-  if (!g->cell_ptr || !g->cell_fill || !g->cell_atoms || !g->atom_cell || !g->atom_wrap || !g->scan_tmp ||
-      !g->edge_ptr || !g->key_unsorted || !g->dist_unsorted || !g->key || !g->atom_counts || !g->edge_rank ||
-      !g->bond_counts || !g->edge_flag)
+  const bool from_candidates = g->cand_ptr != nullptr, edges_only = (g->flags & MB_GRAPH_EDGES_ONLY) != 0;
+  if (from_candidates && (!g->cand_nbr || !g->cand_img || !g->cand_counts)) return MB_ERR_INVALID;
+  if (!from_candidates && (!g->cell_ptr || !g->cell_fill || !g->cell_atoms || !g->atom_cell || !g->atom_wrap))
     return MB_ERR_INVALID;
-  if (!g->center || !g->neighbor || !g->image || !g->dist || !g->rev || !g->d2u || !g->u2d || !g->trip_ptr ||
-      !g->trip_src_ptr || (g->cap_triplets > 0 && (!g->line_graph || !g->trip_src_perm)))
+  if (!g->scan_tmp || !g->edge_ptr || !g->key_unsorted || !g->dist_unsorted || !g->key) return MB_ERR_INVALID;
+  if (!g->center || !g->neighbor || !g->image || !g->dist) return MB_ERR_INVALID;
+  if (edges_only) return MB_OK;
+  if (!g->atom_counts || !g->edge_rank || !g->bond_counts || !g->edge_flag) return MB_ERR_INVALID;
+  if (!g->rev || !g->d2u || !g->u2d || !g->trip_ptr || !g->trip_src_ptr ||
+      (g->cap_triplets > 0 && (!g->line_graph || !g->trip_src_perm)))
     return MB_ERR_INVALID;
   return MB_OK;
 }
@@ -508,12 +588,56 @@ extern "C" int mb_graph_build(const mb_graph* g, void* stream_) {
   return MB_OK;
 }
 
+// ---- Verlet-skin bookkeeping: has any atom moved by half the skin since the candidate list was built?
+namespace mb {
+__global__ void k_skin_check(int n_atoms, const double* __restrict__ cart, const double* __restrict__ ref, double limit2,
+                             int32_t* flag) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  bool far = false;
+  if (i < n_atoms) {
+    const double dx = cart[3 * i] - ref[3 * i], dy = cart[3 * i + 1] - ref[3 * i + 1], dz = cart[3 * i + 2] - ref[3 * i + 2];
+    const double d2 = dx * dx + dy * dy + dz * dz;
+    far = !(d2 < limit2);  // also true for a NaN position: the full search then reports what it finds
+  }
+  if (__syncthreads_or(far) && threadIdx.x == 0) atomicOr(flag, 1);
+}
+
+// One CTA: the flag is cleared only after every thread has acted on it.
+__global__ void __launch_bounds__(1024) k_skin_commit(int n_atoms, const double* __restrict__ cart, double* __restrict__ ref,
+                                                      int32_t* flag) {
+  const bool rebuilt = flag[0] != 0;
+  if (rebuilt)
+    for (int i = threadIdx.x; i < 3 * n_atoms; i += blockDim.x) ref[i] = cart[i];
+  __syncthreads();
+  if (threadIdx.x == 0 && rebuilt) {
+    flag[0] = 0;
+    flag[1] += 1;
+  }
+}
+}  // namespace mb
+
+extern "C" int mb_graph_skin_check(int32_t n_atoms, const double* cart, const double* cart_ref, double half_skin,
+                                   int32_t* flag, void* stream_) {
+  if (n_atoms <= 0 || !cart || !cart_ref || !flag || !(half_skin > 0.0)) return MB_ERR_INVALID;
+  k_skin_check<<<(n_atoms + 255) / 256, 256, 0, (cudaStream_t)stream_>>>(n_atoms, cart, cart_ref, half_skin * half_skin, flag);
+  MB_LAUNCH_CHECK("k_skin_check");
+  return MB_OK;
+}
+
+extern "C" int mb_graph_skin_commit(int32_t n_atoms, const double* cart, double* cart_ref, int32_t* flag, void* stream_) {
+  if (n_atoms <= 0 || !cart || !cart_ref || !flag) return MB_ERR_INVALID;
+  k_skin_commit<<<1, 1024, 0, (cudaStream_t)stream_>>>(n_atoms, cart, cart_ref, flag);
+  MB_LAUNCH_CHECK("k_skin_commit");
+  return MB_OK;
+}
+
 extern "C" int mb_graph_status(const int32_t* counts_host) {
   if (!counts_host) return MB_ERR_INVALID;
   if (counts_host[CT_IMAGE_OVERFLOW]) return MB_ERR_OVERFLOW;
   if (counts_host[CT_ISOLATED]) return MB_ERR_ISOLATED;
   if (counts_host[CT_EDGES] < 0 || counts_host[CT_TRIPLETS] < 0) return MB_ERR_OVERFLOW;
-  if (counts_host[CT_EDGE_CAPACITY] || counts_host[CT_TRIPLET_CAPACITY]) return MB_ERR_CAPACITY;
+  if (counts_host[CT_EDGE_CAPACITY] || counts_host[CT_TRIPLET_CAPACITY] || counts_host[CT_CANDIDATES_UNUSABLE])
+    return MB_ERR_CAPACITY;
   if (counts_host[CT_UNPAIRED]) return MB_ERR_UNPAIRED;
   if (counts_host[CT_TRIPLETS] != counts_host[CT_TRIPLETS_BY_SOURCE]) return MB_ERR_INVALID;
   return MB_OK;

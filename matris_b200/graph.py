@@ -215,11 +215,53 @@ class _GraphBuffers:
         self.counts_host = torch.zeros(64, dtype=torch.int32).pin_memory()
 
 
-def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None) -> BatchedGraph:
+class _Candidates:
+    """Verlet-skin state of one batch: the sorted directed-edge list of a build with the cut-off enlarged by the skin
+    (the candidates), the positions it was built at, and the flag word the device-side displacement check sets."""
+
+    def __init__(self, g: BatchedGraph, skin: float, cap: int, device):
+        lib = _lib.load()
+        self.skin, self.cap = float(skin), int(cap)
+        n_atoms = g.n_atoms
+        n_per = np.asarray(g.atoms_per_graph, dtype=np.int64)
+        grid, self.n_cells = cell_grid(g.lattice64_host, n_per, g.cutoff + self.skin)
+        self.grid = torch.from_numpy(grid).to(device)
+        i64 = lambda n: torch.empty(max(int(n), 1), dtype=torch.int64, device=device)  # noqa: E731
+        f64 = lambda n: torch.empty(max(int(n), 1), dtype=torch.float64, device=device)  # noqa: E731
+        self.bufs = dict(
+            cell_ptr=_i32(self.n_cells + 1, device), cell_fill=_i32(self.n_cells, device),
+            cell_atoms=_i32(n_atoms, device), atom_cell=_i32(4 * n_atoms, device), atom_wrap=_i32(4 * n_atoms, device),
+            scan_tmp=_i32(lib.mb_graph_scan_tmp_len(max(n_atoms, self.n_cells, cap)), device),
+            key_unsorted=i64(cap), dist_unsorted=f64(cap), key=i64(cap),
+            edge_ptr=_i32(n_atoms + 1, device), center=_i32(cap, device), neighbor=_i32(cap, device),
+            image=_i32(3 * cap, device), dist=f64(cap))
+        self.cart_ref = torch.zeros(n_atoms, 3, dtype=torch.float64, device=device)
+        self.flag = torch.tensor([1, 0], dtype=torch.int32, device=device)  # [rebuild wanted, rebuilds so far]
+
+    def invalidate(self):
+        """Force a candidate rebuild at the next call (after a change of the lattices)."""
+        self.flag[:1].fill_(1)
+
+
+def _candidate_capacity(g: BatchedGraph, skin: float) -> int:
+    n = np.asarray(g.atoms_per_graph, dtype=np.float64)
+    lat = g.lattice64_host
+    vol = np.abs(np.einsum("bi,bi->b", lat[:, 0], np.cross(lat[:, 1], lat[:, 2])))
+    cap = int(1.25 * float((n * 4.0 / 3.0 * np.pi * (g.cutoff + skin) ** 3 * n / vol).sum())) + 1024
+    return cap + (cap & 1)
+
+
+def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None, skin: float = 0.0) -> BatchedGraph:
     """Build the graph of the device-resident inputs of ``g`` (positions, lattices, cell grid) and attach the outputs.
     Can be called again after ``g.cart64`` changed on the device: the capacity buffers of the previous build are
-    reused.  One asynchronous launch (mb_graph_build) and one copy of the 16-int status block to the host, which is
-    the only synchronisation: the sizes of the model's tensors depend on the counts in it."""
+    reused.  One asynchronous launch (mb_graph_build) and one copy of the status block to the host, which is
+    the only synchronisation: the sizes of the model's tensors depend on the counts in it.
+
+    ``skin`` > 0 (Angstrom) reuses the neighbour search across calls: a candidate list with the cut-off enlarged by
+    the skin is kept with the batch and rebuilt (on the device, decided on the device) only when some atom has moved
+    by half the skin since; every call then tests the candidates instead of searching the cells.  The graph is the
+    one a fresh build gives, bit for bit.  The lattices must stay as they are between calls (fixed-cell MD and
+    relaxation); after writing to them call ``g._candidates.invalidate()``."""
     lib = _lib.load()
     device = g.cart64.device
     n_atoms, n_struct, n_cells = g.n_atoms, g.n_struct, g.n_cells
@@ -228,29 +270,68 @@ def build_on_device(g: BatchedGraph, tol: float = 1e-8, stream=None) -> BatchedG
         buf = getattr(g, "_buffers", None)
         if buf is None:
             buf = g._buffers = _GraphBuffers(g, *_capacity_estimate(g), device)
-        for attempt in range(4):
+        cand = None
+        if skin > 0.0:
+            cand = getattr(g, "_candidates", None)
+            if cand is None or cand.skin != float(skin):
+                cand = g._candidates = _Candidates(g, skin, _candidate_capacity(g, skin), device)
+
+        def base_desc():
             m = _lib.MbGraph()
-            m.n_atoms, m.n_struct, m.n_cells = n_atoms, n_struct, n_cells
-            m.cap_edges, m.cap_triplets = buf.cap_e, buf.cap_t
-            m.cutoff, m.line_cutoff, m.tol = g.cutoff, g.line_cutoff, float(tol)
+            m.n_atoms, m.n_struct = n_atoms, n_struct
+            m.tol = float(tol)
             m.cart, m.lattice, m.inv_lattice = g.cart64.data_ptr(), g.lattice64.data_ptr(), g.inv_lattice64.data_ptr()
-            m.atom_struct, m.grid = g.atom_struct.data_ptr(), g.grid.data_ptr()
+            m.atom_struct = g.atom_struct.data_ptr()
+            return m
+
+        for attempt in range(6):
+            if cand is not None:
+                # displacement check -> candidate rebuild if the flag is set -> record the positions it was built at
+                _lib.call("mb_graph_skin_check", n_atoms, g.cart64.data_ptr(), cand.cart_ref.data_ptr(), 0.5 * cand.skin,
+                          cand.flag.data_ptr(), st)
+                c = base_desc()
+                c.n_cells, c.cap_edges, c.cap_triplets, c.flags = cand.n_cells, cand.cap, 0, _lib.MB_GRAPH_EDGES_ONLY
+                c.cutoff, c.line_cutoff, c.grid = g.cutoff + cand.skin, 0.0, cand.grid.data_ptr()
+                for k, v in cand.bufs.items():
+                    setattr(c, k, v.data_ptr())
+                c.counts = buf.counts.data_ptr() + 64  # ints 16..31 of the block that is copied to the host
+                c.run_if = cand.flag.data_ptr()
+                _lib.call("mb_graph_build", C.byref(c), st)
+                _lib.call("mb_graph_skin_commit", n_atoms, g.cart64.data_ptr(), cand.cart_ref.data_ptr(),
+                          cand.flag.data_ptr(), st)
+            m = base_desc()
+            m.n_cells, m.cap_edges, m.cap_triplets = n_cells, buf.cap_e, buf.cap_t
+            m.cutoff, m.line_cutoff, m.grid = g.cutoff, g.line_cutoff, g.grid.data_ptr()
             for k, v in buf.scratch.items():
                 setattr(m, k, v.data_ptr())
             for k, v in buf.out.items():
                 setattr(m, k, v.data_ptr())
             m.counts = buf.counts.data_ptr()
+            if cand is not None:
+                m.cand_ptr, m.cand_nbr, m.cand_img = (cand.bufs[k].data_ptr() for k in ("edge_ptr", "neighbor", "image"))
+                m.cand_counts = buf.counts.data_ptr() + 64
             _lib.call("mb_graph_build", C.byref(m), st)
             buf.counts_host.copy_(buf.counts, non_blocking=True)
             torch.cuda.current_stream().synchronize() if stream is None else torch.cuda.synchronize()
             counts = buf.counts_host.numpy()
+            if cand is not None and counts[9]:
+                # the candidate build did not run to its end: a real error, or its buffers were too small
+                cstat = lib.mb_graph_status(counts[16:32].ctypes.data_as(C.POINTER(C.c_int32)))
+                if cstat != _lib.MB_ERR_CAPACITY:
+                    _lib.check(cstat if cstat != _lib.MB_OK else _lib.MB_ERR_INVALID, "mb_graph_build (candidates)")
+                rebuilds = int(cand.flag[1])
+                cand = g._candidates = _Candidates(g, skin, int(1.1 * counts[16]) + 64, device)
+                cand.flag[1] = rebuilds
+                continue
             status = lib.mb_graph_status(counts.ctypes.data_as(C.POINTER(C.c_int32)))
             if status != _lib.MB_ERR_CAPACITY:
                 break
             # enlarge to what this build needed (plus a margin for the steps to come) and run it again
             cap_e = max(buf.cap_e, int(1.1 * counts[0]) + 64)
             cap_t = int(1.1 * counts[2]) + 64 if counts[7] else max(buf.cap_t, int(1.5 * buf.cap_t * cap_e / buf.cap_e))
+            old = buf
             buf = g._buffers = _GraphBuffers(g, cap_e, cap_t, device)
+            buf.counts.copy_(old.counts)  # ints 16..31: the status of the candidate build, which is still valid
         _lib.check(status, "mb_graph_build")
         ne, nb, nt = int(counts[0]), int(counts[1]), int(counts[2])
         g.n_edges, g.n_bonds, g.n_triplets = ne, nb, nt

@@ -81,6 +81,25 @@ def test_device_resident_nve_follows_the_host_loop():
     report("device-resident NVE momenta vs host loop", torch.tensor(runs[1][1]), torch.tensor(runs[0][1]), 1e-5)
 
 
+def test_md_with_a_verlet_skin_retraces_the_rebuild_every_step_trajectory():
+    """Neighbour-list reuse changes how the graph is found, not the graph: a hot NVE run (atoms move far enough to
+    trigger candidate rebuilds) with a skin must retrace the run that rebuilds at every step, up to the summation
+    order of the force scatter (float atomics)."""
+    from matris_b200 import MatRIS
+    from matris_b200.applications import MolecularDynamics
+    model = MatRIS.from_dict(random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=0)).to("cuda")
+    runs = []
+    for skin in (0.0, 0.4):
+        md = MolecularDynamics(_atoms(workloads.random_crystals(1, seed=3)[0]), model=model, ensemble="nve", timestep=2.0,
+                               starting_temperature=3000, task="ef", device="cuda", seed=5, skin=skin)
+        md.run(40)
+        runs.append((md.atoms.get_positions(), md.atoms.get_momenta()))
+    moved = np.abs(runs[0][0] - workloads.random_crystals(1, seed=3)[0].cart).max()
+    assert moved > 0.2, f"atoms moved {moved:.3f} A only: no candidate rebuild was exercised"
+    report("NVE positions with skin 0.4 vs rebuild every step", torch.tensor(runs[1][0]), torch.tensor(runs[0][0]), 1e-6)
+    report("NVE momenta with skin 0.4 vs rebuild every step", torch.tensor(runs[1][1]), torch.tensor(runs[0][1]), 1e-5)
+
+
 def test_device_resident_evaluation_equals_predict_at_the_same_positions():
     """The loops that keep their state on the GPU derive the model's float32 positions from the float64 ones on the
     device; the results stored at the end must be those of a fresh evaluation of the final positions."""

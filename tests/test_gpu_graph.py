@@ -153,3 +153,68 @@ def test_periodic_image_beyond_the_packed_range_is_an_error_before_anything_is_p
     cart[0] += 200 * cr.lattice[0]
     with pytest.raises(MbError, match="out of range"):
         build_batched_graph([cr.numbers], [cart], [cr.lattice])
+
+
+GRAPH_FIELDS = ("edge_ptr", "center", "neighbor", "image", "dist64", "rev", "d2u", "u2d", "trip_ptr", "trip_src_ptr",
+                "line_graph", "trip_src_perm")
+
+
+def _same_graph(a, b, what):
+    assert (a.n_edges, a.n_bonds, a.n_triplets) == (b.n_edges, b.n_bonds, b.n_triplets), what
+    for k in GRAPH_FIELDS:
+        assert torch.equal(getattr(a, k), getattr(b, k)), f"{what}: {k} differs from the fresh build"
+
+
+@pytest.mark.parametrize("skin", [0.3, 1.0])
+def test_verlet_skin_reuse_gives_the_fresh_graph(skin):
+    """A random walk of all atoms: every step's graph from the candidate list must be bit-identical to a full rebuild
+    at the same positions, across steps that keep the list and steps that trigger its rebuild; the list must be
+    rebuilt when (and only when) an atom has moved half the skin since the last rebuild."""
+    from matris_b200.graph import HostBatch, build_on_device, set_positions_on_device, upload
+    crystals = workloads.random_crystals(6, seed=11) + [workloads.cu_fcc()]
+    args = ([c.numbers for c in crystals], [c.cart for c in crystals], [c.lattice for c in crystals])
+    g_skin = upload(HostBatch(*args, 6.0), 6.0, 4.0, torch.device("cuda"))
+    g_full = upload(HostBatch(*args, 6.0), 6.0, 4.0, torch.device("cuda"))
+    x = g_skin.cart64.clone()
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    ref = x.clone()
+    expected_rebuilds = 0
+    for step in range(14):
+        if step:
+            scale = 0.25 if step == 9 else 0.03   # one large move among small ones
+            x = x + scale * torch.randn(x.shape, dtype=torch.float64, device="cuda", generator=gen)
+        moved = float((x - ref).norm(dim=1).max())
+        if step == 0 or moved >= 0.5 * skin:
+            expected_rebuilds += 1
+            ref = x.clone()
+        for g in (g_skin, g_full):
+            set_positions_on_device(g, x)
+        build_on_device(g_skin, skin=skin)
+        build_on_device(g_full)
+        _same_graph(g_skin, g_full, f"skin {skin}, step {step}")
+        assert int(g_skin._candidates.flag[1]) == expected_rebuilds, f"step {step}: moved {moved:.3f}"
+    assert expected_rebuilds < 14, "the walk never reused a list: the test would show nothing"
+
+
+def test_verlet_skin_candidate_capacity_grows():
+    """A candidate buffer that is too small is enlarged and the build repeated; the result is still the fresh graph."""
+    from matris_b200 import graph as G
+    crystals = workloads.random_crystals(4, seed=5)
+    args = ([c.numbers for c in crystals], [c.cart for c in crystals], [c.lattice for c in crystals])
+    g_skin = G.upload(G.HostBatch(*args, 6.0), 6.0, 4.0, torch.device("cuda"))
+    g_full = G.upload(G.HostBatch(*args, 6.0), 6.0, 4.0, torch.device("cuda"))
+    g_skin._candidates = G._Candidates(g_skin, 0.5, 512, torch.device("cuda"))  # far too few candidates
+    G.build_on_device(g_skin, skin=0.5)
+    G.build_on_device(g_full)
+    assert g_skin._candidates.cap > 512
+    _same_graph(g_skin, g_full, "after the candidate buffers grew")
+
+
+def test_verlet_skin_isolated_atom_is_reported():
+    from matris_b200 import graph as G
+    from matris_b200._lib import MbError
+    lat = np.eye(3) * 30.0
+    g = G.upload(G.HostBatch([np.array([29, 29])], [np.array([[0.0, 0, 0], [15.0, 15, 15]])], [lat], 6.0), 6.0, 4.0,
+                 torch.device("cuda"))
+    with pytest.raises((ValueError, MbError)):
+        G.build_on_device(g, skin=0.5)
