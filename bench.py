@@ -417,7 +417,7 @@ def main():
     if rank == 0:
         torch.cuda.synchronize()
         with ClockSampler(local_rank) as clocks_peak:
-            tf32_peak, peak_ms = ops.mma_rate("tf32", 400000)  # >= 50 ms of resident-operand tcgen05.mma issue
+            mma_peak, peak_ms = ops.mma_rate("bf16", 400000)  # >= 50 ms of resident-operand tcgen05.mma issue
         _lib.profile = []
         step_resident(gather=False)  # rank 0 only: no collective in here
         torch.cuda.synchronize()
@@ -452,21 +452,30 @@ def main():
         peak_gb = float(peaks.get("hbm_gbs", 6650.0))
         src = "measured" if peaks else "fallback"
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
+        ach_gb = gemm_bytes / (gemm_ms * 1e-3) / 1e9
         n_gemm = sum(per[k][0] for k in GEMM_CALLS if k in per)
-        # DRAM traffic per launch: an ncu capture of a 151,552-row K=384 N=256 launch measured 0.906 x (A rows read +
-        # output rows written); scaled here to the average launch of the step by its algorithmic bytes.
+        # DRAM traffic per launch: ncu captures of 151,552-row launches measured 0.91 - 0.95 x the algorithmic bytes
+        # (A rows read + gate / residual rows read + output rows written); scaled here to the average launch of the
+        # step by its algorithmic bytes.
         pk = clocks_peak.summary()
         roofline = {"kernel": "k_gemm_ps + k_gated_fwd (mb_gemm, mb_gated_mlp_fwd)", "bound": "tensor", "achieved": ach,
-                    "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.906 * gemm_bytes / n_gemm,
-                    "traffic_note": "bytes per average launch, scaled from one ncu capture by the algorithmic bytes",
+                    "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf, "traffic": 0.93 * gemm_bytes / n_gemm,
+                    "traffic_note": "bytes per average launch, scaled from ncu captures by the algorithmic bytes",
                     "peak_source": src + " bf16 sustained",
                     "launches": n_gemm, "avg_launch_ms": gemm_ms / n_gemm,
-                    "flops_per_step": gemm_flops, "tf32_issued_tflops": 3.0 * ach,
-                    "tf32_peak_timed_tflops": tf32_peak, "tf32_peak_timed_ms": peak_ms,
-                    "tf32_peak_timed_sm_mhz": pk["sm_mhz"], "frac_of_tf32_peak": 3.0 * ach / tf32_peak,
-                    "note": "tcgen05 kind::tf32 with a 3-term operand split: 3 tensor FLOPs are issued per algorithmic "
-                            "FLOP; tf32_peak_timed = CUDA-event-timed tcgen05.mma issue loop on resident operands in "
-                            "this run (mb_bench_mma_rate), with the SM clock sampled during it"}
+                    "flops_per_step": gemm_flops, "mma_kind": "kind::f16, 3xBF16 operand split",
+                    "mma_issued_tflops": 3.0 * ach, "mma_peak_timed_tflops": mma_peak, "mma_peak_timed_ms": peak_ms,
+                    "mma_peak_timed_sm_mhz": pk["sm_mhz"], "frac_of_mma_peak": 3.0 * ach / mma_peak,
+                    "hbm_view": {"algorithmic_bytes_per_step": gemm_bytes, "achieved_gbs": ach_gb, "peak_gbs": peak_gb,
+                                 "frac": ach_gb / peak_gb,
+                                 "floor_ms_hbm": gemm_bytes / (peak_gb * 1e9) * 1e3,
+                                 "floor_ms_tensor": gemm_flops / (peak_tf * 1e12) * 1e3,
+                                 "note": "with the activations these launches read and write (fp32 rows, z1 / z2 kept "
+                                         "for the backward) their HBM floor is above their tensor floor: the HBM "
+                                         "fraction is what the time follows"},
+                    "note": "tcgen05 kind::f16 with a 3-term bf16 operand split: 3 tensor FLOPs are issued per "
+                            "algorithmic FLOP; mma_peak_timed = CUDA-event-timed tcgen05.mma issue loop on resident "
+                            "operands in this run (mb_bench_mma_rate), with the SM clock sampled during it"}
         gms = sum(per[k][1] for k in per if k.startswith("mb_graph"))
         gbytes = 26.0 * g.n_edges + 20.0 * g.n_triplets + 16.0 * g.n_atoms
         roofline_graph = {"kernels": "mb_graph_*", "bound": "hbm", "achieved": gbytes / (gms * 1e-3) / 1e9,

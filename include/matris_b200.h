@@ -385,11 +385,13 @@ int mb_edge_geometry_bwd(int32_t n_atoms, int32_t n_struct, int64_t n_edges, con
  * Limits and rules:
  *  - at most MB_STATIC_MAX_EDGES directed edges and MB_STATIC_MAX_ATOMS atoms per call; larger problems are
  *    rejected with MB_ERR_TOO_LARGE before anything is launched (use mb_edge_geometry_bwd for those);
- *  - the array (3*MB_STATIC_MAX_EDGES + 9*MB_STATIC_MAX_ATOMS floats, about 7.1 MB) is part of the library image:
- *    every GPU that loads the library holds it until the process exits;
+ *  - the array (3*MB_STATIC_MAX_EDGES + 9*MB_STATIC_MAX_ATOMS floats = 7,471,104 bytes: 7.5 MB, 7.1 MiB) is part of
+ *    the library image: every GPU that loads the library holds it until the process exits;
  *  - the first call on a device looks the array's device address up (with that device current) and remembers it;
- *    make that first call during set-up, before any stream capture is started;
- *  - it calls no cudaMalloc, cudaFree or other allocating routine;
+ *    where the CUDA runtime loads modules lazily, that first call is also what loads the module, and the driver
+ *    allocates the module's device memory (the array included) then.  Make that first call during set-up, from one
+ *    thread, before any stream capture is started;
+ *  - after that first call it calls no cudaMalloc, cudaFree or other allocating routine;
  *  - all calls share the one array and it keeps whatever the previous call left there.  Nothing has to start at
  *    zero: each call overwrites every element it later reads.  Two calls that overlap on the GPU (different
  *    streams, or different host threads without ordering) race on the array: serialise them.

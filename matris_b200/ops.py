@@ -124,7 +124,9 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
     if _lib.profile is not None:
         _lib.profile_meta = dict(flops=sum(2.0 * n_rows * D * D * len(b["srcs"]) for b in blocks), rows=int(n_rows),
                                  k=D * len(blocks[0]["srcs"]), n=D * len(blocks),
-                                 bytes=4.0 * n_rows * D * (len(blocks[0]["srcs"]) + len(blocks)))
+                                 bytes=4.0 * n_rows * D * (len(blocks[0]["srcs"]) + len(blocks) +
+                                                           sum(b.get("gate") is not None for b in blocks) +
+                                                           sum(b.get("res") is not None for b in blocks)))
     call("mb_gemm", C.byref(_lib.MbGemmDesc.from_buffer(buf)), _stream())
 
 
