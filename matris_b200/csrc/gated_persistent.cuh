@@ -40,7 +40,6 @@ constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): 
 static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word");
 
-__device__ __forceinline__ float sigmoid_fast_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 template <bool BF>
 __global__ void __launch_bounds__(GP_THREADS, 1)
@@ -333,7 +332,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         for (int hh = 0; hh < 2; ++hh) {
           float sx[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sx[i] = silu_fast_f(x[16 * hh + i]);
+          for (int i = 0; i < 16; ++i) sx[i] = silu_fma_f(x[16 * hh + i]);
           if (BF) {
             uint32_t hi[8], lo[8];
             split_bf16(sx, hi, lo);
@@ -413,7 +412,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
           float o[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = silu_fast_f(y[8 * jj + i] * rinv * w[i]);
+          for (int i = 0; i < 8; ++i) o[i] = silu_fma_f(y[8 * jj + i] * rinv * w[i]);
           st8(park + 8 * jj, o);
         }
       } else {
@@ -438,7 +437,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
             const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
             float o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fast_f(y[8 * jj + i] * rinv * w[i]);
+            for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fma_f(y[8 * jj + i] * rinv * w[i]);
             if (hout) st8(park + 8 * jj, o);
             if (out2) {
               const float4 ra = rws[2 * jj], rb = rws[2 * jj + 1];
