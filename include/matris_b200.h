@@ -412,6 +412,15 @@ int mb_bessel_bwd(int32_t n_bonds, const int32_t* u2d, const float* len, const f
                   const float* freq_b, float cut_b, int32_t p, const float* drbf_a, const float* drbf_b,
                   float* dlen, void* stream);
 
+/* GaussianExpansion (distance_expansion = "gaussian"; matris/model/basis_function.py:189-216, built in
+ * matris/model/feature_embed.py:86-99): rbf[u,k] = exp(coeff (d_u - offset[k])^2), seven offsets per set (the module's
+ * `offset` buffer), coeff = -0.5 / (2 (offset[1] - offset[0]))^2; no envelope.  Same layout as mb_bessel_*. */
+int mb_gaussian_fwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* off_a, float coeff_a,
+                    const float* off_b, float coeff_b, float* rbf_a, float* rbf_b, void* stream);
+int mb_gaussian_bwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* off_a, float coeff_a,
+                    const float* off_b, float coeff_b, const float* drbf_a, const float* drbf_b, float* dlen,
+                    void* stream);
+
 /* Angle basis of ThreebodyEmbedding + SphericalExpansion (matris/model/feature_embed.py:183-197,
  * matris/model/basis_function.py:222-338): x = (u_a . u_b)(1-1e-6), theta = acos x, 16 = 4 radial orders x 4
  * roots of spherical Bessel functions at |u_b|/cutoff times real m=0 harmonics of cos(theta). */
@@ -420,6 +429,14 @@ int mb_angle_basis_fwd(int64_t n_trip, const int32_t* line_graph, const float* u
 /* dunit[tDE] += ..., dunit[sDE] += ... (atomic) from dbasis [T,16] */
 int mb_angle_basis_bwd(int64_t n_trip, const int32_t* line_graph, const float* unit, float factor, float cutoff,
                        const float* dbasis, float* dunit, void* stream);
+
+/* Angle basis of ThreebodyEmbedding + FourierExpansion (three_body_expansion = "fourier";
+ * matris/model/basis_function.py:79-113 with num_angular = 7): basis[t] = [1/sqrt 2, sin(f_k theta), cos(f_k theta)]
+ * / sqrt(pi), k = 0..2, theta as above, f = the module's `frequencies` [3].  basis / dbasis are [T,7]. */
+int mb_fourier_basis_fwd(int64_t n_trip, const int32_t* line_graph, const float* unit, const float* freq,
+                         float* basis, void* stream);
+int mb_fourier_basis_bwd(int64_t n_trip, const int32_t* line_graph, const float* unit, const float* freq,
+                         const float* dbasis, float* dunit, void* stream);
 
 #ifdef __cplusplus
 }

@@ -115,6 +115,10 @@ _SIGNATURES = {
     "mb_bessel_bwd": [_i32, _vp, _vp, _vp, _f32, _vp, _f32, _i32, _vp, _vp, _vp, _vp],
     "mb_angle_basis_fwd": [_i64, _vp, _vp, _f32, _f32, _vp, _vp],
     "mb_angle_basis_bwd": [_i64, _vp, _vp, _f32, _f32, _vp, _vp, _vp],
+    "mb_gaussian_fwd": [_i32, _vp, _vp, _vp, _f32, _vp, _f32, _vp, _vp, _vp],
+    "mb_gaussian_bwd": [_i32, _vp, _vp, _vp, _f32, _vp, _f32, _vp, _vp, _vp, _vp],
+    "mb_fourier_basis_fwd": [_i64, _vp, _vp, _vp, _vp, _vp],
+    "mb_fourier_basis_bwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _OTHER = {
     "mb_version": (C.c_int, []),

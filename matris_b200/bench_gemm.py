@@ -9,7 +9,7 @@ random indices (default 0: all segments read row r).
 
 K: reduction width (a multiple of 128: K/128 concatenated sources), N: output width (a multiple of 128: N/128 column
 blocks), act: SiLU on load, gate: SiLU' gate in the epilogue, rows: default 151,552 (8 tiles per SM on 148 SMs),
-mode: tcgen05 (persistent kernel, default) | tcgen05_tile | simt; scatter: 0 plain store (default), 1 atomic
+mode: tcgen05 (persistent 3xBF16 kernel, default) | tcgen05_tf32 | tcgen05_tile | simt; scatter: 0 plain store (default), 1 atomic
 scatter-add to rows/5 targets in sorted order (runs of five equal targets), 2 the same targets in random order.
 """
 import sys

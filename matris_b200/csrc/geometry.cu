@@ -166,6 +166,40 @@ __global__ void k_bessel_bwd(int n_bonds, const int32_t* __restrict__ u2d, const
   dlen[e] += acc;  // each bond owns one directed edge: no race
 }
 
+// Gaussian distance expansion (distance_expansion = "gaussian"; matris/model/basis_function.py:189-216):
+// out[k] = exp(coeff (d - offset[k])^2) for the pairwise and the three-body set of seven offsets; no envelope.
+__global__ void k_gaussian_fwd(int n_bonds, const int32_t* __restrict__ u2d, const float* __restrict__ len,
+                               const float* __restrict__ off_a, float coeff_a, const float* __restrict__ off_b,
+                               float coeff_b, float* __restrict__ ra, float* __restrict__ rb) {
+  const int u = blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_bonds) return;
+  const float d = len[u2d[u]];
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    const float ta = d - off_a[k], tb = d - off_b[k];
+    ra[7 * (int64_t)u + k] = expf(coeff_a * (ta * ta));
+    rb[7 * (int64_t)u + k] = expf(coeff_b * (tb * tb));
+  }
+}
+
+__global__ void k_gaussian_bwd(int n_bonds, const int32_t* __restrict__ u2d, const float* __restrict__ len,
+                               const float* __restrict__ off_a, float coeff_a, const float* __restrict__ off_b,
+                               float coeff_b, const float* __restrict__ dra, const float* __restrict__ drb,
+                               float* __restrict__ dlen) {
+  const int u = blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_bonds) return;
+  const int e = u2d[u];
+  const float d = len[e];
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    const float ta = d - off_a[k], tb = d - off_b[k];
+    acc += dra[7 * (int64_t)u + k] * expf(coeff_a * (ta * ta)) * (2.f * coeff_a * ta);
+    acc += drb[7 * (int64_t)u + k] * expf(coeff_b * (tb * tb)) * (2.f * coeff_b * tb);
+  }
+  dlen[e] += acc;  // each bond owns one directed edge: no race
+}
+
 // ------------------------------------------------------------------ angle basis
 // Coefficients of the closed-form spherical Bessel radial functions j_l(z_{l,n} r)
 // for l = 0..3 at their first four roots z_{l,n} (the published MatterSim /
@@ -251,6 +285,50 @@ __global__ void k_angle_basis_bwd(int64_t n_trip, const int32_t* __restrict__ lg
   const float dtheta = dct * (-sinf(theta));
   const float dx = dtheta * (-rsqrtf(1.f - x * x));
   const float dd = dx * ANGLE_SHRINK;
+  atomicAdd(dunit + 3 * a, dd * bx); atomicAdd(dunit + 3 * a + 1, dd * by); atomicAdd(dunit + 3 * a + 2, dd * bz);
+  atomicAdd(dunit + 3 * b, dd * ax); atomicAdd(dunit + 3 * b + 1, dd * ay); atomicAdd(dunit + 3 * b + 2, dd * az);
+}
+
+// Fourier angle expansion (three_body_expansion = "fourier"; matris/model/basis_function.py:79-113,
+// matris/model/feature_embed.py:183-203): theta = acos(x (1 - 1e-6)), basis = [1/sqrt 2, sin(f_k theta), cos(f_k theta)]
+// / sqrt(pi) with three frequencies f_k (seven values per triplet).
+#define FOURIER_INV_SQRT_PI 0.5641895835477563f
+__global__ void k_fourier_fwd(int64_t n_trip, const int32_t* __restrict__ lg, const float* __restrict__ unit,
+                              const float* __restrict__ freq, float* __restrict__ basis) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_trip) return;
+  const int64_t a = lg[5 * t + 2], b = lg[5 * t + 4];
+  const float x = (unit[3 * a] * unit[3 * b] + unit[3 * a + 1] * unit[3 * b + 1] + unit[3 * a + 2] * unit[3 * b + 2]) *
+                  ANGLE_SHRINK;
+  const float theta = acosf(x);
+  float* out = basis + 7 * t;
+  out[0] = 0.70710677f * FOURIER_INV_SQRT_PI;
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const float ang = theta * freq[k];
+    out[1 + k] = sinf(ang) * FOURIER_INV_SQRT_PI;
+    out[4 + k] = cosf(ang) * FOURIER_INV_SQRT_PI;
+  }
+}
+
+__global__ void k_fourier_bwd(int64_t n_trip, const int32_t* __restrict__ lg, const float* __restrict__ unit,
+                              const float* __restrict__ freq, const float* __restrict__ dbasis,
+                              float* __restrict__ dunit) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_trip) return;
+  const int64_t a = lg[5 * t + 2], b = lg[5 * t + 4];
+  const float ax = unit[3 * a], ay = unit[3 * a + 1], az = unit[3 * a + 2];
+  const float bx = unit[3 * b], by = unit[3 * b + 1], bz = unit[3 * b + 2];
+  const float x = (ax * bx + ay * by + az * bz) * ANGLE_SHRINK;
+  const float theta = acosf(x);
+  float dtheta = 0.f;
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const float f = freq[k], ang = theta * f;
+    dtheta += (dbasis[7 * t + 1 + k] * cosf(ang) - dbasis[7 * t + 4 + k] * sinf(ang)) * f;
+  }
+  dtheta *= FOURIER_INV_SQRT_PI;
+  const float dd = dtheta * (-rsqrtf(1.f - x * x)) * ANGLE_SHRINK;
   atomicAdd(dunit + 3 * a, dd * bx); atomicAdd(dunit + 3 * a + 1, dd * by); atomicAdd(dunit + 3 * a + 2, dd * bz);
   atomicAdd(dunit + 3 * b, dd * ax); atomicAdd(dunit + 3 * b + 1, dd * ay); atomicAdd(dunit + 3 * b + 2, dd * az);
 }
@@ -356,6 +434,45 @@ extern "C" int mb_bessel_bwd(int32_t n_bonds, const int32_t* u2d, const float* l
   k_bessel_bwd<<<grid1(n_bonds), GEO_THREADS, 0, STREAM>>>(n_bonds, u2d, len, freq_a, cut_a, freq_b, cut_b, p, drbf_a,
                                                          drbf_b, dlen);
   MB_LAUNCH_CHECK("k_bessel_bwd");
+  return MB_OK;
+}
+
+extern "C" int mb_gaussian_fwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* off_a, float coeff_a,
+                               const float* off_b, float coeff_b, float* rbf_a, float* rbf_b, void* stream) {
+  MB_REQUIRE(n_bonds >= 0 && u2d && len && off_a && off_b && rbf_a && rbf_b);
+  if (n_bonds == 0) return MB_OK;
+  k_gaussian_fwd<<<grid1(n_bonds), GEO_THREADS, 0, STREAM>>>(n_bonds, u2d, len, off_a, coeff_a, off_b, coeff_b, rbf_a,
+                                                           rbf_b);
+  MB_LAUNCH_CHECK("k_gaussian_fwd");
+  return MB_OK;
+}
+
+extern "C" int mb_gaussian_bwd(int32_t n_bonds, const int32_t* u2d, const float* len, const float* off_a, float coeff_a,
+                               const float* off_b, float coeff_b, const float* drbf_a, const float* drbf_b,
+                               float* dlen, void* stream) {
+  MB_REQUIRE(n_bonds >= 0 && u2d && len && off_a && off_b && drbf_a && drbf_b && dlen);
+  if (n_bonds == 0) return MB_OK;
+  k_gaussian_bwd<<<grid1(n_bonds), GEO_THREADS, 0, STREAM>>>(n_bonds, u2d, len, off_a, coeff_a, off_b, coeff_b, drbf_a,
+                                                           drbf_b, dlen);
+  MB_LAUNCH_CHECK("k_gaussian_bwd");
+  return MB_OK;
+}
+
+extern "C" int mb_fourier_basis_fwd(int64_t n_trip, const int32_t* line_graph, const float* unit, const float* freq,
+                                    float* basis, void* stream) {
+  MB_REQUIRE(n_trip >= 0 && line_graph && unit && freq && basis);
+  if (n_trip == 0) return MB_OK;
+  k_fourier_fwd<<<grid1(n_trip), GEO_THREADS, 0, STREAM>>>(n_trip, line_graph, unit, freq, basis);
+  MB_LAUNCH_CHECK("k_fourier_fwd");
+  return MB_OK;
+}
+
+extern "C" int mb_fourier_basis_bwd(int64_t n_trip, const int32_t* line_graph, const float* unit, const float* freq,
+                                    const float* dbasis, float* dunit, void* stream) {
+  MB_REQUIRE(n_trip >= 0 && line_graph && unit && freq && dbasis && dunit);
+  if (n_trip == 0) return MB_OK;
+  k_fourier_bwd<<<grid1(n_trip), GEO_THREADS, 0, STREAM>>>(n_trip, line_graph, unit, freq, dbasis, dunit);
+  MB_LAUNCH_CHECK("k_fourier_bwd");
   return MB_OK;
 }
 

@@ -73,15 +73,27 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
     SW = ops.SplitWeight
     P.emb_w = SW(get("atom_embedding.atom_swish_layer.linear.weight"))
     e = "edge_embedding."
-    P.freq2, P.freq3 = get(e + "pairwise_rbf_expansion.frequencies").contiguous(), get(
-        e + "threebody_rbf_expansion.frequencies").contiguous()
+    P.gaussian = str(cfg["distance_expansion"]).lower() == "gaussian"
+    if P.gaussian:
+        # GaussianExpansion: the offsets are a buffer, the coefficient is derived from them at construction
+        # (matris/model/basis_function.py:203-205: float32 spacing, then Python float arithmetic)
+        P.freq2, P.freq3 = get(e + "pairwise_rbf_expansion.offset").contiguous(), get(
+            e + "threebody_rbf_expansion.offset").contiguous()
+        P.coeff2, P.coeff3 = (-0.5 / (2.0 * (o[1] - o[0])).item() ** 2 for o in (P.freq2.cpu(), P.freq3.cpu()))
+    else:
+        P.freq2, P.freq3 = get(e + "pairwise_rbf_expansion.frequencies").contiguous(), get(
+            e + "threebody_rbf_expansion.frequencies").contiguous()
     P.e_w1 = get(e + "edge_linear1.weight").contiguous()
     P.e_w2 = SW(get(e + "edge_linear2.weight"))
     P.e_w3 = SW(get(e + "swish_layer.linear.weight"))
     P.e_w2t, P.e_w3t = P.e_w2.t(), P.e_w3.t()
     P.e_lnw, P.e_lnb = get(e + "edge_init_norm.weight").contiguous(), get(e + "edge_init_norm.bias").contiguous()
     t = "three_body_embedding."
-    P.sph_factor = float(sd[t + "expansion.factor"])
+    P.fourier = str(cfg["three_body_expansion"]).lower() == "fourier"
+    if P.fourier:
+        P.t_freq = get(t + "expansion.frequencies").contiguous()
+    else:
+        P.sph_factor = float(sd[t + "expansion.factor"])
     P.t_wa = get(t + "angle_embedding.weight").contiguous()
     P.t_wb = SW(get(t + "swish_layer.linear.weight"))
     P.t_wbt = P.t_wb.t()
@@ -346,9 +358,21 @@ class EdgeGeometryFn(torch.autograd.Function):
         return dcart, (dstrain if ctx.has_strain else None), None
 
 
+def _rbf_forward(P, g, length, cfg):
+    if P.gaussian:
+        return ops.gaussian_fwd(g.u2d, length, P.freq2, P.coeff2, P.freq3, P.coeff3)
+    return ops.bessel_fwd(g.u2d, length, P.freq2, cfg["pairwise_cutoff"], P.freq3, cfg["three_body_cutoff"],
+                          cfg["envelope_exponent"])
+
+
+def _angle_basis(P, g, unit, cfg):
+    if P.fourier:
+        return ops.fourier_basis_fwd(g.line_graph, unit, P.t_freq)
+    return ops.angle_basis_fwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"])
+
+
 def _edge_embed_forward(P, g, length, cfg):
-    rbf2, rbf3 = ops.bessel_fwd(g.u2d, length, P.freq2, cfg["pairwise_cutoff"], P.freq3, cfg["three_body_cutoff"],
-                                cfg["envelope_exponent"])
+    rbf2, rbf3 = _rbf_forward(P, g, length, cfg)
     e1 = ops.small_linear_fwd(rbf2, P.e_w1)
     e2 = ops.linear(e1, P.e_w2)
     # both directed copies of a bond carry the same row, so their mean is the row itself:
@@ -382,8 +406,11 @@ class EdgeEmbedFn(torch.autograd.Function):
         de1 = ops.linear(de2, P.e_w2t)
         d2 = d_rbf2.contiguous().clone()
         ops.small_linear_bwd(de1, P.e_w1, d2, accumulate=True)
-        dlen = ops.bessel_bwd(g.u2d, length, P.freq2, cfg["pairwise_cutoff"], P.freq3, cfg["three_body_cutoff"],
-                              cfg["envelope_exponent"], d2, d_rbf3.contiguous())
+        if P.gaussian:
+            dlen = ops.gaussian_bwd(g.u2d, length, P.freq2, P.coeff2, P.freq3, P.coeff3, d2, d_rbf3.contiguous())
+        else:
+            dlen = ops.bessel_bwd(g.u2d, length, P.freq2, cfg["pairwise_cutoff"], P.freq3, cfg["three_body_cutoff"],
+                                  cfg["envelope_exponent"], d2, d_rbf3.contiguous())
         return dlen, None, None, None
 
 
@@ -393,7 +420,7 @@ class AngleEmbedFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, unit, P, g, cfg):
         unit = unit.contiguous()
-        basis = ops.angle_basis_fwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"])
+        basis = _angle_basis(P, g, unit, cfg)
         t1 = ops.small_linear_fwd(basis, P.t_wa)
         trip = ops.linear(t1, P.t_wb, out_act=1)
         ctx.save_for_backward(unit)
@@ -405,7 +432,7 @@ class AngleEmbedFn(torch.autograd.Function):
     def backward(ctx, d_trip):
         (unit,) = ctx.saved_tensors
         P, g, cfg = ctx.P, ctx.g, ctx.cfg
-        basis = ops.angle_basis_fwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"])
+        basis = _angle_basis(P, g, unit, cfg)
         t1 = ops.small_linear_fwd(basis, P.t_wa)
         z = ops.linear(t1, P.t_wb)
         del basis, t1
@@ -413,7 +440,10 @@ class AngleEmbedFn(torch.autograd.Function):
         dt1 = ops.linear(dz, P.t_wbt)
         del z, dz
         dbasis = ops.small_linear_bwd(dt1, P.t_wa)
-        dunit = ops.angle_basis_bwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"], dbasis)
+        if P.fourier:
+            dunit = ops.fourier_basis_bwd(g.line_graph, unit, P.t_freq, dbasis)
+        else:
+            dunit = ops.angle_basis_bwd(g.line_graph, unit, P.sph_factor, cfg["pairwise_cutoff"], dbasis)
         return dunit, None, None, None
 
 

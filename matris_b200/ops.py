@@ -363,6 +363,34 @@ def bessel_bwd(u2d, length, fa, ca, fb, cb, p, dra, drb):
     return dlen
 
 
+def gaussian_fwd(u2d, length, oa, ca, ob, cb):
+    nb = u2d.shape[0]
+    ra, rb = new(nb, 7, length), new(nb, 7, length)
+    call("mb_gaussian_fwd", nb, ptr(u2d), ptr(length), ptr(oa), float(ca), ptr(ob), float(cb), ptr(ra), ptr(rb), _stream())
+    return ra, rb
+
+
+def gaussian_bwd(u2d, length, oa, ca, ob, cb, dra, drb):
+    dlen = torch.zeros_like(length)
+    call("mb_gaussian_bwd", u2d.shape[0], ptr(u2d), ptr(length), ptr(oa), float(ca), ptr(ob), float(cb), ptr(dra),
+         ptr(drb), ptr(dlen), _stream())
+    return dlen
+
+
+def fourier_basis_fwd(line_graph, unit, freq):
+    nt = line_graph.shape[0]
+    basis = new(nt, 7, unit)
+    call("mb_fourier_basis_fwd", nt, ptr(line_graph), ptr(unit), ptr(freq), ptr(basis), _stream())
+    return basis
+
+
+def fourier_basis_bwd(line_graph, unit, freq, dbasis):
+    dunit = torch.zeros_like(unit)
+    call("mb_fourier_basis_bwd", line_graph.shape[0], ptr(line_graph), ptr(unit), ptr(freq), ptr(dbasis), ptr(dunit),
+         _stream())
+    return dunit
+
+
 def angle_basis_fwd(line_graph, unit, factor, cutoff):
     nt = line_graph.shape[0]
     basis = new(nt, 16, unit)

@@ -43,11 +43,16 @@ def full_config(config: dict | None = None, **overrides) -> OrderedDict:
 def check_supported(cfg: dict) -> None:
     """The CUDA path implements the default architecture family only; anything
     else is rejected here rather than silently evaluated differently."""
-    want = dict(distance_expansion="bessel", three_body_expansion="sh", graph_conv_mlp="gatemlp",
-                activation_type="silu", norm_type="rms")
+    want = dict(graph_conv_mlp="gatemlp", activation_type="silu", norm_type="rms")
     for k, v in want.items():
         if str(cfg[k]).lower() != v:
             raise NotImplementedError(f"matris_b200 implements {k}={v!r} only (got {cfg[k]!r})")
+    if str(cfg["distance_expansion"]).lower() not in ("bessel", "gaussian"):
+        raise NotImplementedError(f"distance_expansion={cfg['distance_expansion']!r}: 'Bessel' or 'Gaussian'")
+    if str(cfg["three_body_expansion"]).lower() not in ("sh", "fourier"):
+        raise NotImplementedError(f"three_body_expansion={cfg['three_body_expansion']!r}: 'SH' or 'fourier'")
+    if str(cfg["three_body_expansion"]).lower() == "fourier" and int(cfg["num_angular"]) != 7:
+        raise NotImplementedError("matris_b200 implements num_angular=7 only")
     for k in ("node_feat_dim", "edge_feat_dim", "three_body_feat_dim"):
         if int(cfg[k]) != 128:
             raise NotImplementedError(f"matris_b200 kernels are specialised for {k}=128 (got {cfg[k]})")
@@ -72,15 +77,22 @@ def schema(config: dict | None = None) -> "OrderedDict[str, tuple]":
         s["reference_energy.fc.weight"] = (1, MAX_ELEMENTS)
     s["atom_embedding.embedding.weight"] = (MAX_ELEMENTS, D)
     s["atom_embedding.atom_swish_layer.linear.weight"] = (D, D)
-    s["edge_embedding.pairwise_rbf_expansion.frequencies"] = (R,)
-    s["edge_embedding.threebody_rbf_expansion.frequencies"] = (R,)
+    # BesselExpansion holds `frequencies`, GaussianExpansion an `offset` buffer (basis_function.py:116-216)
+    rbf_key = "frequencies" if str(cfg["distance_expansion"]).lower() == "bessel" else "offset"
+    s["edge_embedding.pairwise_rbf_expansion." + rbf_key] = (R,)
+    s["edge_embedding.threebody_rbf_expansion." + rbf_key] = (R,)
     s["edge_embedding.edge_linear1.weight"] = (D, R)
     s["edge_embedding.edge_linear2.weight"] = (D, D)
     s["edge_embedding.swish_layer.linear.weight"] = (D, D)
     s["edge_embedding.edge_init_norm.weight"] = (D,)
     s["edge_embedding.edge_init_norm.bias"] = (D,)
-    s["three_body_embedding.expansion.factor"] = ()
-    s["three_body_embedding.angle_embedding.weight"] = (D, A)
+    if str(cfg["three_body_expansion"]).lower() == "fourier":  # FourierExpansion(max_f = (num_angular - 1) // 2)
+        F_ = int(cfg["num_angular"])
+        s["three_body_embedding.expansion.frequencies"] = ((F_ - 1) // 2,)
+        s["three_body_embedding.angle_embedding.weight"] = (D, F_)
+    else:
+        s["three_body_embedding.expansion.factor"] = ()
+        s["three_body_embedding.angle_embedding.weight"] = (D, A)
     s["three_body_embedding.swish_layer.linear.weight"] = (D, D)
 
     def gated(prefix, k_in):
@@ -123,7 +135,8 @@ def schema(config: dict | None = None) -> "OrderedDict[str, tuple]":
     return s
 
 
-BUFFER_KEYS = ("three_body_embedding.expansion.factor",)
+BUFFER_KEYS = ("three_body_embedding.expansion.factor", "edge_embedding.pairwise_rbf_expansion.offset",
+               "edge_embedding.threebody_rbf_expansion.offset")
 
 
 def atomref_table(name: str) -> torch.Tensor:
@@ -156,6 +169,11 @@ def random_state_dict(config: dict | None = None, seed: int = 0, jitter: float =
             v = atomref_table(cfg["reference_energy"]).numpy()
         elif key.endswith("expansion.factor"):
             v = np.sqrt(np.float32(2.0 / float(cfg["pairwise_cutoff"]) ** 3), dtype=np.float32)
+        elif key.endswith("expansion.offset"):  # torch.linspace(0, cutoff, num_gaussians) (basis_function.py:203)
+            stop = cfg["pairwise_cutoff"] if "pairwise" in key else cfg["three_body_cutoff"]
+            v = torch.linspace(0.0, float(stop), shape[0]).numpy()
+        elif key == "three_body_embedding.expansion.frequencies":  # arange(1, max_f + 1) (basis_function.py:97-103)
+            v = np.arange(1, shape[0] + 1, dtype=np.float64) * (1 + 0.2 * jitter * g.uniform(-1, 1, shape))
         elif key.endswith("frequencies"):
             v = np.pi * np.arange(1, shape[0] + 1, dtype=np.float64) * (1 + 0.2 * jitter * g.uniform(-1, 1, shape))
         elif key.endswith("embedding.weight") and key.startswith("atom_embedding"):

@@ -73,6 +73,19 @@ def bessel(dist, freqs, cutoff, p):
     return envelope(d, cutoff, float(p)) * out
 
 
+def gaussian(dist, offset):
+    """GaussianExpansion.forward (matris/model/basis_function.py:189-216)."""
+    coeff = -0.5 / (2.0 * (offset[1] - offset[0])).item() ** 2
+    return torch.exp(coeff * (dist[:, None] - offset[None, :]) ** 2)
+
+
+def fourier_basis(theta, freqs):
+    """FourierExpansion.forward (matris/model/basis_function.py:106-113): [1/sqrt 2, sin, cos] / sqrt(pi)."""
+    ang = torch.outer(theta, freqs)
+    first = torch.full_like(theta, float(1 / torch.sqrt(torch.tensor([2.0]))))[:, None]
+    return torch.cat([first, torch.sin(ang), torch.cos(ang)], dim=1) / math.sqrt(math.pi)
+
+
 def spherical_basis(dist, theta, factor, cutoff, max_n=4, max_l=4):
     c = _sph_coef().to(dist.dtype)
     x = dist / cutoff
@@ -235,11 +248,14 @@ def process_graphs(graphs, compute_stress, dtype=torch.float32):
 
 # ------------------------------------------------------------------ whole model
 def _check_config(cfg):
-    want = dict(distance_expansion="bessel", three_body_expansion="sh", graph_conv_mlp="gatemlp",
-                activation_type="silu", norm_type="rms")
+    want = dict(graph_conv_mlp="gatemlp", activation_type="silu", norm_type="rms")
     for k, v in want.items():
         if str(cfg.get(k, v)).lower() != v:
             raise NotImplementedError(f"oracle covers {k}={v!r} only, got {cfg[k]!r}")
+    if str(cfg.get("distance_expansion", "bessel")).lower() not in ("bessel", "gaussian"):
+        raise NotImplementedError(f"oracle covers Bessel and Gaussian distance expansions, got {cfg['distance_expansion']!r}")
+    if str(cfg.get("three_body_expansion", "sh")).lower() not in ("sh", "fourier"):
+        raise NotImplementedError(f"oracle covers SH and Fourier angle expansions, got {cfg['three_body_expansion']!r}")
     if not cfg.get("is_conservation", True):
         raise NotImplementedError("oracle covers the conservative force/stress head only")
 
@@ -259,8 +275,12 @@ def forward(sd, cfg, graphs, task="ef", dtype=torch.float32):
     node = F.silu(F.linear(pe("embedding.weight")[bg["atomic_numbers"] - 1], pe("atom_swish_layer.linear.weight")))
     pe = P.sub("edge_embedding")
     du = bg["edge_lengths"][u2d]
-    rbf2 = bessel(du, pe("pairwise_rbf_expansion.frequencies"), rc2, p_env)
-    rbf3 = bessel(du, pe("threebody_rbf_expansion.frequencies"), rc3, p_env)
+    if str(cfg.get("distance_expansion", "bessel")).lower() == "gaussian":
+        rbf2 = gaussian(du, pe("pairwise_rbf_expansion.offset"))
+        rbf3 = gaussian(du, pe("threebody_rbf_expansion.offset"))
+    else:
+        rbf2 = bessel(du, pe("pairwise_rbf_expansion.frequencies"), rc2, p_env)
+        rbf3 = bessel(du, pe("threebody_rbf_expansion.frequencies"), rc3, p_env)
     e = F.linear(F.linear(rbf2, pe("edge_linear1.weight"))[d2u], pe("edge_linear2.weight"))
     e = F.layer_norm(e, (e.shape[1],), pe("edge_init_norm.weight"), pe("edge_init_norm.bias"))
     edge = F.silu(F.linear(pair_mean(e, d2u), pe("swish_layer.linear.weight")))
@@ -271,8 +291,11 @@ def forward(sd, cfg, graphs, task="ef", dtype=torch.float32):
         ua = bg["unit_edge_vectors"][lgd["target_DE_index"]]
         ub = bg["unit_edge_vectors"][lgd["source_DE_index"]]
         theta = torch.acos((ua * ub).sum(dim=1) * (1 - 1e-6))
-        basis = spherical_basis(torch.norm(ub, dim=1), theta, pe("expansion.factor"), rc2,
-                                cfg.get("max_n", 4), cfg.get("max_l", 4))
+        if str(cfg.get("three_body_expansion", "sh")).lower() == "fourier":
+            basis = fourier_basis(theta, pe("expansion.frequencies"))
+        else:
+            basis = spherical_basis(torch.norm(ub, dim=1), theta, pe("expansion.factor"), rc2,
+                                    cfg.get("max_n", 4), cfg.get("max_l", 4))
         trip = F.silu(F.linear(F.linear(basis, pe("angle_embedding.weight")), pe("swish_layer.linear.weight")))
     # interaction blocks (interaction_block.py:372-446)
     sde = cfg.get("use_smoothed_for_delta_edge", False)

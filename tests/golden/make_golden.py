@@ -50,6 +50,9 @@ CASES = {
     # non-default options: biases in the FFN layers, smoothed rows into the atom graph's edge update
     "random2_L2_bias_smoothed": (lambda: workloads.random_crystals(2, seed=11), 2, "efsm", 0.1,
                                  dict(use_bias=True, use_smoothed_for_delta_edge=True)),
+    # non-default bases: Gaussian distance expansion, Fourier angle expansion
+    "random2_L2_gaussian_fourier": (lambda: workloads.random_crystals(2, seed=11), 2, "efsm", 0.1,
+                                    dict(distance_expansion="Gaussian", three_body_expansion="fourier")),
 }
 
 

@@ -490,6 +490,54 @@ def test_angle_basis_fwd_bwd(ops):
     report("angle_basis_bwd dunit", ops.angle_basis_bwd(dev(lg, torch.int32), dev(unit), factor, 6.0, dev(db)), dU, 2e-3, rel=True)
 
 
+def test_gaussian_fwd_bwd(ops):
+    from oracle.model import gaussian
+    nb = 400
+    g = torch.Generator().manual_seed(4)
+    length = torch.rand(2 * nb, generator=g) * 5.2 + 0.8
+    u2d = torch.randperm(2 * nb, generator=g)[:nb]
+    oa, ob = torch.linspace(0.0, 6.0, 7), torch.linspace(0.0, 4.0, 7)
+    ca, cb = (-0.5 / (2.0 * (o[1] - o[0])).item() ** 2 for o in (oa, ob))
+    ra, rb = ops.gaussian_fwd(dev(u2d, torch.int32), dev(length), dev(oa), ca, dev(ob), cb)
+    Ld = length.double().requires_grad_(True)
+    ref_a, ref_b = gaussian(Ld[u2d], oa.double()), gaussian(Ld[u2d], ob.double())
+    report("gaussian_fwd rc=6", ra, ref_a, 2e-6)
+    report("gaussian_fwd rc=4", rb, ref_b, 2e-6)
+    da, db = rnd(nb, 7, seed=3), rnd(nb, 7, seed=4)
+    (dl,) = torch.autograd.grad((ref_a * da.double()).sum() + (ref_b * db.double()).sum(), Ld)
+    report("gaussian_bwd dlen", ops.gaussian_bwd(dev(u2d, torch.int32), dev(length), dev(oa), ca, dev(ob), cb, dev(da), dev(db)),
+           dl, 1e-5)
+
+
+def test_fourier_basis_fwd_bwd(ops):
+    from oracle.model import fourier_basis
+    ne, nt = 60, 900
+    g = torch.Generator().manual_seed(5)
+    v = torch.randn(ne, 3, generator=g)
+    unit = (v / v.norm(dim=1, keepdim=True)).float()
+    lg = torch.zeros(nt, 5, dtype=torch.int64)
+    lg[:, 2], lg[:, 4] = torch.randint(0, ne, (nt,), generator=g), torch.randint(0, ne, (nt,), generator=g)
+    lg[:5, 4] = lg[:5, 2]                                         # collinear (theta = 0) rows
+    freq = torch.arange(1, 4).float() * (1 + 0.02 * rnd(3, seed=1))
+    basis = ops.fourier_basis_fwd(dev(lg, torch.int32), dev(unit), dev(freq))
+    U = unit.double().requires_grad_(True)
+    x = (U[lg[:, 2]] * U[lg[:, 4]]).sum(1) * (1 - 1e-6)
+    theta = torch.acos(x)
+    ref = fourier_basis(theta, freq.double())
+    # theta = acos(x) is ill-conditioned in float32 where |x| -> 1 (one ulp of x moves theta by percents there: the
+    # reference's own float32 result has the same spread), so values are compared away from collinearity and the
+    # collinear rows are checked for finiteness and the constant first column
+    ok = (x.detach().abs() < 0.999)
+    assert 5 <= int((~ok).sum()) < 60
+    report("fourier_basis_fwd", basis.cpu()[ok], ref[ok], 2e-6)
+    assert torch.isfinite(basis).all()
+    report("fourier_basis_fwd constant column", basis[:, 0], ref[:, 0], 1e-7)
+    db = rnd(nt, 7, seed=1)
+    db[~ok] = 0.0
+    (dU,) = torch.autograd.grad((ref * db.double()).sum(), U)
+    report("fourier_basis_bwd dunit", ops.fourier_basis_bwd(dev(lg, torch.int32), dev(unit), dev(freq), dev(db)), dU, 2e-4, rel=True)
+
+
 def test_edge_geometry_fwd_bwd(ops):
     from matris_b200.graph import build_batched_graph
     from matris_b200 import workloads
