@@ -195,7 +195,7 @@ int mb_gemm(const mb_gemm_desc* desc, void* stream);
  * and accumulates lo*hi + hi*lo + hi*hi in fp32 tensor memory:
  *   0 (default) persistent kernels, one CTA per SM, 3xBF16: hi = bf16(x), lo = bf16(x - hi), kind::f16 MMAs at twice
  *               the tf32 rate; an operand pair carries 16 mantissa bits;
- *   3           the same kernels with 3xTF32: hi = x cut to tf32, lo = x - hi, kind::tf32 MMAs; 22 mantissa bits;
+ *   3           the persistent GEMM kernel with 3xTF32: hi = x cut to tf32, lo = x - hi, kind::tf32 MMAs; 22 mantissa bits;
  *   2           3xTF32 in a one-tile-per-CTA kernel;
  *   1           fp32 SIMT FMA (bit-faithful fp32, the cross-check).
  * A test knob: it is process-wide and not meant to be switched while other host threads launch.
@@ -232,10 +232,10 @@ int mb_bench_mma_rate(int kind, int iters, float* elapsed_ms, int* n_sms, void* 
  *   h  = SiLU(RMSNorm(z2[:, :128]) * norm_core) * sigmoid(RMSNorm(z2[:, 128:]) * norm_gate)
  *   out2 = h + res_w * res      (optional)
  * Layer 1's accumulator never leaves tensor memory: it is read back, biased, passed through SiLU, split into
- * tf32 hi / lo and stored as the A operand of layer 2 on chip; RMSNorm and the gate run in the epilogue of
- * layer 2.  z1 / z2 are written only when the pointers are given (the backward pass wants them).  In GEMM
- * modes 1 and 2 (see mb_set_gemm_mode) the same result is composed from mb_gemm and mb_gate_fwd, which needs
- * z1 and z2 as scratch: they are required there. */
+ * bf16 hi / lo and stored as the A operand of layer 2 on chip; RMSNorm and the gate run in the epilogue of
+ * layer 2.  z1 / z2 are written only when the pointers are given (the backward pass wants them).  The fused kernel
+ * exists for the default GEMM mode (0, 3xBF16); in modes 1, 2 and 3 (see mb_set_gemm_mode) the same result is
+ * composed from mb_gemm and mb_gate_fwd, which needs z1 and z2 as scratch: they are required there. */
 typedef struct mb_gated_mlp {
   int64_t n_rows;
   int32_t n_src;               /* 1..4 ; K = 128 * n_src */

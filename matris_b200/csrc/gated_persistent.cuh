@@ -4,68 +4,73 @@
 //   z2 = SiLU(z1) (.) W2^T + b2   per branch: [rows, 128] x [128, 128]
 //   h  = SiLU(RMSNorm(z2_core) w_core) * sigmoid(RMSNorm(z2_gate) w_gate)  (+ optional out2 = h + res_w * res)
 //
-// One persistent CTA per SM.  The unit of work is (128-row tile, branch); a CTA takes row tiles blockIdx.x,
-// + gridDim.x, ... and runs the core unit and then the gate unit of each.  A unit is two chained contractions on the
-// same tensor-memory accumulator (unit k uses accumulator k & 1):
+// 3xBF16 arithmetic (see gemm_persistent.cuh).  One persistent CTA per SM.  The unit of work is (128-row tile, branch);
+// a CTA takes row tiles blockIdx.x, + gridDim.x, ... and runs the core unit (even k) and then the gate unit (odd k) of
+// each.  A unit is two chained contractions on one tensor-memory accumulator (unit k uses accumulator k % 3):
 //
-//   L1(k)   12 or 16 K chunks (of 32 floats) of X against rows 128 j.. of W1  ->  D (128 x 128 fp32)
-//   mid(k)  the eight epilogue warps read D back (tcgen05.ld, thread = row), add b1, optionally write z1, apply SiLU,
-//           split into hi / lo (bf16 or tf32, see gemm_persistent.cuh) and store the result as the A operand of
-//           layer 2 into four A buffers (tcgen05.st): z1 never travels through shared or global memory on its way
-//           to layer 2
-//   L2(k)   4 K chunks against rows 128 j.. of W2, written over D (every column of D has been read by then)
-//   epi(k)  D -> registers, + b2, optional z2 store, RMSNorm (the two warps that share a row exchange their partial
-//           sums of squares through shared memory), then  core unit: c = SiLU(.) is parked in the output row;
-//           gate unit: the same thread reads c back, multiplies by sigmoid(.) and writes h / out2.
+//   L1(k)   12 or 16 K chunks (of 32 floats) of X against rows 128 (k & 1).. of W1  ->  D (128 x 128 fp32)
+//   mid(k)  four epilogue warps read D back (tcgen05.ld, thread = row), add b1, optionally write z1, apply SiLU,
+//           split into bf16 hi / lo and store the result as the A operand of layer 2 into the four A buffers
+//           (tcgen05.st): z1 never travels through shared or global memory on its way to layer 2
+//   L2(k)   4 K chunks against rows 128 (k & 1).. of W2, written over D (every column of D has been read by then)
+//   epi(k)  the same four warps: pass 1 reads D (+ b2, optional z2 store) for the row's sum of squares, pass 2 reads
+//           it again, normalises and activates; the core unit parks c = SiLU(.) in the output row, the gate unit
+//           reads it back, multiplies by sigmoid(.) and writes h / out2.
 //
-// The tensor pipe executes L1(0) L1(1) L2(0) L1(2) L2(1) ... L1(n-1) L2(n-2) L2(n-1): while it works on L1(k+1) the
-// epilogue warps drain unit k-1 and prepare unit k's layer-2 operand, so neither hand-off idles the tensor cores for
-// longer than one tcgen05.st + mbarrier round trip.  All roles walk that one chunk sequence (counter g): chunk g uses
-// A buffer g % NB and W-slot use g / CPW, exactly as in k_gemm_ps, and every phase has a multiple of four chunks.
+// The eight epilogue warps form two groups of four (one warp per tensor-memory lane quarter, each owning whole rows):
+// group 0 takes the even units, group 1 the odd ones.  While one group waits for DRAM in its epilogue the other
+// prepares the next layer-2 operand, so the tensor pipe is not starved by the epilogue's memory traffic; with three
+// accumulators an accumulator can stay with its epilogue for a whole extra unit before layer 1 needs it again.
+// The tensor pipe executes L1(0) L1(1) L2(0) L1(2) L2(1) ... L1(n-1) L2(n-2) L2(n-1).  All roles walk that one chunk
+// sequence (counter g): chunk g uses A buffer g % 4 and W-slot use g / 2, exactly as in k_gemm_ps.
 //
-// Tensor memory (512 columns): accumulators at 0 and 128, A buffers from 256 on (hi | lo each).
-// Shared memory: W ring 4 x 32 KB | producer patches 64 KB | sums of squares 2 KB | per-channel constants 3.5 KB |
-// barriers | descriptor copy.
+// Tensor memory (512 columns): accumulators at 0, 128, 256; four A buffers of 32 columns (hi | lo) from 384.
+// Shared memory: W ring 4 x 32 KB | producer patches 64 KB | per-channel constants 3.5 KB | barriers | descriptor.
 // Every mbarrier wait is bounded; on expiry the status word is set, the role stops waiting and runs to the common exit.
 
 struct alignas(64) GatedMaps { CUtensorMap w1[2]; CUtensorMap w2[2]; };  // hi, lo of W1 [256, K] and W2 [256, 128]
 
 constexpr int GP_THREADS = PS_THREADS;
-constexpr int GP_XSUM_OFF = PS_RING_BYTES + PS_PATCH_BYTES;
-constexpr int GP_CONST_OFF = GP_XSUM_OFF + 2 * 2 * 128 * 4;  // b1[256] b2[256] norm_core[128] norm_gate[128] res_w[128]
+constexpr uint32_t GP_NB = 4;        // A buffers
+constexpr uint32_t GP_A_BASE = 384;  // their first tensor-memory column
+constexpr int GP_CONST_OFF = PS_RING_BYTES + PS_PATCH_BYTES;  // b1[256] b2[256] norm_core[128] norm_gate[128] res_w[128]
 constexpr int GP_BAR_OFF = GP_CONST_OFF + 896 * 4;
-constexpr int GP_DESC_OFF = GP_BAR_OFF + 320;
+constexpr int GP_DESC_OFF = GP_BAR_OFF + 448;
 constexpr int GP_SMEM_BYTES = GP_DESC_OFF + (int)((sizeof(mb_gated_mlp) + 15) / 16 * 16);
 constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): float32 machine epsilon
 static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word");
 
-
-template <bool BF>
 __global__ void __launch_bounds__(GP_THREADS, 1)
 k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant__ GatedMaps maps) {
-  using Fmt = PsFormat<BF>;
-  constexpr uint32_t NB = Fmt::N_ABUF, CPW = Fmt::CH_PER_W;
+  constexpr uint32_t NB = GP_NB;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GP_BAR_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 300);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GP_BAR_OFF + 416);
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0) atomicOr(&g_gemm_status, 2);
     return;
   }
-  // barriers: a_ready[8] (A chunk stored: 4 warps) | a_done[8] (its MMAs retired) | w_ready[4] (W slot landed) |
-  //           w_done[4] (slot free) | d1_full[2] | d2_full[2] | d_free[2] (8 epilogue warps) | l2_free[4]
+  // barriers: a_ready[4] (A chunk stored: 4 warps) | a_done[4] (its MMAs retired) | w_ready[4] (W slot landed) |
+  //           w_done[4] (slot free) | d1_full[6] | d2_full[6] | d_free[6] (4 epilogue warps) | l2_free[2][4] |
+  //           park_ready[4][2]
   // A parity wait can tell apart only the current and the preceding phase of a barrier, so every waiter must see
-  // every phase of the barriers it waits on.  The MMA warp sees every chunk and the TMA warp every W-slot use.  The
-  // producers skip the layer-2 chunks and the epilogue warps skip the layer-1 chunks, so
-  //   * the epilogue warps wait for "the A buffer of layer-2 chunk c may be written" on l2_free[c], which completes
-  //     exactly once per unit: it is committed with the chunk, NB chunks earlier, that used the same buffer;
-  //   * the producers wait for the previous layer-1 phase to be complete (d1_full) before the first chunk of a phase
-  //     that follows a layer-2 phase: a_done[b] is then at most one phase away from the one they wait for.
-  const uint32_t a_ready = smem_u32(bars), a_done = smem_u32(bars + 8);
-  const uint32_t w_ready = smem_u32(bars + 16), w_done = smem_u32(bars + 20);
-  const uint32_t d1_full = smem_u32(bars + 24), d2_full = smem_u32(bars + 26), d_free = smem_u32(bars + 28);
-  const uint32_t l2_free = smem_u32(bars + 30);
+  // every phase of the barriers it waits on.  The MMA warp sees every chunk and the TMA warp every W-slot use.
+  //   * The per-unit barriers d1_full / d2_full / d_free are indexed by k % 6: a barrier then always belongs to the
+  //     same accumulator (k % 3) and the same epilogue group (k % 2), and completes once every six units.
+  //   * The epilogue warps skip the layer-1 chunks: "the A buffer of layer-2 chunk c may be written" comes on
+  //     l2_free[group][c], which completes once per unit of that group; it is committed with an earlier chunk that
+  //     used the same buffer.
+  //   * The producers skip the layer-2 chunks: they wait for the previous layer-1 phase to be complete (d1_full)
+  //     before the first chunk of a phase that follows a layer-2 phase, so that a_done[b] is at most one phase
+  //     away from the one they wait for.
+  //   * park_ready[q][t & 1]: the core unit's parked values of lane quarter q and row tile t are in memory (group 0 ->
+  //     group 1).  Group 0 can be two tiles ahead of group 1's wait (not three: layer 1 of its third tile needs the
+  //     accumulator group 1 still holds), so two barriers alternate; each completes once per two tiles.
+  const uint32_t a_ready = smem_u32(bars), a_done = smem_u32(bars + 4);
+  const uint32_t w_ready = smem_u32(bars + 8), w_done = smem_u32(bars + 12);
+  const uint32_t d1_full = smem_u32(bars + 16), d2_full = smem_u32(bars + 22), d_free = smem_u32(bars + 28);
+  const uint32_t l2_free = smem_u32(bars + 34), park_ready = smem_u32(bars + 42);
   const uint32_t ring = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const mb_gated_mlp& d = *reinterpret_cast<const mb_gated_mlp*>(smem + GP_DESC_OFF);
@@ -100,6 +105,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     else if (p & 1) { is_l2 = false; k = (p + 1) >> 1; }
     else { is_l2 = true; k = (p >> 1) - 1; }
   };
+  // first chunk of L2(k) in the chunk sequence
+  auto l2_start = [&](int k) { return (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k); };
 
   // ---- producer state (same gather as k_gemm_ps; both units of a row tile read the same rows)
   const int pw = (warp - PS_PROD_WARP0) & 7;
@@ -153,12 +160,13 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
 
   if (warp == PS_MMA_WARP) {
     if (lane == 0) {
-      for (int b = 0; b < 8; ++b) { mbar_init(a_ready + 8 * b, 4); mbar_init(a_done + 8 * b, 1); }
       for (int b = 0; b < 4; ++b) {
-        mbar_init(w_ready + 8 * b, 1); mbar_init(w_done + 8 * b, 1); mbar_init(l2_free + 8 * b, 1);
+        mbar_init(a_ready + 8 * b, 4); mbar_init(a_done + 8 * b, 1);
+        mbar_init(w_ready + 8 * b, 1); mbar_init(w_done + 8 * b, 1);
       }
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(d1_full + 8 * b, 1); mbar_init(d2_full + 8 * b, 1); mbar_init(d_free + 8 * b, 8);
+      for (int b = 0; b < 8; ++b) { mbar_init(l2_free + 8 * b, 1); mbar_init(park_ready + 8 * b, 1); }
+      for (int b = 0; b < 6; ++b) {
+        mbar_init(d1_full + 8 * b, 1); mbar_init(d2_full + 8 * b, 1); mbar_init(d_free + 8 * b, 4);
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -185,23 +193,22 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     bool alive = true;
     uint32_t g = 0;
     // Hand-over of the A buffers to the layer-2 writers (the epilogue warps): chunk t of layer-2 phase k_l2 may be
-    // written once the chunk NB before it has retired, which is signalled on l2_free[t], one completion per unit.  The
-    // writers of unit k must have seen completion k before completion k + 1 can happen (a parity wait cannot tell
-    // two phases apart), so the signal is never given before the same chunk of the preceding layer-2 phase, which
-    // needs their operand: sig_first = max(first chunk of the phase - NB, first chunk of the preceding layer-2 phase).
-    auto l2_start = [&](int k) { return (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k); };
+    // written once the chunk NB before it has retired, which is signalled on l2_free[k_l2 & 1][t].  The writers of a
+    // group must have seen one completion before the next can happen, so the signal is never given before the same
+    // chunk of the preceding layer-2 phase, which needs the other group's operand and comes after this group's
+    // previous one: sig_first = max(first chunk of the phase - NB, first chunk of the preceding layer-2 phase).
     int k_l2 = 0;
     uint32_t sig_first = l2_start(0) - NB;  // n_units >= 2 and nch1 >= 4: never negative
     for (int p = 0; p < n_phases; ++p) {
       bool is_l2;
       int k;
       decode(p, is_l2, k);
-      const int acc = k & 1;
-      const uint32_t d_tmem = tmem_u + 128u * acc;
+      const int k6 = k % 6;
+      const uint32_t d_tmem = tmem_u + 128u * (uint32_t)(k % 3);
       const int nch = is_l2 ? 4 : nch1;
-      const uint32_t full_bar = (is_l2 ? d2_full : d1_full) + 8 * acc;
+      const uint32_t full_bar = (is_l2 ? d2_full : d1_full) + 8 * k6;
       for (int c = 0; c < nch; ++c, ++g) {
-        const uint32_t ab = g % NB, wu = g / CPW, slot = wu & 3;
+        const uint32_t ab = g % NB, wu = g >> 1, slot = wu & 3;
         if (c == 0 && is_l2) {
           // Layer 2 overwrites the accumulator that holds z1: its first MMA may issue only when all four operand
           // chunks have been read out of it and stored (each a_ready phase below implies that chunk's tcgen05.ld).
@@ -210,25 +217,26 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         } else {
           if (alive) alive = mbar_wait(a_ready + 8 * ab, (g / NB) & 1);
         }
-        if (g % CPW == 0 && alive) alive = mbar_wait(w_ready + 8 * slot, (wu >> 2) & 1);
-        // layer 1 of unit k overwrites the accumulator unit k - 2 left: its epilogue must have taken it
-        if (c == 0 && !is_l2 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
+        if ((g & 1) == 0 && alive) alive = mbar_wait(w_ready + 8 * slot, (wu >> 2) & 1);
+        // layer 1 of unit k overwrites the accumulator unit k - 3 left: its epilogue must have read it twice
+        if (c == 0 && !is_l2 && k >= 3 && alive)
+          alive = mbar_wait(d_free + 8 * ((k - 3) % 6), (uint32_t)(((k - 3) / 6) & 1));
         alive = __all_sync(0xffffffffu, alive);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t wb = ring_u + slot * 2 * TC_TILE_BYTES;
-        const uint32_t ta = tmem_u + 256 + Fmt::A_COLS * ab;
+        const uint32_t ta = tmem_u + GP_A_BASE + 32u * ab;
         // < 4: this chunk's retirement frees layer-2 chunk t_l2 of unit k_l2
         const uint32_t t_l2 = k_l2 < n_units ? g - sig_first : 4u;
         if (elected) {
-          issue_chunk_mmas<BF>(d_tmem, ta, wb, g % CPW, c == 0);
+          issue_chunk_mmas<true>(d_tmem, ta, wb, g & 1, c == 0);
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                        :: "r"(a_done + 8 * ab) : "memory");
-          if (g % CPW == CPW - 1)
+          if (g & 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(w_done + 8 * slot) : "memory");
           if (t_l2 < 4u)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                         :: "r"(l2_free + 8 * t_l2) : "memory");
+                         :: "r"(l2_free + 8 * (4 * (k_l2 & 1) + t_l2)) : "memory");
           if (c == nch - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(full_bar) : "memory");
@@ -252,7 +260,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       bool is_l2;
       int k;
       decode(p, is_l2, k);
-      const int n_w = (is_l2 ? 4 : nch1) / (int)CPW;
+      const int n_w = (is_l2 ? 4 : nch1) / 2;
       const int wrow = 128 * (k & 1);  // first weight row of this unit's branch
       const CUtensorMap* const m_hi = is_l2 ? &maps.w2[0] : &maps.w1[0];
       const CUtensorMap* const m_lo = is_l2 ? &maps.w2[1] : &maps.w1[1];
@@ -265,8 +273,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         if (elected) {
           const uint32_t dst = ring_u + slot * 2 * TC_TILE_BYTES;
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(2 * TC_TILE_BYTES) : "memory");
-          tma_load_2d(dst, m_hi, bar, wi * Fmt::W_BOX_K, wrow);
-          tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, wi * Fmt::W_BOX_K, wrow);
+          tma_load_2d(dst, m_hi, bar, wi * 64, wrow);
+          tma_load_2d(dst + TC_TILE_BYTES, m_lo, bar, wi * 64, wrow);
         }
         __syncwarp();
       }
@@ -275,48 +283,50 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       for (uint32_t i = wu >= 4 ? wu - 4 : 0; i < wu; ++i) mbar_wait(w_ready + 8 * (i & 3), (i >> 2) & 1);
     }
   } else if (warp >= PS_EPI_WARP0) {
-    // ---------------------------------------------------------------- epilogue warps: mid(k) then epi(k), unit by unit
-    // Warp (q, hf): rows 32 q.. of the tile (its TMEM lane quarter), columns 64 hf.. of the branch; thread = row.
-    const int e = warp - PS_EPI_WARP0, q = warp & 3, hf = e >> 2;
+    // ---------------------------------------------------------------- epilogue warps: mid(k) then epi(k) of every
+    // other unit.  Warp (q, grp): rows 32 q.. of the tile (its tensor-memory lane quarter), all 128 columns of the
+    // units k = grp, grp + 2, ... (grp 0: core branch, grp 1: gate branch); thread = row.
+    const int e = warp - PS_EPI_WARP0, q = warp & 3, grp = e >> 2;
     const uint32_t lane_q = tmem_base + ((uint32_t)(q * 32) << 16);
-    float* const xs = reinterpret_cast<float*>(smem + GP_XSUM_OFF);
-    const float4* const b1s = reinterpret_cast<const float4*>(cst);
-    const float4* const b2s = reinterpret_cast<const float4*>(cst + 256);
+    const float4* const b1s = reinterpret_cast<const float4*>(cst) + 32 * grp;
+    const float4* const b2s = reinterpret_cast<const float4*>(cst + 256) + 32 * grp;
+    const float4* const nws = reinterpret_cast<const float4*>(cst + 512 + 128 * grp);
+    const float4* const rws = reinterpret_cast<const float4*>(cst + 768);
     float* const z1 = d.z1;
     float* const z2 = d.z2;
     float* const hout = d.h;
     float* const out2 = d.out2;
     const float* const res = d.res;
     bool alive = true;
-    for (int k = 0; k < n_units; ++k) {
-      const int acc = k & 1;  // = branch: 0 core, 1 gate
+    for (int k = grp; k < n_units; k += 2) {
+      const int k6 = k % 6;
+      const uint32_t par6 = (uint32_t)((k / 6) & 1), part = (uint32_t)((k >> 1) & 1);
+      const uint32_t park_bar = park_ready + 8 * (2 * q + (int)part), park_par = (uint32_t)((k >> 2) & 1);
       const int64_t row = (int64_t)(first_rt + (k >> 1) * step_rt) * 128 + q * 32 + lane;
       const bool valid = row < n_rows;
-      const uint32_t upar = (uint32_t)((k >> 1) & 1);
-      const uint32_t d_lane = lane_q + 128u * acc + 64u * hf;
+      const uint32_t d_lane = lane_q + 128u * (uint32_t)(k % 3);
       // ------------------------------------------------ mid(k): z1 -> SiLU -> hi / lo -> A operand of layer 2
-      if (alive) alive = mbar_wait(d1_full + 8 * acc, upar);
+      if (alive) alive = mbar_wait(d1_full + 8 * k6, par6);
       alive = __all_sync(0xffffffffu, alive);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t gl2 = (uint32_t)((k + 2 < n_units ? k + 2 : n_units) * nch1 + 4 * k);  // first chunk of L2(k)
+      const uint32_t gl2 = l2_start(k);
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * hf + cc;  // K chunk of layer 2 = columns 32 c.. of this branch's z1
+      for (int c = 0; c < 4; ++c) {  // K chunk of layer 2 = columns 32 c.. of this branch's z1
         float x[32];
         {
           uint32_t v[32];
-          MB_TMEM_LD32(d_lane + 32u * cc, v);
+          MB_TMEM_LD32(d_lane + 32u * c, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
         }
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {  // same address in every lane: a broadcast read
-          const float4 bv = b1s[32 * acc + 8 * c + jj];
+          const float4 bv = b1s[8 * c + jj];
           x[4 * jj] += bv.x; x[4 * jj + 1] += bv.y; x[4 * jj + 2] += bv.z; x[4 * jj + 3] += bv.w;
         }
         if (z1 && valid) {
-          float* zp = z1 + row * d.ld_z1 + 128 * acc + 32 * c;
+          float* zp = z1 + row * d.ld_z1 + 128 * grp + 32 * c;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             float o[8];
@@ -326,128 +336,140 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           }
         }
         __syncwarp();
-        const uint32_t gi = gl2 + (uint32_t)c, ab = gi % NB;
-        const uint32_t ta = lane_q + 256 + Fmt::A_COLS * ab;
+        const uint32_t ab = (gl2 + (uint32_t)c) % NB;
+        const uint32_t ta = lane_q + GP_A_BASE + 32u * ab;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           float sx[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) sx[i] = silu_fma_f(x[16 * hh + i]);
-          if (BF) {
-            uint32_t hi[8], lo[8];
-            split_bf16(sx, hi, lo);
-            if (hh == 0) {
-              if (alive) alive = mbar_wait(l2_free + 8 * c, (uint32_t)(k & 1));  // the A buffer may take this chunk
-              __syncwarp();
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            MB_TMEM_ST8(ta + 8 * hh, hi);
-            MB_TMEM_ST8(ta + 16 + 8 * hh, lo);
-          } else {
-            uint32_t hi[16], lo[16];
-            split_tf32(sx, hi, lo);
-            if (hh == 0) {
-              if (alive) alive = mbar_wait(l2_free + 8 * c, (uint32_t)(k & 1));  // the A buffer may take this chunk
-              __syncwarp();
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            MB_TMEM_ST16(ta + 16 * hh, hi);
-            MB_TMEM_ST16(ta + 32 + 16 * hh, lo);
+          uint32_t hi[8], lo[8];
+          split_bf16(sx, hi, lo);
+          if (hh == 0) {
+            if (alive) alive = mbar_wait(l2_free + 8 * (4 * grp + c), part);  // the A buffer may take this chunk
+            __syncwarp();
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           }
+          MB_TMEM_ST8(ta + 8 * hh, hi);
+          MB_TMEM_ST8(ta + 16 + 8 * hh, lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(a_ready + 8 * ab);
       }
-      // ------------------------------------------------ epi(k): z2 -> RMSNorm -> activation -> h
-      if (alive) alive = mbar_wait(d2_full + 8 * acc, upar);
+      // ------------------------------------------------ epi(k), pass 1: + b2, optional z2 store, sum of squares
+      if (alive) alive = mbar_wait(d2_full + 8 * k6, par6);
       alive = __all_sync(0xffffffffu, alive);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float y[64];
-      {
-        uint32_t v0[32], v1[32];
-        MB_TMEM_LD32(d_lane, v0);
-        MB_TMEM_LD32(d_lane + 32u, v1);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { y[i] = __uint_as_float(v0[i]); y[32 + i] = __uint_as_float(v1[i]); }
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(d_free + 8 * acc);  // the accumulator is in registers: the next unit may overwrite it
       float ss = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float y[32];
+        {
+          uint32_t v[32];
+          MB_TMEM_LD32(d_lane + 32u * c, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        const float4 bv = b2s[32 * acc + 16 * hf + jj];
-        y[4 * jj] += bv.x; y[4 * jj + 1] += bv.y; y[4 * jj + 2] += bv.z; y[4 * jj + 3] += bv.w;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) ss = fmaf(y[4 * jj + i], y[4 * jj + i], ss);
-      }
-      if (z2 && valid) {
-        float* zp = z2 + row * d.ld_z2 + 128 * acc + 64 * hf;
+          for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(v[i]);
+        }
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
-          float o[8];
+          const float4 bv = b2s[8 * c + jj];
+          y[4 * jj] += bv.x; y[4 * jj + 1] += bv.y; y[4 * jj + 2] += bv.z; y[4 * jj + 3] += bv.w;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = y[8 * jj + i];
-          st8(zp + 8 * jj, o);
+          for (int i = 0; i < 4; ++i) ss = fmaf(y[4 * jj + i], y[4 * jj + i], ss);
         }
-      }
-      // the other half of the row's sum of squares comes from the partner warp (same quarter, other column half)
-      __syncwarp();
-      xs[acc * 256 + hf * 128 + q * 32 + lane] = ss;
-      asm volatile("bar.sync %0, 64;" :: "r"(1 + q) : "memory");
-      ss += xs[acc * 256 + (hf ^ 1) * 128 + q * 32 + lane];
-      const float rinv = rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
-      // the core unit parks c = SiLU(.) in the output row; the gate unit (same thread, next unit) reads it back
-      float* const park = (hout ? hout + row * d.ld_h : out2 + row * d.ld_out2) + 64 * hf;
-      const float4* const nws = reinterpret_cast<const float4*>(cst + 512 + 128 * acc + 64 * hf);
-      if (!alive || !valid) {
-        // nothing to write for rows past the end (or after an expired wait)
-      } else if (acc == 0) {
+        if (z2 && valid && alive) {
+          float* zp = z2 + row * d.ld_z2 + 128 * grp + 32 * c;
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const float4 wa = nws[2 * jj], wb = nws[2 * jj + 1];
-          const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-          float o[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = silu_fma_f(y[8 * jj + i] * rinv * w[i]);
-          st8(park + 8 * jj, o);
-        }
-      } else {
-        // 16 columns per round: the parked values and the residual row are requested together, so a round costs one
-        // memory latency (both were touched by this SM a moment ago and sit in L2)
-        const float* const rrow = out2 ? res + row * d.ld_res + 64 * hf : nullptr;
-        float* const orow = out2 ? out2 + row * d.ld_out2 + 64 * hf : nullptr;
-        const float4* const rws = reinterpret_cast<const float4*>(cst + 768 + 64 * hf);
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          float cp[2][8], rr[2][8];
-          ld8(park + 16 * b, cp[0]);
-          ld8(park + 16 * b + 8, cp[1]);
-          if (out2) {
-            ld8(rrow + 16 * b, rr[0]);
-            ld8(rrow + 16 * b + 8, rr[1]);
-          }
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const int jj = 2 * b + t;
-            const float4 wa = nws[2 * jj], wb = nws[2 * jj + 1];
-            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+          for (int jj = 0; jj < 4; ++jj) {
             float o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fma_f(y[8 * jj + i] * rinv * w[i]);
-            if (hout) st8(park + 8 * jj, o);
-            if (out2) {
-              const float4 ra = rws[2 * jj], rb = rws[2 * jj + 1];
-              const float rw[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+            for (int i = 0; i < 8; ++i) o[i] = y[8 * jj + i];
+            st8(zp + 8 * jj, o);
+          }
+        }
+        __syncwarp();
+      }
+      const float rinv = rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
+      // the core unit parks c = SiLU(.) in the output row; the gate unit's warp of the same lane quarter reads it back
+      float* const park = hout ? hout + row * d.ld_h : out2 + row * d.ld_out2;
+      if (grp == 1) {
+        if (alive) alive = mbar_wait(park_bar, park_par);
+        alive = __all_sync(0xffffffffu, alive);
+      }
+      // ------------------------------------------------ pass 2: normalise, activate, write
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float y[32];
+        {
+          uint32_t v[32];
+          MB_TMEM_LD32(d_lane + 32u * c, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = fmaf(rw[i], rr[t][i], o[i]);
-              st8(orow + 8 * jj, o);
+          for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(v[i]);
+        }
+        if (c == 3) {  // the accumulator has been read for the last time: layer 1 of unit k + 3 may overwrite it
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(d_free + 8 * k6);
+        }
+        if (alive && valid) {  // nothing to write for rows past the end (or after an expired wait)
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const float4 bv = b2s[8 * c + jj], wv = nws[8 * c + jj];
+          y[4 * jj] = (y[4 * jj] + bv.x) * rinv * wv.x;
+          y[4 * jj + 1] = (y[4 * jj + 1] + bv.y) * rinv * wv.y;
+          y[4 * jj + 2] = (y[4 * jj + 2] + bv.z) * rinv * wv.z;
+          y[4 * jj + 3] = (y[4 * jj + 3] + bv.w) * rinv * wv.w;
+        }
+        if (grp == 0) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = silu_fma_f(y[8 * jj + i]);
+            st8(park + 32 * c + 8 * jj, o);
+          }
+        } else {
+          // 16 columns per round: the parked values and the residual row are requested together, so a round costs one
+          // memory latency (both were touched by this SM a moment ago and sit in L2)
+          const float* const rrow = out2 ? res + row * d.ld_res + 32 * c : nullptr;
+          float* const orow = out2 ? out2 + row * d.ld_out2 + 32 * c : nullptr;
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            float cp[2][8], rr[2][8];
+            ld8(park + 32 * c + 16 * b, cp[0]);
+            ld8(park + 32 * c + 16 * b + 8, cp[1]);
+            if (out2) {
+              ld8(rrow + 16 * b, rr[0]);
+              ld8(rrow + 16 * b + 8, rr[1]);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int jj = 2 * b + t;
+              float o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fma_f(y[8 * jj + i]);
+              if (hout) st8(park + 32 * c + 8 * jj, o);
+              if (out2) {
+                const float4 ra = rws[8 * c + 2 * jj], rb = rws[8 * c + 2 * jj + 1];
+                const float rw[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = fmaf(rw[i], rr[t][i], o[i]);
+                st8(orow + 8 * jj, o);
+              }
             }
           }
         }
+        }
+        __syncwarp();  // the lanes meet again before the next (warp-wide) tensor-memory load
+      }
+      if (grp == 0) {  // the parked values of this lane quarter are complete and visible to the CTA
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(park_bar);
       }
       __syncwarp();
     }
@@ -469,7 +491,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         continue;
       }
       if (k >= 2) {  // this phase follows a layer-2 phase (see the note on the barriers)
-        if (alive) alive = mbar_wait(d1_full + 8 * ((k - 1) & 1), (uint32_t)(((k - 1) >> 1) & 1));
+        if (alive) alive = mbar_wait(d1_full + 8 * ((k - 1) % 6), (uint32_t)(((k - 1) / 6) & 1));
         alive = __all_sync(0xffffffffu, alive);
       }
       for (int c = par; c < nch1; c += 2, ++n) {
@@ -479,8 +501,8 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         __syncwarp();
         const uint32_t patch = patch0 + (uint32_t)(n & 1) * (32 * 128);
         const bool act = (act_mask >> (c >> 2)) & 1;
-        const uint32_t ta = lane_base + 256 + Fmt::A_COLS * ab;
-        convert_chunk<BF>(patch, lane, act, ta, [&]() {
+        const uint32_t ta = lane_base + GP_A_BASE + 32u * ab;
+        convert_chunk<true>(patch, lane, act, ta, [&]() {
           if (gi >= NB && alive) alive = mbar_wait(a_done + 8 * ab, ((gi / NB) - 1) & 1);  // A buffer ab is free again
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         });

@@ -635,8 +635,7 @@ static int device_config(int* n_sm) {
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
-    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
-    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
     int n = 0;
     MB_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     c.n_sm = n;
@@ -889,27 +888,23 @@ extern "C" int mb_gated_mlp_fwd(const mb_gated_mlp* g, void* stream_) {
                        (!g->h || ok32(g->h, g->ld_h)) && (!g->out2 || (ok32(g->out2, g->ld_out2) && ok32(g->res, g->ld_res))) &&
                        (!g->b1 || ok32(g->b1, 0)) && (!g->b2 || ok32(g->b2, 0)) && ok32(g->norm_core, 0) &&
                        ok32(g->norm_gate, 0) && (!g->res_w || ok32(g->res_w, 0));
-  if ((mb::g_gemm_mode != 0 && mb::g_gemm_mode != 3) || !wide_ok) return gated_mlp_composed(g, stream_);
-  const bool bf16 = mb::g_gemm_mode == 0;
-  const void* w1h = bf16 ? (const void*)g->W1_hi16 : (const void*)g->W1_hi;
-  const void* w1l = bf16 ? (const void*)g->W1_lo16 : (const void*)g->W1_lo;
-  const void* w2h = bf16 ? (const void*)g->W2_hi16 : (const void*)g->W2_hi;
-  const void* w2l = bf16 ? (const void*)g->W2_lo16 : (const void*)g->W2_lo;
+  // The fused kernel computes with the 3xBF16 split (the default mode); the other modes compose the three launches.
+  if (mb::g_gemm_mode != 0 || !wide_ok) return gated_mlp_composed(g, stream_);
+  const void* w1h = g->W1_hi16, *w1l = g->W1_lo16, *w2h = g->W2_hi16, *w2l = g->W2_lo16;
   if (!w1h || !w1l || !w2h || !w2l) return MB_ERR_INVALID;
   if (!mb::aligned16(w1h) || !mb::aligned16(w1l) || !mb::aligned16(w2h) || !mb::aligned16(w2l)) return MB_ERR_INVALID;
-  if (bf16 && ((g->ldw1 & 7) || (g->ldw2 & 7))) return MB_ERR_INVALID;
+  if ((g->ldw1 & 7) || (g->ldw2 & 7)) return MB_ERR_INVALID;
   int n_sm = 0;
   int rc = mb::device_config(&n_sm);
   if (rc) return rc;
   mb::GatedMaps maps;
-  if ((rc = mb::weight_map(w1h, g->ldw1, 128 * g->n_src, &maps.w1[0], 256, bf16))) return rc;
-  if ((rc = mb::weight_map(w1l, g->ldw1, 128 * g->n_src, &maps.w1[1], 256, bf16))) return rc;
-  if ((rc = mb::weight_map(w2h, g->ldw2, 128, &maps.w2[0], 256, bf16))) return rc;
-  if ((rc = mb::weight_map(w2l, g->ldw2, 128, &maps.w2[1], 256, bf16))) return rc;
+  if ((rc = mb::weight_map(w1h, g->ldw1, 128 * g->n_src, &maps.w1[0], 256, true))) return rc;
+  if ((rc = mb::weight_map(w1l, g->ldw1, 128 * g->n_src, &maps.w1[1], 256, true))) return rc;
+  if ((rc = mb::weight_map(w2h, g->ldw2, 128, &maps.w2[0], 256, true))) return rc;
+  if ((rc = mb::weight_map(w2l, g->ldw2, 128, &maps.w2[1], 256, true))) return rc;
   const long long n_tiles = (g->n_rows + 127) / 128;
   const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
-  if (bf16) mb::k_gated_fwd<true><<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
-  else mb::k_gated_fwd<false><<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
+  mb::k_gated_fwd<<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
   MB_LAUNCH_CHECK("k_gated_fwd");
   return MB_OK;
 }

@@ -141,7 +141,7 @@ def gated_mlp_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True)
     ref = srcs[0][0]
     n_rows = int(n_rows)
     # the composed path of the non-default GEMM modes uses z1 / z2 as scratch
-    save = save or _gemm_mode in (1, 2)
+    save = save or _gemm_mode != 0
     z1 = new(n_rows, 2 * D, ref) if save else None
     z2 = new(n_rows, 2 * D, ref) if save else None
     h = new(n_rows, D, ref) if want_h else None

@@ -238,8 +238,8 @@ def test_gated_mlp_fwd_fused_equals_composed(ops):
     ops.set_gemm_mode("tcgen05")
     for i, name in enumerate(("z1", "z2", "h", "out2")):
         report(f"gated_mlp_fwd fused 3xBF16 vs simt-composed {name}", outs["tcgen05"][i], outs["simt"][i], TOL_BF16)
-        report(f"gated_mlp_fwd fused 3xTF32 vs simt-composed {name}", outs["tcgen05_tf32"][i], outs["simt"][i], TOL_TF32)
-        report(f"gated_mlp_fwd fused 3xTF32 vs tile-composed {name}", outs["tcgen05_tf32"][i], outs["tcgen05_tile"][i],
+        report(f"gated_mlp_fwd 3xTF32-composed vs simt-composed {name}", outs["tcgen05_tf32"][i], outs["simt"][i], TOL_TF32)
+        report(f"gated_mlp_fwd 3xTF32-composed vs tile-composed {name}", outs["tcgen05_tf32"][i], outs["tcgen05_tile"][i],
                TOL_TF32)
 
 
