@@ -86,7 +86,7 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
                :: "r"(tmem_d), "r"(tmem_a), "l"(db), "r"(TC_IDESC_BF16), "r"(accumulate) : "memory");
 }
 
-// per-format constants of the persistent kernels
+// per-format constants of the persistent GEMM kernel
 template <bool BF> struct PsFormat {
   static constexpr uint32_t A_COLS = BF ? 32 : 64;   // tensor-memory columns of one A chunk (hi | lo)
   static constexpr uint32_t N_ABUF = BF ? 8 : 4;     // A buffers (256 columns in all)

@@ -410,9 +410,10 @@ _gemm_mode = 0
 
 
 def set_gemm_mode(mode: str) -> None:
-    """'tcgen05' (default): persistent tensor-core kernels, 3-term BF16 operand split; 'tcgen05_tf32': the same kernels
-    with a 3-term TF32 split; 'tcgen05_tile': a one-tile-per-CTA tensor-core kernel (3-term TF32); 'simt': exact fp32
-    FMA cross-check.  A test knob."""
+    """'tcgen05' (default): persistent tensor-core kernels (GEMM and fused gated MLP), 3-term BF16 operand split;
+    'tcgen05_tf32': the persistent GEMM with a 3-term TF32 split; 'tcgen05_tile': a one-tile-per-CTA tensor-core
+    kernel (3-term TF32); 'simt': exact fp32 FMA cross-check.  Outside the default mode a gated MLP is composed from
+    two GEMM launches and the gate kernel.  A test knob."""
     global _gemm_mode
     _gemm_mode = {"tcgen05": 0, "simt": 1, "tcgen05_tile": 2, "tcgen05_tf32": 3}[mode]
     _lib.check(_lib.load().mb_set_gemm_mode(_gemm_mode), "mb_set_gemm_mode")
