@@ -50,23 +50,7 @@ __device__ __forceinline__ float silu_grad_fast_f(float x) {
   return s * (1.0f + x * (1.0f - s));
 }
 
-// The same on the FMA pipe wherever possible, for the persistent tensor-core kernels: there the 16-lane special-function
-// pipe (ex2, rcp, float -> bf16 conversions) is the busiest unit of the SM, so the reciprocal is a Newton iteration
-// (integer first guess, three steps, relative error < 1e-7) and only the exponential stays on that pipe.  The
-// argument of the exponential is capped so that 1 + e^-x stays a normal number the first guess can handle; below
-// x = -80 the results differ from the exact ones by less than 1e-30.
-__device__ __forceinline__ float sigmoid_fma_f(float x) {
-  const float y = 1.0f + __expf(fminf(-x, 80.0f));
-  float r = __uint_as_float(0x7EF311C7u - __float_as_uint(y));
-#pragma unroll
-  for (int it = 0; it < 3; ++it) r = fmaf(r, fmaf(-y, r, 1.0f), r);
-  return r;
-}
-__device__ __forceinline__ float silu_fma_f(float x) { return x * sigmoid_fma_f(x); }
-__device__ __forceinline__ float silu_grad_fma_f(float x) {
-  const float s = sigmoid_fma_f(x);
-  return s * (1.0f + x * (1.0f - s));
-}
+__device__ __forceinline__ float sigmoid_fast_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

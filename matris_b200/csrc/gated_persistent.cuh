@@ -342,7 +342,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         for (int hh = 0; hh < 2; ++hh) {
           float sx[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sx[i] = silu_fma_f(x[16 * hh + i]);
+          for (int i = 0; i < 16; ++i) sx[i] = silu_fast_f(x[16 * hh + i]);
           uint32_t hi[8], lo[8];
           split_bf16(sx, hi, lo);
           if (hh == 0) {
@@ -429,7 +429,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           for (int jj = 0; jj < 4; ++jj) {
             float o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = silu_fma_f(y[8 * jj + i]);
+            for (int i = 0; i < 8; ++i) o[i] = silu_fast_f(y[8 * jj + i]);
             st8(park + 32 * c + 8 * jj, o);
           }
         } else {
@@ -451,7 +451,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
               const int jj = 2 * b + t;
               float o[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fma_f(y[8 * jj + i]);
+              for (int i = 0; i < 8; ++i) o[i] = cp[t][i] * sigmoid_fast_f(y[8 * jj + i]);
               if (hout) st8(park + 32 * c + 8 * jj, o);
               if (out2) {
                 const float4 ra = rws[8 * c + 2 * jj], rb = rws[8 * c + 2 * jj + 1];

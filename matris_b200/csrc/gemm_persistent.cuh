@@ -53,20 +53,21 @@ __device__ __forceinline__ void st8(float* p, const float (&v)[8]) {
                   "r"(v[7]) : "memory")
 
 // two floats -> one 32-bit word of two bf16 (round to nearest even): `first` in the low half (the lower K index)
-// hi / lo split of 16 consecutive K values into 8 + 8 packed words (BF16): hi = bf16(x), lo = bf16(x - hi), the first
-// value of a pair in the low half of the word.  Integer arithmetic only: the conversion instruction runs on the
-// special-function pipe, which the activations already keep busy.  Adding half a bf16 ulp to the bit pattern and
-// keeping the upper 16 bits rounds to nearest (ties away from zero, which differs from the conversion instruction on
-// exact ties only); __byte_perm picks the two upper halves into one word.
+// Two floats -> one word of two bf16 (round to nearest even), the first value in the low half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float first, float second) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(second), "f"(first));
+  return r;
+}
+
+// hi / lo split of 16 consecutive K values into 8 + 8 packed words (BF16): hi = bf16(x), lo = bf16(x - hi) ...
 __device__ __forceinline__ void split_bf16(const float (&x)[16], uint32_t (&hi)[8], uint32_t (&lo)[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint32_t a = __float_as_uint(x[2 * i]) + 0x8000u, b = __float_as_uint(x[2 * i + 1]) + 0x8000u;
-    hi[i] = __byte_perm(a, b, 0x7632);
-    const float r0 = x[2 * i] - __uint_as_float(a & 0xFFFF0000u);
-    const float r1 = x[2 * i + 1] - __uint_as_float(b & 0xFFFF0000u);
-    const uint32_t c = __float_as_uint(r0) + 0x8000u, d = __float_as_uint(r1) + 0x8000u;
-    lo[i] = __byte_perm(c, d, 0x7632);
+    hi[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
+    const float r0 = x[2 * i] - __uint_as_float(hi[i] << 16);
+    const float r1 = x[2 * i + 1] - __uint_as_float(hi[i] & 0xFFFF0000u);
+    lo[i] = pack_bf16x2(r0, r1);
   }
 }
 // ... or into 16 + 16 words (TF32): hi = x cut to tf32's 10 mantissa bits, lo = the exact remainder
@@ -135,7 +136,7 @@ __device__ __forceinline__ void convert_chunk(uint32_t patch, int lane, bool act
     }
     if (act) {
 #pragma unroll
-      for (int q = 0; q < 16; ++q) x[q] = silu_fma_f(x[q]);
+      for (int q = 0; q < 16; ++q) x[q] = silu_fast_f(x[q]);
     }
     if (BF) {
       uint32_t hi[8], lo[8];
@@ -439,11 +440,11 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
             }
             if constexpr (decltype(has_gate)::value) {
 #pragma unroll
-              for (int q = 0; q < 8; ++q) o[q] *= silu_grad_fma_f(z[j][q]);
+              for (int q = 0; q < 8; ++q) o[q] *= silu_grad_fast_f(z[j][q]);
             }
             if constexpr (decltype(has_act)::value) {
 #pragma unroll
-              for (int q = 0; q < 8; ++q) o[q] = silu_fma_f(o[q]);
+              for (int q = 0; q < 8; ++q) o[q] = silu_fast_f(o[q]);
             }
             if constexpr (decltype(has_res)::value) {
               float x[8];
@@ -515,9 +516,9 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
               float o[4] = {av[i].x + bias4.x, av[i].y + bias4.y, av[i].z + bias4.z, av[i].w + bias4.w};
               if (cb.gate) {
                 const float4 z = ld4(cb.gate + gr * cb.ld_gate + cb.col_gate + col);
-                o[0] *= silu_grad_fma_f(z.x); o[1] *= silu_grad_fma_f(z.y); o[2] *= silu_grad_fma_f(z.z); o[3] *= silu_grad_fma_f(z.w);
+                o[0] *= silu_grad_fast_f(z.x); o[1] *= silu_grad_fast_f(z.y); o[2] *= silu_grad_fast_f(z.z); o[3] *= silu_grad_fast_f(z.w);
               }
-              if (out_act) { o[0] = silu_fma_f(o[0]); o[1] = silu_fma_f(o[1]); o[2] = silu_fma_f(o[2]); o[3] = silu_fma_f(o[3]); }
+              if (out_act) { o[0] = silu_fast_f(o[0]); o[1] = silu_fast_f(o[1]); o[2] = silu_fast_f(o[2]); o[3] = silu_fast_f(o[3]); }
               if (cb.res) {
                 const float4 x = ld4(cb.res + gr * cb.ld_res + cb.col_res + col);
                 o[0] = fmaf(resw4.x, x.x, o[0]); o[1] = fmaf(resw4.y, x.y, o[1]); o[2] = fmaf(resw4.z, x.z, o[2]); o[3] = fmaf(resw4.w, x.w, o[3]);

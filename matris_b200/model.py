@@ -55,6 +55,18 @@ def _pack_gated(get, prefix, dev):
         k=w1.shape[1])
 
 
+def _pack_mlp(get, prefix, bias):
+    """The plain-MLP variant of an update block (graph_conv_mlp = "MLP"): nn.Sequential(MLP, RMSNorm)
+    (matris/model/interaction_block.py:39-62, 172-184): weights, transposes for the backward products, norm weight."""
+    w1, w2 = get(prefix + "0.layers.0.weight"), get(prefix + "0.layers.3.weight")
+    SW = ops.SplitWeight
+    return SimpleNamespace(
+        kind="mlp", w1=SW(w1), w2=SW(w2), w1t=SW(w1.t()), w2t=SW(w2.t()),
+        b1=get(prefix + "0.layers.0.bias").contiguous() if bias else None,
+        b2=get(prefix + "0.layers.3.bias").contiguous() if bias else None,
+        nw=get(prefix + "1.weight").contiguous(), k=w1.shape[1])
+
+
 def _pack_ffn(get, prefix, bias):
     """node_FFN / edge_FFN (matris/model/interaction_block.py:197-210): two linear layers, biases only with use_bias."""
     w1, w2 = get(prefix + "layers.0.weight"), get(prefix + "layers.3.weight")
@@ -98,12 +110,16 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
     P.t_wb = SW(get(t + "swish_layer.linear.weight"))
     P.t_wbt = P.t_wb.t()
     P.layers = []
+    if str(cfg["graph_conv_mlp"]).lower() == "mlp":
+        pack_update = lambda prefix: _pack_mlp(get, prefix, bool(cfg["use_bias"]))  # noqa: E731
+    else:
+        pack_update = lambda prefix: _pack_gated(get, prefix, device)  # noqa: E731
     for i in range(int(cfg["num_layers"])):
         L = SimpleNamespace()
         for gname in ("atom", "line"):
             p = f"interaction_block.{i}.attn_block_{gname}_graph."
-            A = SimpleNamespace(node=_pack_gated(get, p + "node_nonlinear_update.", device),
-                                edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
+            A = SimpleNamespace(node=pack_update(p + "node_nonlinear_update."),
+                                edge=pack_update(p + "edge_nonlinear_update."),
                                 wn=get(p + "node_res_weight").reshape(-1).contiguous(),
                                 we=get(p + "edge_res_weight").reshape(-1).contiguous())
             A.wst = SW(torch.cat([get(p + "source_weight_linear.weight"), get(p + "target_weight_linear.weight")],
@@ -111,7 +127,7 @@ def pack_parameters(sd: dict, cfg: dict, device) -> SimpleNamespace:
             A.wstt = A.wst.t()                        # [128,256]
             setattr(L, "attn_" + gname, A)
             p = f"interaction_block.{i}.refine_block_{gname}_graph."
-            R = SimpleNamespace(edge=_pack_gated(get, p + "edge_nonlinear_update.", device),
+            R = SimpleNamespace(edge=pack_update(p + "edge_nonlinear_update."),
                                 nffn=_pack_ffn(get, p + "node_FFN.", bool(cfg["use_bias"])),
                                 effn=_pack_ffn(get, p + "edge_FFN.", bool(cfg["use_bias"])),
                                 smoothed_edge=bool(cfg["use_smoothed_for_delta_edge"]) and gname == "atom",
@@ -154,13 +170,43 @@ def row_graphs(g: BatchedGraph):
 def gated_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True):
     """GatedMLP.forward (matris/model/functions.py:300-311) in one kernel: returns (z1, z2, h, out2) with
     z1 = X W1^T + b1 (core|gate pre-activations) and z2 = SiLU(z1) W2^T + b2 (pre-norm) only when ``save``."""
+    if getattr(p, "kind", "gated") == "mlp":
+        return _mlp_fwd(p, n_rows, srcs, want_h, res, res_w)
     return ops.gated_mlp_fwd(p, n_rows, srcs, want_h=want_h, res=res, res_w=res_w, save=save)
+
+
+def _mlp_fwd(p, n_rows, srcs, want_h, res, res_w):
+    """The plain-MLP variant of an update block: h = RMSNorm(W2 SiLU(W1 x + b1) + b2); same return convention, with
+    z1 / z2 the two [rows,128] pre-activation / pre-norm tensors (always produced: they are the intermediates)."""
+    like = srcs[0][0]
+    z1, z2 = ops.new(n_rows, D, like), ops.new(n_rows, D, like)
+    gemm(n_rows, [B(srcs, p.w1, bias=p.b1, out=z1)])
+    gemm(n_rows, [B([S(z1, None, 0, 1)], p.w2, bias=p.b2, out=z2)])
+    h = ops.rmsnorm_fwd(z2, p.nw)
+    out2 = None
+    if res is not None:
+        out2 = h.clone()
+        ops.scale_rows(res, res_w, y=out2, accumulate=True)
+    return z1, z2, (h if want_h else None), out2
 
 
 def gated_bwd(p, n_rows, z1, z2, dh, dests):
     """Backward through the gated MLP: dests[c] = (tensor, idx, mode[, res, res_w]) for K segment c.  With ``res``
     the block stores ``gemm + res_w * res`` (the residual branch's gradient joins in the epilogue instead of in a
     separate scaling pass followed by an accumulate)."""
+    if getattr(p, "kind", "gated") == "mlp":
+        dy = ops.rmsnorm_bwd(z2, p.nw, dh.contiguous())
+        da1 = torch.empty_like(z1)
+        gemm(n_rows, [B([S(dy)], p.w2t, gate=z1, out=da1)])
+        blocks = []
+        for c, dest in enumerate(dests):
+            t, idx, mode = dest[:3]
+            if t is None:
+                continue
+            res, res_w = (dest[3], dest[4]) if len(dest) > 3 else (None, None)
+            blocks.append(B([S(da1)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode, res=res, res_w=res_w))
+        gemm(n_rows, blocks)
+        return
     dz2 = ops.gate_bwd(z2, p.nc, p.ng, dh)
     dz1 = torch.empty_like(z1)
     gemm(n_rows, [B([S(dz2, None, D * j)], p.w2t, w_row=D * j, gate=z1, gate_col=D * j, out=dz1, out_col=D * j)

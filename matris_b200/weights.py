@@ -43,10 +43,12 @@ def full_config(config: dict | None = None, **overrides) -> OrderedDict:
 def check_supported(cfg: dict) -> None:
     """The CUDA path implements the default architecture family only; anything
     else is rejected here rather than silently evaluated differently."""
-    want = dict(graph_conv_mlp="gatemlp", activation_type="silu", norm_type="rms")
+    want = dict(activation_type="silu", norm_type="rms")
     for k, v in want.items():
         if str(cfg[k]).lower() != v:
             raise NotImplementedError(f"matris_b200 implements {k}={v!r} only (got {cfg[k]!r})")
+    if str(cfg["graph_conv_mlp"]).lower() not in ("gatemlp", "mlp"):
+        raise NotImplementedError(f"graph_conv_mlp={cfg['graph_conv_mlp']!r}: 'GateMLP' or 'MLP'")
     if str(cfg["distance_expansion"]).lower() not in ("bessel", "gaussian"):
         raise NotImplementedError(f"distance_expansion={cfg['distance_expansion']!r}: 'Bessel' or 'Gaussian'")
     if str(cfg["three_body_expansion"]).lower() not in ("sh", "fourier"):
@@ -95,7 +97,16 @@ def schema(config: dict | None = None) -> "OrderedDict[str, tuple]":
         s["three_body_embedding.angle_embedding.weight"] = (D, A)
     s["three_body_embedding.swish_layer.linear.weight"] = (D, D)
 
+    plain_mlp = str(cfg["graph_conv_mlp"]).lower() == "mlp"
+
     def gated(prefix, k_in):
+        if plain_mlp:  # nn.Sequential(MLP(in, D, D, bias=use_bias), RMSNorm) (interaction_block.py:39-62, 172-184)
+            for j, k in ((0, k_in), (3, D)):
+                s[f"{prefix}0.layers.{j}.weight"] = (D, k)
+                if cfg["use_bias"]:
+                    s[f"{prefix}0.layers.{j}.bias"] = (D,)
+            s[prefix + "1.weight"] = (D,)
+            return
         s[prefix + "gate_norm.weight"] = (D,)
         s[prefix + "core_norm.weight"] = (D,)
         for branch in ("mlp_core", "mlp_gate"):
@@ -178,7 +189,7 @@ def random_state_dict(config: dict | None = None, seed: int = 0, jitter: float =
             v = np.pi * np.arange(1, shape[0] + 1, dtype=np.float64) * (1 + 0.2 * jitter * g.uniform(-1, 1, shape))
         elif key.endswith("embedding.weight") and key.startswith("atom_embedding"):
             v = g.standard_normal(shape)
-        elif key.endswith("_norm.weight") or key.endswith("res_weight"):
+        elif key.endswith("_norm.weight") or key.endswith("res_weight") or key.endswith("_update.1.weight"):
             v = 1.0 + jitter * g.uniform(-1, 1, shape)
         elif key.endswith("edge_init_norm.bias"):
             v = jitter * g.uniform(-1, 1, shape)

@@ -143,6 +143,9 @@ class _P:
     def sub(self, name):
         return _P(self.sd, self.prefix + name + ".")
 
+    def has(self, name):
+        return self.prefix + name in self.sd
+
 
 def mlp2(p, x, bias):
     h = F.silu(F.linear(x, p("layers.0.weight"), p("layers.0.bias") if bias else None))
@@ -150,6 +153,11 @@ def mlp2(p, x, bias):
 
 
 def gated_mlp(p, x):
+    """GatedMLP.forward (matris/model/functions.py:245-311), or - where the state dict holds the plain-MLP variant of
+    the block (graph_conv_mlp = "MLP": nn.Sequential(MLP, norm), matris/model/interaction_block.py:39-62) - that."""
+    if p.has("0.layers.0.weight"):
+        y = mlp2(p.sub("0"), x, p.has("0.layers.0.bias"))  # biases only with use_bias
+        return F.rms_norm(y, (y.shape[1],), p("1.weight"), None)
     core = F.rms_norm(mlp2(p.sub("mlp_core"), x, True), (p("core_norm.weight").shape[0],),
                       p("core_norm.weight"), None)
     gate = F.rms_norm(mlp2(p.sub("mlp_gate"), x, True), (p("gate_norm.weight").shape[0],),
@@ -248,10 +256,12 @@ def process_graphs(graphs, compute_stress, dtype=torch.float32):
 
 # ------------------------------------------------------------------ whole model
 def _check_config(cfg):
-    want = dict(graph_conv_mlp="gatemlp", activation_type="silu", norm_type="rms")
+    want = dict(activation_type="silu", norm_type="rms")
     for k, v in want.items():
         if str(cfg.get(k, v)).lower() != v:
             raise NotImplementedError(f"oracle covers {k}={v!r} only, got {cfg[k]!r}")
+    if str(cfg.get("graph_conv_mlp", "gatemlp")).lower() not in ("gatemlp", "mlp"):
+        raise NotImplementedError(f"oracle covers graph_conv_mlp 'GateMLP' and 'MLP', got {cfg['graph_conv_mlp']!r}")
     if str(cfg.get("distance_expansion", "bessel")).lower() not in ("bessel", "gaussian"):
         raise NotImplementedError(f"oracle covers Bessel and Gaussian distance expansions, got {cfg['distance_expansion']!r}")
     if str(cfg.get("three_body_expansion", "sh")).lower() not in ("sh", "fourier"):

@@ -26,7 +26,7 @@ def load_golden(name):
 
 GOLDEN_CASES = ["cu32_L10", "cu32_L2_jit", "cu32_ideal_L1", "random2_L2", "pu4si6_L2", "cu1_L1", "perov_L3",
                 "fe432_L2", "lipscl256_L2", "random8_L2", "democif_L2", "random2_L2_bias_smoothed",
-                "random2_L2_gaussian_fourier"]
+                "random2_L2_gaussian_fourier", "random2_L2_mlp_bias"]
 
 
 def golden_config(meta):

@@ -53,6 +53,9 @@ CASES = {
     # non-default bases: Gaussian distance expansion, Fourier angle expansion
     "random2_L2_gaussian_fourier": (lambda: workloads.random_crystals(2, seed=11), 2, "efsm", 0.1,
                                     dict(distance_expansion="Gaussian", three_body_expansion="fourier")),
+    # the plain-MLP variant of the update blocks, with biases
+    "random2_L2_mlp_bias": (lambda: workloads.random_crystals(2, seed=11), 2, "efsm", 0.1,
+                            dict(graph_conv_mlp="MLP", use_bias=True)),
 }
 
 
