@@ -289,22 +289,27 @@ int mb_seg_attn_fwd(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* src_
                     const int32_t* emap, const float* logits, const float* h, float* agg_t, float* agg_s,
                     float* stats, void* stream);
 /* per row: dh = a_t*dagg_t[tgt] + a_s*dagg_s[src] + dh_scale*dh_in[dh_map ? dh_map[r] : r];
- * dlogits[r] = (a_s*dagg_s*(h-agg_s) | a_t*dagg_t*(h-agg_t)) */
+ * dlogits[r] = (a_s*dagg_s*(h-agg_s) | a_t*dagg_t*(h-agg_t)).
+ * With gate_dz != NULL the row's dh is not written: it goes on, in registers, through the adjoint of the gated MLP's
+ * tail (what mb_gate_bwd computes from gate_z = z2 [rows,256] and the two norm weights) and gate_dz [rows,256]
+ * receives the result; dh may then be NULL. */
 int mb_seg_attn_bwd(int64_t n_rows, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
                     const int32_t* emap, const float* logits, const float* h, const float* agg_t,
                     const float* agg_s, const float* stats, const float* dagg_t, const float* dagg_s,
                     const float* dh_in, const int32_t* dh_map, float dh_scale, float* dh, float* dlogits,
-                    void* stream);
+                    const float* gate_z, const float* gate_wc, const float* gate_wg, float* gate_dz, void* stream);
 
 /* Refinement aggregation (matris/model/interaction_block.py:246-262):
  * agg[n] = sum_{r in target segment n} h[r] * s[r]; s[r] = env[emap[r]] (atom graph, src == NULL)
  * or env[src[r]] * env[n] (line graph). */
 int mb_seg_smooth_sum_fwd(int32_t n_nodes, const int32_t* tgt_ptr, const int32_t* emap, const int32_t* src,
                           int32_t idx_stride, const float* env, const float* h, float* agg, void* stream);
-/* per row: dh[r] (+)= dagg[tgt[r]] * s[r]   (accumulate != 0: add to existing dh) */
+/* per row: dh[r] (+)= dagg[tgt[r]] * s[r]   (accumulate != 0: add to existing dh).  gate_z / gate_wc / gate_wg /
+ * gate_dz as in mb_seg_attn_bwd: the finished dh row goes through the gated MLP's tail adjoint instead of to memory. */
 int mb_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
                                const int32_t* emap, const float* env, const float* dagg, float* dh,
-                               int32_t accumulate, void* stream);
+                               int32_t accumulate, const float* gate_z, const float* gate_wc, const float* gate_wg,
+                               float* gate_dz, void* stream);
 /* gradient w.r.t. env.  Atom graph (src_ptr == NULL): denv[u] = sum over the two directed rows e of
  * bond u of (dagg[tgt[e]] + drow[e])*h[e]  (u2d / rev give the rows; drow, optional, is a gradient that reached
  * the smoothed rows h*s directly: use_smoothed_for_delta_edge, matris/model/interaction_block.py:262-266).

@@ -90,9 +90,10 @@ _SIGNATURES = {
     "mb_gate_fwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_gate_bwd": [_i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_seg_attn_fwd": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
-    "mb_seg_attn_bwd": [_i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp],
+    "mb_seg_attn_bwd": [_i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp,
+                        _vp, _vp, _vp],
     "mb_seg_smooth_sum_fwd": [_i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp],
-    "mb_seg_smooth_sum_bwd_rows": [_i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp],
+    "mb_seg_smooth_sum_bwd_rows": [_i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
     "mb_seg_smooth_sum_bwd_env": [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "mb_mul_rows_gather": [_i64, _vp, _vp, _vp, _vp, _vp],
     "mb_pair_mean_res": [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],

@@ -58,13 +58,16 @@ __global__ void k_gate_fwd(int64_t n_rows, const float* __restrict__ z, const fl
   }
 }
 
-__global__ void k_gate_bwd(int64_t n_rows, const float* __restrict__ z, const float* __restrict__ wc,
-                           const float* __restrict__ wg, const float* __restrict__ dh, float* __restrict__ dz) {
-  MB_ROW_PROLOGUE(n_rows)
+// Adjoint of  h = SiLU(RMSNorm(z_core) w_core) * sigmoid(RMSNorm(z_gate) w_gate)  for one row held by a warp (lane =
+// four channels at c): g = dh of the row, result written to dz[row, 0:128 | 128:256].  Shared by k_gate_bwd and by the
+// kernels that produce dh and can hand it over in registers.
+__device__ __forceinline__ void gate_bwd_row(int64_t row, int c, const float* __restrict__ z,
+                                             const float* __restrict__ wc, const float* __restrict__ wg, float4 g,
+                                             float* __restrict__ dz) {
   const float4 xc = ld4(z + row * 256 + c), xg = ld4(z + row * 256 + 128 + c);
   const float rc = rsqrtf(warp_sum(dot4(xc, xc)) * (1.f / 128.f) + RMS_EPS);
   const float rg = rsqrtf(warp_sum(dot4(xg, xg)) * (1.f / 128.f) + RMS_EPS);
-  const float4 gwc = ld4(wc + c), gwg = ld4(wg + c), g = ld4(dh + row * 128 + c);
+  const float4 gwc = ld4(wc + c), gwg = ld4(wg + c);
   const float4 nc = scl4(xc, rc), ng = scl4(xg, rg);
   const float4 yc = mul4(nc, gwc), yg = mul4(ng, gwg);
   float dnc[4], dng[4];
@@ -80,6 +83,12 @@ __global__ void k_gate_bwd(int64_t n_rows, const float* __restrict__ z, const fl
   const float mc = warp_sum(dot4(dn_c, nc)) * (1.f / 128.f), mg = warp_sum(dot4(dn_g, ng)) * (1.f / 128.f);
   st4(dz + row * 256 + c, scl4(sub4(dn_c, scl4(nc, mc)), rc));
   st4(dz + row * 256 + 128 + c, scl4(sub4(dn_g, scl4(ng, mg)), rg));
+}
+
+__global__ void k_gate_bwd(int64_t n_rows, const float* __restrict__ z, const float* __restrict__ wc,
+                           const float* __restrict__ wg, const float* __restrict__ dh, float* __restrict__ dz) {
+  MB_ROW_PROLOGUE(n_rows)
+  gate_bwd_row(row, c, z, wc, wg, ld4(dh + row * 128 + c), dz);
 }
 
 // ------------------------------------------------------------------ attention aggregation
@@ -169,7 +178,9 @@ __global__ void k_seg_attn_bwd(int64_t n_rows, const int32_t* __restrict__ tgt, 
                                const float* __restrict__ agg_s, const float* __restrict__ stats,
                                const float* __restrict__ dagg_t, const float* __restrict__ dagg_s,
                                const float* __restrict__ dh_in, const int32_t* __restrict__ dh_map, float dh_scale,
-                               float* __restrict__ dh, float* __restrict__ dlogits) {
+                               float* __restrict__ dh, float* __restrict__ dlogits, const float* __restrict__ gate_z,
+                               const float* __restrict__ gate_wc, const float* __restrict__ gate_wg,
+                               float* __restrict__ gate_dz) {
   MB_ROW_PROLOGUE(n_rows)
   const int64_t nt = tgt[row * idx_stride], ns = src[row * idx_stride];
   const int64_t er = emap ? emap[row] : row;
@@ -183,7 +194,8 @@ __global__ void k_seg_attn_bwd(int64_t n_rows, const int32_t* __restrict__ tgt, 
     const int64_t mr = dh_map ? dh_map[row] : row;
     o = add4(o, scl4(ld4(dh_in + mr * 128 + c), dh_scale));
   }
-  st4(dh + row * 128 + c, o);
+  if (gate_dz) gate_bwd_row(row, c, gate_z, gate_wc, gate_wg, o, gate_dz);  // dh goes on in registers
+  else st4(dh + row * 128 + c, o);
   st4(dlogits + row * 256 + c, mul4(gs, sub4(hv, ld4(agg_s + ns * 128 + c))));
   st4(dlogits + row * 256 + 128 + c, mul4(gt, sub4(hv, ld4(agg_t + nt * 128 + c))));
 }
@@ -210,7 +222,9 @@ __global__ void k_seg_smooth_sum_fwd(int n_nodes, const int32_t* __restrict__ tg
 __global__ void k_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* __restrict__ tgt,
                                           const int32_t* __restrict__ src, int idx_stride,
                                           const int32_t* __restrict__ emap, const float* __restrict__ env,
-                                          const float* __restrict__ dagg, float* __restrict__ dh, int accumulate) {
+                                          const float* __restrict__ dagg, float* __restrict__ dh, int accumulate,
+                                          const float* __restrict__ gate_z, const float* __restrict__ gate_wc,
+                                          const float* __restrict__ gate_wg, float* __restrict__ gate_dz) {
   MB_ROW_PROLOGUE(n_rows)
   const int64_t nt = tgt[row * idx_stride];
   float4 s;
@@ -218,7 +232,8 @@ __global__ void k_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* __restr
   else s = ld4(env + (int64_t)emap[row] * 128 + c);
   float4 o = mul4(ld4(dagg + nt * 128 + c), s);
   if (accumulate) o = add4(o, ld4(dh + row * 128 + c));
-  st4(dh + row * 128 + c, o);
+  if (gate_dz) gate_bwd_row(row, c, gate_z, gate_wc, gate_wg, o, gate_dz);  // dh goes on in registers
+  else st4(dh + row * 128 + c, o);
 }
 
 __global__ void k_smooth_env_bwd_atom(int n_bonds, const int32_t* __restrict__ u2d, const int32_t* __restrict__ rev,
@@ -453,13 +468,14 @@ extern "C" int mb_seg_attn_bwd(int64_t n_rows, const int32_t* tgt, const int32_t
                                const int32_t* emap, const float* logits, const float* h, const float* agg_t,
                                const float* agg_s, const float* stats, const float* dagg_t, const float* dagg_s,
                                const float* dh_in, const int32_t* dh_map, float dh_scale, float* dh, float* dlogits,
+                               const float* gate_z, const float* gate_wc, const float* gate_wg, float* gate_dz,
                                void* stream) {
   MB_REQUIRE(n_rows >= 0 && tgt && src && idx_stride > 0 && logits && h && agg_t && agg_s && stats && dagg_t &&
-             dagg_s && dh && dlogits);
+             dagg_s && dlogits && (gate_dz ? (gate_z && gate_wc && gate_wg) : dh != nullptr));
   if (n_rows == 0) return MB_OK;
   k_seg_attn_bwd<<<row_grid(n_rows), RW_THREADS, 0, STREAM>>>(n_rows, tgt, src, idx_stride, emap, logits, h, agg_t,
                                                              agg_s, stats, dagg_t, dagg_s, dh_in, dh_map, dh_scale,
-                                                             dh, dlogits);
+                                                             dh, dlogits, gate_z, gate_wc, gate_wg, gate_dz);
   MB_LAUNCH_CHECK("k_seg_attn_bwd");
   return MB_OK;
 }
@@ -477,11 +493,14 @@ extern "C" int mb_seg_smooth_sum_fwd(int32_t n_nodes, const int32_t* tgt_ptr, co
 
 extern "C" int mb_seg_smooth_sum_bwd_rows(int64_t n_rows, const int32_t* tgt, const int32_t* src, int32_t idx_stride,
                                           const int32_t* emap, const float* env, const float* dagg, float* dh,
-                                          int32_t accumulate, void* stream) {
-  MB_REQUIRE(n_rows >= 0 && tgt && (emap || src) && env && dagg && dh && idx_stride > 0);
+                                          int32_t accumulate, const float* gate_z, const float* gate_wc,
+                                          const float* gate_wg, float* gate_dz, void* stream) {
+  MB_REQUIRE(n_rows >= 0 && tgt && (emap || src) && env && dagg && idx_stride > 0 && (dh || (gate_dz && !accumulate)) &&
+             (!gate_dz || (gate_z && gate_wc && gate_wg)));
   if (n_rows == 0) return MB_OK;
   k_seg_smooth_sum_bwd_rows<<<row_grid(n_rows), RW_THREADS, 0, STREAM>>>(n_rows, tgt, src, idx_stride, emap, env,
-                                                                        dagg, dh, accumulate);
+                                                                        dagg, dh, accumulate, gate_z, gate_wc, gate_wg,
+                                                                        gate_dz);
   MB_LAUNCH_CHECK("k_seg_smooth_sum_bwd_rows");
   return MB_OK;
 }

@@ -190,10 +190,17 @@ def _mlp_fwd(p, n_rows, srcs, want_h, res, res_w):
     return z1, z2, (h if want_h else None), out2
 
 
-def gated_bwd(p, n_rows, z1, z2, dh, dests):
+def _gate_args(p, z2):
+    """What the kernels that produce a gated MLP's dh need to apply the tail adjoint themselves (None for the
+    plain-MLP variant, whose tail is an RMSNorm handled in ``gated_bwd``)."""
+    return None if getattr(p, "kind", "gated") == "mlp" else (z2, p.nc, p.ng)
+
+
+def gated_bwd(p, n_rows, z1, z2, dh, dests, dz2=None):
     """Backward through the gated MLP: dests[c] = (tensor, idx, mode[, res, res_w]) for K segment c.  With ``res``
     the block stores ``gemm + res_w * res`` (the residual branch's gradient joins in the epilogue instead of in a
-    separate scaling pass followed by an accumulate)."""
+    separate scaling pass followed by an accumulate).  ``dz2``: the tail adjoint, where the producer of dh has
+    already applied it (then ``dh`` is not read)."""
     if getattr(p, "kind", "gated") == "mlp":
         dy = ops.rmsnorm_bwd(z2, p.nw, dh.contiguous())
         da1 = torch.empty_like(z1)
@@ -207,7 +214,8 @@ def gated_bwd(p, n_rows, z1, z2, dh, dests):
             blocks.append(B([S(da1)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode, res=res, res_w=res_w))
         gemm(n_rows, blocks)
         return
-    dz2 = ops.gate_bwd(z2, p.nc, p.ng, dh)
+    if dz2 is None:
+        dz2 = ops.gate_bwd(z2, p.nc, p.ng, dh)
     dz1 = torch.empty_like(z1)
     gemm(n_rows, [B([S(dz2, None, D * j)], p.w2t, w_row=D * j, gate=z1, gate_col=D * j, out=dz1, out_col=D * j)
                   for j in (0, 1)])
@@ -272,8 +280,11 @@ class AttentionFn(torch.autograd.Function):
                   [(d_node, None, OUT_ADD), (dagg_t, None, OUT_STORE), (dagg_s, None, OUT_STORE)])
         del z1n, z2n
         # softmax-weighted aggregation
+        # (the row gradient dh goes straight on through the gated MLP's tail adjoint: dz2 comes back instead)
+        gate = _gate_args(P.edge, z2)
         dh, dlogits = ops.seg_attn_bwd(rg.tgt, rg.src, rg.emap, logits, h, agg_t, agg_s, stats, dagg_t, dagg_s,
-                                       d_edge_out, rg.emap, 0.5 if rg.is_atom else 1.0)
+                                       d_edge_out, rg.emap, 0.5 if rg.is_atom else 1.0, gate=gate)
+        dz2, dh = (dh, None) if gate is not None else (None, dh)
         del logits, h, agg_t, agg_s, stats, dagg_t, dagg_s
         # edge update (line graph: rows map one to one, so the residual gradient we * d_edge_out rides in the
         # epilogue of the store; atom graph: two directed rows add into one bond row, so it is laid down first)
@@ -284,8 +295,9 @@ class AttentionFn(torch.autograd.Function):
         else:
             d_edge = torch.empty_like(d_edge_out)
             edge_dest = (d_edge, None, OUT_STORE, d_edge_out, P.we)
-        gated_bwd(P.edge, R, z1, z2, dh, [edge_dest, (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)])
-        del z1, z2, dh
+        gated_bwd(P.edge, R, z1, z2, dh, [edge_dest, (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)],
+                  dz2=dz2)
+        del z1, z2, dh, dz2
         gemm(R, [B([S(dlogits, None, 0), S(dlogits, None, D)], P.wstt, out=d_edge, out_idx=rg.emap, mode=emode)])
         return d_node, d_edge, None, None
 
@@ -358,7 +370,8 @@ class RefineFn(torch.autograd.Function):
             drow, dh = dh, ops.mul_rows_gather(dh, env, rg.emap)
         # smoothed aggregation
         src = None if rg.is_atom else rg.src
-        ops.seg_smooth_sum_bwd_rows(rg.tgt, src, rg.emap, env, dagg, dh, accumulate=True)
+        dz2 = ops.seg_smooth_sum_bwd_rows(rg.tgt, src, rg.emap, env, dagg, dh, accumulate=True,
+                                          gate=_gate_args(P.edge, z2))  # with a gate: dh is finished in registers
         denv = ops.seg_smooth_sum_bwd_env(env.shape[0], rg.tgt_ptr, None if rg.is_atom else rg.src_ptr, rg.src_perm,
                                           rg.tgt, src if src is not None else rg.src, rg.u2d, rg.rev, env, h, dagg,
                                           drow=drow)
@@ -375,7 +388,7 @@ class RefineFn(torch.autograd.Function):
             d_edge = torch.empty_like(d_edge_out)  # stored once: gemm + we * d_edge_out in the epilogue
             dests = [(d_edge, None, OUT_STORE, d_edge_out, P.we), (d_atom, rg.ctr, OUT_ATOMIC),
                      (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
-        gated_bwd(P.edge, R, z1, z2, dh, dests)
+        gated_bwd(P.edge, R, z1, z2, dh, dests, dz2=dz2)
         return d_node, d_edge, d_rbf, d_atom, None, None
 
 

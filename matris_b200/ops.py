@@ -214,13 +214,21 @@ def seg_attn_fwd(n_nodes, tgt_ptr, src_ptr, src_perm, emap, logits, h):
     return agg_t, agg_s, stats
 
 
-def seg_attn_bwd(tgt, src, emap, logits, h, agg_t, agg_s, stats, dagg_t, dagg_s, dh_in, dh_map, dh_scale):
+def seg_attn_bwd(tgt, src, emap, logits, h, agg_t, agg_s, stats, dagg_t, dagg_s, dh_in, dh_map, dh_scale, gate=None):
+    """``gate`` = (z2, w_core, w_gate): the row gradient goes straight through the gated MLP's tail adjoint and the
+    first result is dz2 [rows,256] instead of dh [rows,128]."""
     n = h.shape[0]
-    dh, dlogits = new(n, D, h), new(n, 2 * D, h)
+    dlogits = new(n, 2 * D, h)
+    if gate is None:
+        first, gz, gc, gg = new(n, D, h), None, None, None
+    else:
+        gz, gc, gg = gate
+        first = new(n, 2 * D, h)
     call("mb_seg_attn_bwd", n, ptr(tgt), ptr(src), 1, ptr(emap), ptr(logits), ptr(h), ptr(agg_t), ptr(agg_s),
-         ptr(stats), ptr(dagg_t), ptr(dagg_s), ptr(dh_in), ptr(dh_map), float(dh_scale), ptr(dh), ptr(dlogits),
-         _stream())
-    return dh, dlogits
+         ptr(stats), ptr(dagg_t), ptr(dagg_s), ptr(dh_in), ptr(dh_map), float(dh_scale),
+         ptr(first) if gate is None else None, ptr(dlogits), ptr(gz), ptr(gc), ptr(gg),
+         None if gate is None else ptr(first), _stream())
+    return first, dlogits
 
 
 def seg_smooth_sum_fwd(n_nodes, tgt_ptr, emap, src, env, h):
@@ -229,9 +237,14 @@ def seg_smooth_sum_fwd(n_nodes, tgt_ptr, emap, src, env, h):
     return agg
 
 
-def seg_smooth_sum_bwd_rows(tgt, src, emap, env, dagg, dh, accumulate=True):
+def seg_smooth_sum_bwd_rows(tgt, src, emap, env, dagg, dh, accumulate=True, gate=None):
+    """``gate`` = (z2, w_core, w_gate): returns dz2 [rows,256], the finished row gradient passed through the gated
+    MLP's tail adjoint (dh is then read, if ``accumulate``, but not written); otherwise updates dh in place."""
+    gz, gc, gg = gate if gate is not None else (None, None, None)
+    dz = new(dh.shape[0], 2 * D, dh) if gate is not None else None
     call("mb_seg_smooth_sum_bwd_rows", dh.shape[0], ptr(tgt), ptr(src), 1, ptr(emap), ptr(env), ptr(dagg), ptr(dh),
-         int(accumulate), _stream())
+         int(accumulate), ptr(gz), ptr(gc), ptr(gg), ptr(dz), _stream())
+    return dz
 
 
 def seg_smooth_sum_bwd_env(n_nodes, tgt_ptr, src_ptr, src_perm, tgt, src, u2d, rev, env, h, dagg, drow=None):

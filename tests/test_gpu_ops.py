@@ -327,6 +327,12 @@ def test_seg_attn_fwd_bwd(ops, with_emap):
     dh, dlg = ops.seg_attn_bwd(d["tgt"], d["src"], d["emap"], d["lg"], d["h"], agg_t, agg_s, stats, dev(dt), dev(ds),
                                dev(dh_in), d["emap"], scale)
     report("seg_attn_bwd dh", dh, dH, 1e-5)
+    # the same call with the gated MLP's tail adjoint applied to the row gradient in registers: dz2 instead of dh
+    z2, wc, wg = rnd(R, 256, seed=8), 1 + 0.1 * rnd(128, seed=9), 1 + 0.1 * rnd(128, seed=10)
+    dz2, dlg2 = ops.seg_attn_bwd(d["tgt"], d["src"], d["emap"], d["lg"], d["h"], agg_t, agg_s, stats, dev(dt), dev(ds),
+                                 dev(dh_in), d["emap"], scale, gate=(dev(z2), dev(wc), dev(wg)))
+    report("seg_attn_bwd with the gate adjoint: dz2", dz2, ops.gate_bwd(dev(z2), dev(wc), dev(wg), dh), 1e-6)
+    assert torch.equal(dlg2, dlg)
     if with_emap:  # per-row logits gradients are summed over rows sharing a logits row
         dlg_sum = torch.zeros(Ne, 256, dtype=torch.float64).index_add_(0, emap, dlg.cpu().double())
         report("seg_attn_bwd dlogits (summed)", dlg_sum, dL, 2e-5)
@@ -369,6 +375,12 @@ def test_seg_smooth_sum_fwd_bwd(ops, line):
     dh = dev(dh0.clone())
     ops.seg_smooth_sum_bwd_rows(d_tgt, d_src if line else None, d_emap, dev(env), dev(dagg), dh, accumulate=True)
     report(f"seg_smooth_sum_bwd_rows line={line}", dh, dh0.double() + dH, 1e-5)
+    z2, wc, wg = rnd(len(tgt), 256, seed=8), 1 + 0.1 * rnd(128, seed=9), 1 + 0.1 * rnd(128, seed=10)
+    dh_in = dev(dh0.clone())
+    dz2 = ops.seg_smooth_sum_bwd_rows(d_tgt, d_src if line else None, d_emap, dev(env), dev(dagg), dh_in, accumulate=True,
+                                      gate=(dev(z2), dev(wc), dev(wg)))
+    report(f"seg_smooth_sum_bwd_rows with the gate adjoint line={line}", dz2, ops.gate_bwd(dev(z2), dev(wc), dev(wg), dh), 1e-6)
+    assert torch.equal(dh_in.cpu(), dh0), "with a gate the incoming dh is read, not written"
     denv = ops.seg_smooth_sum_bwd_env(env.shape[0], dev(tptr, i32), dev(sptr, i32) if line else None, dev(perm, i32),
                                       d_tgt, d_src, None if line else dev(u2d, i32), None if line else dev(rev, i32),
                                       dev(env), dev(h), dev(dagg))
