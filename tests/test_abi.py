@@ -95,6 +95,38 @@ def test_version_and_status_strings(lib):
     assert b"capacity" in lib.mb_status_string(7)
 
 
+def test_invalid_arguments_are_status_codes_before_any_launch(lib):
+    """Argument validation happens on the host before a device is touched: NULL descriptors, impossible sizes and
+    missing pointers come back as MB_ERR_INVALID (no exception, no trap, no CUDA call), also on a box without a GPU."""
+    import ctypes as C
+    assert lib.mb_gemm(None, None) == 1
+    d = _lib.MbGemmDesc()
+    d.n_rows, d.n_blocks = 10, 0
+    assert lib.mb_gemm(C.byref(d), None) == 1                   # no column block
+    d.n_blocks = 5
+    assert lib.mb_gemm(C.byref(d), None) == 1                   # more than four
+    assert lib.mb_gated_mlp_fwd(None, None) == 1
+    g = _lib.MbGatedMlp()
+    g.n_rows, g.n_src = 10, 7
+    assert lib.mb_gated_mlp_fwd(C.byref(g), None) == 1          # K segments out of range
+    assert lib.mb_graph_build(None, None) == 1
+    m = _lib.MbGraph()
+    m.n_atoms, m.n_struct, m.n_cells, m.cap_edges = 4, 1, 1, 64
+    assert lib.mb_graph_build(C.byref(m), None) == 1            # no buffers given
+    assert lib.mb_graph_status(None) == 1
+    counts = (C.c_int32 * 16)()
+    assert lib.mb_graph_status(counts) == 0
+    counts[3] = 2
+    assert lib.mb_graph_status(counts) == 5                     # isolated atoms
+    counts[3], counts[6] = 0, 1
+    assert lib.mb_graph_status(counts) == 7                     # edge capacity too small
+    counts[6], counts[9] = 0, 1
+    assert lib.mb_graph_status(counts) == 7                     # candidate list unusable: rebuild it
+    assert lib.mb_graph_skin_check(0, None, None, 0.25, None, None) == 1
+    assert lib.mb_set_gemm_mode(9) == 1
+    assert lib.mb_set_gemm_mode(0) == 0
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
