@@ -169,14 +169,22 @@ profile = None       # set to a list to record (name, start_event, end_event, me
 profile_meta = None  # filled by the caller (e.g. algorithmic FLOPs of a GEMM) just before call()
 
 
+_bound: dict = {}  # entry points by name, bound on first use
+
+
 def call(name: str, *args) -> None:
     """Call an int-returning entry point and raise on a non-zero status."""
     global launch_count, profile_meta
-    lib = load()
+    fn = _bound.get(name)
+    if fn is None:
+        fn = _bound[name] = getattr(load(), name)
     launch_count += 1
     if profile is None:
-        check(getattr(lib, name)(*args), name)
+        status = fn(*args)
+        if status:
+            check(status, name)
         return
+    lib = load()
     import torch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

@@ -683,7 +683,8 @@ class MatRIS(nn.Module):
             if flag is None:
                 flag = self._gemm_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
             self.check_status()
-            out = self._evaluate(g, task)
+            with ops.pinned_stream():  # one stream look-up per evaluation instead of one per launch
+                out = self._evaluate(g, task)
             ops.gemm_status_async(flag)
             return out
 

@@ -19,8 +19,30 @@ D = 128
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+_pinned_stream = None
+
+
+class pinned_stream:
+    """Within the block every entry point launches on the stream that is current at entry (looked up once instead
+    of once per launch).  The autograd engine runs backward functions on that same stream, from its own thread,
+    so the handle is shared process-wide for the duration of the block; blocks do not nest across devices."""
+
+    def __enter__(self):
+        global _pinned_stream
+        self.outer, _pinned_stream = _pinned_stream, None
+        _pinned_stream = _stream()
+        return self
+
+    def __exit__(self, *exc):
+        global _pinned_stream
+        _pinned_stream = self.outer
+        return False
+
+
 def _stream():
     """Raw handle of torch's current stream on the current device (the stream every entry point launches on)."""
+    if _pinned_stream is not None:
+        return _pinned_stream
     if _raw_stream is not None:
         return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
@@ -38,7 +60,7 @@ class SplitWeight:
     ``hi`` = tf32-rounded values, ``lo`` = w - hi (float32) for the 3xTF32 cores.
     ``w`` itself feeds the exact-fp32 SIMT core."""
 
-    __slots__ = ("w", "hi", "lo", "hi16", "lo16", "shape")
+    __slots__ = ("w", "hi", "lo", "hi16", "lo16", "shape", "ptrs", "ldw")
 
     def __init__(self, w: torch.Tensor):
         w = w.detach().contiguous()
@@ -47,6 +69,10 @@ class SplitWeight:
         self.w, self.hi, self.lo, self.shape = w, hi.contiguous(), (w - hi).contiguous(), w.shape
         self.hi16 = w.to(torch.bfloat16).contiguous()          # round to nearest even
         self.lo16 = (w - self.hi16.float()).to(torch.bfloat16).contiguous()
+        # device addresses and row stride, looked up once: the descriptor packing runs for every launch
+        self.ptrs = (w.data_ptr(), self.hi.data_ptr(), self.lo.data_ptr(), self.hi16.data_ptr(), self.lo16.data_ptr())
+        self.ldw = w.stride(0)
+        assert w.dim() == 2 and w.stride(1) == 1
 
     def t(self) -> "SplitWeight":
         return SplitWeight(self.w.t())
@@ -104,16 +130,15 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
         for _ in range(4 - len(srcs)):
             flat += _NO_SRC
         sw = as_split(b["W"])
-        W = sw.w
-        ldw = W.stride(0)
-        assert W.dim() == 2 and W.stride(1) == 1 and W.shape[1] >= D * len(srcs)
+        ldw = sw.ldw
+        assert sw.shape[1] >= D * len(srcs)
         w_off = 4 * ldw * int(b["w_row"])
         w_off16 = w_off // 2
+        pw, ph, pl, ph16, pl16 = sw.ptrs
         bias, gate, res, res_w, out, out_idx = b["bias"], b["gate"], b["res"], b["res_w"], b["out"], b["out_idx"]
         _BLK_FMT.pack_into(
             buf, _BLK_OFF + j * _BLK_SIZE, len(srcs), int(b["out_act"]), *flat,
-            W.data_ptr() + w_off, sw.hi.data_ptr() + w_off, sw.lo.data_ptr() + w_off,
-            sw.hi16.data_ptr() + w_off16, sw.lo16.data_ptr() + w_off16, ldw,
+            pw + w_off, ph + w_off, pl + w_off, ph16 + w_off16, pl16 + w_off16, ldw,
             0 if bias is None else bias.data_ptr() + 4 * int(b["bias_off"]),
             0 if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0),
             0 if gate is None else int(b["gate_col"]), 0,
@@ -162,9 +187,9 @@ def gated_mlp_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True)
 
     buf = _GATED_FMT.pack(
         n_rows, len(srcs), 0, *flat,
-        w1.w.data_ptr(), w1.hi.data_ptr(), w1.lo.data_ptr(), w1.hi16.data_ptr(), w1.lo16.data_ptr(), w1.w.stride(0),
+        *w1.ptrs, w1.ldw,
         0 if p.b1 is None else p.b1.data_ptr(),
-        w2.w.data_ptr(), w2.hi.data_ptr(), w2.lo.data_ptr(), w2.hi16.data_ptr(), w2.lo16.data_ptr(), w2.w.stride(0),
+        *w2.ptrs, w2.ldw,
         0 if p.b2 is None else p.b2.data_ptr(),
         p.nc.data_ptr(), p.ng.data_ptr(), *pl(z1), *pl(z2), *pl(h),
         0 if res is None else res.data_ptr(), 0 if res is None or res_w is None else res_w.data_ptr(),

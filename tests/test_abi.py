@@ -148,6 +148,8 @@ def test_gemm_descriptor_packing_matches_ctypes_mirror(monkeypatch):
         def __init__(self, w):
             self.w, self.hi, self.lo, self.shape = w, w.clone(), w.clone(), w.shape
             self.hi16, self.lo16 = w.to(torch.bfloat16), w.to(torch.bfloat16)
+            self.ptrs = tuple(t.data_ptr() for t in (self.w, self.hi, self.lo, self.hi16, self.lo16))
+            self.ldw = w.stride(0)
 
     monkeypatch.setattr(ops, "as_split", lambda w: w if isinstance(w, FakeSplit) else FakeSplit(w))
     x, idx, W = torch.randn(300, 256), torch.arange(300, dtype=torch.int32), FakeSplit(torch.randn(256, 384))
