@@ -116,36 +116,43 @@ assert _BLK_FMT.size == _BLK_SIZE and _HDR_FMT.size == _BLK_OFF and _DESC_SIZE =
 _NO_SRC = (0, 0, 0, 0, 0)
 
 
+_PAD = ((), _NO_SRC, _NO_SRC * 2, _NO_SRC * 3, _NO_SRC * 4)  # by number of missing sources
+
+
 def gemm(n_rows: int, blocks: list[dict]) -> None:
     if n_rows == 0:
         return
     buf = bytearray(_DESC_SIZE)
-    _HDR_FMT.pack_into(buf, 0, int(n_rows), len(blocks), 0)
-    for j, b in enumerate(blocks):
+    _HDR_FMT.pack_into(buf, 0, n_rows, len(blocks), 0)
+    off = _BLK_OFF
+    for b in blocks:
         srcs = b["srcs"]
+        n_src = len(srcs)
         flat = []
         for t, idx, col, act in srcs:
             assert t.dtype == torch.float32 and t.stride(-1) == 1
-            flat += (t.data_ptr(), 0 if idx is None else idx.data_ptr(), t.stride(0), int(col), int(act))
-        for _ in range(4 - len(srcs)):
-            flat += _NO_SRC
-        sw = as_split(b["W"])
+            flat += (t.data_ptr(), 0 if idx is None else idx.data_ptr(), t.stride(0), col, act)
+        flat += _PAD[4 - n_src]
+        sw = b["W"]
+        if type(sw) is not SplitWeight:
+            sw = as_split(sw)
         ldw = sw.ldw
-        assert sw.shape[1] >= D * len(srcs)
-        w_off = 4 * ldw * int(b["w_row"])
+        assert sw.shape[1] >= D * n_src
+        w_off = 4 * ldw * b["w_row"]
         w_off16 = w_off // 2
         pw, ph, pl, ph16, pl16 = sw.ptrs
         bias, gate, res, res_w, out, out_idx = b["bias"], b["gate"], b["res"], b["res_w"], b["out"], b["out_idx"]
         _BLK_FMT.pack_into(
-            buf, _BLK_OFF + j * _BLK_SIZE, len(srcs), int(b["out_act"]), *flat,
+            buf, off, n_src, b["out_act"], *flat,
             pw + w_off, ph + w_off, pl + w_off, ph16 + w_off16, pl16 + w_off16, ldw,
-            0 if bias is None else bias.data_ptr() + 4 * int(b["bias_off"]),
+            0 if bias is None else bias.data_ptr() + 4 * b["bias_off"],
             0 if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0),
-            0 if gate is None else int(b["gate_col"]), 0,
+            0 if gate is None else b["gate_col"], 0,
             0 if res is None else res.data_ptr(), 0 if res is None or res_w is None else res_w.data_ptr(),
-            0 if res is None else res.stride(0), 0 if res is None else int(b["res_col"]), int(b["mode"]),
-            out.data_ptr(), 0 if out_idx is None else out_idx.data_ptr(), out.stride(0), int(b["out_col"]),
-            float(b["scale"]))
+            0 if res is None else res.stride(0), 0 if res is None else b["res_col"], b["mode"],
+            out.data_ptr(), 0 if out_idx is None else out_idx.data_ptr(), out.stride(0), b["out_col"],
+            b["scale"])
+        off += _BLK_SIZE
     if _lib.profile is not None:
         _lib.profile_meta = dict(flops=sum(2.0 * n_rows * D * D * len(b["srcs"]) for b in blocks), rows=int(n_rows),
                                  k=D * len(blocks[0]["srcs"]), n=D * len(blocks),
