@@ -565,7 +565,8 @@ class MatRIS(nn.Module):
         self._ref_table = None
         self._packed_device = None
         self.last_batch = None
-        self.keep_activations = None  # None: decide per call from free memory; True / False: force
+        # None: decide per call from free memory; True / False: keep / recompute all; n: keep the last n layers' internals
+        self.keep_activations = None
 
     # -- parameter tree -------------------------------------------------------------------
     def _register(self, key, value, buffer, trainable):
@@ -707,8 +708,12 @@ class MatRIS(nn.Module):
         atom_rg, line_rg = row_graphs(g)
         want_f, want_s = "f" in task, "s" in task
         need_grad = want_f or want_s
-        # bytes of sub-block internals over all layers: ~6.7 KB per triplet row and ~6.2 KB per directed edge
-        est = len(P.layers) * (6.7e3 * g.n_triplets + 6.2e3 * g.n_edges)
+        # bytes of sub-block internals per layer: ~6.7 KB per triplet row and ~6.2 KB per directed edge.  The internals
+        # of the LAST n_keep layers are kept for the backward pass (they are consumed and released first), those of
+        # the earlier layers are recomputed there: n_keep = all layers when everything fits in 45 % of the memory the
+        # allocator can still hand out, otherwise as many as do.
+        n_layers = len(P.layers)
+        per_layer = 6.7e3 * g.n_triplets + 6.2e3 * g.n_edges
         keep = self.keep_activations
         if keep is None:
             # Memory the allocator can hand out = device total - what lives outside this allocator - what it has
@@ -721,10 +726,13 @@ class MatRIS(nn.Module):
                 free, total = torch.cuda.mem_get_info(self.device)
                 st["total"], st["outside"] = total, total - free - torch.cuda.memory_reserved(self.device)
             st["calls"] += 1
-            keep = est < 0.45 * (st["total"] - st["outside"] - torch.cuda.memory_allocated(self.device))
-        atom_rg.keep = bool(keep)
-        if line_rg is not None:
-            line_rg.keep = bool(keep)
+            budget = 0.45 * (st["total"] - st["outside"] - torch.cuda.memory_allocated(self.device))
+            n_keep = n_layers if per_layer * n_layers < budget else max(0, int(budget // max(per_layer, 1.0)))
+        elif isinstance(keep, bool):
+            n_keep = n_layers if keep else 0
+        else:
+            n_keep = max(0, min(n_layers, int(keep)))  # an integer: keep the internals of that many (last) layers
+        self.last_kept_layers = n_keep
         out = {}
         with torch.set_grad_enabled(need_grad):
             cart = g.cart32.detach().clone().requires_grad_(need_grad)
@@ -735,7 +743,10 @@ class MatRIS(nn.Module):
             node = ops.linear(ops.embedding(g.numbers, -1, P.emb_table), P.emb_w, out_act=1)
             edge, rbf2, rbf3 = EdgeEmbedFn.apply(length, P, g, cfg)
             trip = AngleEmbedFn.apply(unit, P, g, cfg) if line_rg is not None else None
-            for L in P.layers:
+            for i, L in enumerate(P.layers):
+                atom_rg.keep = i >= n_layers - n_keep
+                if line_rg is not None:
+                    line_rg.keep = atom_rg.keep
                 e_att, t_att = edge, trip
                 if trip is not None:
                     e_att, t_att = AttentionFn.apply(edge, trip, L.attn_line, line_rg)

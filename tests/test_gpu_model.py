@@ -194,18 +194,21 @@ def test_state_dict_roundtrip_and_from_dict():
 
 
 def test_recompute_equals_kept_activations():
-    """The two memory policies (keep sub-block internals / recompute them in backward) agree."""
+    """The memory policies (keep sub-block internals / recompute them in backward / keep those of the last n layers
+    only) agree."""
     from matris_b200 import MatRIS
     crystals = workloads.random_crystals(3, seed=9)
-    ck = random_checkpoint(dict(num_layers=2, reference_energy="mpa"), seed=5)
+    ck = random_checkpoint(dict(num_layers=3, reference_energy="mpa"), seed=5)
     model = MatRIS.from_dict(ck).to("cuda")
     res = {}
-    for keep in (True, False):
+    for keep, kept in ((True, 3), (False, 0), (1, 1), (2, 2), (None, 3)):
         model.keep_activations = keep
         out = model.predict(crystals, "efs")
+        assert model.last_kept_layers == kept, (keep, model.last_kept_layers)
         res[keep] = (torch.cat(list(out["f"])).cpu(), torch.stack(out["s"]).cpu())
-    report("keep vs recompute F", res[True][0], res[False][0], 2e-6)
-    report("keep vs recompute S", res[True][1] / GPA, res[False][1] / GPA, 2e-7)
+    for keep in (False, 1, 2, None):
+        report(f"keep all vs keep_activations={keep}: F", res[True][0], res[keep][0], 2e-6)
+        report(f"keep all vs keep_activations={keep}: S", res[True][1] / GPA, res[keep][1] / GPA, 2e-7)
 
 
 def test_forward_raises_once_after_an_expired_wait_and_recovers():
