@@ -729,10 +729,16 @@ class MatRIS(nn.Module):
             avail = st["total"] - st["outside"] - torch.cuda.memory_allocated(self.device)
             budget = 0.45 * avail
             n_keep = n_layers if per_layer * n_layers < budget else max(0, int(budget // max(per_layer, 1.0)))
-            # What an evaluation holds besides the kept internals (the sub-blocks' saved inputs of all layers and the
-            # temporaries of the backward pass) was measured at 20.3 - 20.8 KB per triplet, a kept layer at 3.4 -
-            # 3.5 KB per triplet (6.6 M and 4.2 M triplets): never plan beyond 92 % of the memory with those figures.
-            while 0 < n_keep < n_layers and (21.0e3 + 3.6e3 * n_keep) * g.n_triplets > 0.92 * avail:
+            # Second bound, on the peak of the backward pass (saved inputs of all layers + the temporaries of one
+            # recomputed layer + gradients).  Measured on three graph shapes (4.1 M - 6.6 M triplets, 1.0 M - 1.7 M
+            # directed edges): 17.4 KB per triplet + 13.8 KB per directed edge with nothing kept, growing by 2.5 KB
+            # per triplet + 4.3 KB per directed edge per kept layer; that peak must stay below 92 % of the memory.
+            base = 18.0e3 * g.n_triplets + 14.2e3 * g.n_edges
+            step = 2.6e3 * g.n_triplets + 4.4e3 * g.n_edges
+            # Third bound, on the end of the forward pass (saved inputs of all layers, about 17 KB per triplet, + the
+            # kept internals).
+            inputs = 17.0e3 * g.n_triplets + 2.0e3 * g.n_edges
+            while 0 < n_keep < n_layers and max(base + step * n_keep, inputs + per_layer * n_keep) > 0.92 * avail:
                 n_keep -= 1
         elif isinstance(keep, bool):
             n_keep = n_layers if keep else 0
