@@ -235,11 +235,20 @@ int mb_bench_mma_rate(int kind, int iters, float* elapsed_ms, int* n_sms, void* 
  * bf16 hi / lo and stored as the A operand of layer 2 on chip; RMSNorm and the gate run in the epilogue of
  * layer 2.  z1 / z2 are written only when the pointers are given (the backward pass wants them).  The fused kernel
  * exists for the default GEMM mode (0, 3xBF16); in modes 1, 2 and 3 (see mb_set_gemm_mode) the same result is
- * composed from mb_gemm and mb_gate_fwd, which needs z1 and z2 as scratch: they are required there. */
+ * composed from mb_gemm and mb_gate_fwd, which needs z1 and z2 as scratch: they are required there.
+ *
+ * kind = MB_MLP_PLAIN runs the same pipeline for a plain two-layer perceptron (node_FFN / edge_FFN,
+ * matris/model/interaction_block.py:197-210):
+ *   z1 = X W1^T + b1            W1 [128, K], b1 [128]
+ *   h  = SiLU(z1) W2^T + b2     W2 [128, 128], b2 [128];   out2 = h + res_w * res (optional)
+ * z1 is then [R, 128] (optional in mode 0, required as scratch in the other modes); z2, norm_core and norm_gate are
+ * not read. */
+#define MB_MLP_GATED 0
+#define MB_MLP_PLAIN 1
 typedef struct mb_gated_mlp {
   int64_t n_rows;
   int32_t n_src;               /* 1..4 ; K = 128 * n_src */
-  int32_t pad;
+  int32_t kind;                /* MB_MLP_GATED or MB_MLP_PLAIN */
   mb_src src[4];               /* src[].act is honoured (SiLU on load) */
   const float* W1;             /* [256, K] row-major (SIMT mode) */
   const float* W1_hi;          /* tf32(W1) */

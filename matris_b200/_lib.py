@@ -64,7 +64,7 @@ class MbGemmDesc(C.Structure):
 
 class MbGatedMlp(C.Structure):
     _fields_ = [
-        ("n_rows", _i64), ("n_src", _i32), ("pad", _i32), ("src", MbSrc * 4),
+        ("n_rows", _i64), ("n_src", _i32), ("kind", _i32), ("src", MbSrc * 4),
         ("W1", _vp), ("W1_hi", _vp), ("W1_lo", _vp), ("W1_hi16", _vp), ("W1_lo16", _vp), ("ldw1", _i64), ("b1", _vp),
         ("W2", _vp), ("W2_hi", _vp), ("W2_lo", _vp), ("W2_hi16", _vp), ("W2_lo16", _vp), ("ldw2", _i64), ("b2", _vp),
         ("norm_core", _vp), ("norm_gate", _vp),

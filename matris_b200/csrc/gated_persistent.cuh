@@ -17,6 +17,10 @@
 //           it again, normalises and activates; the core unit parks c = SiLU(.) in the output row, the gate unit
 //           reads it back, multiplies by sigmoid(.) and writes h / out2.
 //
+// kind = MB_MLP_PLAIN runs the same pipeline for a plain two-layer MLP  y = W2 SiLU(W1 x + b1) + b2  (+ out2 = y +
+// res_w * res): one unit per row tile (W1 [128, K], W2 [128, 128]), no normalisation, nothing parked; z1 is then the
+// [rows, 128] pre-activation of the hidden layer.
+//
 // The eight epilogue warps form two groups of four (one warp per tensor-memory lane quarter, each owning whole rows):
 // group 0 takes the even units, group 1 the odd ones.  While one group waits for DRAM in its epilogue the other
 // prepares the next layer-2 operand, so the tensor pipe is not starved by the epilogue's memory traffic; with three
@@ -41,6 +45,7 @@ constexpr float GP_RMS_EPS = 1.1920928955078125e-07f;  // nn.RMSNorm(eps=None): 
 static_assert(GP_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 static_assert(sizeof(mb_gated_mlp) % 4 == 0, "descriptor is copied word by word");
 
+template <bool PLAIN>
 __global__ void __launch_bounds__(GP_THREADS, 1)
 k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant__ GatedMaps maps) {
   constexpr uint32_t NB = GP_NB;
@@ -74,6 +79,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   const uint32_t ring = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const mb_gated_mlp& d = *reinterpret_cast<const mb_gated_mlp*>(smem + GP_DESC_OFF);
+  constexpr bool plain = PLAIN;  // MB_MLP_PLAIN: one unit per row tile, branch 0 only
   {
     const uint32_t* src = reinterpret_cast<const uint32_t*>(&d_param);
     uint32_t* dst = reinterpret_cast<uint32_t*>(smem + GP_DESC_OFF);
@@ -85,10 +91,10 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   float* const cst = reinterpret_cast<float*>(smem + GP_CONST_OFF);
   for (int i = tid; i < 896; i += GP_THREADS) {
     float v;
-    if (i < 256) v = d.b1 ? d.b1[i] : 0.f;
-    else if (i < 512) v = d.b2 ? d.b2[i - 256] : 0.f;
-    else if (i < 640) v = d.norm_core[i - 512];
-    else if (i < 768) v = d.norm_gate[i - 640];
+    if (i < 256) v = (d.b1 && !(plain && i >= 128)) ? d.b1[i] : 0.f;
+    else if (i < 512) v = (d.b2 && !(plain && i >= 384)) ? d.b2[i - 256] : 0.f;
+    else if (i < 640) v = plain ? 1.f : d.norm_core[i - 512];
+    else if (i < 768) v = plain ? 1.f : d.norm_gate[i - 640];
     else v = d.res_w ? d.res_w[i - 768] : 1.f;
     cst[i] = v;
   }
@@ -96,7 +102,9 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   const int n_row_tiles = (int)((n_rows + 127) >> 7);
   const int n_src = d.n_src, nch1 = 4 * n_src;
   const int first_rt = (int)blockIdx.x, step_rt = (int)gridDim.x;
-  const int n_units = 2 * ((n_row_tiles - first_rt + step_rt - 1) / step_rt);  // the grid never exceeds the tile count
+  const int n_tiles_mine = (n_row_tiles - first_rt + step_rt - 1) / step_rt;  // the grid never exceeds the tile count
+  const int n_units = plain ? n_tiles_mine : 2 * n_tiles_mine;
+  const int unit_shift = plain ? 0 : 1;  // row tile of unit k = k >> unit_shift, branch = plain ? 0 : k & 1
   const int n_phases = 2 * n_units;
   // phase p of the tensor pipe's sequence -> (layer, unit)
   auto decode = [&](int p, bool& is_l2, int& k) {
@@ -119,7 +127,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
   int g_unit = 0, g_seg = 0, g_cnt = 0;
   bool g_second = false;
   auto resolve_rows = [&](int unit, int seg) {
-    const int64_t row0 = (int64_t)(first_rt + (unit >> 1) * step_rt) * 128;
+    const int64_t row0 = (int64_t)(first_rt + (unit >> unit_shift) * step_rt) * 128;
     const int32_t* idx = d.src[seg].idx;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -139,7 +147,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       const mb_src& s = d.src[g_seg];
       const float* base = s.ptr + s.col + lc * 4 + par * TC_BK;
       const int64_t ld = s.ld;
-      const int64_t row0 = s.idx ? 0 : (int64_t)(first_rt + (g_unit >> 1) * step_rt) * 128;
+      const int64_t row0 = s.idx ? 0 : (int64_t)(first_rt + (g_unit >> unit_shift) * step_rt) * 128;
 #pragma unroll
       for (int i = 0; i < 8; ++i) a_ptr[i] = base + (row0 + a_row[i]) * ld;
       MB_CP16(de, 0, a_ptr[0], 0);    MB_CP16(dq, 512, a_ptr[1], 0);  MB_CP16(de, 1024, a_ptr[2], 0); MB_CP16(dq, 1536, a_ptr[3], 0);
@@ -261,7 +269,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       int k;
       decode(p, is_l2, k);
       const int n_w = (is_l2 ? 4 : nch1) / 2;
-      const int wrow = 128 * (k & 1);  // first weight row of this unit's branch
+      const int wrow = plain ? 0 : 128 * (k & 1);  // first weight row of this unit's branch
       const CUtensorMap* const m_hi = is_l2 ? &maps.w2[0] : &maps.w1[0];
       const CUtensorMap* const m_lo = is_l2 ? &maps.w2[1] : &maps.w1[1];
       for (int wi = 0; wi < n_w && alive; ++wi, ++wu) {
@@ -287,10 +295,11 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
     // other unit.  Warp (q, grp): rows 32 q.. of the tile (its tensor-memory lane quarter), all 128 columns of the
     // units k = grp, grp + 2, ... (grp 0: core branch, grp 1: gate branch); thread = row.
     const int e = warp - PS_EPI_WARP0, q = warp & 3, grp = e >> 2;
+    const int br = plain ? 0 : grp;  // branch of this group's units
     const uint32_t lane_q = tmem_base + ((uint32_t)(q * 32) << 16);
-    const float4* const b1s = reinterpret_cast<const float4*>(cst) + 32 * grp;
-    const float4* const b2s = reinterpret_cast<const float4*>(cst + 256) + 32 * grp;
-    const float4* const nws = reinterpret_cast<const float4*>(cst + 512 + 128 * grp);
+    const float4* const b1s = reinterpret_cast<const float4*>(cst) + 32 * br;
+    const float4* const b2s = reinterpret_cast<const float4*>(cst + 256) + 32 * br;
+    const float4* const nws = reinterpret_cast<const float4*>(cst + 512 + 128 * br);
     const float4* const rws = reinterpret_cast<const float4*>(cst + 768);
     float* const z1 = d.z1;
     float* const z2 = d.z2;
@@ -302,7 +311,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       const int k6 = k % 6;
       const uint32_t par6 = (uint32_t)((k / 6) & 1), part = (uint32_t)((k >> 1) & 1);
       const uint32_t park_bar = park_ready + 8 * (2 * q + (int)part), park_par = (uint32_t)((k >> 2) & 1);
-      const int64_t row = (int64_t)(first_rt + (k >> 1) * step_rt) * 128 + q * 32 + lane;
+      const int64_t row = (int64_t)(first_rt + (k >> unit_shift) * step_rt) * 128 + q * 32 + lane;
       const bool valid = row < n_rows;
       const uint32_t d_lane = lane_q + 128u * (uint32_t)(k % 3);
       // ------------------------------------------------ mid(k): z1 -> SiLU -> hi / lo -> A operand of layer 2
@@ -326,7 +335,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           x[4 * jj] += bv.x; x[4 * jj + 1] += bv.y; x[4 * jj + 2] += bv.z; x[4 * jj + 3] += bv.w;
         }
         if (z1 && valid) {
-          float* zp = z1 + row * d.ld_z1 + 128 * grp + 32 * c;
+          float* zp = z1 + row * d.ld_z1 + 128 * br + 32 * c;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             float o[8];
@@ -364,7 +373,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float ss = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < (plain ? 0 : 4); ++c) {
         float y[32];
         {
           uint32_t v[32];
@@ -381,7 +390,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           for (int i = 0; i < 4; ++i) ss = fmaf(y[4 * jj + i], y[4 * jj + i], ss);
         }
         if (z2 && valid && alive) {
-          float* zp = z2 + row * d.ld_z2 + 128 * grp + 32 * c;
+          float* zp = z2 + row * d.ld_z2 + 128 * br + 32 * c;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             float o[8];
@@ -392,10 +401,10 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         }
         __syncwarp();
       }
-      const float rinv = rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
+      const float rinv = plain ? 1.0f : rsqrtf(ss * (1.0f / 128.0f) + GP_RMS_EPS);
       // the core unit parks c = SiLU(.) in the output row; the gate unit's warp of the same lane quarter reads it back
       float* const park = hout ? hout + row * d.ld_h : out2 + row * d.ld_out2;
-      if (grp == 1) {
+      if (grp == 1 && !plain) {
         if (alive) alive = mbar_wait(park_bar, park_par);
         alive = __all_sync(0xffffffffu, alive);
       }
@@ -424,7 +433,35 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
           y[4 * jj + 2] = (y[4 * jj + 2] + bv.z) * rinv * wv.z;
           y[4 * jj + 3] = (y[4 * jj + 3] + bv.w) * rinv * wv.w;
         }
-        if (grp == 0) {
+        if (plain) {
+          // y = W2 SiLU(.) + b2 is the result: h and / or out2 = y + res_w * res (16 columns of the residual per round)
+          const float* const rrow = out2 ? res + row * d.ld_res + 32 * c : nullptr;
+          float* const orow = out2 ? out2 + row * d.ld_out2 + 32 * c : nullptr;
+          float* const hrow = hout ? hout + row * d.ld_h + 32 * c : nullptr;
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            float rr[2][8];
+            if (out2) {
+              ld8(rrow + 16 * b, rr[0]);
+              ld8(rrow + 16 * b + 8, rr[1]);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int jj = 2 * b + t;
+              float o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = y[8 * jj + i];
+              if (hout) st8(hrow + 8 * jj, o);
+              if (out2) {
+                const float4 ra = rws[8 * c + 2 * jj], rb = rws[8 * c + 2 * jj + 1];
+                const float rw[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = fmaf(rw[i], rr[t][i], o[i]);
+                st8(orow + 8 * jj, o);
+              }
+            }
+          }
+        } else if (grp == 0) {
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             float o[8];
@@ -466,7 +503,7 @@ k_gated_fwd(const __grid_constant__ mb_gated_mlp d_param, const __grid_constant_
         }
         __syncwarp();  // the lanes meet again before the next (warp-wide) tensor-memory load
       }
-      if (grp == 0) {  // the parked values of this lane quarter are complete and visible to the CTA
+      if (grp == 0 && !plain) {  // the parked values of this lane quarter are complete and visible to the CTA
         __threadfence_block();
         __syncwarp();
         if (lane == 0) mbar_arrive(park_bar);

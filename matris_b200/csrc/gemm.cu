@@ -635,7 +635,8 @@ static int device_config(int* n_sm) {
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
     MB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ps<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES));
-    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
+    MB_CUDA_CHECK(cudaFuncSetAttribute(k_gated_fwd<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM_BYTES));
     int n = 0;
     MB_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     c.n_sm = n;
@@ -837,6 +838,35 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
 // The same result as the fused kernel from the separate kernels (GEMM modes 1 and 2, or operands that are only
 // 16-byte aligned): two mb_gemm launches and the row-wise gate kernel, with z1 / z2 as scratch.
 static int gated_mlp_composed(const mb_gated_mlp* g, void* stream_) {
+  if (g->kind == MB_MLP_PLAIN) {
+    if (!g->z1 || !g->W1 || !g->W2) return MB_ERR_INVALID;
+    mb_gemm_desc a = {}, b = {};
+    a.n_rows = b.n_rows = g->n_rows;
+    a.n_blocks = b.n_blocks = 1;
+    mb_colblock& ca = a.blk[0];
+    ca.n_src = g->n_src;
+    for (int s = 0; s < g->n_src; ++s) ca.src[s] = g->src[s];
+    ca.W = g->W1; ca.W_hi = g->W1_hi; ca.W_lo = g->W1_lo; ca.W_hi16 = g->W1_hi16; ca.W_lo16 = g->W1_lo16;
+    ca.ldw = g->ldw1; ca.bias = g->b1;
+    ca.out = g->z1; ca.ld_out = g->ld_z1; ca.out_scale = 1.f; ca.mode = MB_OUT_STORE;
+    int rc = mb_gemm(&a, stream_);
+    if (rc) return rc;
+    mb_colblock& cb = b.blk[0];
+    cb.n_src = 1;
+    cb.src[0].ptr = g->z1; cb.src[0].ld = g->ld_z1; cb.src[0].act = 1;
+    cb.W = g->W2; cb.W_hi = g->W2_hi; cb.W_lo = g->W2_lo; cb.W_hi16 = g->W2_hi16; cb.W_lo16 = g->W2_lo16;
+    cb.ldw = g->ldw2; cb.bias = g->b2; cb.out_scale = 1.f; cb.mode = MB_OUT_STORE;
+    if (g->h) {  // h = y; out2, when also wanted, by a second pass of the (cheap) second layer
+      cb.out = g->h; cb.ld_out = g->ld_h;
+      if ((rc = mb_gemm(&b, stream_))) return rc;
+    }
+    if (g->out2) {
+      cb.out = g->out2; cb.ld_out = g->ld_out2;
+      cb.res = g->res; cb.res_w = g->res_w; cb.ld_res = g->ld_res;
+      if ((rc = mb_gemm(&b, stream_))) return rc;
+    }
+    return MB_OK;
+  }
   if (!g->z1 || !g->z2 || g->ld_z2 != 256 || !g->W1 || !g->W2) return MB_ERR_INVALID;
   if ((g->h && g->ld_h != 128) || (g->out2 && (g->ld_out2 != 128 || g->ld_res != 128))) return MB_ERR_INVALID;
   mb_gemm_desc a = {}, b = {};
@@ -875,7 +905,9 @@ static int gated_mlp_composed(const mb_gated_mlp* g, void* stream_) {
 
 extern "C" int mb_gated_mlp_fwd(const mb_gated_mlp* g, void* stream_) {
   if (!g || g->n_rows < 0 || g->n_src < 1 || g->n_src > 4) return MB_ERR_INVALID;
-  if (!g->norm_core || !g->norm_gate || (!g->h && !g->out2) || (g->out2 && !g->res)) return MB_ERR_INVALID;
+  if (g->kind != MB_MLP_GATED && g->kind != MB_MLP_PLAIN) return MB_ERR_INVALID;
+  const bool plain = g->kind == MB_MLP_PLAIN;
+  if ((!plain && (!g->norm_core || !g->norm_gate)) || (!g->h && !g->out2) || (g->out2 && !g->res)) return MB_ERR_INVALID;
   if (g->ldw1 < 128 * g->n_src || (g->ldw1 & 3) || g->ldw2 < 128 || (g->ldw2 & 3)) return MB_ERR_INVALID;
   for (int s = 0; s < g->n_src; ++s) {
     const mb_src& sr = g->src[s];
@@ -884,10 +916,10 @@ extern "C" int mb_gated_mlp_fwd(const mb_gated_mlp* g, void* stream_) {
   if (g->n_rows == 0) return MB_OK;
   if ((g->n_rows + 127) / 128 > 0x3fffffffLL) return MB_ERR_OVERFLOW;
   auto ok32 = [](const void* p, int64_t ld) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0 && (ld & 7) == 0; };
-  const bool wide_ok = (!g->z1 || ok32(g->z1, g->ld_z1)) && (!g->z2 || ok32(g->z2, g->ld_z2)) &&
+  const bool wide_ok = (!g->z1 || ok32(g->z1, g->ld_z1)) && (plain || !g->z2 || ok32(g->z2, g->ld_z2)) &&
                        (!g->h || ok32(g->h, g->ld_h)) && (!g->out2 || (ok32(g->out2, g->ld_out2) && ok32(g->res, g->ld_res))) &&
-                       (!g->b1 || ok32(g->b1, 0)) && (!g->b2 || ok32(g->b2, 0)) && ok32(g->norm_core, 0) &&
-                       ok32(g->norm_gate, 0) && (!g->res_w || ok32(g->res_w, 0));
+                       (!g->b1 || ok32(g->b1, 0)) && (!g->b2 || ok32(g->b2, 0)) &&
+                       (plain || (ok32(g->norm_core, 0) && ok32(g->norm_gate, 0))) && (!g->res_w || ok32(g->res_w, 0));
   // The fused kernel computes with the 3xBF16 split (the default mode); the other modes compose the three launches.
   if (mb::g_gemm_mode != 0 || !wide_ok) return gated_mlp_composed(g, stream_);
   const void* w1h = g->W1_hi16, *w1l = g->W1_lo16, *w2h = g->W2_hi16, *w2l = g->W2_lo16;
@@ -898,13 +930,15 @@ extern "C" int mb_gated_mlp_fwd(const mb_gated_mlp* g, void* stream_) {
   int rc = mb::device_config(&n_sm);
   if (rc) return rc;
   mb::GatedMaps maps;
-  if ((rc = mb::weight_map(w1h, g->ldw1, 128 * g->n_src, &maps.w1[0], 256, true))) return rc;
-  if ((rc = mb::weight_map(w1l, g->ldw1, 128 * g->n_src, &maps.w1[1], 256, true))) return rc;
-  if ((rc = mb::weight_map(w2h, g->ldw2, 128, &maps.w2[0], 256, true))) return rc;
-  if ((rc = mb::weight_map(w2l, g->ldw2, 128, &maps.w2[1], 256, true))) return rc;
+  const int w_rows = plain ? 128 : 256;
+  if ((rc = mb::weight_map(w1h, g->ldw1, 128 * g->n_src, &maps.w1[0], w_rows, true))) return rc;
+  if ((rc = mb::weight_map(w1l, g->ldw1, 128 * g->n_src, &maps.w1[1], w_rows, true))) return rc;
+  if ((rc = mb::weight_map(w2h, g->ldw2, 128, &maps.w2[0], w_rows, true))) return rc;
+  if ((rc = mb::weight_map(w2l, g->ldw2, 128, &maps.w2[1], w_rows, true))) return rc;
   const long long n_tiles = (g->n_rows + 127) / 128;
   const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
-  mb::k_gated_fwd<<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
+  if (plain) mb::k_gated_fwd<true><<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
+  else mb::k_gated_fwd<false><<<grid, mb::GP_THREADS, mb::GP_SMEM_BYTES, (cudaStream_t)stream_>>>(*g, maps);
   MB_LAUNCH_CHECK("k_gated_fwd");
   return MB_OK;
 }

@@ -312,17 +312,15 @@ def _refine_forward(P, rg, node, edge, rbf, atom_feat, save=True):
     z1, z2, h, _ = gated_fwd(P.edge, R, srcs, save=save)
     env = ops.small_linear_fwd(rbf, P.wenv)               # [bonds,128]
     agg = ops.seg_smooth_sum_fwd(Nn, rg.tgt_ptr, rg.emap, None if rg.is_atom else rg.src, env, h)
-    zn = ops.linear(agg, P.nffn.w1, bias=P.nffn.b1)
-    node_out = ops.linear(zn, P.nffn.w2, bias=P.nffn.b2, in_act=1, res=node, res_w=P.wn)
+    zn, _, node_out = ops.ffn_fwd(P.nffn, agg, want_y=False, res=node, res_w=P.wn, save=save)
     # the edge update reads the unsmoothed rows unless use_smoothed_for_delta_edge (atom graph only,
     # interaction_block.py:262-266): then it reads h * s, s = the envelope row of the edge's bond
     ffn_in = ops.mul_rows_gather(h, env, rg.emap) if P.smoothed_edge else h
-    ze = ops.linear(ffn_in, P.effn.w1, bias=P.effn.b1)
     if rg.is_atom:
-        y = ops.linear(ze, P.effn.w2, bias=P.effn.b2, in_act=1)
+        ze, y, _ = ops.ffn_fwd(P.effn, ffn_in, save=save)
         edge_out = ops.pair_mean_res(Ne, rg.u2d, rg.rev, y, edge, P.we)
     else:
-        edge_out = ops.linear(ze, P.effn.w2, bias=P.effn.b2, in_act=1, res=edge, res_w=P.we)
+        ze, _, edge_out = ops.ffn_fwd(P.effn, ffn_in, want_y=False, res=edge, res_w=P.we, save=save)
     return node_out, edge_out, (z1, z2, h, env, zn, ze)
 
 

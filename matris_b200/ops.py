@@ -209,6 +209,47 @@ def gated_mlp_fwd(p, n_rows, srcs, want_h=True, res=None, res_w=None, save=True)
     return z1, z2, h, out2
 
 
+def ffn_fwd(p, x, want_y=True, res=None, res_w=None, save=True):
+    """Two-layer perceptron  y = W2 SiLU(W1 x + b1) + b2  as one launch of the fused kernel in its plain form
+    (mb_gated_mlp_fwd with kind = MB_MLP_PLAIN).  ``p`` holds w1 [128, K], b1, w2 [128, 128], b2.  Returns
+    (z1, y, out2): z1 = W1 x + b1 only when ``save`` (the backward pass reads it), y only when ``want_y``,
+    out2 = y + res_w * res only when ``res`` is given."""
+    n_rows = int(x.shape[0])
+    w1, w2 = as_split(p.w1), as_split(p.w2)
+    k = w1.shape[1]
+    assert w1.shape[0] == D and k % D == 0 and x.shape[1] == k and tuple(w2.shape) == (D, D)
+    assert x.dtype == torch.float32 and x.stride(-1) == 1
+    save = save or _gemm_mode != 0  # the composed path of the non-default GEMM modes uses z1 as scratch
+    z1 = new(n_rows, D, x) if save else None
+    y = new(n_rows, D, x) if want_y else None
+    out2 = new(n_rows, D, x) if res is not None else None
+    if n_rows == 0:
+        return z1, y, out2
+    n_src = k // D
+    flat = []
+    for s in range(n_src):
+        flat += (x.data_ptr(), 0, x.stride(0), D * s, 0)
+    for _ in range(4 - n_src):
+        flat += _NO_SRC
+
+    def pl(t):
+        return (0, 0) if t is None else (t.data_ptr(), t.stride(0))
+
+    buf = _GATED_FMT.pack(
+        n_rows, n_src, 1, *flat,
+        *w1.ptrs, w1.ldw, 0 if p.b1 is None else p.b1.data_ptr(),
+        *w2.ptrs, w2.ldw, 0 if p.b2 is None else p.b2.data_ptr(),
+        0, 0, *pl(z1), 0, 0, *pl(y),
+        0 if res is None else res.data_ptr(), 0 if res is None or res_w is None else res_w.data_ptr(),
+        0 if res is None else res.stride(0), *pl(out2))
+    if _lib.profile is not None:
+        cols = n_src + (z1 is not None) + (y is not None) + 2 * (out2 is not None)
+        _lib.profile_meta = dict(flops=2.0 * n_rows * D * D * (n_src + 1), rows=n_rows, k=k, n=D, fused=True,
+                                 bytes=4.0 * n_rows * D * cols)
+    call("mb_gated_mlp_fwd", C.byref(_lib.MbGatedMlp.from_buffer_copy(buf)), _stream())
+    return z1, y, out2
+
+
 def linear(x, W, bias=None, out_act=0, in_act=0, gate=None, res=None, res_w=None, scale=1.0, idx=None, out=None):
     """y[R,128*nb] = epilogue(x[R,128*ns] @ W^T): plain dense layer built on gemm()."""
     n_rows = x.shape[0] if idx is None else idx.shape[0]

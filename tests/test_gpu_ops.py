@@ -243,6 +243,64 @@ def test_gated_mlp_fwd_fused_equals_composed(ops):
                TOL_TF32)
 
 
+def _ffn_weights(k, seed, bias=True):
+    from types import SimpleNamespace
+    host = SimpleNamespace(w1=rnd(128, k, seed=seed, scale=k ** -0.5), w2=rnd(128, 128, seed=seed + 2, scale=128 ** -0.5),
+                           b1=rnd(128, seed=seed + 1, scale=0.1) if bias else None,
+                           b2=rnd(128, seed=seed + 3, scale=0.1) if bias else None)
+    device = SimpleNamespace(**{k_: None if v is None else dev(v) for k_, v in vars(host).items()})
+    return host, device
+
+
+def _ffn_ref(hp, x):
+    """node_FFN / edge_FFN (matris/model/interaction_block.py:197-210) in float64."""
+    z1 = F.linear(x.double(), hp.w1.double(), None if hp.b1 is None else hp.b1.double())
+    return z1, F.linear(F.silu(z1), hp.w2.double(), None if hp.b2 is None else hp.b2.double())
+
+
+@pytest.mark.parametrize("n_rows", [1, 127, 129, 1000, 148 * 128 + 77, 148 * 128 * 3 + 5])
+def test_ffn_fwd_row_counts(ops, n_rows):
+    """The plain two-layer form of the fused kernel: one, an even and an odd number of tiles per CTA, ragged last
+    tiles, every output requested, against float64."""
+    hp, dp = _ffn_weights(128, seed=61)
+    x, res, rw = rnd(n_rows, 128, seed=62), rnd(n_rows, 128, seed=63), rnd(128, seed=64)
+    z1, y, out2 = ops.ffn_fwd(dp, dev(x), res=dev(res), res_w=dev(rw))
+    assert ops.gemm_status() == 0
+    r1, ry = _ffn_ref(hp, x)
+    report(f"ffn_fwd z1 R={n_rows}", z1, r1, TOL_BF16)
+    report(f"ffn_fwd y R={n_rows}", y, ry, TOL_BF16)
+    report(f"ffn_fwd out2 R={n_rows}", out2, ry + rw.double() * res.double(), TOL_BF16)
+
+
+@pytest.mark.parametrize("k,bias", [(128, False), (256, True), (512, True)])
+def test_ffn_fwd_output_subsets_and_modes(ops, k, bias):
+    """Without z1 (the no-save path), y only, out2 only with a unit residual weight, wider inputs, no biases; and the
+    same result composed from two GEMM launches in the other GEMM modes."""
+    R = 5000 + 13
+    hp, dp = _ffn_weights(k, seed=71, bias=bias)
+    x, res = rnd(R, k, seed=72), rnd(R, 128, seed=73)
+    dx, dres = dev(x), dev(res)
+    r1, ry = _ffn_ref(hp, x)
+    z1, y, out2 = ops.ffn_fwd(dp, dx, save=False)
+    assert z1 is None and out2 is None
+    report(f"ffn_fwd K={k} y (no save)", y, ry, TOL_BF16)
+    z1, y, out2 = ops.ffn_fwd(dp, dx, want_y=False, res=dres, save=True)
+    assert y is None
+    report(f"ffn_fwd K={k} out2 only", out2, ry + res.double(), TOL_BF16)
+    report(f"ffn_fwd K={k} z1", z1, r1, TOL_BF16)
+    assert ops.gemm_status() == 0
+    try:
+        for mode, tol in (("simt", 2e-6), ("tcgen05_tile", 1e-5), ("tcgen05_tf32", TOL_TF32)):
+            ops.set_gemm_mode(mode)
+            z1, y, out2 = ops.ffn_fwd(dp, dx, res=dres, save=False)
+            report(f"ffn_fwd K={k} composed in mode {mode}: y", y, ry, tol)
+            report(f"ffn_fwd K={k} composed in mode {mode}: out2", out2, ry + res.double(), tol)
+            report(f"ffn_fwd K={k} composed in mode {mode}: z1", z1, r1, tol)
+            assert ops.gemm_status() == 0
+    finally:
+        ops.set_gemm_mode("tcgen05")
+
+
 def test_bounded_wait_expiry_sets_status_and_clears(ops):
     """The failure path of the tensor-core kernels: a wait that runs out raises the status word, nothing hangs, and
     the next kernel runs normally.  The wait is made to run out by a self-test kernel that waits (a few polls) on a
