@@ -8,6 +8,9 @@
 Default workload: the high-throughput screen of random ABX3 perovskite cells (2x2x2 supercells, 40 atoms, seed 4),
 task "efsm", 512 cells per GPU, MatRIS with 10 interaction blocks and seeded random-init weights.  One step = graph
 build + forward + backward for the whole batch + the gather of energies, forces, stresses and magnetic moments.
+A rank evaluates its structures the way `MatRIS.predict` does: as one batch when the internals of every layer fit in
+memory beside it, otherwise as contiguous sub-batches that do, one after another (the structures are independent;
+the backward pass then recomputes nothing).
 N > 1 (one process per GPU under torchrun): the list of 512 N cells is sharded over the ranks by predicted cost
 (matris_b200.parallel), every rank evaluates its share, and the results are gathered to rank 0 with one NCCL gather
 per step; no other collective is on the path.  `--scaling strong` keeps the total fixed (256 random crystals by
@@ -337,12 +340,29 @@ def main():
         return flat
 
     # ---- device-resident arm: positions/lattices already in HBM; a step = graph build + forward + backward + gather
-    hb = HostBatch([c.numbers for c in mine], [c.cart for c in mine], [c.lattice for c in mine], cut)
-    g = upload(hb, cut, lcut, device)
+    # The rank's structures are evaluated as the sub-batches MatRIS.predict would form (split_for_memory: one batch
+    # when the internals of every layer fit in memory beside it, else contiguous ranges that do, so that the
+    # backward pass recomputes nothing); every sub-batch's inputs are resident before the timed region.
+    def resident(part):
+        hb_ = HostBatch([c.numbers for c in part], [c.cart for c in part], [c.lattice for c in part], cut)
+        return hb_, upload(hb_, cut, lcut, device)
+
+    hb, g = resident(mine)
+    build_on_device(g)
+    ranges = model.split_for_memory(g)
+    h2d_step = hb.h2d_bytes
+    if len(ranges) > 1:
+        del g
+        parts = [resident(mine[a:b]) for a, b in ranges]
+        h2d_step += sum(p[0].h2d_bytes for p in parts)  # predict uploads the whole list once to plan, then the parts
+        graphs = [p[1] for p in parts]
+    else:
+        graphs = [g]
 
     def step_resident(gather=True):
-        build_on_device(g)
-        out = model(g, task=task)
+        for g_ in graphs:
+            build_on_device(g_)
+        out = model.forward_batches(graphs, task=task)
         if gather:
             gather_results(out)
         return out
@@ -390,7 +410,7 @@ def main():
         ev1.record()
         barrier()
     t_e2e = torch.tensor([ev0.elapsed_time(ev1) * 1e-3], device=device)
-    h2d = torch.tensor([float(hb.h2d_bytes)], device=device)
+    h2d = torch.tensor([float(h2d_step)], device=device)
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
         dist.all_reduce(h2d, op=dist.ReduceOp.SUM)
@@ -399,8 +419,9 @@ def main():
     model.check_status()
 
     # ---- per-rank table (what limits the scaling can be read from it)
-    mine_row = torch.tensor([my_ms, float(n_atoms), float(g.n_edges), float(g.n_triplets), t_gather, float(len(mine))],
-                            device=device)
+    n_edges_mine, n_triplets_mine = sum(g_.n_edges for g_ in graphs), sum(g_.n_triplets for g_ in graphs)
+    mine_row = torch.tensor([my_ms, float(n_atoms), float(n_edges_mine), float(n_triplets_mine), t_gather,
+                             float(len(mine)), float(len(graphs)), float(model.last_kept_layers)], device=device)
     rows = [torch.empty_like(mine_row) for _ in range(world)] if (world > 1 and rank == 0) else None
     if world > 1:
         dist.gather(mine_row, rows, dst=0)
@@ -409,7 +430,8 @@ def main():
     rank_table = None
     if rank == 0:
         rank_table = [{"rank": r, "ms_per_step": round(float(x[0]), 3), "atoms": int(x[1]), "directed_edges": int(x[2]),
-                       "triplets": int(x[3]), "last_gather_ms": round(float(x[4]), 3), "structures": int(x[5])}
+                       "triplets": int(x[3]), "last_gather_ms": round(float(x[4]), 3), "structures": int(x[5]),
+                       "sub_batches": int(x[6]), "kept_layers_last_sub_batch": int(x[7])}
                       for r, x in enumerate(rows)]
 
     # ---- one instrumented step: per-kernel device time (CUDA events on the launching stream)
@@ -477,7 +499,7 @@ def main():
                             "algorithmic FLOP; mma_peak_timed = CUDA-event-timed tcgen05.mma issue loop on resident "
                             "operands in this run (mb_bench_mma_rate), with the SM clock sampled during it"}
         gms = sum(per[k][1] for k in per if k.startswith("mb_graph"))
-        gbytes = 26.0 * g.n_edges + 20.0 * g.n_triplets + 16.0 * g.n_atoms
+        gbytes = 26.0 * n_edges_mine + 20.0 * n_triplets_mine + 16.0 * n_atoms
         roofline_graph = {"kernels": "mb_graph_*", "bound": "hbm", "achieved": gbytes / (gms * 1e-3) / 1e9,
                           "peak": peak_gb, "unit": "GB/s", "frac": gbytes / (gms * 1e-3) / 1e9 / peak_gb,
                           "traffic": None, "algorithmic_bytes": gbytes, "ms": gms, "peak_source": src}
@@ -535,7 +557,10 @@ def main():
                            "atoms": atoms_job, "structures": len(crystals),
                            "l2": "per-step working set (>1 GB of activations) exceeds the 126 MB L2",
                            "parallelism": f"structures sharded by predicted cost over {world} rank(s); one gather of "
-                                          "E, F, S, M per step, no other collective"},
+                                          "E, F, S, M per step, no other collective",
+                           "sub_batches": f"rank 0 evaluates its {len(mine)} structures as {len(graphs)} sub-batch(es) "
+                                          "chosen by MatRIS.split_for_memory (all layers' internals kept, no "
+                                          "recomputation in the backward pass)"},
                 "ranks": rank_table,
                 "clocks": clocks.summary(), "clocks_e2e": clocks_e2e.summary(),
                 "e2e": {"value": atoms_job * args.steps / t_e2e, "unit": "atoms*evals/s",

@@ -540,6 +540,50 @@ class _Node(nn.Module):
     """Anonymous container so that parameters sit under the reference's dotted key names."""
 
 
+def kept_layers_for(n_layers: int, n_triplets: int, n_edges: int, avail: float) -> int:
+    """The memory policy of ``MatRIS.kept_layers`` as a function of the available bytes."""
+    per_layer = 6.7e3 * n_triplets + 6.2e3 * n_edges
+    budget = 0.45 * avail
+    n_keep = n_layers if per_layer * n_layers < budget else max(0, int(budget // max(per_layer, 1.0)))
+    # Second bound, on the peak of the backward pass (saved inputs of all layers + the temporaries of one recomputed
+    # layer + gradients).  Measured on three graph shapes (4.1 M - 6.6 M triplets, 1.0 M - 1.7 M directed edges):
+    # 17.4 KB per triplet + 13.8 KB per directed edge with nothing kept, growing by 2.5 KB per triplet + 4.3 KB per
+    # directed edge per kept layer; that peak must stay below 92 % of the memory.
+    base = 18.0e3 * n_triplets + 14.2e3 * n_edges
+    step = 2.6e3 * n_triplets + 4.4e3 * n_edges
+    # Third bound, on the end of the forward pass (saved inputs of all layers, about 17 KB per triplet, + the kept
+    # internals).
+    inputs = 17.0e3 * n_triplets + 2.0e3 * n_edges
+    while 0 < n_keep < n_layers and max(base + step * n_keep, inputs + per_layer * n_keep) > 0.92 * avail:
+        n_keep -= 1
+    return n_keep
+
+
+def split_ranges(triplets, edges, fits) -> list[tuple[int, int]]:
+    """Cut a list of structures (per-structure triplet and directed-edge counts) into contiguous ranges with
+    ``fits(sum of triplets, sum of edges)`` true for every range, as few as a greedy walk needs and then balanced
+    by triplet + edge rows.  A structure that does not fit alone gets a range of its own."""
+    triplets, edges = np.asarray(triplets, dtype=np.int64), np.asarray(edges, dtype=np.int64)
+    n = len(triplets)
+    greedy, a, t, e = [], 0, 0, 0
+    for i in range(n):
+        if i > a and not fits(t + int(triplets[i]), e + int(edges[i])):
+            greedy.append((a, i))
+            a, t, e = i, 0, 0
+        t, e = t + int(triplets[i]), e + int(edges[i])
+    greedy.append((a, n))
+    if len(greedy) == 1:
+        return greedy
+    cum = np.cumsum(triplets + edges, dtype=np.float64)
+    for parts in range(len(greedy), min(n, len(greedy) + 2) + 1):
+        cuts = [0] + [int(np.searchsorted(cum, cum[-1] * k / parts, side="left")) + 1 for k in range(1, parts)] + [n]
+        ranges = [(cuts[k], cuts[k + 1]) for k in range(parts)]
+        if all(b > a for a, b in ranges) and all(fits(int(triplets[a:b].sum()), int(edges[a:b].sum())) or b - a == 1
+                                                 for a, b in ranges):
+            return ranges
+    return greedy
+
+
 class MatRIS(nn.Module):
     """Drop-in for the reference's ``MatRIS`` (matris/model/model.py:30-317)."""
 
@@ -565,6 +609,8 @@ class MatRIS(nn.Module):
         self.last_batch = None
         # None: decide per call from free memory; True / False: keep / recompute all; n: keep the last n layers' internals
         self.keep_activations = None
+        # plan as if at most this many bytes of device memory were available (None: what the device has left)
+        self.memory_limit_bytes = None
 
     # -- parameter tree -------------------------------------------------------------------
     def _register(self, key, value, buffer, trainable):
@@ -700,48 +746,61 @@ class MatRIS(nn.Module):
             raise MbError(f"a tensor-core kernel's bounded wait expired (status {status}): the results of that "
                           "evaluation are invalid")
 
+    # -- memory policy -----------------------------------------------------------------------
+    def _available_bytes(self) -> float:
+        """Memory the allocator can still hand out = device total - what lives outside this allocator - what it has
+        allocated (capped by ``memory_limit_bytes`` when set).  The driver query behind the middle term costs
+        milliseconds (during which the GPU idles at the start of an evaluation), so it is refreshed every 64th call
+        only; the last term is a counter."""
+        st = getattr(self, "_mem_state", None)
+        if st is None:
+            st = self._mem_state = {"calls": 0, "total": 0, "outside": 0}
+        if st["calls"] % 64 == 0:
+            free, total = torch.cuda.mem_get_info(self.device)
+            st["total"], st["outside"] = total, total - free - torch.cuda.memory_reserved(self.device)
+        st["calls"] += 1
+        avail = st["total"] - st["outside"] - torch.cuda.memory_allocated(self.device)
+        if self.memory_limit_bytes is not None:
+            avail = min(avail, float(self.memory_limit_bytes))
+        return avail
+
+    def kept_layers(self, n_triplets: int, n_edges: int, avail: float | None = None) -> int:
+        """How many (last) layers keep their sub-block internals for the backward pass on a batch with that many
+        triplet rows and directed edges; the internals of the earlier layers are recomputed there.  The internals
+        take ~6.7 KB per triplet row and ~6.2 KB per directed edge per layer and are consumed and released last
+        layer first: all layers are kept when that fits in 45 % of the available memory, otherwise as many as do,
+        within two more bounds (see below).  ``keep_activations`` overrides: True / False / a number of layers."""
+        n_layers = int(self.config["num_layers"])
+        keep = self.keep_activations
+        if keep is not None:
+            if isinstance(keep, bool):
+                return n_layers if keep else 0
+            return max(0, min(n_layers, int(keep)))
+        return kept_layers_for(n_layers, n_triplets, n_edges, self._available_bytes() if avail is None else avail)
+
+    def split_for_memory(self, g: BatchedGraph, headroom: float = 0.93) -> list[tuple[int, int]]:
+        """Contiguous ranges of the structures of batch ``g`` such that every range, evaluated as a batch of its own,
+        keeps the internals of all layers (no recomputation in the backward pass): ``[(0, n_struct)]`` when the
+        whole batch does.  Structures are independent, so evaluating the ranges one after another gives the same
+        results; on a batch that would recompute most layers it is about a fifth faster.  ``headroom`` scales the
+        available memory the plan may count on (the ranges' own graphs and results take some)."""
+        if g.n_struct <= 1 or self.keep_activations is not None:
+            return [(0, g.n_struct)]
+        n_layers = int(self.config["num_layers"])
+        avail = headroom * self._available_bytes()
+        if kept_layers_for(n_layers, g.n_triplets, g.n_edges, avail / headroom) == n_layers:
+            return [(0, g.n_struct)]
+        _, ep, _, tp = g.structure_slices()
+        return split_ranges(np.diff(tp), np.diff(ep), lambda t, e: kept_layers_for(n_layers, t, e, avail) == n_layers)
+
     def _evaluate(self, g: BatchedGraph, task: str):
         cfg = self.config
         P = self.packed(self.device)
         atom_rg, line_rg = row_graphs(g)
         want_f, want_s = "f" in task, "s" in task
         need_grad = want_f or want_s
-        # bytes of sub-block internals per layer: ~6.7 KB per triplet row and ~6.2 KB per directed edge.  The internals
-        # of the LAST n_keep layers are kept for the backward pass (they are consumed and released first), those of
-        # the earlier layers are recomputed there: n_keep = all layers when everything fits in 45 % of the memory the
-        # allocator can still hand out, otherwise as many as do.
         n_layers = len(P.layers)
-        per_layer = 6.7e3 * g.n_triplets + 6.2e3 * g.n_edges
-        keep = self.keep_activations
-        if keep is None:
-            # Memory the allocator can hand out = device total - what lives outside this allocator - what it has
-            # allocated.  The driver query behind the middle term costs milliseconds (during which the GPU idles at
-            # the start of an evaluation), so it is refreshed every 64th call only; the last term is a counter.
-            st = getattr(self, "_mem_state", None)
-            if st is None:
-                st = self._mem_state = {"calls": 0, "total": 0, "outside": 0}
-            if st["calls"] % 64 == 0:
-                free, total = torch.cuda.mem_get_info(self.device)
-                st["total"], st["outside"] = total, total - free - torch.cuda.memory_reserved(self.device)
-            st["calls"] += 1
-            avail = st["total"] - st["outside"] - torch.cuda.memory_allocated(self.device)
-            budget = 0.45 * avail
-            n_keep = n_layers if per_layer * n_layers < budget else max(0, int(budget // max(per_layer, 1.0)))
-            # Second bound, on the peak of the backward pass (saved inputs of all layers + the temporaries of one
-            # recomputed layer + gradients).  Measured on three graph shapes (4.1 M - 6.6 M triplets, 1.0 M - 1.7 M
-            # directed edges): 17.4 KB per triplet + 13.8 KB per directed edge with nothing kept, growing by 2.5 KB
-            # per triplet + 4.3 KB per directed edge per kept layer; that peak must stay below 92 % of the memory.
-            base = 18.0e3 * g.n_triplets + 14.2e3 * g.n_edges
-            step = 2.6e3 * g.n_triplets + 4.4e3 * g.n_edges
-            # Third bound, on the end of the forward pass (saved inputs of all layers, about 17 KB per triplet, + the
-            # kept internals).
-            inputs = 17.0e3 * g.n_triplets + 2.0e3 * g.n_edges
-            while 0 < n_keep < n_layers and max(base + step * n_keep, inputs + per_layer * n_keep) > 0.92 * avail:
-                n_keep -= 1
-        elif isinstance(keep, bool):
-            n_keep = n_layers if keep else 0
-        else:
-            n_keep = max(0, min(n_layers, int(keep)))  # an integer: keep the internals of that many (last) layers
+        n_keep = self.kept_layers(g.n_triplets, g.n_edges)
         self.last_kept_layers = n_keep
         out = {}
         with torch.set_grad_enabled(need_grad):
@@ -805,9 +864,37 @@ class MatRIS(nn.Module):
         return comp @ table
 
     # -- convenience ------------------------------------------------------------------------
+    def plan_batches(self, structures) -> list[BatchedGraph]:
+        """The device-resident graphs ``predict`` evaluates for a list of structures: one batch when the internals of
+        every layer fit in memory beside it, otherwise the contiguous sub-batches of ``split_for_memory``."""
+        structures = list(structures)
+        g = self.graph_converter.batch(structures)
+        ranges = self.split_for_memory(g)
+        if len(ranges) == 1:
+            return [g]
+        del g
+        return [self.graph_converter.batch(structures[a:b]) for a, b in ranges]
+
+    def forward_batches(self, graphs: Sequence[BatchedGraph], task: str = "efsm") -> dict:
+        """Evaluate sub-batches one after another and join the results in order: the dictionary ``forward`` returns
+        for the concatenated list of structures."""
+        outs = [self.forward(g, task=task) for g in graphs]
+        if len(outs) == 1:
+            return outs[0]
+        res = {"e": torch.cat([o["e"] for o in outs]), "atoms_per_graph": torch.cat([o["atoms_per_graph"] for o in outs])}
+        ref = [o["ref_energy"] for o in outs]
+        res["ref_energy"] = torch.cat(ref) if torch.is_tensor(ref[0]) else ref[0]
+        if "f" in outs[0]:
+            res["f"] = tuple(t for o in outs for t in o["f"])
+        for k in ("s", "m"):
+            if k in outs[0]:
+                res[k] = [t for o in outs for t in o[k]]
+        return res
+
     def predict(self, structures, task: str = "efsm"):
-        """Evaluate a list of structures (any accepted structure type) as one batch."""
-        return self.forward(self.graph_converter.batch(structures), task=task)
+        """Evaluate a list of structures (any accepted structure type): as one batch, or, when the backward pass of
+        that batch would have to recompute layers for lack of memory, as the sub-batches of ``plan_batches``."""
+        return self.forward_batches(self.plan_batches(structures), task=task)
 
     def predict_sharded(self, structures, task: str = "efsm", group=None, dst: int = 0):
         """``predict`` over all ranks of a ``torch.distributed`` group (one process per GPU, every rank passes the

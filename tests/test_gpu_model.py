@@ -211,6 +211,38 @@ def test_recompute_equals_kept_activations():
         report(f"keep all vs keep_activations={keep}: S", res[True][1] / GPA, res[keep][1] / GPA, 2e-7)
 
 
+def test_predict_in_sub_batches_equals_one_batch():
+    """With little memory to plan with, predict evaluates a list of structures as contiguous sub-batches that keep
+    every layer's internals; the results are those of the single batch (which then recomputes), in order."""
+    from matris_b200 import MatRIS
+    crystals = workloads.random_crystals(12, seed=13)
+    ck = random_checkpoint(dict(num_layers=3, reference_energy="mpa"), seed=5)
+    model = MatRIS.from_dict(ck).to("cuda")
+    g = model.graph_converter.batch(crystals)
+    assert model.split_for_memory(g) == [(0, 12)]
+    one = model.predict(crystals, "efsm")
+    assert model.last_kept_layers == 3
+    # room for the internals of about a third of the batch: 45 % of the limit = a third of what all layers take
+    model.memory_limit_bytes = 3 * (6.7e3 * g.n_triplets + 6.2e3 * g.n_edges) / 0.45 / 3
+    ranges = model.split_for_memory(g)
+    assert len(ranges) >= 3 and ranges[0][0] == 0 and ranges[-1][1] == 12
+    assert all(a[1] == b[0] and a[0] < a[1] for a, b in zip(ranges, ranges[1:]))
+    graphs = model.plan_batches(crystals)
+    assert [x.n_struct for x in graphs] == [b - a for a, b in ranges]
+    parts = model.predict(crystals, "efsm")
+    assert model.last_kept_layers == 3  # the last sub-batch kept everything
+    assert torch.equal(parts["atoms_per_graph"].cpu(), one["atoms_per_graph"].cpu())
+    report("sub-batches vs one batch: E", parts["e"], one["e"], 1e-6, rel=True)
+    # a float32 matrix product over the batch's composition table: rounding depends on the batch shape
+    report("sub-batches vs one batch: reference energy", parts["ref_energy"], one["ref_energy"], 1e-6, rel=True)
+    assert len(parts["f"]) == len(parts["s"]) == len(parts["m"]) == 12
+    report("sub-batches vs one batch: F", torch.cat(list(parts["f"])), torch.cat(list(one["f"])), 2e-6)
+    report("sub-batches vs one batch: S", torch.stack(parts["s"]) / GPA, torch.stack(one["s"]) / GPA, 2e-7)
+    report("sub-batches vs one batch: M", torch.cat(parts["m"]), torch.cat(one["m"]), 2e-6)
+    model.keep_activations = False       # an explicit policy is taken as given: no split
+    assert model.split_for_memory(g) == [(0, 12)]
+
+
 def test_forward_raises_once_after_an_expired_wait_and_recovers():
     """An expired bounded wait surfaces as one exception (at the next forward, or at check_status once the stream
     has been synchronised) and the model then works again."""

@@ -64,3 +64,44 @@ def test_graph_converter_follows_the_model():
     assert model.graph_converter.device is None
     model.to("meta")  # any non-CUDA device: the converter keeps its default
     assert model.graph_converter.device is None
+
+
+def test_memory_policy_bounds_and_sub_batch_ranges():
+    """kept_layers_for: everything is kept while it fits, fewer layers as memory shrinks, never more than the bounds
+    allow; split_ranges: contiguous, complete, every range fits, balanced, single structures that do not fit alone
+    stay alone."""
+    import numpy as np
+
+    from matris_b200.model import kept_layers_for, split_ranges
+
+    T, E = 6_600_000, 1_410_000   # the 512-perovskite batch
+    assert kept_layers_for(10, T, E, 190e9) == 1
+    assert kept_layers_for(10, T // 8, E // 8, 190e9) == 10
+    assert kept_layers_for(10, T, E, 2000e9) == 10
+    assert kept_layers_for(10, T, E, 50e9) == 0
+    kept = [kept_layers_for(10, T, E, a * 1e9) for a in (100, 190, 300, 500, 900, 1300)]
+    assert kept == sorted(kept) and kept[-1] == 10
+    for a, k in zip((100, 190, 300, 500, 900), kept):
+        if 0 < k < 10:  # the bounds on the backward-pass peak and on the end of the forward pass hold
+            assert (18.0e3 + 2.6e3 * k) * T + (14.2e3 + 4.4e3 * k) * E <= 0.92 * a * 1e9
+            assert (17.0e3 + 6.7e3 * k) * T + (2.0e3 + 6.2e3 * k) * E <= 0.92 * a * 1e9
+
+    rng = np.random.default_rng(0)
+    trip = rng.integers(5_000, 20_000, 512)
+    edge = rng.integers(1_000, 4_000, 512)
+    fits = lambda t, e: kept_layers_for(10, t, e, 0.93 * 190e9) == 10
+    ranges = split_ranges(trip, edge, fits)
+    assert ranges[0][0] == 0 and ranges[-1][1] == 512
+    assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    assert all(fits(int(trip[a:b].sum()), int(edge[a:b].sum())) for a, b in ranges)
+    rows = [int((trip[a:b] + edge[a:b]).sum()) for a, b in ranges]
+    assert max(rows) < 1.15 * min(rows)                       # balanced
+    need = (6.7e3 * trip.sum() + 6.2e3 * edge.sum()) * 10 / (0.45 * 0.93 * 190e9)
+    assert need <= len(ranges) <= need + 3                    # about as few ranges as the memory allows
+    assert split_ranges(trip[:20], edge[:20], fits) == [(0, 20)]
+    # one structure too large to keep everything: a range of its own, its neighbours unaffected
+    trip2 = trip.copy()
+    trip2[100] = 40_000_000
+    ranges2 = split_ranges(trip2, edge, fits)
+    assert (100, 101) in ranges2 and ranges2[0][0] == 0 and ranges2[-1][1] == 512
+    assert all(fits(int(trip2[a:b].sum()), int(edge[a:b].sum())) or (a, b) == (100, 101) for a, b in ranges2)
