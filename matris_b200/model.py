@@ -155,13 +155,14 @@ def row_graphs(g: BatchedGraph):
     if getattr(g, "_row_graphs", None) is None:
         atom = SimpleNamespace(is_atom=True, n_rows=g.n_edges, n_nodes=g.n_atoms, n_edge_rows=g.n_bonds,
                                tgt=g.center, src=g.neighbor, ctr=None, tgt_ptr=g.edge_ptr, src_ptr=g.edge_ptr,
-                               src_perm=g.rev, emap=g.d2u, u2d=g.u2d, rev=g.rev, keep=False)
+                               src_perm=g.rev, emap=g.d2u, u2d=g.u2d, rev=g.rev, keep=False, skip_edge_out=False)
         line = None
         if g.n_triplets:
             c = g.lg_cols
             line = SimpleNamespace(is_atom=False, n_rows=g.n_triplets, n_nodes=g.n_bonds, n_edge_rows=g.n_triplets,
                                    ctr=c[0], tgt=c[1], src=c[3], tgt_ptr=g.trip_ptr, src_ptr=g.trip_src_ptr,
-                                   src_perm=g.trip_src_perm, emap=None, u2d=None, rev=None, keep=False)
+                                   src_perm=g.trip_src_perm, emap=None, u2d=None, rev=None, keep=False,
+                                   skip_edge_out=False)
         g._row_graphs = (atom, line)
     return g._row_graphs
 
@@ -303,7 +304,7 @@ class AttentionFn(torch.autograd.Function):
 
 
 # ------------------------------------------------------------------ refinement layer
-def _refine_forward(P, rg, node, edge, rbf, atom_feat, save=True):
+def _refine_forward(P, rg, node, edge, rbf, atom_feat, save=True, want_edge=True):
     R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
     if rg.is_atom:
         srcs = [S(edge, rg.emap), S(node, rg.tgt), S(node, rg.src)]
@@ -315,6 +316,8 @@ def _refine_forward(P, rg, node, edge, rbf, atom_feat, save=True):
     zn, _, node_out = ops.ffn_fwd(P.nffn, agg, want_y=False, res=node, res_w=P.wn, save=save)
     # the edge update reads the unsmoothed rows unless use_smoothed_for_delta_edge (atom graph only,
     # interaction_block.py:262-266): then it reads h * s, s = the envelope row of the edge's bond
+    if not want_edge:  # the last layer's edge update feeds nothing
+        return node_out, None, (z1, z2, h, env, zn, None)
     ffn_in = ops.mul_rows_gather(h, env, rg.emap) if P.smoothed_edge else h
     if rg.is_atom:
         ze, y, _ = ops.ffn_fwd(P.effn, ffn_in, save=save)
@@ -333,10 +336,14 @@ class RefineFn(torch.autograd.Function):
         if atom_feat is not None:
             atom_feat = atom_feat.contiguous()
         keep = bool(rg.keep and any(ctx.needs_input_grad))
-        node_out, edge_out, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat, save=keep)
+        want_edge = not rg.skip_edge_out
+        node_out, edge_out, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat, save=keep, want_edge=want_edge)
         ctx.save_for_backward(node, edge, rbf, atom_feat)
-        ctx.P, ctx.rg = P, rg
+        ctx.P, ctx.rg, ctx.want_edge = P, rg, want_edge
         ctx.inter = inter if keep else None
+        if not want_edge:  # a placeholder nobody reads, so that the signature stays (node, edge)
+            edge_out = edge.new_empty(0)
+            ctx.mark_non_differentiable(edge_out)
         return node_out, edge_out
 
     @staticmethod
@@ -345,10 +352,12 @@ class RefineFn(torch.autograd.Function):
         node, edge, rbf, atom_feat = ctx.saved_tensors
         P, rg = ctx.P, ctx.rg
         R, Nn, Ne = rg.n_rows, rg.n_nodes, rg.n_edge_rows
-        d_node_out, d_edge_out = d_node_out.contiguous(), d_edge_out.contiguous()
+        want_edge = ctx.want_edge
+        d_node_out = d_node_out.contiguous()
+        d_edge_out = d_edge_out.contiguous() if want_edge else None
         inter, ctx.inter = ctx.inter, None
         if inter is None:
-            _, _, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat)
+            _, _, inter = _refine_forward(P, rg, node, edge, rbf, atom_feat, want_edge=want_edge)
         z1, z2, h, env, zn, ze = inter
         del inter
         # node FFN
@@ -357,18 +366,21 @@ class RefineFn(torch.autograd.Function):
         dagg = ops.linear(dzn, P.nffn.w1t)
         del zn, dzn
         # edge FFN (atom graph: the mean over the two directions is a gather * 0.5)
-        if rg.is_atom:
-            dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze, scale=0.5, idx=rg.emap)
-        else:
-            dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze)
-        dh = ops.linear(dze, P.effn.w1t)
-        del ze, dze
         drow = None
-        if P.smoothed_edge:  # dh so far is the gradient of the smoothed rows h * s
-            drow, dh = dh, ops.mul_rows_gather(dh, env, rg.emap)
+        if want_edge:
+            if rg.is_atom:
+                dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze, scale=0.5, idx=rg.emap)
+            else:
+                dze = ops.linear(d_edge_out, P.effn.w2t, gate=ze)
+            dh = ops.linear(dze, P.effn.w1t)
+            del ze, dze
+            if P.smoothed_edge:  # dh so far is the gradient of the smoothed rows h * s
+                drow, dh = dh, ops.mul_rows_gather(dh, env, rg.emap)
+        else:
+            dh = ops.new(R, D, dagg)  # no edge update, no gradient from it: the aggregation's term starts the row
         # smoothed aggregation
         src = None if rg.is_atom else rg.src
-        dz2 = ops.seg_smooth_sum_bwd_rows(rg.tgt, src, rg.emap, env, dagg, dh, accumulate=True,
+        dz2 = ops.seg_smooth_sum_bwd_rows(rg.tgt, src, rg.emap, env, dagg, dh, accumulate=want_edge,
                                           gate=_gate_args(P.edge, z2))  # with a gate: dh is finished in registers
         denv = ops.seg_smooth_sum_bwd_env(env.shape[0], rg.tgt_ptr, None if rg.is_atom else rg.src_ptr, rg.src_perm,
                                           rg.tgt, src if src is not None else rg.src, rg.u2d, rg.rev, env, h, dagg,
@@ -379,13 +391,13 @@ class RefineFn(torch.autograd.Function):
         # gated MLP
         if rg.is_atom:
             d_atom = None
-            d_edge = ops.scale_rows(d_edge_out, P.we)
+            d_edge = ops.scale_rows(d_edge_out, P.we) if want_edge else torch.zeros_like(edge)
             dests = [(d_edge, rg.emap, OUT_ATOMIC), (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
         else:
             d_atom = torch.zeros_like(atom_feat)
-            d_edge = torch.empty_like(d_edge_out)  # stored once: gemm + we * d_edge_out in the epilogue
-            dests = [(d_edge, None, OUT_STORE, d_edge_out, P.we), (d_atom, rg.ctr, OUT_ATOMIC),
-                     (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
+            d_edge = torch.empty_like(edge)  # stored once: gemm (+ we * d_edge_out in the epilogue)
+            edge_dest = (d_edge, None, OUT_STORE, d_edge_out, P.we) if want_edge else (d_edge, None, OUT_STORE)
+            dests = [edge_dest, (d_atom, rg.ctr, OUT_ATOMIC), (d_node, rg.tgt, OUT_ATOMIC), (d_node, rg.src, OUT_ATOMIC)]
         gated_bwd(P.edge, R, z1, z2, dh, dests, dz2=dz2)
         return d_node, d_edge, d_rbf, d_atom, None, None
 
@@ -814,8 +826,10 @@ class MatRIS(nn.Module):
             trip = AngleEmbedFn.apply(unit, P, g, cfg) if line_rg is not None else None
             for i, L in enumerate(P.layers):
                 atom_rg.keep = i >= n_layers - n_keep
+                # after the last layer only the atom features are read: its two refinements need no edge update
+                atom_rg.skip_edge_out = i == n_layers - 1
                 if line_rg is not None:
-                    line_rg.keep = atom_rg.keep
+                    line_rg.keep, line_rg.skip_edge_out = atom_rg.keep, atom_rg.skip_edge_out
                 e_att, t_att = edge, trip
                 if trip is not None:
                     e_att, t_att = AttentionFn.apply(edge, trip, L.attn_line, line_rg)

@@ -85,7 +85,7 @@ def test_refinement_layer_forward_backward(setup, which):
     A = None if af is None else af.double().requires_grad_(True)
     rn, re_ = refinement_layer(_P(sd, f"interaction_block.0.refine_block_{which}_graph."), N, E, Rb, gd, emap, A)
     leaves = [N, E, Rb] + ([A] if A is not None else [])
-    grads = torch.autograd.grad((rn * dn.double()).sum() + (re_ * de.double()).sum(), leaves)
+    grads = torch.autograd.grad((rn * dn.double()).sum() + (re_ * de.double()).sum(), leaves, retain_graph=True)
     n_in, e_in, r_in = dev(node).requires_grad_(True), dev(edge).requires_grad_(True), dev(rbf).requires_grad_(True)
     a_in = None if af is None else dev(af).requires_grad_(True)
     on, oe = RefineFn.apply(n_in, e_in, r_in, a_in, getattr(P.layers[0], "refine_" + which), rg)
@@ -94,6 +94,18 @@ def test_refinement_layer_forward_backward(setup, which):
     mine = torch.autograd.grad([on, oe], [n_in, e_in, r_in] + ([a_in] if a_in is not None else []), [dev(dn), dev(de)])
     for name, a, b in zip(["node", "edge", "rbf", "atom"], mine, grads):
         report_feat(f"refine[{which}] d {name}", a, b, 2e-4)
+    # the last layer's form: the edge update is not computed (a placeholder comes back) and sends no gradient
+    grads = torch.autograd.grad((rn * dn.double()).sum(), leaves)
+    rg.skip_edge_out = True
+    try:
+        on, oe = RefineFn.apply(n_in, e_in, r_in, a_in, getattr(P.layers[0], "refine_" + which), rg)
+        assert oe.numel() == 0 and not oe.requires_grad
+        report_feat(f"refine[{which}] node, no edge update", on, rn, 3e-5)
+        mine = torch.autograd.grad([on], [n_in, e_in, r_in] + ([a_in] if a_in is not None else []), [dev(dn)])
+    finally:
+        rg.skip_edge_out = False
+    for name, a, b in zip(["node", "edge", "rbf", "atom"], mine, grads):
+        report_feat(f"refine[{which}] d {name}, no edge update", a, b, 2e-4)
 
 
 def _evaluate(ck, crystals, task, keep=None):
