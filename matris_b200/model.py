@@ -826,7 +826,8 @@ class MatRIS(nn.Module):
             trip = AngleEmbedFn.apply(unit, P, g, cfg) if line_rg is not None else None
             for i, L in enumerate(P.layers):
                 atom_rg.keep = i >= n_layers - n_keep
-                # after the last layer only the atom features are read: its two refinements need no edge update
+                # after the last layer only the atom features are read (matris/model/model.py:215-231; the edge features
+                # go to the non-conservative force head only): its two refinements need no edge update
                 atom_rg.skip_edge_out = i == n_layers - 1
                 if line_rg is not None:
                     line_rg.keep, line_rg.skip_edge_out = atom_rg.keep, atom_rg.skip_edge_out
