@@ -2,7 +2,10 @@
 
     python -m matris_b200.bench_gemm K N [act] [gate] [rows] [mode] [scatter]
     python -m matris_b200.bench_gemm gated K [rows] [save] [res] [gather]
+    python -m matris_b200.bench_gemm ffn K [rows] [save] [res]
 
+ffn: the plain two-layer form of the fused kernel (K -> 128 -> 128, `ops.ffn_fwd`); save: also write z1 (default 1);
+res: write out2 = y + res_w * res instead of y (default 1).
 gated: the fused gated-MLP forward (K -> 256 -> 2 x 128 -> 128); save: also write z1 / z2 (default 1); res: also
 write out2 = h + res_w * res (default 1); gather: 1 = K segments 1.. are gathered from a table of rows/6 rows through
 random indices (default 0: all segments read row r).
@@ -62,9 +65,44 @@ def gated(argv):
           f"{flops / ms / 1e9:.1f} TFLOP/s fp32-equivalent, {gbytes / ms * 1e3:.0f} GB/s of algorithmic traffic")
 
 
+def ffn(argv):
+    from types import SimpleNamespace
+    K = int(argv[0])
+    rows = int(argv[1]) if len(argv) > 1 else 148 * 128 * 8
+    save = bool(int(argv[2])) if len(argv) > 2 else True
+    with_res = bool(int(argv[3])) if len(argv) > 3 else True
+    torch.manual_seed(0)
+    dev = "cuda"
+    p = SimpleNamespace(w1=ops.SplitWeight(torch.randn(128, K, device=dev) * K ** -0.5), b1=torch.randn(128, device=dev) * 0.1,
+                        w2=ops.SplitWeight(torch.randn(128, 128, device=dev) * 128 ** -0.5),
+                        b2=torch.randn(128, device=dev) * 0.1)
+    x = torch.randn(rows, K, device=dev)
+    res = torch.randn(rows, 128, device=dev) if with_res else None
+    rw = torch.randn(128, device=dev) if with_res else None
+
+    def launch():
+        return ops.ffn_fwd(p, x, want_y=not with_res, res=res, res_w=rw, save=save)
+
+    for _ in range(3):
+        launch()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    launch()
+    e1.record()
+    torch.cuda.synchronize()
+    assert ops.gemm_status() == 0
+    ms = e0.elapsed_time(e1)
+    flops = 2.0 * rows * 128 * (K + 128)
+    gbytes = 4.0 * rows * (K + 128 * (1 + save + with_res)) / 1e9
+    print(f"ffn rows={rows} K={K} save={int(save)} res={int(with_res)}: {ms:.3f} ms, "
+          f"{flops / ms / 1e9:.1f} TFLOP/s fp32-equivalent, {gbytes / ms * 1e3:.0f} GB/s of algorithmic traffic")
+
+
 def main(argv):
     if argv[0] == "gated":
         return gated(argv[1:])
+    if argv[0] == "ffn":
+        return ffn(argv[1:])
     K, N = int(argv[0]), int(argv[1])
     act = int(argv[2]) if len(argv) > 2 else 0
     gate = int(argv[3]) if len(argv) > 3 else 0
