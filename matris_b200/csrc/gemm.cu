@@ -824,9 +824,22 @@ extern "C" int mb_gemm(const mb_gemm_desc* desc, void* stream_) {
     }
     const long long n_tiles = gx * desc->n_blocks;
     if (persistent) {
-      const unsigned grid = (unsigned)(n_tiles < n_sm ? n_tiles : n_sm);
-      if (bf16) mb::k_gemm_ps<true><<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
-      else mb::k_gemm_ps<false><<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
+      // Shared-A mode: all column blocks read the same A operand and its chunks fit the kernel's A buffers (eight
+      // 32-float chunks in bf16 form, four in tf32 form): a CTA then converts the A rows of a row tile once for all
+      // of its column blocks.
+      bool shared_a = desc->n_blocks > 1 && desc->blk[0].n_src * 4 <= (bf16 ? 8 : 4);
+      for (int j = 1; j < desc->n_blocks && shared_a; ++j) {
+        const mb_colblock& a = desc->blk[0], &b = desc->blk[j];
+        shared_a = a.n_src == b.n_src;
+        for (int s = 0; s < a.n_src && shared_a; ++s)
+          shared_a = a.src[s].ptr == b.src[s].ptr && a.src[s].idx == b.src[s].idx && a.src[s].ld == b.src[s].ld &&
+                     a.src[s].col == b.src[s].col && a.src[s].act == b.src[s].act;
+      }
+      const long long n_items = shared_a ? gx : n_tiles;
+      const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+      const int sa = shared_a ? 1 : 0;
+      if (bf16) mb::k_gemm_ps<true><<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps, sa);
+      else mb::k_gemm_ps<false><<<grid, mb::PS_THREADS, mb::PS_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps, sa);
     } else {
       mb::k_gemm_tc<<<(unsigned)n_tiles, mb::TC_THREADS, mb::TC_SMEM_BYTES, (cudaStream_t)stream_>>>(*desc, maps);
     }

@@ -32,6 +32,12 @@
 //               cores already work on the next tile.  Scatter / accumulate modes go through a 4 KB patch per warp
 //               instead, so that their memory-side reductions leave as 128-byte row segments.
 //
+// Shared-A mode (shared_a != 0; the host picks it when every column block reads the SAME A operand and its K chunks
+// fit the A buffers, i.e. K <= 256 in bf16 form): a CTA takes whole row tiles and runs their column blocks one after
+// the other; chunk c of the tile lives in A buffer c, is gathered and converted ONCE, read by every block's MMAs and
+// handed back to the producers by the last block's.  (Otherwise the tiles of one row tile run on neighbouring CTAs
+// and each gathers and converts the A rows for itself.)
+//
 // Tensor memory (512 columns): accumulators at 0 and 128, A buffers from 256 on (hi | lo each).
 // Shared memory: W ring 4 x 32 KB | producer patches 64 KB | epilogue patches 32 KB | barriers | descriptor copy.
 // Every mbarrier wait is bounded; on expiry a status word is set, the role stops waiting and runs to the common exit,
@@ -170,7 +176,7 @@ static_assert(PS_SMEM_BYTES <= 227 * 1024, "shared memory of one CTA");
 
 template <bool BF>
 __global__ void __launch_bounds__(PS_THREADS, 1)
-k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ TcMaps maps) {
+k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ TcMaps maps, const int shared_a) {
   using Fmt = PsFormat<BF>;
   constexpr uint32_t NB = Fmt::N_ABUF, CPW = Fmt::CH_PER_W;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -203,17 +209,29 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
   const int n_blocks = d.n_blocks;
   // Tiles are numbered row tile * n_blocks + column block; this CTA takes tiles blockIdx.x, + gridDim.x, ...  Every
   // role walks that sequence as a (row tile, column block) pair advanced by (step_rt, step_jb): no division in loops.
+  // Shared-A mode: this CTA takes row tiles blockIdx.x, + gridDim.x, ... and walks the column blocks of each.
   const int n_row_tiles = (int)((n_rows + 127) >> 7);
-  const int first_rt = (int)(blockIdx.x / (unsigned)n_blocks), first_jb = (int)(blockIdx.x % (unsigned)n_blocks);
-  const int step_rt = (int)(gridDim.x / (unsigned)n_blocks), step_jb = (int)(gridDim.x % (unsigned)n_blocks);
+  const bool sh = shared_a != 0;
+  const int first_rt = sh ? (int)blockIdx.x : (int)(blockIdx.x / (unsigned)n_blocks);
+  const int first_jb = sh ? 0 : (int)(blockIdx.x % (unsigned)n_blocks);
+  const int step_rt = sh ? (int)gridDim.x : (int)(gridDim.x / (unsigned)n_blocks);
+  const int step_jb = sh ? 0 : (int)(gridDim.x % (unsigned)n_blocks);
   // When every tile of this CTA belongs to the same column block and that block has a single 128-wide K segment,
   // its W tiles fill w_period ring slots once and stay there for the whole kernel.
-  const bool w_resident = step_jb == 0 && d.blk[first_jb].n_src == 1;
+  const bool w_resident = !sh && step_jb == 0 && d.blk[first_jb].n_src == 1;
   const uint32_t w_period = w_resident ? 4u / CPW : 4u;
-  auto next_tile = [&](int& rt, int& jb) {
+  auto next_tile = [&](int& rt, int& jb) {  // the (row tile, column block) sequence of the MMA, TMA and epilogue warps
+    if (sh) {
+      if (++jb == n_blocks) { jb = 0; rt += step_rt; }
+      return;
+    }
     jb += step_jb;
     rt += step_rt;
     if (jb >= n_blocks) { jb -= n_blocks; ++rt; }
+  };
+  auto next_a_tile = [&](int& rt, int& jb) {  // the sequence of A tiles the producers gather and convert
+    if (sh) rt += step_rt;  // once per row tile, from column block 0's sources
+    else next_tile(rt, jb);
   };
 
   // ---- producer state
@@ -263,7 +281,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
       MB_CP16(de, 2048, a_ptr[4], 256); MB_CP16(dq, 2560, a_ptr[5], 256); MB_CP16(de, 3072, a_ptr[6], 256); MB_CP16(dq, 3584, a_ptr[7], 256);
       if (++g_seg == g_nsrc) {  // on to the next tile
         g_seg = 0;
-        next_tile(g_rt, g_jb);
+        next_a_tile(g_rt, g_jb);
         if (g_rt < n_row_tiles) g_nsrc = d.blk[g_jb].n_src;
       }
       if (g_rt < n_row_tiles) resolve_rows(g_rt, g_jb, g_seg);
@@ -308,14 +326,18 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     for (int j = 0; j < n_blocks; ++j) nch_of |= (uint32_t)(d.blk[j].n_src * 4) << (8 * j);
     nch_of = __shfl_sync(0xffffffffu, nch_of, 0);
     uint32_t g = 0;  // chunks issued so far (all tiles); a multiple of 4 at every tile start
+    uint32_t t_sh = 0;  // shared-A mode: row tiles finished
     int k = 0;
     for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb), ++k) {
       const int acc = k & 1;
       const uint32_t d_tmem = tmem_u + 128u * acc;
       const int nch = (int)((nch_of >> (8 * jb)) & 0xffu);
+      const bool first_blk = !sh || jb == 0, last_blk = !sh || jb == n_blocks - 1;
       for (int c = 0; c < nch; ++c, ++g) {
-        const uint32_t ab = g % NB, wu = g / CPW, slot = wu % w_period;  // A buffer, W-slot use and ring slot of chunk g
-        if (alive) alive = mbar_wait(a_ready + 8 * ab, (g / NB) & 1);  // A rows stored
+        // A buffer, W-slot use and ring slot of chunk g (shared-A mode: chunk c of the row tile sits in buffer c)
+        const uint32_t ab = sh ? (uint32_t)c : g % NB, wu = g / CPW, slot = wu % w_period;
+        // A rows stored (shared-A mode: seen once per row tile, by its first column block)
+        if (first_blk && alive) alive = mbar_wait(a_ready + 8 * ab, (sh ? t_sh : g / NB) & 1);
         if (g % CPW == 0 && alive) alive = mbar_wait(w_ready + 8 * slot, (wu / w_period) & 1);  // W tiles landed
         if (c == 0 && k >= 2 && alive) alive = mbar_wait(d_free + 8 * acc, (uint32_t)(((k >> 1) - 1) & 1));
         alive = __all_sync(0xffffffffu, alive);
@@ -324,8 +346,9 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         const uint32_t ta = tmem_u + 256 + Fmt::A_COLS * ab;
         if (elected) {
           issue_chunk_mmas<BF>(d_tmem, ta, wb, g % CPW, c == 0);
-          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                       :: "r"(a_done + 8 * ab) : "memory");
+          if (last_blk)  // the A buffer goes back to the producers
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(a_done + 8 * ab) : "memory");
           if (g % CPW == CPW - 1)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                          :: "r"(w_done + 8 * slot) : "memory");
@@ -335,6 +358,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         }
         __syncwarp();
       }
+      if (sh && jb == n_blocks - 1) ++t_sh;
     }
   } else if (warp == PS_TMA_WARP) {
     // ---------------------------------------------------------------- TMA warp: W_hi / W_lo tiles, up to 4 chunks ahead
@@ -547,7 +571,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
     bool alive = true;
     uint32_t g = 0;
     int n = 0;  // chunks this warp has converted
-    for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_tile(rt, jb)) {
+    for (int rt = first_rt, jb = first_jb; rt < n_row_tiles; next_a_tile(rt, jb)) {
       const mb_colblock& cb = d.blk[jb];
       const int nch = cb.n_src * 4;
       int act_mask = 0;
@@ -570,7 +594,7 @@ k_gemm_ps(const __grid_constant__ mb_gemm_desc d_param, const __grid_constant__ 
         __syncwarp();  // all lanes have read their patch rows and written their A rows
         if (lane == 0) mbar_arrive(a_ready + 8 * ab);
       }
-      g += (uint32_t)nch;
+      g += sh ? NB : (uint32_t)nch;  // shared-A mode: chunk c always in buffer c, one barrier phase per row tile
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   }

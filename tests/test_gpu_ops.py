@@ -108,6 +108,40 @@ def test_gemm_large_mixed_direct_and_gathered_sources(ops):
     report("tcgen05 3xTF32 (direct + gathered A, 157 tiles) vs simt", outs["tcgen05_tf32"], outs["simt"], TOL_TF32)
 
 
+@pytest.mark.parametrize("n_rows", [100, 148 * 128 + 77, 148 * 128 * 3 + 5])
+def test_gemm_column_blocks_sharing_one_a_operand(ops, n_rows):
+    """The shape of the gated MLP's input gradient: every column block reads the same K = 256 rows (the persistent
+    kernel then converts them once per row tile), one block stored with a residual, three scattered with atomics to
+    different targets; one, several and an odd number of row tiles per CTA, ragged last tile.  And K = 128 with two
+    column blocks, which shares the operand in the 3xTF32 form too.  Against the fp32 SIMT core."""
+    R, n1 = n_rows, 997
+    x, W = rnd(R, 256, seed=31), rnd(512, 256, seed=32, scale=0.1)
+    res, rw = rnd(R, 128, seed=33), rnd(128, seed=34)
+    g = torch.Generator().manual_seed(R)
+    idx = [dev(torch.randint(0, n1, (R,), generator=g), torch.int32) for _ in range(3)]
+    dx, dW, dres, drw = dev(x), dev(W), dev(res), dev(rw)
+    outs = {}
+    for mode in ("simt", "tcgen05", "tcgen05_tf32"):
+        ops.set_gemm_mode(mode)
+        edge = torch.empty(R, 128, device="cuda")
+        acc = [torch.zeros(n1, 128, device="cuda") for _ in range(2)]
+        srcs = [ops.S(dx, None, 0), ops.S(dx, None, 128)]
+        ops.gemm(R, [ops.B(srcs, dW, w_row=0, out=edge, res=dres, res_w=drw),
+                     ops.B(srcs, dW, w_row=128, out=acc[0], out_idx=idx[0], mode=ops.OUT_ATOMIC),
+                     ops.B(srcs, dW, w_row=256, out=acc[1], out_idx=idx[1], mode=ops.OUT_ATOMIC),
+                     ops.B(srcs, dW, w_row=384, out=acc[1], out_idx=idx[2], mode=ops.OUT_ATOMIC)])
+        y = ops.linear(dx[:, :128].contiguous(), dW[:256, :128].contiguous(), out_act=1)
+        assert ops.gemm_status() == 0
+        outs[mode] = [edge.cpu(), acc[0].cpu(), acc[1].cpu(), y.cpu()]
+    ops.set_gemm_mode("tcgen05")
+    # the scatter targets sum about R / 997 rows each: the bound scales with the largest sum
+    for i, name in enumerate(("stored block + residual", "scatter 1", "scatter 2 + 3", "K = 128, two blocks, SiLU")):
+        report(f"shared A R={R}: 3xBF16 vs simt, {name}", outs["tcgen05"][i], outs["simt"][i], TOL_BF16)
+        report(f"shared A R={R}: 3xTF32 vs simt, {name}", outs["tcgen05_tf32"][i], outs["simt"][i], TOL_TF32)
+    want = F.linear(x.double(), W[:128].double()) + rw.double() * res.double()
+    report(f"shared A R={R}: 3xBF16 vs float64, stored block", outs["tcgen05"][0], want, TOL_BF16)
+
+
 def test_status_word_copy_in_stream_order(ops):
     flag = torch.full((1,), 7, dtype=torch.int32).pin_memory()
     x, W = dev(rnd(300, 128, seed=1)), dev(rnd(128, 128, seed=2))
