@@ -105,3 +105,36 @@ def test_memory_policy_bounds_and_sub_batch_ranges():
     ranges2 = split_ranges(trip2, edge, fits)
     assert (100, 101) in ranges2 and ranges2[0][0] == 0 and ranges2[-1][1] == 512
     assert all(fits(int(trip2[a:b].sum()), int(edge[a:b].sum())) or (a, b) == (100, 101) for a, b in ranges2)
+
+
+def test_forward_batches_joins_results_in_order(monkeypatch):
+    """forward_batches concatenates the per-sub-batch dictionaries in order (host logic, no device needed)."""
+    ck = random_checkpoint(dict(num_layers=1, reference_energy="mpa"), seed=3)
+    model = MatRIS.from_dict(ck)
+    sizes = {"a": [2, 3], "b": [4], "c": [1, 1, 5]}
+
+    def fake_forward(g, task="efsm", is_training=False):
+        n = sizes[g]
+        base = float(ord(g))
+        return {"e": torch.full((len(n),), base), "ref_energy": torch.full((len(n),), -base),
+                "atoms_per_graph": torch.tensor(n, dtype=torch.int32),
+                "f": tuple(torch.full((k, 3), base) for k in n), "s": [torch.full((3, 3), base) for _ in n],
+                "m": [torch.full((k,), base) for k in n]}
+
+    monkeypatch.setattr(model, "forward", fake_forward)
+    out = model.forward_batches(["a", "b", "c"], task="efsm")
+    assert out["atoms_per_graph"].tolist() == [2, 3, 4, 1, 1, 5]
+    assert out["e"].tolist() == [97.0, 97.0, 98.0, 99.0, 99.0, 99.0] and out["ref_energy"].tolist()[2] == -98.0
+    assert isinstance(out["f"], tuple) and [t.shape[0] for t in out["f"]] == [2, 3, 4, 1, 1, 5]
+    assert len(out["s"]) == 6 and [t.numel() for t in out["m"]] == [2, 3, 4, 1, 1, 5]
+    assert float(out["f"][2][0, 0]) == 98.0 and float(out["m"][5][0]) == 99.0
+    # a single sub-batch is returned as it is; a model without reference energies keeps its scalar 0
+    one = model.forward_batches(["b"], task="efsm")
+    assert one["e"].tolist() == [98.0]
+
+    def fake_no_ref(g, task="e", is_training=False):
+        return {"e": torch.zeros(len(sizes[g])), "ref_energy": 0, "atoms_per_graph": torch.tensor(sizes[g])}
+
+    monkeypatch.setattr(model, "forward", fake_no_ref)
+    out = model.forward_batches(["a", "c"], task="e")
+    assert out["ref_energy"] == 0 and out["e"].numel() == 5 and "f" not in out
