@@ -206,13 +206,13 @@ def gated_bwd(p, n_rows, z1, z2, dh, dests, dz2=None):
         dy = ops.rmsnorm_bwd(z2, p.nw, dh.contiguous())
         da1 = torch.empty_like(z1)
         gemm(n_rows, [B([S(dy)], p.w2t, gate=z1, out=da1)])
-        blocks = []
+        blocks, srcs = [], [S(da1)]  # one list of sources for all column blocks
         for c, dest in enumerate(dests):
             t, idx, mode = dest[:3]
             if t is None:
                 continue
             res, res_w = (dest[3], dest[4]) if len(dest) > 3 else (None, None)
-            blocks.append(B([S(da1)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode, res=res, res_w=res_w))
+            blocks.append(B(srcs, p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode, res=res, res_w=res_w))
         gemm(n_rows, blocks)
         return
     if dz2 is None:
@@ -221,14 +221,13 @@ def gated_bwd(p, n_rows, z1, z2, dh, dests, dz2=None):
     gemm(n_rows, [B([S(dz2, None, D * j)], p.w2t, w_row=D * j, gate=z1, gate_col=D * j, out=dz1, out_col=D * j)
                   for j in (0, 1)])
     del dz2
-    blocks = []
+    blocks, srcs = [], [S(dz1, None, 0), S(dz1, None, D)]  # one list of sources for all column blocks
     for c, dest in enumerate(dests):
         t, idx, mode = dest[:3]
         if t is None:
             continue
         res, res_w = (dest[3], dest[4]) if len(dest) > 3 else (None, None)
-        blocks.append(B([S(dz1, None, 0), S(dz1, None, D)], p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode,
-                        res=res, res_w=res_w))
+        blocks.append(B(srcs, p.w1t, w_row=D * c, out=t, out_idx=idx, mode=mode, res=res, res_w=res_w))
     gemm(n_rows, blocks)
 
 

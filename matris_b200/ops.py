@@ -125,14 +125,17 @@ def gemm(n_rows: int, blocks: list[dict]) -> None:
     buf = bytearray(_DESC_SIZE)
     _HDR_FMT.pack_into(buf, 0, n_rows, len(blocks), 0)
     off = _BLK_OFF
+    last_srcs = flat = None
     for b in blocks:
         srcs = b["srcs"]
         n_src = len(srcs)
-        flat = []
-        for t, idx, col, act in srcs:
-            assert t.dtype == torch.float32 and t.stride(-1) == 1
-            flat += (t.data_ptr(), 0 if idx is None else idx.data_ptr(), t.stride(0), col, act)
-        flat += _PAD[4 - n_src]
+        if srcs is not last_srcs:  # column blocks that share one list of sources share its packed form
+            flat = []
+            for t, idx, col, act in srcs:
+                assert t.dtype == torch.float32 and t.stride(-1) == 1
+                flat += (t.data_ptr(), 0 if idx is None else idx.data_ptr(), t.stride(0), col, act)
+            flat += _PAD[4 - n_src]
+            last_srcs = srcs
         sw = b["W"]
         if type(sw) is not SplitWeight:
             sw = as_split(sw)

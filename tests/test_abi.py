@@ -158,6 +158,13 @@ def test_gemm_descriptor_packing_matches_ctypes_mirror(monkeypatch):
                          bias_off=128 * j, gate=g, gate_col=128 * j, res=r, res_col=128 * j, res_w=rw, out=out,
                          out_idx=idx, out_col=128 * j, mode=ops.OUT_ATOMIC, scale=0.5, out_act=1) for j in (0, 1)])
     assert captured["name"] == "mb_gemm"
+    separate = captured["desc"]
+    # column blocks that share ONE list of sources pack the same bytes as blocks with equal lists of their own
+    shared = [ops.S(x, None, 0, 1), ops.S(x, idx, 128, 0), ops.S(x, idx, 0, 0)]
+    ops.gemm(300, [ops.B(shared, W, w_row=128 * j, bias=bias, bias_off=128 * j, gate=g, gate_col=128 * j, res=r,
+                         res_col=128 * j, res_w=rw, out=out, out_idx=idx, out_col=128 * j, mode=ops.OUT_ATOMIC, scale=0.5,
+                         out_act=1) for j in (0, 1)])
+    assert captured["desc"] == separate
     d = _lib.MbGemmDesc.from_buffer_copy(captured["desc"])
     assert (d.n_rows, d.n_blocks) == (300, 2)
     for j in (0, 1):
